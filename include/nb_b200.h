@@ -1,0 +1,217 @@
+/*
+ * nb_b200.h — C ABI of libnb_b200.so: hand-written sm_100a CUDA for the sampled mini-batch GCN
+ * path of NeutronBench (ALGORITHM:GCNNEIGHBORGPU).
+ *
+ * Conventions
+ *   - Every pointer named d_* is DEVICE memory of the current CUDA device unless the comment says
+ *     "host" or "pinned".  Vertex ids and block-local indices are uint32_t (the reference's
+ *     VertexId, dep/gemini/type.hpp:28); whole-graph CSC offsets are uint64_t so that graphs with
+ *     more than 2^32 edges fit; features, weights and gradients are fp32 row-major.
+ *   - `stream` is a cudaStream_t passed as void*.  Kernels are enqueued on it and the call returns
+ *     without synchronising unless stated (the reference synchronises after every kernel,
+ *     cuda/ntsCUDAGraphOP.cu:366-373; results are identical because all work is stream-ordered).
+ *   - Return value: 0 (NB_OK) on success, a negative nb_status otherwise; nb_last_error() returns a
+ *     message for the calling thread.  Nothing here calls exit() (the reference prints and exits,
+ *     cuda/ntsCUDAGraphOP.cu:13-20).
+ *   - The library never frees or reallocates caller memory.  Scratch memory lives in an nb_ws
+ *     workspace that the caller creates and destroys.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     NB_ERR_CUDA.
+ */
+#ifndef NB_B200_H
+#define NB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nb_status {
+  NB_OK = 0,
+  NB_ERR_INVALID = -1,   /* bad argument (null pointer, zero width, size over a stated limit) */
+  NB_ERR_CUDA = -2,      /* a CUDA runtime call or kernel launch failed                        */
+  NB_ERR_NOMEM = -3,     /* workspace arena exhausted                                          */
+  NB_ERR_OVERFLOW = -4   /* a device-side bounded wait or capacity check gave up               */
+} nb_status;
+
+const char *nb_last_error(void);
+int nb_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Workspace: a bump arena of device scratch memory plus a small pinned host mailbox used to read
+ * sizes back.  If `d_arena` is NULL the workspace allocates `bytes` with cudaMalloc and frees it in
+ * nb_ws_destroy; otherwise it sub-allocates from the caller's buffer and never frees it.
+ * Replaces sampCSC::alloc_dev_array's cudaMalloc/cudaFree churn with 1.2x growth
+ * (core/coocsc.hpp:621-671).  One workspace serves one stream at a time.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct nb_ws nb_ws;
+int nb_ws_create(nb_ws **out, void *d_arena, size_t bytes);
+int nb_ws_destroy(nb_ws *ws);
+int nb_ws_reset(nb_ws *ws);                 /* forget all sub-allocations               */
+size_t nb_ws_used(const nb_ws *ws);         /* bytes currently handed out               */
+size_t nb_ws_high_water(const nb_ws *ws);   /* largest value nb_ws_used ever had        */
+
+/* ------------------------------------------------------------------------------------------------
+ * Aggregation (SpMM).
+ *
+ * nb_spmm_csc_fwd replaces Cuda_Stream::Gather_By_Dst_From_Src with with_weight=true
+ * (cuda/ntsCUDA.hpp:131-135, cuda/ntsCUDAGraphOP.cu:186-210, kernel
+ * cuda/ntsCUDAFuseKernel.cuh:272-290; caller core/ntsMiniBatchGraphOp.hpp:311-315):
+ *     y[d,:] = sum_{j in [column_offset[d], column_offset[d+1])} w[j] * x[row_indices[j],:]
+ * Every row of y is written (empty columns become zero), so y need not be zeroed first.  The sum is
+ * taken edge after edge in CSC order, one multiply and one add per element, exactly like the
+ * reference kernel, so results do not depend on the launch shape.
+ *
+ * nb_spmm_csr_bwd replaces Cuda_Stream::Gather_By_Src_From_Dst (cuda/ntsCUDA.hpp:146-150,
+ * cuda/ntsCUDAGraphOP.cu:269-292, kernel cuda/ntsCUDAFuseKernel.cuh:450-468; caller
+ * core/ntsMiniBatchGraphOp.hpp:365-368):
+ *     gx[s,:] = sum_{j in [row_offset[s], row_offset[s+1])} w[j] * gy[column_indices[j],:]
+ * Atomics-free; the order within a row is the CSR order, so it is deterministic.
+ *
+ * The *_fused variants take no per-edge weight array: the GCN weight
+ * 1/(sqrt(out_deg[src]) * sqrt(in_deg[dst])) (core/ntsBaseOp.hpp:183-186) is formed per edge from the
+ * per-vertex factors src_norm[s] = (float)sqrt(out_deg), dst_norm[v] = (float)sqrt(in_deg) that
+ * nb_block_build emits; the value is bit-identical to the reference's edge_weight_forward /
+ * edge_weight_backward (core/coocsc.hpp:136-163).  nb_spmm_csr_bwd_fused additionally applies the
+ * gradient of the dropout(relu(.)) that produced the block's input: where d_act (s x F, nullable) is
+ * > 0 the sum is multiplied by act_scale, elsewhere it becomes 0.
+ * ---------------------------------------------------------------------------------------------- */
+int nb_spmm_csc_fwd(const float *d_x, float *d_y, const float *d_w, const uint32_t *d_row_indices,
+                    const uint32_t *d_column_offset, uint32_t v, uint32_t F, void *stream);
+int nb_spmm_csr_bwd(const float *d_gy, float *d_gx, const float *d_w, const uint32_t *d_row_offset,
+                    const uint32_t *d_column_indices, uint32_t s, uint32_t F, void *stream);
+int nb_spmm_csc_fwd_fused(const float *d_x, float *d_y, const uint32_t *d_row_indices,
+                          const uint32_t *d_column_offset, const float *d_src_norm,
+                          const float *d_dst_norm, uint32_t v, uint32_t F, void *stream);
+int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t *d_row_offset,
+                          const uint32_t *d_column_indices, const float *d_src_norm,
+                          const float *d_dst_norm, const float *d_act, float act_scale, uint32_t s,
+                          uint32_t F, void *stream);
+
+/* Layer-0 aggregation straight from the feature store, without materialising the gathered input:
+ *     y[d,:] = sum_j w_j * row(source[row_indices[j]])
+ * where row(g) is the cached row d_cache[hashmap[g]] when d_hashmap != NULL and hashmap[g] !=
+ * 0xFFFFFFFF, else feat[g] (device, mapped pinned host, or a peer GPU's memory).  Equals
+ * nb_feature_gather followed by nb_spmm_csc_fwd_fused (core/ntsSampler.hpp:364-376 then
+ * core/ntsMiniBatchGraphOp.hpp:288-318) bit for bit.  cache_ld / feat_ld are the row pitches in
+ * floats (>= F). */
+int nb_spmm_csc_fwd_gather_fused(const float *feat, size_t feat_ld, const float *d_cache,
+                                 size_t cache_ld, const uint32_t *d_hashmap,
+                                 const uint32_t *d_source, float *d_y,
+                                 const uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                                 const float *d_src_norm, const float *d_dst_norm, uint32_t v,
+                                 uint32_t F, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Block construction.
+ *
+ * nb_block_build turns one hop's raw sampled edge list into the reference's sampCSC block
+ * (core/coocsc.hpp:792-813), on the device and without sorting the vertex set:
+ *   dedup + reindex   sampCSC::postprocessing, core/coocsc.hpp:338-425
+ *                     source[] = distinct global ids ascending; row_indices become local ranks
+ *   CSR transpose     sampCSC::generate_csr_from_csc, core/coocsc.hpp:243-309
+ *                     ascending local destinations within each source row
+ *   degrees, weights  sampCSC::update_degree + compute_weight_forward/backward,
+ *                     core/coocsc.hpp:136-216
+ * and replaces the eight host->device copies per layer of copy_data_to_device_async
+ * (core/coocsc.hpp:737-773).  Results are bit-identical to the reference's arrays.
+ *
+ * In:  d_row_indices[e] global source ids in CSC order (overwritten with local ranks),
+ *      d_column_offset[v+1], num_vertices = |V| of the whole graph.
+ * Out: d_source[>= min(|V|, e)], *src_size (host; the call synchronises the stream once to read it),
+ *      d_row_offset[>= min(|V|,e)+1], d_column_indices[e], d_src_norm[>= min(|V|,e)], d_dst_norm[v],
+ *      d_w_fwd[e] / d_w_bwd[e] (either may be NULL when only the fused SpMM variants are used).
+ * Scratch: ws; about |V|/4 + 8*min(|V|,e) bytes.
+ * ---------------------------------------------------------------------------------------------- */
+int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices,
+                   const uint32_t *d_column_offset, uint32_t v, uint32_t e, uint32_t *d_source,
+                   uint32_t *src_size, uint32_t *d_row_offset, uint32_t *d_column_indices,
+                   float *d_src_norm, float *d_dst_norm, float *d_w_fwd, float *d_w_bwd,
+                   void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Fan-out sampling of one hop (Sampler::sample_one, core/ntsSampler.hpp:843-1083, one iteration of
+ * its layer loop up to and excluding postprocessing; init_co core/FullyRepGraph.hpp:199-209).
+ *
+ * nb_sample_hop_offsets: column_offset[i] = prefix sum of min(deg(dst[i]), fanout) (deg when
+ * fanout < 0); *e_size (host) receives the edge count; synchronises the stream once.
+ * nb_sample_hop: for every destination, `fanout` distinct neighbour positions drawn uniformly
+ * (Floyd's subset algorithm on a per-destination Philox4x32-10 stream keyed by `seed`, counter
+ * (draw/4, local destination index, hop, 0)) when deg > fanout, else all neighbours in CSC order;
+ * writes GLOBAL source ids to d_row_indices in the layout nb_block_build consumes.
+ * The reference draws with a thread-local mt19937 under OpenMP (utils/rand.hpp:6-13), so its sampled
+ * sets are not reproducible across runs; parity with it is defined on identical edge lists.
+ * ---------------------------------------------------------------------------------------------- */
+int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offset, const uint32_t *d_dst,
+                          uint32_t v, int fanout, uint32_t *d_column_offset, uint32_t *e_size,
+                          void *stream);
+int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices,
+                  const uint32_t *d_dst, uint32_t v, int fanout, const uint32_t *d_column_offset,
+                  uint64_t seed, uint32_t hop, uint32_t *d_row_indices, void *stream);
+
+/* Whole-graph CSC from a device-resident edge list (u32 src, u32 dst pairs as in the .edge file),
+ * stable in file order like FullyRepGraph::ReadRepGraphFromRawFile (core/FullyRepGraph.hpp:485-560).
+ * d_out_degree / d_in_degree (nullable, |V| each) receive the raw degrees. */
+int nb_graph_build_csc(nb_ws *ws, const uint32_t *d_edges, uint64_t num_edges, uint32_t num_vertices,
+                       uint64_t *d_column_offset, uint32_t *d_row_indices, uint32_t *d_out_degree,
+                       uint32_t *d_in_degree, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Feature and label movement.
+ *
+ * nb_feature_gather: x0[i,:] = row(source[i]) for i < n, with row(g) as in
+ * nb_spmm_csc_fwd_gather_fused.  One call replaces Cuda_Stream::zero_copy_feature_move_gpu
+ * (cuda/ntsCUDAGraphOP.cu:379-396) when d_hashmap is NULL, and the pair
+ * zero_copy_feature_move_gpu_cache + gather_feature_from_gpu_cache (cuda/ntsCUDAGraphOP.cu:398-423)
+ * including the serial host-side hit/miss split of Sampler::load_feature_gpu_cache
+ * (core/ntsSampler.hpp:444-456) otherwise.  `feat` may be device memory, the device alias of mapped
+ * pinned host memory, or (feat_shards != NULL) a table sharded by contiguous node-id range over
+ * `num_shards` pointers (own memory or peer GPUs reached with plain loads): owner = g / shard_rows.
+ *
+ * nb_label_gather: lab[i,:] = label[dst[i],:] with label_size int64 per row
+ * (global_copy_label_move_gpu / global_copy_mulilabel_move_gpu, cuda/ntsCUDATransferKernel.cuh:184-203).
+ *
+ * nb_cache_fill: cache[hashmap[g],:] = feat[g,:] for every g < num_vertices with a slot
+ * (gater_cpu_cache_feature_and_trans_to_gpu, toolkits/GCN_GPU_NEIGHBOR.hpp:899-918).
+ * The slot map itself (descending degree, cache_high_degree + mark_cache_node,
+ * toolkits/GCN_GPU_NEIGHBOR.hpp:919-943) is one-time host work and stays on the host side.
+ * ---------------------------------------------------------------------------------------------- */
+int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, const float *const *feat_shards,
+                      uint32_t num_shards, uint32_t shard_rows, const float *d_cache, size_t cache_ld,
+                      const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
+                      void *stream);
+int nb_label_gather(int64_t *d_lab, const int64_t *d_label, const uint32_t *d_dst, uint32_t n,
+                    uint32_t label_size, void *stream);
+int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t feat_ld,
+                  const uint32_t *d_hashmap, uint32_t num_vertices, uint32_t F, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Dense layer, loss, optimizer (the libtorch calls of vertexForward / Loss / Parameter,
+ * toolkits/GCN_GPU_NEIGHBOR.hpp:715-728, utils/torch_func.hpp:67-82, core/NtsScheduler.hpp:712-715,
+ * 794-811).  fp32 in, fp32 out, fp32 accumulation.
+ *
+ * nb_gemm: C[M x N] = op(A) * op(B).  trans_a = 0: A is M x K row-major; 1: A is K x M (A^T used).
+ *          trans_b likewise for B (K x N, or N x K when 1).  Supported: NN, TN, NT.
+ * nb_relu_dropout: z = dropout(relu(z)) in place; keeps element i when the Philox word
+ *          (counter (i/4, layer, step, 1), key seed) mapped to [0,1) is >= p, scaling by 1/(1-p).
+ * nb_softmax_nll: mean negative log-likelihood of log_softmax(logits) at `label`, its gradient
+ *          (softmax - onehot)/B into d_dlogits (nullable), argmax hits into d_stats[1];
+ *          d_stats[0] = loss (two floats, device).
+ * nb_adam: g = grad + wd*W; M = b1 M + (1-b1) g; V = b2 V + (1-b2) g^2;
+ *          W -= alpha * (M/(1-b1_t)) / (sqrt(V/(1-b2_t)) + eps).
+ * ---------------------------------------------------------------------------------------------- */
+int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
+            int trans_a, int trans_b, void *stream);
+int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32_t layer, uint32_t step,
+                    void *stream);
+int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                   float *d_dlogits, float *d_stats, void *stream);
+int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
+            float b2, float eps, float wd, float b1_t, float b2_t, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NB_B200_H */

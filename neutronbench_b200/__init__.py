@@ -1,0 +1,17 @@
+"""B200-native sampled mini-batch GCN path of NeutronBench (ALGORITHM:GCNNEIGHBORGPU).
+
+The compute path is libnb_b200.so (hand-written sm_100a CUDA behind a C ABI, include/nb_b200.h);
+this package is the host-side mirror of the reference's operator/toolkit interface.  Importing the
+package does not load the library; the first call does, and fails loudly when it is missing.
+"""
+from . import _lib  # noqa: F401
+from .cuda_stream import Cuda_Stream, Workspace  # noqa: F401
+from .graph import FullyRepGraph, SampledSubgraph, Sampler, build_block, sampCSC  # noqa: F401
+from .ops import SingleGPUSampleGraphOp, ntsGraphOp  # noqa: F401
+from .toolkit import GCN_GPU_NEIGHBOR_impl, GCNConfig, GNNDatum, Parameter, cache_slots_by_degree  # noqa: F401
+
+__all__ = [
+    "Cuda_Stream", "Workspace", "FullyRepGraph", "SampledSubgraph", "Sampler", "build_block", "sampCSC",
+    "SingleGPUSampleGraphOp", "ntsGraphOp", "GCN_GPU_NEIGHBOR_impl", "GCNConfig", "GNNDatum", "Parameter",
+    "cache_slots_by_degree",
+]

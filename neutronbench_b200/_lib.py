@@ -1,0 +1,90 @@
+"""ctypes binding of libnb_b200.so (the C ABI declared in include/nb_b200.h).
+
+The library is the product's compute path; there is no CPU or PyTorch fallback.  Loading fails loudly
+when the shared object has not been built (run ``python -c "import __graft_entry__ as g; g.build()"``
+or ``make -C neutronbench_b200/csrc``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnb_b200.so")
+
+u32p = C.c_void_p  # device pointers travel as integers (tensor.data_ptr())
+f32p = C.c_void_p
+u64p = C.c_void_p
+i64p = C.c_void_p
+ptr = C.c_void_p
+
+# name -> (restype, argtypes); mirrors include/nb_b200.h one to one.
+SIGNATURES = {
+    "nb_last_error": (C.c_char_p, []),
+    "nb_version": (C.c_int, []),
+    "nb_ws_create": (C.c_int, [C.POINTER(C.c_void_p), ptr, C.c_size_t]),
+    "nb_ws_destroy": (C.c_int, [ptr]),
+    "nb_ws_reset": (C.c_int, [ptr]),
+    "nb_ws_used": (C.c_size_t, [ptr]),
+    "nb_ws_high_water": (C.c_size_t, [ptr]),
+    "nb_spmm_csc_fwd": (C.c_int, [f32p, f32p, f32p, u32p, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_spmm_csr_bwd": (C.c_int, [f32p, f32p, f32p, u32p, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_spmm_csc_fwd_fused": (C.c_int, [f32p, f32p, u32p, u32p, f32p, f32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_spmm_csr_bwd_fused": (C.c_int, [f32p, f32p, u32p, u32p, f32p, f32p, f32p, C.c_float, C.c_uint32,
+                                        C.c_uint32, ptr]),
+    "nb_spmm_csc_fwd_gather_fused": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, u32p, f32p, u32p, u32p,
+                                               f32p, f32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_block_build": (C.c_int, [ptr, C.c_uint32, u32p, u32p, C.c_uint32, C.c_uint32, u32p,
+                                 C.POINTER(C.c_uint32), u32p, u32p, f32p, f32p, f32p, f32p, ptr]),
+    "nb_sample_hop_offsets": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_int, u32p, C.POINTER(C.c_uint32), ptr]),
+    "nb_sample_hop": (C.c_int, [u64p, u32p, u32p, C.c_uint32, C.c_int, u32p, C.c_uint64, C.c_uint32, u32p, ptr]),
+    "nb_graph_build_csc": (C.c_int, [ptr, u32p, C.c_uint64, C.c_uint32, u64p, u32p, u32p, u32p, ptr]),
+    "nb_feature_gather": (C.c_int, [f32p, f32p, C.c_size_t, ptr, C.c_uint32, C.c_uint32, f32p, C.c_size_t, u32p,
+                                    u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_label_gather": (C.c_int, [i64p, i64p, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_cache_fill": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_gemm": (C.c_int, [ptr, f32p, f32p, f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, ptr]),
+    "nb_relu_dropout": (C.c_int, [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, ptr]),
+    "nb_softmax_nll": (C.c_int, [ptr, f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
+    "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
+                          C.c_float, C.c_float, C.c_float, ptr]),
+}
+
+
+class NbError(RuntimeError):
+    """A libnb_b200 entry point returned a non-zero status."""
+
+    def __init__(self, name: str, status: int, message: str):
+        super().__init__(f"{name} failed with status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library once and attach the signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA extension has not been built. "
+            "Run `make -C neutronbench_b200/csrc` (or __graft_entry__.build()). There is no CPU fallback."
+        )
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def call(name: str, *args):
+    """Call an int-returning entry point and raise NbError on failure."""
+    lib = load()
+    st = getattr(lib, name)(*args)
+    if st != 0:
+        raise NbError(name, st, lib.nb_last_error().decode("utf-8", "replace"))
+    return st

@@ -1,0 +1,108 @@
+// Shared helpers of libnb_b200: status / error string, launch checks, workspace arena, warp utilities.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "nb_b200.h"
+
+#define NB_API extern "C" __attribute__((visibility("default")))
+
+namespace nb {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+void set_error(const char *fmt, ...);
+
+inline int fail(nb_status st, const char *what) {
+  set_error("%s", what);
+  return (int)st;
+}
+
+#define NB_CUDA(call)                                                                         \
+  do {                                                                                        \
+    cudaError_t err__ = (call);                                                               \
+    if (err__ != cudaSuccess) {                                                               \
+      nb::set_error("%s:%d %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString(err__));  \
+      return (int)NB_ERR_CUDA;                                                                \
+    }                                                                                         \
+  } while (0)
+
+#define NB_LAUNCH_CHECK()                                                                     \
+  do {                                                                                        \
+    cudaError_t err__ = cudaGetLastError();                                                   \
+    if (err__ != cudaSuccess) {                                                               \
+      nb::set_error("%s:%d kernel launch -> %s", __FILE__, __LINE__, cudaGetErrorString(err__)); \
+      return (int)NB_ERR_CUDA;                                                                \
+    }                                                                                         \
+  } while (0)
+
+#define NB_REQUIRE(cond, msg)                                  \
+  do {                                                         \
+    if (!(cond)) return nb::fail(NB_ERR_INVALID, msg);         \
+  } while (0)
+
+#define NB_TRY(expr)            \
+  do {                          \
+    int st__ = (expr);          \
+    if (st__ != 0) return st__; \
+  } while (0)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline unsigned div_up(uint64_t a, uint64_t b) { return (unsigned)((a + b - 1) / b); }
+
+// Grid for a grid-stride kernel: enough blocks to cover `items`, capped at `waves` full waves of the
+// 148 SMs at `blocks_per_sm` resident blocks each.
+inline unsigned grid_for(uint64_t items, unsigned block, unsigned blocks_per_sm = 8, unsigned waves = 4) {
+  uint64_t need = (items + block - 1) / block;
+  uint64_t cap = (uint64_t)kNumSMs * blocks_per_sm * waves;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+}  // namespace nb
+
+// The workspace: bump allocator over one device arena + a pinned mailbox for size read-backs.
+struct nb_ws {
+  char *base = nullptr;
+  size_t bytes = 0;
+  size_t used = 0;
+  size_t high = 0;
+  bool owns = false;
+  uint32_t *mailbox = nullptr;  // pinned host, 64 words
+
+  // 256-byte aligned sub-allocation; returns nullptr when the arena is exhausted.
+  void *alloc(size_t n) {
+    size_t start = (used + 255) & ~(size_t)255;
+    if (start + n > bytes) return nullptr;
+    used = start + n;
+    if (used > high) high = used;
+    return base + start;
+  }
+  template <typename T>
+  T *alloc_n(size_t count) {
+    return reinterpret_cast<T *>(alloc(count * sizeof(T)));
+  }
+};
+
+namespace nb {
+// Scoped mark/release so that a call's scratch is returned to the arena when it ends.
+struct WsScope {
+  nb_ws *ws;
+  size_t mark;
+  explicit WsScope(nb_ws *w) : ws(w), mark(w ? w->used : 0) {}
+  ~WsScope() {
+    if (ws) ws->used = mark;
+  }
+};
+
+// Exclusive prefix sum of n uint32 values (d_in may equal d_out).  d_out has n+1 entries when
+// write_total is true (d_out[n] = total).  Scratch from ws.
+int exclusive_scan_u32(nb_ws *ws, const uint32_t *d_in, uint32_t *d_out, uint64_t n, bool write_total,
+                       cudaStream_t stream);
+// Same for 64-bit outputs from 32-bit inputs.
+int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, uint64_t n,
+                              bool write_total, cudaStream_t stream);
+}  // namespace nb

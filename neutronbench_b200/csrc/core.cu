@@ -1,0 +1,187 @@
+// Error string, workspace arena and the device-wide exclusive scan used by the block builder.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace nb {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Three-pass exclusive scan: tile sums -> scan of the tile sums by one block -> per-tile scan.
+// No inter-block waiting, so there is nothing that can spin.  Traffic: reads the input twice and
+// writes the output once (12 bytes per element for u32 -> u32).
+// ---------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+template <typename T>
+__device__ __forceinline__ T block_exclusive_scan(T val, T *total, T *smem /* 32 entries */) {
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T incl = val;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    T n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= (unsigned)o) incl += n;
+  }
+  if (lane == 31) smem[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    T w = (lane < (blockDim.x >> 5)) ? smem[lane] : (T)0;
+    T wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      T n = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= (unsigned)o) wi += n;
+    }
+    smem[lane] = wi - w;  // exclusive prefix of the warp totals
+    if (lane == 31) smem[32] = wi;
+  }
+  __syncthreads();
+  T res = smem[warp] + incl - val;
+  *total = smem[32];
+  __syncthreads();
+  return res;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(kScanThreads) scan_tile_sums(const uint32_t *__restrict__ in,
+                                                               TOut *__restrict__ tile_sums, uint64_t n) {
+  __shared__ TOut smem[33];
+  uint64_t base = (uint64_t)blockIdx.x * kScanTile;
+  TOut sum = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    uint64_t i = base + (uint64_t)k * kScanThreads + threadIdx.x;
+    if (i < n) sum += in[i];
+  }
+  TOut total;
+  block_exclusive_scan<TOut>(sum, &total, smem);
+  if (threadIdx.x == 0) tile_sums[blockIdx.x] = total;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(1024) scan_tile_offsets(TOut *tile_sums, uint64_t tiles, TOut *grand_total) {
+  __shared__ TOut smem[33];
+  TOut carry = 0;
+  for (uint64_t start = 0; start < tiles; start += 1024) {
+    uint64_t i = start + threadIdx.x;
+    TOut v = i < tiles ? tile_sums[i] : (TOut)0;
+    TOut total;
+    TOut ex = block_exclusive_scan<TOut>(v, &total, smem);
+    if (i < tiles) tile_sums[i] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0 && grand_total) *grand_total = carry;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(kScanThreads) scan_tiles(const uint32_t *in, TOut *out,
+                                                           const TOut *__restrict__ tile_offsets, uint64_t n) {
+  __shared__ TOut smem[33];
+  uint64_t base = (uint64_t)blockIdx.x * kScanTile + (uint64_t)threadIdx.x * kScanItems;
+  uint32_t v[kScanItems];
+  TOut sum = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    v[k] = (base + k < n) ? in[base + k] : 0u;
+    sum += v[k];
+  }
+  TOut total;
+  TOut ex = block_exclusive_scan<TOut>(sum, &total, smem) + tile_offsets[blockIdx.x];
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    if (base + k < n) out[base + k] = ex;
+    ex += v[k];
+  }
+}
+
+template <typename TOut>
+static int scan_impl(nb_ws *ws, const uint32_t *d_in, TOut *d_out, uint64_t n, bool write_total,
+                     cudaStream_t stream) {
+  if (n == 0) {
+    if (write_total) NB_CUDA(cudaMemsetAsync(d_out, 0, sizeof(TOut), stream));
+    return 0;
+  }
+  NB_REQUIRE(ws != nullptr, "scan: workspace is null");
+  WsScope scope(ws);
+  uint64_t tiles = (n + kScanTile - 1) / kScanTile;
+  TOut *tile_sums = ws->alloc_n<TOut>(tiles);
+  if (!tile_sums) return fail(NB_ERR_NOMEM, "scan: workspace arena exhausted");
+  scan_tile_sums<TOut><<<(unsigned)tiles, kScanThreads, 0, stream>>>(d_in, tile_sums, n);
+  NB_LAUNCH_CHECK();
+  scan_tile_offsets<TOut><<<1, 1024, 0, stream>>>(tile_sums, tiles, write_total ? d_out + n : nullptr);
+  NB_LAUNCH_CHECK();
+  scan_tiles<TOut><<<(unsigned)tiles, kScanThreads, 0, stream>>>(d_in, d_out, tile_sums, n);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+int exclusive_scan_u32(nb_ws *ws, const uint32_t *d_in, uint32_t *d_out, uint64_t n, bool write_total,
+                       cudaStream_t stream) {
+  return scan_impl<uint32_t>(ws, d_in, d_out, n, write_total, stream);
+}
+int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, uint64_t n,
+                              bool write_total, cudaStream_t stream) {
+  return scan_impl<unsigned long long>(ws, d_in, reinterpret_cast<unsigned long long *>(d_out), n,
+                                       write_total, stream);
+}
+
+}  // namespace nb
+
+NB_API const char *nb_last_error(void) { return nb::g_err; }
+NB_API int nb_version(void) { return 100; }
+
+NB_API int nb_ws_create(nb_ws **out, void *d_arena, size_t bytes) {
+  NB_REQUIRE(out != nullptr, "nb_ws_create: out is null");
+  NB_REQUIRE(bytes >= 4096, "nb_ws_create: arena must be at least 4096 bytes");
+  nb_ws *ws = new nb_ws();
+  if (d_arena) {
+    ws->base = static_cast<char *>(d_arena);
+    ws->owns = false;
+  } else {
+    void *p = nullptr;
+    cudaError_t err = cudaMalloc(&p, bytes);
+    if (err != cudaSuccess) {
+      delete ws;
+      nb::set_error("nb_ws_create: cudaMalloc(%zu) -> %s", bytes, cudaGetErrorString(err));
+      return NB_ERR_CUDA;
+    }
+    ws->base = static_cast<char *>(p);
+    ws->owns = true;
+  }
+  ws->bytes = bytes;
+  cudaError_t err = cudaHostAlloc((void **)&ws->mailbox, 64 * sizeof(uint32_t), cudaHostAllocDefault);
+  if (err != cudaSuccess) {
+    if (ws->owns) cudaFree(ws->base);
+    delete ws;
+    nb::set_error("nb_ws_create: cudaHostAlloc -> %s", cudaGetErrorString(err));
+    return NB_ERR_CUDA;
+  }
+  *out = ws;
+  return 0;
+}
+
+NB_API int nb_ws_destroy(nb_ws *ws) {
+  if (!ws) return 0;
+  if (ws->mailbox) cudaFreeHost(ws->mailbox);
+  if (ws->owns && ws->base) cudaFree(ws->base);
+  delete ws;
+  return 0;
+}
+
+NB_API int nb_ws_reset(nb_ws *ws) {
+  NB_REQUIRE(ws != nullptr, "nb_ws_reset: ws is null");
+  ws->used = 0;
+  return 0;
+}
+NB_API size_t nb_ws_used(const nb_ws *ws) { return ws ? ws->used : 0; }
+NB_API size_t nb_ws_high_water(const nb_ws *ws) { return ws ? ws->high : 0; }

@@ -1,0 +1,265 @@
+// Dense layer pieces: fp32 GEMM (CUDA-core path with split-K), ReLU+dropout, softmax/NLL loss with
+// gradient, Adam.  The reference runs these through libtorch (core/NtsScheduler.hpp:712-715, 794-811;
+// toolkits/GCN_GPU_NEIGHBOR.hpp:715-728; utils/torch_func.hpp:67-82).
+#include "common.cuh"
+#include "philox.cuh"
+
+namespace nb {
+
+// ------------------------------------------------------------------------------------ GEMM (SIMT)
+// C[M x N] = op(A) op(B), element access through strides so that NN / TN / NT share one kernel.
+// 64 x 64 x 16 tiles, 256 threads, 4 x 4 outputs per thread.  blockIdx.z walks split-K slices whose
+// partial products are summed afterwards in slice order (deterministic).
+constexpr int kTM = 64, kTN = 64, kTK = 16;
+
+struct GemmArgs {
+  const float *a, *b;
+  float *c;          // final output, or partial buffer [splits][M][N] when splits > 1
+  int64_t M, N, K;
+  int64_t sa_i, sa_k, sb_k, sb_j;
+  int64_t k_per_split;
+  int splits;
+};
+
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs g) {
+  __shared__ float As[kTK][kTM + 4];
+  __shared__ float Bs[kTK][kTN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each 4 x 4
+  const int64_t row0 = (int64_t)blockIdx.x * kTM, col0 = (int64_t)blockIdx.y * kTN;
+  const int64_t k_begin = (int64_t)blockIdx.z * g.k_per_split;
+  const int64_t k_end = min(g.K, k_begin + g.k_per_split);
+  float acc[4][4] = {};
+  for (int64_t k0 = k_begin; k0 < k_end; k0 += kTK) {
+    // A tile: 64 x 16 elements, 4 per thread.  The faster-varying thread index follows the unit stride.
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int idx = tid + t * 256;
+      int i, k;
+      if (g.sa_k == 1) { k = idx & 15; i = idx >> 4; } else { i = idx & 63; k = idx >> 6; }
+      const int64_t gi = row0 + i, gk = k0 + k;
+      As[k][i] = (gi < g.M && gk < k_end) ? __ldg(g.a + gi * g.sa_i + gk * g.sa_k) : 0.0f;
+    }
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int idx = tid + t * 256;
+      int j, k;
+      if (g.sb_j == 1) { j = idx & 63; k = idx >> 6; } else { k = idx & 15; j = idx >> 4; }
+      const int64_t gj = col0 + j, gk = k0 + k;
+      Bs[k][j] = (gj < g.N && gk < k_end) ? __ldg(g.b + gk * g.sb_k + gj * g.sb_j) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kTK; k++) {
+      const float4 av = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+      const float4 bv = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4]);
+      const float a4[4] = {av.x, av.y, av.z, av.w};
+      const float b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a4[i], b4[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float *out = g.c + (int64_t)blockIdx.z * g.M * g.N;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t gi = row0 + ty * 4 + i;
+    if (gi >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int64_t gj = col0 + tx * 4 + j;
+      if (gj < g.N) out[gi * g.N + gj] = acc[i][j];
+    }
+  }
+}
+
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ c, int64_t mn, int splits) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = partial[i];
+    for (int z = 1; z < splits; z++) s += partial[(int64_t)z * mn + i];
+    c[i] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------ ReLU + dropout
+__global__ void relu_dropout_kernel(float *z, int64_t n, float p, float scale, uint32_t seed_lo, uint32_t seed_hi,
+                                    uint32_t layer, uint32_t step) {
+  const int64_t quads = (n + 3) >> 2;
+  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t r[4] = {0, 0, 0, 0};
+    if (p > 0.0f) philox4x32_10((uint32_t)q, layer, step, 1u, seed_lo, seed_hi, r);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int64_t i = q * 4 + k;
+      if (i >= n) break;
+      float val = z[i] > 0.0f ? z[i] : 0.0f;
+      if (p > 0.0f) {
+        const float u = (float)(r[k] >> 8) * (1.0f / 16777216.0f);
+        val = (u >= p) ? __fmul_rn(val, scale) : 0.0f;
+      }
+      z[i] = val;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ loss
+// One warp per row: max, log-sum-exp, NLL at the label, gradient (softmax - onehot)/B, argmax hit.
+__global__ void softmax_nll_rows_kernel(const float *__restrict__ logits, const int64_t *__restrict__ label, int64_t B,
+                                        int64_t C, float *dlogits, float *row_loss, float *row_hit) {
+  const unsigned lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < B; i += warps) {
+    const float *z = logits + i * C;
+    float m = -INFINITY;
+    int64_t arg = 0;
+    for (int64_t c = lane; c < C; c += 32)
+      if (z[c] > m) { m = z[c]; arg = c; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int64_t oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (om > m || (om == m && oa < arg)) { m = om; arg = oa; }  // first maximum wins, like argmax
+    }
+    float sum = 0.0f;
+    for (int64_t c = lane; c < C; c += 32) sum += expf(z[c] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float lse = logf(sum);
+    const int64_t y = label[i];
+    if (lane == 0) {
+      row_loss[i] = -((z[y] - m) - lse);
+      row_hit[i] = (arg == y) ? 1.0f : 0.0f;
+    }
+    if (dlogits) {
+      const float inv_b = 1.0f / (float)B;
+      for (int64_t c = lane; c < C; c += 32) {
+        const float pr = expf(z[c] - m - lse);
+        dlogits[i * C + c] = (pr - (c == y ? 1.0f : 0.0f)) * inv_b;
+      }
+    }
+  }
+}
+
+// Fixed-shape reduction (one block of 1024 threads, strided partial sums, shared-memory tree): the
+// result does not depend on scheduling.
+__global__ void __launch_bounds__(1024) loss_reduce_kernel(const float *__restrict__ row_loss,
+                                                           const float *__restrict__ row_hit, int64_t B,
+                                                           float *stats) {
+  __shared__ float sl[1024], sh[1024];
+  float l = 0.0f, h = 0.0f;
+  for (int64_t i = threadIdx.x; i < B; i += 1024) { l += row_loss[i]; h += row_hit[i]; }
+  sl[threadIdx.x] = l; sh[threadIdx.x] = h;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) {
+    if (threadIdx.x < o) { sl[threadIdx.x] += sl[threadIdx.x + o]; sh[threadIdx.x] += sh[threadIdx.x + o]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { stats[0] = sl[0] / (float)B; stats[1] = sh[0]; }
+}
+
+// ------------------------------------------------------------------------------------ Adam
+__global__ void adam_kernel(float *W, const float *__restrict__ grad, float *M, float *V, int64_t n, float alpha,
+                            float b1, float b2, float eps, float wd, float c1, float c2) {
+  const float one_m_b1 = 1.0f - b1, one_m_b2 = 1.0f - b2;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float w = W[i];
+    const float g = __fadd_rn(grad[i], __fmul_rn(wd, w));
+    const float m = __fadd_rn(__fmul_rn(b1, M[i]), __fmul_rn(one_m_b1, g));
+    const float v = __fadd_rn(__fmul_rn(b2, V[i]), __fmul_rn(one_m_b2, __fmul_rn(g, g)));
+    M[i] = m;
+    V[i] = v;
+    const float mt = __fdiv_rn(m, c1), vt = __fdiv_rn(v, c2);
+    W[i] = __fsub_rn(w, __fdiv_rn(__fmul_rn(alpha, mt), __fadd_rn(__fsqrt_rn(vt), eps)));
+  }
+}
+
+}  // namespace nb
+
+using namespace nb;
+
+NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
+                   int trans_a, int trans_b, void *stream_) {
+  if (M == 0 || N == 0) return 0;
+  NB_REQUIRE(d_a && d_b && d_c, "nb_gemm: null pointer");
+  NB_REQUIRE(M > 0 && N > 0 && K >= 0, "nb_gemm: negative dimension");
+  NB_REQUIRE(!(trans_a && trans_b), "nb_gemm: TT is not supported");
+  cudaStream_t stream = as_stream(stream_);
+  if (K == 0) {
+    NB_CUDA(cudaMemsetAsync(d_c, 0, (size_t)(M * N) * sizeof(float), stream));
+    return 0;
+  }
+  GemmArgs g{};
+  g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
+  g.sa_i = trans_a ? 1 : K;  g.sa_k = trans_a ? M : 1;
+  g.sb_k = trans_b ? 1 : N;  g.sb_j = trans_b ? K : 1;
+  const int64_t tiles = ((M + kTM - 1) / kTM) * ((N + kTN - 1) / kTN);
+  int splits = 1;
+  if (tiles < 2 * kNumSMs && K >= 4 * kTK * 8) {
+    splits = (int)((2 * kNumSMs + tiles - 1) / tiles);
+    const int64_t max_splits = K / (kTK * 8);
+    if (splits > max_splits) splits = (int)max_splits;
+    if (splits < 1) splits = 1;
+  }
+  g.splits = splits;
+  g.k_per_split = ((K + splits - 1) / splits + kTK - 1) / kTK * kTK;
+  splits = (int)((K + g.k_per_split - 1) / g.k_per_split);
+  g.splits = splits;
+  WsScope scope(ws);
+  float *partial = nullptr;
+  if (splits > 1) {
+    NB_REQUIRE(ws != nullptr, "nb_gemm: split-K needs a workspace");
+    partial = ws->alloc_n<float>((size_t)splits * M * N);
+    if (!partial) return fail(NB_ERR_NOMEM, "nb_gemm: workspace arena exhausted");
+  }
+  g.c = splits > 1 ? partial : d_c;
+  dim3 grid((unsigned)((M + kTM - 1) / kTM), (unsigned)((N + kTN - 1) / kTN), (unsigned)splits);
+  if (grid.y > 65535) return fail(NB_ERR_INVALID, "nb_gemm: N too large for one launch");
+  gemm_simt_kernel<<<grid, 256, 0, stream>>>(g);
+  NB_LAUNCH_CHECK();
+  if (splits > 1) {
+    splitk_reduce_kernel<<<grid_for(M * N, 256), 256, 0, stream>>>(partial, d_c, M * N, splits);
+    NB_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+NB_API int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32_t layer, uint32_t step,
+                           void *stream) {
+  if (n == 0) return 0;
+  NB_REQUIRE(d_z != nullptr && n > 0, "nb_relu_dropout: null pointer");
+  NB_REQUIRE(p >= 0.0f && p < 1.0f, "nb_relu_dropout: drop rate must be in [0,1)");
+  const float scale = p > 0.0f ? 1.0f / (1.0f - p) : 1.0f;
+  relu_dropout_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, as_stream(stream)>>>(d_z, n, p, scale, (uint32_t)seed,
+                                                                                (uint32_t)(seed >> 32), layer, step);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+NB_API int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                          float *d_dlogits, float *d_stats, void *stream_) {
+  NB_REQUIRE(ws && d_logits && d_label && d_stats, "nb_softmax_nll: null pointer");
+  NB_REQUIRE(B > 0 && C > 0, "nb_softmax_nll: empty batch or no classes");
+  cudaStream_t stream = as_stream(stream_);
+  WsScope scope(ws);
+  float *row_loss = ws->alloc_n<float>((size_t)B);
+  float *row_hit = ws->alloc_n<float>((size_t)B);
+  if (!row_loss || !row_hit) return fail(NB_ERR_NOMEM, "nb_softmax_nll: workspace arena exhausted");
+  softmax_nll_rows_kernel<<<grid_for((uint64_t)B * 32, 256), 256, 0, stream>>>(d_logits, d_label, B, C, d_dlogits,
+                                                                               row_loss, row_hit);
+  NB_LAUNCH_CHECK();
+  loss_reduce_kernel<<<1, 1024, 0, stream>>>(row_loss, row_hit, B, d_stats);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+NB_API int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
+                   float b2, float eps, float wd, float b1_t, float b2_t, void *stream) {
+  if (n == 0) return 0;
+  NB_REQUIRE(d_W && d_grad && d_M && d_V && n > 0, "nb_adam: null pointer");
+  adam_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(d_W, d_grad, d_M, d_V, n, alpha, b1, b2, eps, wd,
+                                                               1.0f - b1_t, 1.0f - b2_t);
+  NB_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,292 @@
+"""Sampled mini-batch GCN trainer: the host-side mirror of GCN_GPU_NEIGHBOR_impl
+(toolkits/GCN_GPU_NEIGHBOR.hpp:7-1556) on top of the C ABI.
+
+One training step = sample_one -> feature/label gather -> per layer (aggregate, X*W, relu+dropout) ->
+loss -> backward (dW = Y^T dZ, dY = dZ W^T, transposed-CSR aggregate fused with the relu/dropout
+gradient) -> gradient sum over ranks -> Adam.  Like the reference (core/ntsContext.hpp:292) the
+input-side block is never back-propagated, so an L-layer step runs L forward and L-1 backward
+aggregations.  Every kernel is from libnb_b200.so; torch provides device memory, streams and
+torch.distributed only.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from .cuda_stream import Cuda_Stream, Workspace, ptr
+from .graph import FullyRepGraph, SampledSubgraph, Sampler
+
+
+@dataclass
+class GCNConfig:
+    """The .cfg keys the sampled GCN path reads (core/GraphSegment.cpp:196-405)."""
+    layers: Sequence[int] = (128, 128, 40)        # LAYERS a-b-c
+    fanout: Sequence[int] = (25, 10)              # hop order: seeds first (cfg FANOUT lists the reverse)
+    val_fanout: Optional[Sequence[int]] = None
+    batch_size: int = 1024
+    learn_rate: float = 0.01
+    weight_decay: float = 0.0001
+    drop_rate: float = 0.5
+    classes: int = 1
+    cache_type: str = "none"                      # none | rate | gpu_memory
+    cache_rate: float = 0.0
+    cache_policy: str = "degree"
+    seed: int = 2000
+    fuse_gather: bool = True                      # layer-0 aggregation reads the feature store directly
+    beta1: float = 0.9
+    beta2: float = 0.999
+    epsilon: float = 1e-9                         # toolkits/GCN_GPU_NEIGHBOR.hpp:217
+
+
+class Parameter:
+    """All layer weights in one flat bucket so that the gradient sum and Adam are one call each.
+    Per layer: xavier-uniform W[row x col] (core/NtsScheduler.hpp:641-643), zero M and V, and the
+    running beta powers of Parameter::next (core/NtsScheduler.hpp:700-711)."""
+
+    def __init__(self, layer_sizes: Sequence[int], cfg: GCNConfig, device, generator: Optional[torch.Generator] = None):
+        self.shapes = [(layer_sizes[i], layer_sizes[i + 1]) for i in range(len(layer_sizes) - 1)]
+        self.offsets = [0]
+        for r, c in self.shapes:
+            self.offsets.append(self.offsets[-1] + r * c)
+        n = self.offsets[-1]
+        host = torch.empty(n, dtype=torch.float32)
+        for i, (r, c) in enumerate(self.shapes):
+            bound = math.sqrt(6.0 / (r + c))
+            w = torch.empty(r, c).uniform_(-bound, bound, generator=generator)
+            host[self.offsets[i]: self.offsets[i + 1]] = w.reshape(-1)
+        self.W = host.to(device)
+        self.grad = torch.zeros(n, dtype=torch.float32, device=device)
+        self.M = torch.zeros(n, dtype=torch.float32, device=device)
+        self.V = torch.zeros(n, dtype=torch.float32, device=device)
+        self.cfg = cfg
+        self.beta1_t = np.float32(cfg.beta1)
+        self.beta2_t = np.float32(cfg.beta2)
+
+    def w(self, l: int) -> torch.Tensor:
+        r, c = self.shapes[l]
+        return self.W[self.offsets[l]: self.offsets[l + 1]].view(r, c)
+
+    def g(self, l: int) -> torch.Tensor:
+        r, c = self.shapes[l]
+        return self.grad[self.offsets[l]: self.offsets[l + 1]].view(r, c)
+
+    def learn_with_decay_Adam(self, stream: int):
+        """learnC2G_with_decay_Adam + next (core/NtsScheduler.hpp:794-811, 700-711)."""
+        c = self.cfg
+        _lib.call("nb_adam", ptr(self.W), ptr(self.grad), ptr(self.M), ptr(self.V), self.W.numel(), c.learn_rate,
+                  c.beta1, c.beta2, c.epsilon, c.weight_decay, float(self.beta1_t), float(self.beta2_t), stream)
+        self.beta1_t = np.float32(self.beta1_t * np.float32(c.beta1))
+        self.beta2_t = np.float32(self.beta2_t * np.float32(c.beta2))
+
+
+class GNNDatum:
+    """Feature table, labels and split mask (core/ntsDataloador.hpp:32-476).  Features stay where the
+    caller put them: a CUDA tensor, or a pinned host tensor that the gather kernel reads zero-copy."""
+
+    def __init__(self, feature: torch.Tensor, label: torch.Tensor, mask: np.ndarray):
+        assert feature.dtype == torch.float32 and feature.dim() == 2
+        self.local_feature = feature
+        self.local_label = label      # int64 on the GPU
+        self.local_mask = mask        # 0 train, 1 val, 2 test (core/ntsDataloador.hpp:318-330)
+
+
+def cache_slots_by_degree(out_degree: np.ndarray, cache_num: int) -> np.ndarray:
+    """cache_high_degree + mark_cache_node (toolkits/GCN_GPU_NEIGHBOR.hpp:919-943): nodes ordered by
+    descending out degree take slots 0..cache_num-1, all others 0xFFFFFFFF.  std::sort leaves equal
+    degrees in unspecified order; here ties go by ascending id."""
+    V = len(out_degree)
+    order = np.lexsort((np.arange(V, dtype=np.int64), -out_degree.astype(np.int64)))
+    hashmap = np.full(V, 0xFFFFFFFF, dtype=np.uint32)
+    cache_num = min(int(cache_num), V)
+    hashmap[order[:cache_num]] = np.arange(cache_num, dtype=np.uint32)
+    return hashmap
+
+
+class GCN_GPU_NEIGHBOR_impl:
+    """Trainer with the reference toolkit's structure (init_nn / Forward / Update / run)."""
+
+    def __init__(self, graph: FullyRepGraph, datum: GNNDatum, cfg: GCNConfig, ws: Optional[Workspace] = None,
+                 rank: int = 0, world_size: int = 1):
+        self.graph = graph
+        self.datum = datum
+        self.cfg = cfg
+        self.device = graph.device
+        self.rank, self.world_size = rank, world_size
+        self.layers = len(cfg.layers) - 1
+        assert len(cfg.fanout) == self.layers
+        self.ws = ws if ws is not None else Workspace(default_workspace_bytes(graph.global_vertices, cfg))
+        self.cuda_stream = Cuda_Stream()
+        gen = torch.Generator().manual_seed(cfg.seed)
+        self.P = Parameter(cfg.layers, cfg, self.device, gen)
+        self.step_count = 0
+        self.stats = torch.zeros(2, dtype=torch.float32, device=self.device)
+        self._stats_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        self.dev_cache_feature = None
+        self.dev_cache_node_hashmap = None
+        self.cache_node_num = 0
+        self.feature_on_device = datum.local_feature.is_cuda
+        self.agg_edges_fwd = 0
+        self.agg_edges_bwd = 0
+
+    # ------------------------------------------------------------------ cache (toolkits/...:899-999, 1214-1243)
+    def determine_cache_node_idx(self, node_nums: int):
+        V = self.graph.global_vertices
+        node_nums = min(int(node_nums), V)
+        self.cache_node_num = node_nums
+        if node_nums == 0:
+            return
+        assert self.cfg.cache_policy == "degree", "only CACHE_POLICY:degree is built"
+        out_deg = self.graph.out_degree.cpu().numpy().astype(np.uint32)
+        out_deg = np.maximum(out_deg, 1)  # generate_backward_structure clamp, core/graph.hpp:3983-3986
+        hashmap = cache_slots_by_degree(out_deg, node_nums)
+        self.dev_cache_node_hashmap = torch.from_numpy(hashmap.view(np.int32)).to(self.device)
+        F = self.cfg.layers[0]
+        ld = (F + 3) // 4 * 4  # private layout: rows padded to 16 bytes so that 128-bit loads apply
+        self.dev_cache_feature = torch.zeros((node_nums, ld), dtype=torch.float32, device=self.device)
+        feat = self.datum.local_feature
+        _lib.call("nb_cache_fill", ptr(self.dev_cache_feature), ld, ptr(feat), feat.stride(0),
+                  ptr(self.dev_cache_node_hashmap), V, F, torch.cuda.current_stream().cuda_stream)
+
+    def init_cache(self):
+        c = self.cfg
+        if c.cache_type == "rate":
+            assert 0.0 <= c.cache_rate <= 1.0
+            self.determine_cache_node_idx(int(self.graph.global_vertices * c.cache_rate))
+        elif c.cache_type != "none":
+            raise NotImplementedError(f"cache_type {c.cache_type}")
+
+    # ------------------------------------------------------------------ one step
+    def _aggregate0(self, ssg: SampledSubgraph, stream: int) -> torch.Tensor:
+        blk = ssg.sampled_sgs[0]
+        F = self.cfg.layers[0]
+        feat = self.datum.local_feature
+        Y = torch.empty((blk.v_size, F), dtype=torch.float32, device=self.device)
+        cache, hm = self.dev_cache_feature, self.dev_cache_node_hashmap
+        if self.cfg.fuse_gather:
+            _lib.call("nb_spmm_csc_fwd_gather_fused", ptr(feat), feat.stride(0), ptr(cache),
+                      cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), ptr(Y),
+                      ptr(blk.row_indices), ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size,
+                      F, stream)
+        else:
+            X0 = torch.empty((blk.src_size, F), dtype=torch.float32, device=self.device)
+            _lib.call("nb_feature_gather", ptr(X0), ptr(feat), feat.stride(0), None, 0, 0, ptr(cache),
+                      cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), blk.src_size, F, stream)
+            _lib.call("nb_spmm_csc_fwd_fused", ptr(X0), ptr(Y), ptr(blk.row_indices), ptr(blk.column_offset),
+                      ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, F, stream)
+        return Y
+
+    def forward_backward(self, ssg: SampledSubgraph, train: bool = True):
+        """Runs one batch; leaves loss and hit count in self.stats (device) and dW in P.grad."""
+        c, L = self.cfg, self.layers
+        stream = torch.cuda.current_stream().cuda_stream
+        wsh = self.ws.handle
+        p = c.drop_rate if train else 0.0
+        scale = 1.0 / (1.0 - p) if p > 0 else 1.0
+        Y: List[torch.Tensor] = []
+        X: List[Optional[torch.Tensor]] = [None]
+        for l in range(L):
+            blk = ssg.sampled_sgs[l]
+            if l == 0:
+                y = self._aggregate0(ssg, stream)
+            else:
+                y = torch.empty((blk.v_size, c.layers[l]), dtype=torch.float32, device=self.device)
+                _lib.call("nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(blk.row_indices), ptr(blk.column_offset),
+                          ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, c.layers[l], stream)
+            Y.append(y)
+            z = torch.empty((blk.v_size, c.layers[l + 1]), dtype=torch.float32, device=self.device)
+            _lib.call("nb_gemm", wsh, ptr(y), ptr(self.P.w(l)), ptr(z), blk.v_size, c.layers[l + 1], c.layers[l], 0,
+                      0, stream)
+            if l < L - 1:
+                _lib.call("nb_relu_dropout", ptr(z), z.numel(), p, c.seed, l, self.step_count, stream)
+            X.append(z)
+        last = ssg.sampled_sgs[L - 1]
+        B, C = last.v_size, c.layers[L]
+        lab = torch.empty(B, dtype=torch.int64, device=self.device)
+        _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(last.destination), B, 1, stream)
+        dZ = torch.empty((B, C), dtype=torch.float32, device=self.device) if train else None
+        _lib.call("nb_softmax_nll", wsh, ptr(X[L]), ptr(lab), B, C, ptr(dZ), ptr(self.stats), stream)
+        self.agg_edges_fwd += sum(b.e_size for b in ssg.sampled_sgs)
+        if not train:
+            return
+        for l in range(L - 1, -1, -1):
+            blk = ssg.sampled_sgs[l]
+            Fi, Fo = c.layers[l], c.layers[l + 1]
+            _lib.call("nb_gemm", wsh, ptr(Y[l]), ptr(dZ), ptr(self.P.g(l)), Fi, Fo, blk.v_size, 1, 0, stream)
+            if l == 0:
+                break  # the input-side block is never back-propagated (core/ntsContext.hpp:292)
+            dY = torch.empty((blk.v_size, Fi), dtype=torch.float32, device=self.device)
+            _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), blk.v_size, Fi, Fo, 0, 1, stream)
+            dX = torch.empty((blk.src_size, Fi), dtype=torch.float32, device=self.device)
+            _lib.call("nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(blk.row_offset), ptr(blk.column_indices),
+                      ptr(blk.src_norm), ptr(blk.dst_norm), ptr(X[l]), scale, blk.src_size, Fi, stream)
+            self.agg_edges_bwd += blk.e_size
+            dZ = dX
+
+    def Update(self):
+        """Gradient SUM over ranks (MPI_SUM in the reference, comm/network.h:189-193) then Adam."""
+        if self.world_size > 1:
+            torch.distributed.all_reduce(self.P.grad, op=torch.distributed.ReduceOp.SUM)
+        self.P.learn_with_decay_Adam(torch.cuda.current_stream().cuda_stream)
+
+    def UpdateZero(self):
+        """A rank that ran out of batches still joins the collective with zeros
+        (toolkits/GCN_GPU_NEIGHBOR.hpp:309-313)."""
+        self.P.grad.zero_()
+        self.Update()
+
+    def train_step(self, sampler: Sampler):
+        ssg = sampler.sample_one()
+        self.forward_backward(ssg, train=True)
+        self.Update()
+        self.step_count += 1
+
+    def read_stats(self):
+        """Device -> host read of (loss, hits) of the last batch; the only host sync of a step besides
+        the size read-backs of the block builder."""
+        self._stats_host.copy_(self.stats, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self._stats_host[0]), int(self._stats_host[1])
+
+    def Forward(self, sampler: Sampler, rng: Optional[np.random.RandomState] = None, train: bool = True,
+                max_batches: Optional[int] = None):
+        """One epoch over the sampler's seeds (Forward + zerocopy_version,
+        toolkits/GCN_GPU_NEIGHBOR.hpp:604-800).  Returns (accuracy, mean loss, batches)."""
+        if rng is not None:
+            sampler.shuffle(rng)
+        correct = nodes = batches = 0
+        loss_epoch = 0.0
+        while sampler.sample_not_finished():
+            if max_batches is not None and batches >= max_batches:
+                break
+            ssg = sampler.sample_one()
+            self.forward_backward(ssg, train=train)
+            if train:
+                self.Update()
+                self.step_count += 1
+            loss, hits = self.read_stats()
+            loss_epoch += loss
+            correct += hits
+            nodes += ssg.sampled_sgs[self.layers - 1].v_size
+            batches += 1
+        sampler.restart()
+        return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
+
+
+def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
+    """Arena size for the block builder and split-K partials at this configuration's upper bounds."""
+    v = cfg.batch_size
+    e_max = 0
+    for f in cfg.fanout:
+        e = v * (f if f > 0 else 64)
+        e_max = max(e_max, e)
+        v = min(num_vertices, e)
+    words = (num_vertices + 31) // 32
+    block = 8 * words + 16 * min(num_vertices, e_max) + 8 * e_max
+    widest = max(cfg.layers[i] * cfg.layers[i + 1] for i in range(len(cfg.layers) - 1))
+    splitk = 4 * widest * 320
+    return int(block + splitk + (64 << 20))

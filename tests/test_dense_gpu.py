@@ -1,0 +1,103 @@
+"""Dense pieces against the oracle: GEMM (NN/TN/NT), ReLU+dropout (bit-exact mask), softmax/NLL loss,
+Adam (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import dev_f32, dev_i64, host_f32
+from neutronbench_b200 import _lib
+from neutronbench_b200.cuda_stream import ptr
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-5   # fp32 tolerance of the north star; the GEMMs differ from the oracle only in summation order
+
+
+def _close(a, b, k):
+    scale = np.abs(b).max() + 1e-30
+    assert np.abs(a - b).max() / scale < RTOL * max(1.0, np.sqrt(k) / 8), (np.abs(a - b).max(), scale)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (63, 17, 65), (1024, 128, 41), (3000, 602, 128), (200, 1433, 16)])
+def test_gemm_nn(cuda_device, ws, M, K, N):
+    rng = np.random.RandomState(M + K + N)
+    a, b = rng.randn(M, K).astype(np.float32), rng.randn(K, N).astype(np.float32)
+    c = torch.empty((M, N), device=cuda_device)
+    _lib.call("nb_gemm", ws.handle, ptr(dev_f32(a, cuda_device)), ptr(dev_f32(b, cuda_device)), ptr(c), M, N, K, 0, 0,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    _close(host_f32(c), oracle.gemm_nn(a, b), K)
+
+
+@pytest.mark.parametrize("M,K,N", [(5000, 602, 128), (1024, 128, 41), (70, 3, 5), (25000, 100, 128)])
+def test_gemm_tn_weight_gradient(cuda_device, ws, M, K, N):
+    """dW[K x N] = Y^T[K x M] dZ[M x N]; the long reduction over M runs split-K."""
+    rng = np.random.RandomState(M + N)
+    y, dz = rng.randn(M, K).astype(np.float32), rng.randn(M, N).astype(np.float32)
+    c = torch.empty((K, N), device=cuda_device)
+    _lib.call("nb_gemm", ws.handle, ptr(dev_f32(y, cuda_device)), ptr(dev_f32(dz, cuda_device)), ptr(c), K, N, M, 1, 0,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    _close(host_f32(c), oracle.gemm_tn(y, dz), M)
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 41, 128), (3000, 128, 128), (7, 5, 3)])
+def test_gemm_nt_input_gradient(cuda_device, ws, M, N, K):
+    """dY[M x K] = dZ[M x N] W^T with W[K x N]."""
+    rng = np.random.RandomState(M + N + K)
+    dz, w = rng.randn(M, N).astype(np.float32), rng.randn(K, N).astype(np.float32)
+    c = torch.empty((M, K), device=cuda_device)
+    _lib.call("nb_gemm", ws.handle, ptr(dev_f32(dz, cuda_device)), ptr(dev_f32(w, cuda_device)), ptr(c), M, K, N, 0, 1,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    _close(host_f32(c), oracle.gemm_nt(dz, w), N)
+
+
+@pytest.mark.parametrize("n,p", [(1, 0.5), (1023, 0.5), (4096, 0.0), (100003, 0.3)])
+def test_relu_dropout_bit_exact(cuda_device, n, p):
+    z = np.random.RandomState(n).randn(n).astype(np.float32)
+    ref = oracle.relu_dropout(z, p, seed=2000, layer=1, step=17)
+    dz = dev_f32(z, cuda_device)
+    _lib.call("nb_relu_dropout", ptr(dz), n, p, 2000, 1, 17, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dz).view(np.uint32), ref.view(np.uint32))
+    if p > 0 and n > 1000:
+        kept = (ref[z > 0] != 0).mean()
+        assert abs(kept - (1 - p)) < 0.02
+
+
+@pytest.mark.parametrize("B,C", [(1, 2), (1024, 41), (4096, 47), (777, 172)])
+def test_softmax_nll(cuda_device, ws, B, C):
+    rng = np.random.RandomState(B)
+    logits = (rng.randn(B, C) * 3).astype(np.float32)
+    label = rng.randint(0, C, size=B).astype(np.int64)
+    loss, dref, correct = oracle.softmax_nll(logits, label)
+    d = torch.empty((B, C), device=cuda_device)
+    stats = torch.zeros(2, device=cuda_device)
+    _lib.call("nb_softmax_nll", ws.handle, ptr(dev_f32(logits, cuda_device)), ptr(dev_i64(label, cuda_device)), B, C,
+              ptr(d), ptr(stats), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = stats.cpu().numpy()
+    assert abs(got[0] - loss) <= 1e-5 * max(1.0, abs(loss))
+    assert int(got[1]) == correct
+    np.testing.assert_allclose(host_f32(d), dref, rtol=1e-4, atol=1e-7 / B)
+
+
+def test_adam_bit_exact_over_steps(cuda_device):
+    rng = np.random.RandomState(0)
+    n = 82304 + 3
+    W = rng.randn(n).astype(np.float32) * 0.1
+    M, V = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dW, dM, dV = dev_f32(W, cuda_device), dev_f32(M, cuda_device), dev_f32(V, cuda_device)
+    b1, b2 = np.float32(0.9), np.float32(0.999)
+    b1_t, b2_t = b1, b2
+    for step in range(4):
+        g = rng.randn(n).astype(np.float32) * 0.01
+        oracle.adam(W, g, M, V, 0.01, 0.9, 0.999, 1e-9, 0.0001, float(b1_t), float(b2_t))
+        _lib.call("nb_adam", ptr(dW), ptr(dev_f32(g, cuda_device)), ptr(dM), ptr(dV), n, 0.01, 0.9, 0.999, 1e-9, 0.0001,
+                  float(b1_t), float(b2_t), torch.cuda.current_stream().cuda_stream)
+        b1_t, b2_t = np.float32(b1_t * b1), np.float32(b2_t * b2)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dW).view(np.uint32), W.view(np.uint32))
+    np.testing.assert_array_equal(host_f32(dM).view(np.uint32), M.view(np.uint32))
+    np.testing.assert_array_equal(host_f32(dV).view(np.uint32), V.view(np.uint32))

@@ -1,0 +1,174 @@
+"""Aggregation parity: CUDA SpMM (through the C ABI) against the CPU oracle on identical blocks.
+
+Bar: the north star asks for 1e-5 relative (fp32).  The kernels keep the reference's operation order
+(multiply, add, edge by edge), so the comparison below is bit-exact; the tolerance is only stated for
+the full-size property test at the end.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import dev_f32, dev_i32, host_f32, small_graph
+from neutronbench_b200 import Cuda_Stream, _lib
+from neutronbench_b200.cuda_stream import ptr
+
+pytestmark = pytest.mark.gpu
+
+
+def _block(V=3000, E=40000, seeds=256, fanouts=(10, 5), seed=3, kind="rmat"):
+    edges, co, ri = small_graph(V, E, seed, kind)
+    rng = np.random.RandomState(seed)
+    s = rng.choice(V, size=seeds, replace=False).astype(np.uint32)
+    blocks, _ = oracle.sample_batch(co, ri, V, s, list(fanouts), seed=seed)
+    return blocks
+
+
+@pytest.mark.parametrize("F", [1, 2, 3, 16, 41, 100, 128, 602, 1433])
+def test_forward_explicit_weights_bit_exact(cuda_device, F):
+    blk = _block()[0]
+    rng = np.random.RandomState(F)
+    x = rng.randn(blk.src_size, F).astype(np.float32)
+    ref = oracle.spmm_fwd(x, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
+    dx = dev_f32(x, cuda_device)
+    dy = torch.full((blk.v_size, F), float("nan"), device=cuda_device)
+    cs = Cuda_Stream()
+    cs.Gather_By_Dst_From_Src(ptr(dx), ptr(dy), ptr(dev_f32(blk.edge_weight_forward, cuda_device)),
+                              ptr(dev_i32(blk.row_indices, cuda_device)), ptr(dev_i32(blk.column_offset, cuda_device)),
+                              0, 0, 0, 0, blk.e_size, blk.v_size, F, True, False)
+    cs.CUDA_DEVICE_SYNCHRONIZE()
+    np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("F", [1, 16, 100, 128, 602])
+def test_backward_explicit_weights_bit_exact(cuda_device, F):
+    blk = _block()[1]
+    rng = np.random.RandomState(100 + F)
+    gy = rng.randn(blk.v_size, F).astype(np.float32)
+    ref = oracle.spmm_bwd(gy, blk.edge_weight_backward, blk.row_offset, blk.column_indices)
+    dgy = dev_f32(gy, cuda_device)
+    dgx = torch.full((blk.src_size, F), float("nan"), device=cuda_device)
+    cs = Cuda_Stream()
+    cs.Gather_By_Src_From_Dst(ptr(dgy), ptr(dgx), ptr(dev_f32(blk.edge_weight_backward, cuda_device)),
+                              ptr(dev_i32(blk.row_offset, cuda_device)), ptr(dev_i32(blk.column_indices, cuda_device)),
+                              0, 0, 0, 0, blk.e_size, blk.src_size, F, True, False)
+    cs.CUDA_DEVICE_SYNCHRONIZE()
+    np.testing.assert_array_equal(host_f32(dgx).view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("F", [16, 128, 602])
+def test_fused_weight_variants_equal_explicit(cuda_device, F):
+    blk = _block(fanouts=(25, 10))[0]
+    rng = np.random.RandomState(7 + F)
+    x = rng.randn(blk.src_size, F).astype(np.float32)
+    gy = rng.randn(blk.v_size, F).astype(np.float32)
+    act = np.maximum(rng.randn(blk.src_size, F), 0).astype(np.float32)
+    ref_f = oracle.spmm_fwd(x, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
+    ref_b = oracle.spmm_bwd(gy, blk.edge_weight_backward, blk.row_offset, blk.column_indices, act=act, scale=2.0)
+    st = torch.cuda.current_stream().cuda_stream
+    d = cuda_device
+    ri, co = dev_i32(blk.row_indices, d), dev_i32(blk.column_offset, d)
+    ro, ci = dev_i32(blk.row_offset, d), dev_i32(blk.column_indices, d)
+    sn, dn = dev_f32(blk.src_norm, d), dev_f32(blk.dst_norm, d)
+    dy = torch.empty((blk.v_size, F), device=d)
+    _lib.call("nb_spmm_csc_fwd_fused", ptr(dev_f32(x, d)), ptr(dy), ptr(ri), ptr(co), ptr(sn), ptr(dn), blk.v_size, F,
+              st)
+    dgx = torch.empty((blk.src_size, F), device=d)
+    _lib.call("nb_spmm_csr_bwd_fused", ptr(dev_f32(gy, d)), ptr(dgx), ptr(ro), ptr(ci), ptr(sn), ptr(dn),
+              ptr(dev_f32(act, d)), 2.0, blk.src_size, F, st)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref_f.view(np.uint32))
+    np.testing.assert_array_equal(host_f32(dgx).view(np.uint32), ref_b.view(np.uint32))
+
+
+@pytest.mark.parametrize("F,use_cache", [(602, True), (602, False), (100, True), (128, True)])
+def test_gather_fused_forward_equals_gather_then_spmm(cuda_device, F, use_cache):
+    V = 3000
+    blk = _block(V=V)[0]
+    rng = np.random.RandomState(11)
+    feat = rng.randn(V, F).astype(np.float32)
+    out_deg = rng.randint(1, 50, size=V).astype(np.uint32)
+    hm, ids = oracle.cache_by_degree(out_deg, V // 3)
+    ld = (F + 3) // 4 * 4
+    cache = np.zeros((len(ids), ld), dtype=np.float32)
+    cache[:, :F] = feat[ids]
+    x0 = oracle.feature_gather(feat, blk.source)
+    ref = oracle.spmm_fwd(x0, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
+    d = cuda_device
+    dy = torch.empty((blk.v_size, F), device=d)
+    dfeat = dev_f32(feat, d)
+    dcache = dev_f32(cache, d) if use_cache else None
+    dhm = dev_i32(hm, d) if use_cache else None
+    _lib.call("nb_spmm_csc_fwd_gather_fused", ptr(dfeat), F, ptr(dcache), ld if use_cache else 0, ptr(dhm),
+              ptr(dev_i32(blk.source, d)), ptr(dy), ptr(dev_i32(blk.row_indices, d)),
+              ptr(dev_i32(blk.column_offset, d)), ptr(dev_f32(blk.src_norm, d)), ptr(dev_f32(blk.dst_norm, d)),
+              blk.v_size, F, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref.view(np.uint32))
+
+
+def test_empty_columns_and_empty_block(cuda_device):
+    # two destinations without in-edges around one with three
+    co = np.array([0, 0, 3, 3], dtype=np.uint32)
+    ri = np.array([1, 0, 1], dtype=np.uint32)
+    w = np.array([0.5, 0.25, 2.0], dtype=np.float32)
+    x = np.arange(8, dtype=np.float32).reshape(2, 4)
+    ref = oracle.spmm_fwd(x, w, ri, co)
+    d = cuda_device
+    dy = torch.full((3, 4), float("nan"), device=d)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.call("nb_spmm_csc_fwd", ptr(dev_f32(x, d)), ptr(dy), ptr(dev_f32(w, d)), ptr(dev_i32(ri, d)),
+              ptr(dev_i32(co, d)), 3, 4, st)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dy), ref)
+    assert (host_f32(dy)[0] == 0).all() and (host_f32(dy)[2] == 0).all()
+    _lib.call("nb_spmm_csc_fwd", 0, 0, 0, 0, 0, 0, 4, st)  # v == 0: nothing to do
+
+
+def test_long_rows_and_unaligned_views(cuda_device):
+    """A hub row of 5000 edges (several 32-edge passes) and an x tensor that starts 4 bytes off a
+    16-byte boundary (vector width must fall back)."""
+    rng = np.random.RandomState(5)
+    s, F = 700, 128
+    lens = np.array([5000, 0, 33, 32, 31, 1], dtype=np.uint32)
+    co = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    ri = rng.randint(0, s, size=int(co[-1])).astype(np.uint32)
+    w = rng.rand(int(co[-1])).astype(np.float32)
+    x = rng.randn(s, F).astype(np.float32)
+    ref = oracle.spmm_fwd(x, w, ri, co)
+    d = cuda_device
+    buf = torch.empty(s * F + 1, device=d)
+    xv = buf[1:].view(s, F)
+    xv.copy_(dev_f32(x, d))
+    assert xv.data_ptr() % 16 == 4
+    dy = torch.empty((len(lens), F), device=d)
+    _lib.call("nb_spmm_csc_fwd", ptr(xv), ptr(dy), ptr(dev_f32(w, d)), ptr(dev_i32(ri, d)), ptr(dev_i32(co, d)),
+              len(lens), F, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref.view(np.uint32))
+
+
+def test_linearity_at_full_size(cuda_device):
+    """Reddit-shaped input block sizes (v=25k, fanout 10, F=602): A(x1 + 2 x2) == A x1 + 2 A x2 within
+    1e-5 relative — a size-independent property checked without the CPU oracle."""
+    rng = np.random.RandomState(9)
+    v, s, F, fan = 25000, 140000, 602, 10
+    co = (np.arange(v + 1) * fan).astype(np.uint32)
+    ri = rng.randint(0, s, size=v * fan).astype(np.uint32)
+    w = rng.rand(v * fan).astype(np.float32)
+    d = cuda_device
+    g = torch.Generator(device=d).manual_seed(1)
+    x1 = torch.randn((s, F), device=d, generator=g)
+    x2 = torch.randn((s, F), device=d, generator=g)
+    dri, dco, dw = dev_i32(ri, d), dev_i32(co, d), dev_f32(w, d)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def agg(x):
+        y = torch.empty((v, F), device=d)
+        _lib.call("nb_spmm_csc_fwd", ptr(x), ptr(y), ptr(dw), ptr(dri), ptr(dco), v, F, st)
+        return y
+
+    lhs = agg(x1 + 2 * x2)
+    rhs = agg(x1) + 2 * agg(x2)
+    err = (lhs - rhs).abs().max().item() / rhs.abs().max().item()
+    assert err < 1e-5, err
