@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the sampled mini-batch GCN training path (ALGORITHM:GCNNEIGHBORGPU) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload reddit|arxiv|products] [--impl reference]
+
+A "step" is one mini-batch through the whole hot path: fan-out sampling -> block construction ->
+feature/label gather -> per-layer aggregation + dense layer -> loss -> backward -> gradient sum over
+ranks -> Adam.  Rank 0 prints ONE JSON line.
+
+  value      aggregated edges per second over all ranks, seeds already resident in HBM.
+             Aggregated edges of a step = sum of e_size over the blocks (forward, the reference's
+             Sampler::get_compute_cnt, core/ntsSampler.hpp:629-635) + sum over blocks l >= 1 (backward;
+             the input-side block is never back-propagated, core/ntsContext.hpp:292).
+  e2e        the same metric through the public API (train_step + read_stats) with the batch's seeds
+             copied from pinned host memory and the loss read back to the host every step.
+  roofline   aggregation kernels (spmm_rows_kernel, all launches of the timed region): algorithmic
+             bytes / CUDA-event time against the measured HBM copy bandwidth.
+  cpu_baseline  the CPU oracle (a port of the reference's CPU sampler + MiniBatchFuseOp GCN step)
+             timed on this box's host cores on a few batches of the same workload.
+
+The datasets the reference uses are not available; graphs, features and labels are seeded synthetic
+data with the published shapes (see neutronbench_b200/synth.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool; used only when MEASURED_PEAKS.json is absent
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=0, help="timed steps per rank (0 = one epoch of the workload)")
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cache-rate", type=float, default=None, help="override the workload's GPU cache rate")
+    ap.add_argument("--cpu-batches", type=int, default=3, help="batches timed for the CPU baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fuse-gather", action="store_true")
+    ap.add_argument("--seed", type=int, default=2000)
+    return ap.parse_args()
+
+
+def workload_config(name, args):
+    from neutronbench_b200 import GCNConfig, synth
+    sh = synth.SHAPES[name]
+    hidden = [sh.hidden] * (len(sh.fanout) - 1)
+    cache_rate = {"arxiv": 1.0, "reddit": 1.0, "products": 0.2}[name]
+    if args.cache_rate is not None:
+        cache_rate = args.cache_rate
+    cfg = GCNConfig(layers=[sh.feature] + hidden + [sh.classes], fanout=sh.fanout, batch_size=sh.batch,
+                    learn_rate=0.01, weight_decay=0.0001, drop_rate=0.5,
+                    cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate, seed=args.seed,
+                    fuse_gather=not args.no_fuse_gather)
+    return sh, cfg
+
+
+def build_workload(name, args, device):
+    """Graph topology, features, labels and the train split, all seeded.  Data preparation is not timed."""
+    import torch
+    from neutronbench_b200 import FullyRepGraph, GNNDatum, Workspace, synth
+    sh, cfg = workload_config(name, args)
+    edges = synth.rmat_torch(sh.vertices, sh.edges, sh.rmat, args.seed, device=device)
+    big = Workspace(int(edges.size(0)) * 9 + sh.vertices * 16 + (64 << 20), device)
+    graph = FullyRepGraph.from_edges(edges, sh.vertices, big)
+    torch.cuda.synchronize()
+    del edges
+    big.close()
+    del big
+    torch.cuda.empty_cache()
+    gen = torch.Generator(device=device).manual_seed(args.seed + 1)
+    feat_dev = torch.randn((sh.vertices, sh.feature), generator=gen, device=device, dtype=torch.float32)
+    label = torch.randint(0, sh.classes, (sh.vertices,), generator=gen, device=device, dtype=torch.int64)
+    mask = synth.split_mask(sh.vertices, args.seed)
+    if cfg.cache_type == "rate" and cfg.cache_rate >= 1.0:
+        feature = feat_dev                       # every row is a cache hit; the table only seeds the cache
+    else:
+        feature = feat_dev.cpu().pin_memory()    # misses are zero-copy reads of mapped pinned host memory
+    datum = GNNDatum(feature, label, mask)
+    train_ids = np.nonzero(mask == 0)[0].astype(np.uint32)
+    return sh, cfg, graph, datum, train_ids, feat_dev
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = f"/tmp/nb_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "50", "-i", str(self.index)], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def aggregated_edges(blocks):
+    fwd = sum(b.e_size for b in blocks)
+    bwd = sum(b.e_size for b in blocks[1:])
+    return fwd, bwd
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_arm(sh, cfg, graph, feat_dev, label, train_ids, batches, warmup, seed):
+    """The reference's CPU path as restated by the oracle (sample_one + MiniBatchFuseOp GCN step,
+    toolkits/GCN_CPU_NEIGHBOR.hpp:225-427) on the host cores: OpenMP aggregation, BLAS dense layers
+    (numpy stands in for libtorch's CPU mm).  Returns (edges/s, ms per batch, threads, per-batch ms)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    co = graph.column_offset.cpu().numpy().astype(np.uint64)
+    ri = graph.row_indices.cpu().numpy().view(np.uint32)
+    feat = feat_dev.cpu().numpy()
+    lab = label.cpu().numpy()
+    rng = np.random.RandomState(seed)
+    W0 = np.concatenate([rng.uniform(-1, 1, cfg.layers[i] * cfg.layers[i + 1]).astype(np.float32)
+                         * np.float32(np.sqrt(6.0 / (cfg.layers[i] + cfg.layers[i + 1])))
+                         for i in range(len(cfg.layers) - 1)])
+    net = oracle.GCN(cfg.layers, W0, cfg.learn_rate, cfg.weight_decay, cfg.drop_rate, cfg.seed, blas=True)
+    threads = oracle.lib().orc_num_threads()
+    times, edges = [], 0
+    for b in range(warmup + batches):
+        seeds = train_ids[b * cfg.batch_size: (b + 1) * cfg.batch_size]
+        t0 = time.perf_counter()
+        blocks, _ = oracle.sample_batch(co, ri, sh.vertices, seeds, list(cfg.fanout), cfg.seed, b)
+        net.train_step(blocks, feat, lab)
+        dt = time.perf_counter() - t0
+        if b >= warmup:
+            times.append(dt)
+            f, bw = aggregated_edges(blocks)
+            edges += f + bw
+    total = sum(times)
+    return edges / total, 1e3 * total / len(times), threads, [1e3 * t for t in times]
+
+
+def main():
+    args = parse_args()
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
+        return 0
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1 and args.impl != "reference":
+        dist.init_process_group("nccl", device_id=device)
+
+    from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, Sampler, _lib
+    sh, cfg, graph, datum, train_ids, feat_dev = build_workload(args.workload, args, device)
+    batches_per_epoch = (len(train_ids) + cfg.batch_size - 1) // cfg.batch_size
+
+    workload_desc = {
+        "workload": f"{sh.name}-shaped synthetic R-MAT: {sh.vertices} nodes, {graph.global_edges} edges (incl. self "
+                    f"loops), feature {sh.feature}, layers {'-'.join(map(str, cfg.layers))}, fanout "
+                    f"{list(cfg.fanout)} (hop order), batch {cfg.batch_size}, cache_rate {cfg.cache_rate}",
+        "batches_per_epoch": batches_per_epoch,
+        "l2_policy": "inputs larger than L2 (feature store >> 126 MB, each step touches a new random subset)",
+        "parallelism": f"dp{world}",
+        "fuse_gather": cfg.fuse_gather,
+    }
+
+    if args.impl == "reference":
+        K = args.steps if args.steps > 0 else 3
+        W = max(args.warmup, 0)
+        W = min(W, 2)
+        eps, ms, threads, per = cpu_arm(sh, cfg, graph, feat_dev, datum.local_label, train_ids, K, W, args.seed)
+        line = {"impl": "reference", "metric": "aggregated_edges_per_s", "value": eps, "unit": "edges/s",
+                "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_desc,
+                "epoch_time_s": ms * batches_per_epoch / 1e3,
+                "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port",
+                                 "sample": f"{K} mini-batches of the workload after {W} warm-up, all host threads"},
+                "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world)
+    tk.init_cache()
+    del feat_dev
+    # this rank's share of the shuffled train list: contiguous shard (data parallel over mini-batches)
+    rng = np.random.RandomState(args.seed)
+    ids = train_ids.copy()
+    rng.shuffle(ids)
+    shard = ids[rank::world] if world > 1 else ids
+    K = args.steps if args.steps > 0 else (len(shard) + cfg.batch_size - 1) // cfg.batch_size
+    W = max(args.warmup, 3)
+    need = (W + K) * cfg.batch_size
+    reps = (need + len(shard) - 1) // len(shard)
+    seeds_all = np.tile(shard, reps)[:need]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(staged: bool, record_events: bool):
+        smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
+        if staged:
+            smp.stage_seeds_on_device()
+        for _ in range(W):
+            tk.train_step(smp)
+            if not staged:
+                tk.read_stats()
+        barrier()
+        tk.agg_edges_fwd = tk.agg_edges_bwd = 0
+        tk.events = [] if record_events else None
+        launches0 = _lib.load().nb_launch_count()
+        clocks = ClockSampler(local_rank)
+        if rank == 0 and record_events:
+            clocks.start()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(K):
+            tk.train_step(smp)
+            if not staged:
+                tk.read_stats()
+        t1.record()
+        barrier()
+        ms = t0.elapsed_time(t1)
+        clk = clocks.stop() if (rank == 0 and record_events) else None
+        launches = _lib.load().nb_launch_count() - launches0
+        edges = tk.agg_edges_fwd + tk.agg_edges_bwd
+        ev = tk.events
+        tk.events = None
+        return ms, edges, launches, clk, ev
+
+    ms_a, edges_a, launches, clk, events = run(staged=True, record_events=True)
+    ms_b, edges_b, _, _, _ = run(staged=False, record_events=False)
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    ms_a, ms_b = reduce_max(ms_a), reduce_max(ms_b)
+    edges_a, edges_b = reduce_sum(edges_a), reduce_sum(edges_b)
+
+    # roofline of the aggregation kernels from the events recorded inside the timed region
+    agg_ms = sum(s.elapsed_time(e) for (_, _, s, e) in events)
+    agg_bytes = sum(b for (_, b, _, _) in events)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak = float(json.load(open(peaks_path))["hbm_gbs"])
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    achieved = agg_bytes / (agg_ms * 1e-3) / 1e9 if agg_ms > 0 else 0.0
+    per_kernel = {}
+    for (name, b, s, e) in events:
+        d = per_kernel.setdefault(name, [0, 0.0, 0])
+        d[0] += b
+        d[1] += s.elapsed_time(e)
+        d[2] += 1
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": peak_src, "kernel": "spmm_rows_kernel (all aggregation launches)",
+                "launches": len(events), "avg_launch_ms": agg_ms / max(len(events), 1),
+                "per_call": {k: {"GBps": v[0] / (v[1] * 1e-3) / 1e9 if v[1] > 0 else 0.0, "ms_avg": v[1] / v[2],
+                                 "bytes_avg": v[0] / v[2]} for k, v in per_kernel.items()}}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    value = edges_a / (ms_a * 1e-3)
+    e2e_value = edges_b / (ms_b * 1e-3)
+    hops = len(cfg.fanout)
+    line = {
+        "metric": "aggregated_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms_a / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": workload_desc,
+        "epoch_time_s": (ms_a / K) * ((batches_per_epoch + world - 1) // world) / 1e3,
+        "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": ms_b / K,
+                "epoch_time_s": (ms_b / K) * ((batches_per_epoch + world - 1) // world) / 1e3,
+                "h2d_bytes_per_step": cfg.batch_size * 4, "d2h_bytes_per_step": 8 + hops * 12},
+        "gpu_launches": int(launches), "roofline": roofline, "clocks": clk,
+        "aggregated_edges_per_step": edges_a / (K * world),
+    }
+    if not args.no_cpu_baseline and world == 1:
+        sh2, cfg2, graph2 = sh, cfg, graph
+        feat_for_cpu = datum.local_feature if not datum.local_feature.is_cuda else datum.local_feature
+        eps, ms, threads, per = cpu_arm(sh2, cfg2, graph2, feat_for_cpu, datum.local_label, train_ids,
+                                        args.cpu_batches, 1, args.seed)
+        line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port",
+                                "ms_per_step": ms, "epoch_time_s": ms * batches_per_epoch / 1e3,
+                                "sample": f"{args.cpu_batches} mini-batches of the same workload after 1 warm-up "
+                                          f"batch, OpenMP + BLAS on all host threads"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

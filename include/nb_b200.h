@@ -38,6 +38,8 @@ typedef enum nb_status {
 
 const char *nb_last_error(void);
 int nb_version(void);
+/* Number of CUDA kernels this library has launched in the calling process so far. */
+uint64_t nb_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Workspace: a bump arena of device scratch memory plus a small pinned host mailbox used to read

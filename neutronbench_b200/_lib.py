@@ -22,6 +22,7 @@ ptr = C.c_void_p
 SIGNATURES = {
     "nb_last_error": (C.c_char_p, []),
     "nb_version": (C.c_int, []),
+    "nb_launch_count": (C.c_uint64, []),
     "nb_ws_create": (C.c_int, [C.POINTER(C.c_void_p), ptr, C.c_size_t]),
     "nb_ws_destroy": (C.c_int, [ptr]),
     "nb_ws_reset": (C.c_int, [ptr]),

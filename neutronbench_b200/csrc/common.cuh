@@ -29,8 +29,13 @@ inline int fail(nb_status st, const char *what) {
     }                                                                                         \
   } while (0)
 
+// Every kernel launch in the library is followed by NB_LAUNCH_CHECK, which also counts it
+// (nb_launch_count reports the total, so that callers can state how many kernels a step ran).
+extern unsigned long long g_launches;
+
 #define NB_LAUNCH_CHECK()                                                                     \
   do {                                                                                        \
+    __atomic_fetch_add(&nb::g_launches, 1ull, __ATOMIC_RELAXED);                              \
     cudaError_t err__ = cudaGetLastError();                                                   \
     if (err__ != cudaSuccess) {                                                               \
       nb::set_error("%s:%d kernel launch -> %s", __FILE__, __LINE__, cudaGetErrorString(err__)); \

@@ -6,6 +6,7 @@
 namespace nb {
 
 static thread_local char g_err[512] = "";
+unsigned long long g_launches = 0;
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -139,6 +140,7 @@ int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, 
 
 NB_API const char *nb_last_error(void) { return nb::g_err; }
 NB_API int nb_version(void) { return 100; }
+NB_API uint64_t nb_launch_count(void) { return __atomic_load_n(&nb::g_launches, __ATOMIC_RELAXED); }
 
 NB_API int nb_ws_create(nb_ws **out, void *d_arena, size_t bytes) {
   NB_REQUIRE(out != nullptr, "nb_ws_create: out is null");

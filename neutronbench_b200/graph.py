@@ -183,6 +183,7 @@ class Sampler:
         self.cs = Cuda_Stream()
         self.update_batch_size(batch_size)
         self._pinned_seeds = None
+        self._dev_nids = None
 
     # core/ntsSampler.hpp:259-265
     def update_batch_size(self, batch_size: int):
@@ -204,6 +205,15 @@ class Sampler:
     def shuffle(self, rng: np.random.RandomState):
         """Per-epoch reshuffle of the seed list (toolkits/GCN_GPU_NEIGHBOR.hpp:742-745)."""
         rng.shuffle(self.sample_nids)
+        self._dev_nids = None
+
+    def stage_seeds_on_device(self):
+        """Upload the whole (shuffled) seed list once; later batches slice it on the device instead of
+        copying their seeds from pinned host memory every step."""
+        self._dev_nids = torch.from_numpy(self.sample_nids.view(np.int32).copy()).to(self.whole_graph.device)
+
+    def unstage_seeds(self):
+        self._dev_nids = None
 
     def get_compute_cnt(self) -> int:
         """Sum of e_size over the blocks (core/ntsSampler.hpp:629-635)."""
@@ -228,7 +238,10 @@ class Sampler:
         self.work_offset += actl
         g = self.whole_graph
         stream = torch.cuda.current_stream().cuda_stream
-        dst = self._seeds_to_device(seeds)
+        if self._dev_nids is not None:
+            dst = self._dev_nids[self.work_offset - actl: self.work_offset]
+        else:
+            dst = self._seeds_to_device(seeds)
         v = actl
         blocks = []
         for hop in range(self.layers):

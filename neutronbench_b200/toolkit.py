@@ -132,6 +132,34 @@ class GCN_GPU_NEIGHBOR_impl:
         self.feature_on_device = datum.local_feature.is_cuda
         self.agg_edges_fwd = 0
         self.agg_edges_bwd = 0
+        self.events = None  # when a list: (name, algorithmic bytes, start event, end event) per aggregation
+
+    def _timed(self, name: str, nbytes: int, fn):
+        """Runs fn(); with self.events set, brackets it with CUDA events on the current stream."""
+        if self.events is None:
+            fn()
+            return
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        self.events.append((name, nbytes, s, e))
+
+    @staticmethod
+    def agg_bytes_fwd(blk, F: int, gather_fused: bool = False, cached: bool = False) -> int:
+        """Compulsory traffic of one forward aggregation: every source row read once, every destination
+        row written once, row indices, column offsets, the two sqrt-degree vectors; the gather-fused
+        form also reads the global ids (and cache slots) of the sources."""
+        s, v, e = blk.src_size, blk.v_size, blk.e_size
+        b = 4 * F * (s + v) + 4 * e + 4 * (v + 1) + 4 * (s + v)
+        if gather_fused:
+            b += 4 * s + (4 * s if cached else 0)
+        return b
+
+    @staticmethod
+    def agg_bytes_bwd(blk, F: int, masked: bool = True) -> int:
+        s, v, e = blk.src_size, blk.v_size, blk.e_size
+        return 4 * F * (v + s) + 4 * e + 4 * (s + 1) + 4 * (s + v) + (4 * F * s if masked else 0)
 
     # ------------------------------------------------------------------ cache (toolkits/...:899-999, 1214-1243)
     def determine_cache_node_idx(self, node_nums: int):
@@ -168,16 +196,17 @@ class GCN_GPU_NEIGHBOR_impl:
         Y = torch.empty((blk.v_size, F), dtype=torch.float32, device=self.device)
         cache, hm = self.dev_cache_feature, self.dev_cache_node_hashmap
         if self.cfg.fuse_gather:
-            _lib.call("nb_spmm_csc_fwd_gather_fused", ptr(feat), feat.stride(0), ptr(cache),
-                      cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), ptr(Y),
-                      ptr(blk.row_indices), ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size,
-                      F, stream)
+            self._timed("fwd0_gather_fused", self.agg_bytes_fwd(blk, F, True, hm is not None), lambda: _lib.call(
+                "nb_spmm_csc_fwd_gather_fused", ptr(feat), feat.stride(0), ptr(cache),
+                cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), ptr(Y), ptr(blk.row_indices),
+                ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, F, stream))
         else:
             X0 = torch.empty((blk.src_size, F), dtype=torch.float32, device=self.device)
             _lib.call("nb_feature_gather", ptr(X0), ptr(feat), feat.stride(0), None, 0, 0, ptr(cache),
                       cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), blk.src_size, F, stream)
-            _lib.call("nb_spmm_csc_fwd_fused", ptr(X0), ptr(Y), ptr(blk.row_indices), ptr(blk.column_offset),
-                      ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, F, stream)
+            self._timed("fwd0", self.agg_bytes_fwd(blk, F), lambda: _lib.call(
+                "nb_spmm_csc_fwd_fused", ptr(X0), ptr(Y), ptr(blk.row_indices), ptr(blk.column_offset),
+                ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, F, stream))
         return Y
 
     def forward_backward(self, ssg: SampledSubgraph, train: bool = True):
@@ -195,8 +224,9 @@ class GCN_GPU_NEIGHBOR_impl:
                 y = self._aggregate0(ssg, stream)
             else:
                 y = torch.empty((blk.v_size, c.layers[l]), dtype=torch.float32, device=self.device)
-                _lib.call("nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(blk.row_indices), ptr(blk.column_offset),
-                          ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, c.layers[l], stream)
+                self._timed(f"fwd{l}", self.agg_bytes_fwd(blk, c.layers[l]), lambda: _lib.call(
+                    "nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(blk.row_indices), ptr(blk.column_offset),
+                    ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, c.layers[l], stream))
             Y.append(y)
             z = torch.empty((blk.v_size, c.layers[l + 1]), dtype=torch.float32, device=self.device)
             _lib.call("nb_gemm", wsh, ptr(y), ptr(self.P.w(l)), ptr(z), blk.v_size, c.layers[l + 1], c.layers[l], 0,
@@ -222,8 +252,9 @@ class GCN_GPU_NEIGHBOR_impl:
             dY = torch.empty((blk.v_size, Fi), dtype=torch.float32, device=self.device)
             _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), blk.v_size, Fi, Fo, 0, 1, stream)
             dX = torch.empty((blk.src_size, Fi), dtype=torch.float32, device=self.device)
-            _lib.call("nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(blk.row_offset), ptr(blk.column_indices),
-                      ptr(blk.src_norm), ptr(blk.dst_norm), ptr(X[l]), scale, blk.src_size, Fi, stream)
+            self._timed(f"bwd{l}", self.agg_bytes_bwd(blk, Fi), lambda: _lib.call(
+                "nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(blk.row_offset), ptr(blk.column_indices),
+                ptr(blk.src_norm), ptr(blk.dst_norm), ptr(X[l]), scale, blk.src_size, Fi, stream))
             self.agg_edges_bwd += blk.e_size
             dZ = dX
 

@@ -7,6 +7,8 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+if os.path.join(ROOT, 'tests') not in sys.path:
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
 
 
 def pytest_configure(config):
@@ -38,3 +40,13 @@ def ws(cuda_device):
     w = Workspace(512 << 20)
     yield w
     w.close()
+
+
+@pytest.fixture(autouse=True)
+def _release_device_temporaries():
+    yield
+    try:
+        import helpers
+        helpers.KEEP_ALIVE.clear()
+    except Exception:
+        pass

@@ -17,16 +17,27 @@ def small_graph(V=3000, E=40000, seed=1, kind="rmat"):
     return edges, co, ri
 
 
+# Device tensors made by the dev_* helpers stay referenced until the test ends: the C ABI takes raw
+# addresses, so a temporary whose last Python reference is gone could be recycled by torch's caching
+# allocator while a kernel still reads it.  tests/conftest.py clears the list after every test.
+KEEP_ALIVE = []
+
+
+def _keep(t):
+    KEEP_ALIVE.append(t)
+    return t
+
+
 def dev_i32(a, device):
-    return torch.from_numpy(np.ascontiguousarray(a).astype(np.uint32).view(np.int32)).to(device)
+    return _keep(torch.from_numpy(np.ascontiguousarray(a).astype(np.uint32).view(np.int32)).to(device))
 
 
 def dev_i64(a, device):
-    return torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(device)
+    return _keep(torch.from_numpy(np.ascontiguousarray(a).astype(np.int64)).to(device))
 
 
 def dev_f32(a, device):
-    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)
+    return _keep(torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device))
 
 
 def host_u32(t, n=None):

@@ -234,7 +234,10 @@ class GCN:
     """CPU restatement of one GCN_CPU_NEIGHBOR / GCN_GPU_NEIGHBOR training step on given blocks
     (toolkits/GCN_CPU_NEIGHBOR.hpp:225-427): forward, loss, backward, Adam."""
 
-    def __init__(self, layer_sizes, W_flat, lr, wd, drop, seed, b1=0.9, b2=0.999, eps=1e-9):
+    def __init__(self, layer_sizes, W_flat, lr, wd, drop, seed, b1=0.9, b2=0.999, eps=1e-9, blas=False):
+        # blas=True routes the dense products through numpy's BLAS (the stand-in for libtorch's CPU mm
+        # when the oracle is timed as the host baseline); blas=False uses the plain-C loops.
+        self.blas = blas
         self.sizes = list(layer_sizes)
         self.L = len(self.sizes) - 1
         self.offs = [0]
@@ -262,7 +265,7 @@ class GCN:
             b = blocks[l]
             y = spmm_fwd(X[l], b.edge_weight_forward, b.row_indices, b.column_offset)
             Y.append(y)
-            z = gemm_nn(y, self.w(l))
+            z = (y @ self.w(l)) if self.blas else gemm_nn(y, self.w(l))
             if l < L - 1:
                 z = relu_dropout(z, p, self.seed, l, self.step)
             X.append(z)
@@ -271,10 +274,10 @@ class GCN:
         if train:
             for l in range(L - 1, -1, -1):
                 b = blocks[l]
-                self.grad[self.offs[l]: self.offs[l + 1]] = gemm_tn(Y[l], dZ).reshape(-1)
+                self.grad[self.offs[l]: self.offs[l + 1]] = ((Y[l].T @ dZ) if self.blas else gemm_tn(Y[l], dZ)).reshape(-1)
                 if l == 0:
                     break
-                dY = gemm_nt(dZ, self.w(l))
+                dY = (dZ @ self.w(l).T) if self.blas else gemm_nt(dZ, self.w(l))
                 dZ = spmm_bwd(dY, b.edge_weight_backward, b.row_offset, b.column_indices, act=X[l], scale=scale)
             adam(self.W, self.grad, self.M, self.V, self.lr, self.b1, self.b2, self.eps, self.wd, float(self.b1_t),
                  float(self.b2_t))
