@@ -98,13 +98,29 @@ int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t *d_row_
  * 0xFFFFFFFF, else feat[g] (device, mapped pinned host, or a peer GPU's memory).  Equals
  * nb_feature_gather followed by nb_spmm_csc_fwd_fused (core/ntsSampler.hpp:364-376 then
  * core/ntsMiniBatchGraphOp.hpp:288-318) bit for bit.  cache_ld / feat_ld are the row pitches in
- * floats (>= F). */
-int nb_spmm_csc_fwd_gather_fused(const float *feat, size_t feat_ld, const float *d_cache,
+ * floats (>= F); s and e are the block's source and edge counts; ws (nullable) provides 8*e bytes
+ * of scratch for the staged path. */
+int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache,
                                  size_t cache_ld, const uint32_t *d_hashmap,
                                  const uint32_t *d_source, float *d_y,
                                  const uint32_t *d_row_indices, const uint32_t *d_column_offset,
                                  const float *d_src_norm, const float *d_dst_norm, uint32_t v,
-                                 uint32_t F, void *stream);
+                                 uint32_t s, uint32_t e, uint32_t F, void *stream);
+
+/* Where the rows are 16-byte aligned (base aligned, width a multiple of 4 floats or a padded pitch)
+ * and F <= 1024, the aggregation entry points above stage source rows through shared memory with
+ * non-multicast TMA bulk copies; otherwise they use direct vector loads.  Both give identical bits.
+ * By default only rows of 256 floats or more are staged (narrow rows are faster with direct loads).
+ * nb_set_staged_spmm(0) forces the direct-load path, 2 stages every width the alignment rules allow,
+ * 1 restores the default; returns the previous on/off setting.
+ * nb_device_error_flags reads (and so synchronises with) the device-side error word: bit 0 is set
+ * when a bounded wait on a copy barrier gave up. */
+int nb_set_staged_spmm(int enabled);
+/* The staged gather-fused aggregation cuts wide rows into column panels whose distinct source data
+ * (s rows x panel width) stays below this many bytes, so that reuse of a source row hits L2
+ * (0 = never cut).  Returns the previous value; default 48 MiB. */
+uint64_t nb_set_l2_panel_bytes(uint64_t bytes);
+int nb_device_error_flags(uint32_t *flags);
 
 /* ------------------------------------------------------------------------------------------------
  * Block construction.

@@ -33,8 +33,11 @@ SIGNATURES = {
     "nb_spmm_csc_fwd_fused": (C.c_int, [f32p, f32p, u32p, u32p, f32p, f32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_spmm_csr_bwd_fused": (C.c_int, [f32p, f32p, u32p, u32p, f32p, f32p, f32p, C.c_float, C.c_uint32,
                                         C.c_uint32, ptr]),
-    "nb_spmm_csc_fwd_gather_fused": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, u32p, f32p, u32p, u32p,
-                                               f32p, f32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_spmm_csc_fwd_gather_fused": (C.c_int, [ptr, f32p, C.c_size_t, f32p, C.c_size_t, u32p, u32p, f32p, u32p, u32p,
+                                               f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, ptr]),
+    "nb_set_l2_panel_bytes": (C.c_uint64, [C.c_uint64]),
+    "nb_set_staged_spmm": (C.c_int, [C.c_int]),
+    "nb_device_error_flags": (C.c_int, [C.POINTER(C.c_uint32)]),
     "nb_block_build": (C.c_int, [ptr, C.c_uint32, u32p, u32p, C.c_uint32, C.c_uint32, u32p,
                                  C.POINTER(C.c_uint32), u32p, u32p, f32p, f32p, f32p, f32p, ptr]),
     "nb_sample_hop_offsets": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_int, u32p, C.POINTER(C.c_uint32), ptr]),

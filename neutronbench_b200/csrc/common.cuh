@@ -93,6 +93,36 @@ struct nb_ws {
 };
 
 namespace nb {
+// Arguments of the shared-memory-staged aggregation kernel (spmm_tma.cu).
+struct TmaSpmmArgs {
+  const float *x;          // base of the rows that the TMA unit copies: row(ref) = x + ref * x_ld
+  size_t x_ld;             // pitch in floats, a multiple of 4; x is 16-byte aligned
+  const float *miss;       // base of rows whose reference has bit 31 set (copied by the lanes), or null
+  size_t miss_ld;
+  float *y;                // n x F output
+  const uint32_t *offs;    // n + 1 offsets
+  const uint32_t *ref;     // per edge: row reference
+  const float *w;          // per edge weight, or null to form it from the two factors below
+  const float *norm_row;   // [n]
+  const float *norm_idx;   // indexed by ref (only valid when references are plain local indices)
+  const float *act;        // nullable n x F activation for the relu/dropout gradient mask
+  float act_scale;
+  uint32_t n, F;
+  uint32_t src_rows_hint;  // number of distinct rows the references can name (0 = unknown): sizes the panels
+  uint32_t slot_bytes, copy_bytes, seg, fpad, panels, panel_floats;   // filled by launch_spmm_tma
+  int l2_prefetch;
+  int out_vec;             // widest vector (floats) usable for y and act rows: 4, 2 or 1
+};
+bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F);
+int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream);
+int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, uint32_t e, const uint32_t *source,
+                       const uint32_t *hashmap, bool feat_is_hit, const float *norm_idx, const float *norm_row,
+                       uint32_t *ref, float *w, cudaStream_t stream);
+int read_tma_error_flag(unsigned int *value);
+extern uint64_t g_l2_panel_bytes;
+extern int g_staged_min_width;
+extern int g_staged_spmm;  // 1: use the TMA-staged aggregation where its alignment rules hold
+
 // Scoped mark/release so that a call's scratch is returned to the arena when it ends.
 struct WsScope {
   nb_ws *ws;

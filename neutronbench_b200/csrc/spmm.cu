@@ -1,17 +1,18 @@
 // Aggregation kernels: forward CSC SpMM, backward transposed-CSR SpMM, fused-weight and
-// gather-fused variants.  HBM-bound: every lane issues 8- or 16-byte coalesced loads, a warp owns one
-// (output row, 32*VEC-float tile) and keeps UNROLL source rows in flight.
+// gather-fused variants.  HBM-bound: every lane issues 8- or 16-byte coalesced loads; a warp owns one
+// (output row, chunk of CT tiles of 32*VEC floats) and keeps U source rows x CT tiles in flight.
 //
 // Arithmetic contract: out[k] = (((0 + x0[k]*w0) + x1[k]*w1) + ...) with one IEEE multiply and one
 // IEEE add per edge, in edge order.  __fmul_rn/__fadd_rn are never contracted into an FMA, so the
 // result equals the reference kernel's atomicAdd(out, in*w) sequence
 // (cuda/ntsCUDAFuseKernel.cuh:272-290, 450-468) bit for bit and is independent of the launch shape.
+#include <initializer_list>
+
 #include "common.cuh"
 
 namespace nb {
 
 constexpr int kSpmmWarps = 8;    // warps per CTA
-constexpr int kSpmmUnroll = 8;   // source rows in flight per warp
 
 template <int VEC>
 struct Vec;
@@ -73,23 +74,28 @@ struct SpmmArgs {
   const uint32_t *source;
   uint32_t n;
   uint32_t F;
-  uint32_t tiles;          // ceil(F / (32*VEC))
+  uint32_t tiles;          // chunks per row: ceil(F / (CT*32*VEC))
 };
 
-template <int VEC, int MODE, bool MASK>
+// A warp owns one (output row, chunk) where a chunk is CT consecutive tiles of 32*VEC floats.  Per
+// edge a lane issues CT independent vector loads, and U edges are in flight, so CT*U loads per lane
+// hide the latency of the index chain (offsets -> indices -> [ids -> cache slots] -> rows), which is
+// paid once per chunk.  Wide rows (F = 602: VEC 2, CT 5 -> 2 chunks) need it most.
+template <int VEC, int CT, int U, int MODE, bool MASK>
 __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmArgs a) {
   const unsigned lane = threadIdx.x & 31;
   const uint64_t warp_global = (uint64_t)blockIdx.x * kSpmmWarps + (threadIdx.x >> 5);
-  const uint32_t r = (uint32_t)(warp_global / a.tiles);
+  const uint32_t r = (uint32_t)(warp_global / a.tiles);   // a.tiles = chunks per row
   if (r >= a.n) return;
-  const uint32_t tile = (uint32_t)(warp_global - (uint64_t)r * a.tiles);
-  const uint32_t col = tile * (32 * VEC) + lane * VEC;
-  const bool active = col < a.F;
+  const uint32_t chunk = (uint32_t)(warp_global - (uint64_t)r * a.tiles);
+  const uint32_t col0 = chunk * (CT * 32 * VEC) + lane * VEC;
 
   const uint32_t start = a.offs[r], end = a.offs[r + 1];
-  float acc[VEC];
+  float acc[CT][VEC];
 #pragma unroll
-  for (int k = 0; k < VEC; k++) acc[k] = 0.0f;
+  for (int t = 0; t < CT; t++)
+#pragma unroll
+    for (int k = 0; k < VEC; k++) acc[t][k] = 0.0f;
 
   float nr = 0.0f;
   if constexpr (MODE != kExplicitW) nr = a.norm_row[r];
@@ -115,38 +121,49 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmAr
       }
     }
     const uint32_t cnt = min(32u, end - base);
-    for (uint32_t jj = 0; jj < cnt; jj += kSpmmUnroll) {
-      float vals[kSpmmUnroll][VEC];
-      float ws[kSpmmUnroll];
+    for (uint32_t jj = 0; jj < cnt; jj += U) {
+      float vals[U][CT][VEC];
+      float ws[U];
 #pragma unroll
-      for (int u = 0; u < kSpmmUnroll; u++) {
+      for (int u = 0; u < U; u++) {
         const unsigned src_lane = (jj + u) & 31;  // lanes >= cnt hold nullptr / 0 weights
         const uintptr_t p = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_ptr, src_lane);
         ws[u] = __shfl_sync(0xffffffffu, my_w, src_lane);
-        if (active && (jj + u) < cnt) {
-          load_vec<VEC>(vals[u], reinterpret_cast<const float *>(p) + col);
-        } else {
+        const bool valid = (jj + u) < cnt;
 #pragma unroll
-          for (int k = 0; k < VEC; k++) vals[u][k] = 0.0f;
+        for (int t = 0; t < CT; t++) {
+          const uint32_t col = col0 + t * (32 * VEC);
+          if (valid && col < a.F) {
+            load_vec<VEC>(vals[u][t], reinterpret_cast<const float *>(p) + col);
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; k++) vals[u][t][k] = 0.0f;
+          }
         }
       }
 #pragma unroll
-      for (int u = 0; u < kSpmmUnroll; u++) {
+      for (int u = 0; u < U; u++) {
         if ((jj + u) < cnt) {
 #pragma unroll
-          for (int k = 0; k < VEC; k++) acc[k] = __fadd_rn(acc[k], __fmul_rn(vals[u][k], ws[u]));
+          for (int t = 0; t < CT; t++)
+#pragma unroll
+            for (int k = 0; k < VEC; k++) acc[t][k] = __fadd_rn(acc[t][k], __fmul_rn(vals[u][t][k], ws[u]));
         }
       }
     }
   }
-  if (!active) return;
-  if constexpr (MASK) {
-    float av[VEC];
-    load_vec<VEC>(av, a.act + (size_t)r * a.F + col);
 #pragma unroll
-    for (int k = 0; k < VEC; k++) acc[k] = av[k] > 0.0f ? __fmul_rn(acc[k], a.act_scale) : 0.0f;
+  for (int t = 0; t < CT; t++) {
+    const uint32_t col = col0 + t * (32 * VEC);
+    if (col >= a.F) continue;
+    if constexpr (MASK) {
+      float av[VEC];
+      load_vec<VEC>(av, a.act + (size_t)r * a.F + col);
+#pragma unroll
+      for (int k = 0; k < VEC; k++) acc[t][k] = av[k] > 0.0f ? __fmul_rn(acc[t][k], a.act_scale) : 0.0f;
+    }
+    store_vec<VEC>(a.y + (size_t)r * a.F + col, acc[t]);
   }
-  store_vec<VEC>(a.y + (size_t)r * a.F + col, acc);
 }
 
 static inline bool aligned_to(const void *p, size_t bytes) {
@@ -164,31 +181,86 @@ static int pick_vec(uint32_t F, std::initializer_list<size_t> pitches, std::init
   return 1;
 }
 
-template <int MODE, bool MASK>
-static int launch_spmm(SpmmArgs a, int vec, cudaStream_t stream) {
-  if (a.n == 0) return 0;
-  a.tiles = (a.F + 32 * vec - 1) / (32 * vec);
+template <int VEC, int CT, int U, int MODE, bool MASK>
+static int launch_one(SpmmArgs a, cudaStream_t stream) {
+  a.tiles = (a.F + CT * 32 * VEC - 1) / (CT * 32 * VEC);  // chunks per row
   const uint64_t warps = (uint64_t)a.n * a.tiles;
   const uint64_t blocks = (warps + kSpmmWarps - 1) / kSpmmWarps;
   if (blocks > 0x7fffffffull) return fail(NB_ERR_INVALID, "spmm: too many rows for one launch");
-  switch (vec) {
-    case 4: spmm_rows_kernel<4, MODE, MASK><<<(unsigned)blocks, kSpmmWarps * 32, 0, stream>>>(a); break;
-    case 2: spmm_rows_kernel<2, MODE, MASK><<<(unsigned)blocks, kSpmmWarps * 32, 0, stream>>>(a); break;
-    default: spmm_rows_kernel<1, MODE, MASK><<<(unsigned)blocks, kSpmmWarps * 32, 0, stream>>>(a); break;
-  }
+  spmm_rows_kernel<VEC, CT, U, MODE, MASK><<<(unsigned)blocks, kSpmmWarps * 32, 0, stream>>>(a);
   NB_LAUNCH_CHECK();
   return 0;
+}
+
+template <int VEC, int MODE, bool MASK>
+static int launch_vec(const SpmmArgs &a, cudaStream_t stream) {
+  const uint32_t tiles = (a.F + 32 * VEC - 1) / (32 * VEC);
+  if (tiles >= 5) return launch_one<VEC, 5, (VEC == 4 ? 2 : 4), MODE, MASK>(a, stream);
+  if (tiles >= 2) return launch_one<VEC, 2, (VEC == 4 ? 4 : 8), MODE, MASK>(a, stream);
+  return launch_one<VEC, 1, 8, MODE, MASK>(a, stream);
+}
+
+template <int MODE, bool MASK>
+static int launch_spmm(const SpmmArgs &a, int vec, cudaStream_t stream) {
+  if (a.n == 0) return 0;
+  switch (vec) {
+    case 4: return launch_vec<4, MODE, MASK>(a, stream);
+    case 2: return launch_vec<2, MODE, MASK>(a, stream);
+    default: return launch_vec<1, MODE, MASK>(a, stream);
+  }
+}
+
+int g_staged_spmm = 1;
+
+// Staged (TMA) path for the plain forms: references are the block-local indices themselves.
+static int try_staged(const float *x, float *y, const uint32_t *offs, const uint32_t *idx, const float *w,
+                      const float *norm_row, const float *norm_idx, const float *act, float act_scale, uint32_t n,
+                      uint32_t F, cudaStream_t stream, bool *done) {
+  *done = false;
+  if (!g_staged_spmm || !tma_spmm_applicable(x, F, F)) return 0;
+  TmaSpmmArgs t{};
+  t.x = x; t.x_ld = F; t.y = y; t.offs = offs; t.ref = idx; t.w = w; t.norm_row = norm_row; t.norm_idx = norm_idx;
+  t.act = act; t.act_scale = act_scale; t.n = n; t.F = F;
+  t.out_vec = pick_vec(F, {}, {y, act});
+  *done = true;
+  return launch_spmm_tma(t, stream);
 }
 
 }  // namespace nb
 
 using namespace nb;
 
+NB_API int nb_set_staged_spmm(int enabled) {
+  const int old = g_staged_spmm;
+  g_staged_spmm = enabled ? 1 : 0;
+  if (enabled > 1) g_staged_min_width = 1;   // 2: stage every width the alignment rules allow
+  else g_staged_min_width = 256;
+  return old;
+}
+
+NB_API uint64_t nb_set_l2_panel_bytes(uint64_t bytes) {
+  const uint64_t old = g_l2_panel_bytes;
+  g_l2_panel_bytes = bytes;
+  return old;
+}
+
+NB_API int nb_device_error_flags(uint32_t *flags) {
+  NB_REQUIRE(flags != nullptr, "nb_device_error_flags: null pointer");
+  unsigned int v = 0;
+  NB_TRY(read_tma_error_flag(&v));
+  *flags = v;
+  return 0;
+}
+
 NB_API int nb_spmm_csc_fwd(const float *d_x, float *d_y, const float *d_w, const uint32_t *d_row_indices,
                            const uint32_t *d_column_offset, uint32_t v, uint32_t F, void *stream) {
   if (v == 0) return 0;
   NB_REQUIRE(d_x && d_y && d_w && d_row_indices && d_column_offset, "nb_spmm_csc_fwd: null pointer");
   NB_REQUIRE(F > 0, "nb_spmm_csc_fwd: feature width is zero");
+  bool done;
+  NB_TRY(try_staged(d_x, d_y, d_column_offset, d_row_indices, d_w, nullptr, nullptr, nullptr, 1.0f, v, F,
+                    as_stream(stream), &done));
+  if (done) return 0;
   SpmmArgs a{};
   a.x = d_x; a.x_ld = F; a.y = d_y; a.offs = d_column_offset; a.idx = d_row_indices; a.w = d_w;
   a.n = v; a.F = F;
@@ -200,6 +272,10 @@ NB_API int nb_spmm_csr_bwd(const float *d_gy, float *d_gx, const float *d_w, con
   if (s == 0) return 0;
   NB_REQUIRE(d_gy && d_gx && d_w && d_row_offset && d_column_indices, "nb_spmm_csr_bwd: null pointer");
   NB_REQUIRE(F > 0, "nb_spmm_csr_bwd: feature width is zero");
+  bool done;
+  NB_TRY(try_staged(d_gy, d_gx, d_row_offset, d_column_indices, d_w, nullptr, nullptr, nullptr, 1.0f, s, F,
+                    as_stream(stream), &done));
+  if (done) return 0;
   SpmmArgs a{};
   a.x = d_gy; a.x_ld = F; a.y = d_gx; a.offs = d_row_offset; a.idx = d_column_indices; a.w = d_w;
   a.n = s; a.F = F;
@@ -213,6 +289,10 @@ NB_API int nb_spmm_csc_fwd_fused(const float *d_x, float *d_y, const uint32_t *d
   NB_REQUIRE(d_x && d_y && d_row_indices && d_column_offset && d_src_norm && d_dst_norm,
              "nb_spmm_csc_fwd_fused: null pointer");
   NB_REQUIRE(F > 0, "nb_spmm_csc_fwd_fused: feature width is zero");
+  bool done;
+  NB_TRY(try_staged(d_x, d_y, d_column_offset, d_row_indices, nullptr, d_dst_norm, d_src_norm, nullptr, 1.0f, v, F,
+                    as_stream(stream), &done));
+  if (done) return 0;
   SpmmArgs a{};
   a.x = d_x; a.x_ld = F; a.y = d_y; a.offs = d_column_offset; a.idx = d_row_indices;
   a.norm_row = d_dst_norm; a.norm_idx = d_src_norm; a.n = v; a.F = F;
@@ -227,6 +307,10 @@ NB_API int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t 
   NB_REQUIRE(d_gy && d_gx && d_row_offset && d_column_indices && d_src_norm && d_dst_norm,
              "nb_spmm_csr_bwd_fused: null pointer");
   NB_REQUIRE(F > 0, "nb_spmm_csr_bwd_fused: feature width is zero");
+  bool done;
+  NB_TRY(try_staged(d_gy, d_gx, d_row_offset, d_column_indices, nullptr, d_src_norm, d_dst_norm, d_act, act_scale, s,
+                    F, as_stream(stream), &done));
+  if (done) return 0;
   SpmmArgs a{};
   a.x = d_gy; a.x_ld = F; a.y = d_gx; a.offs = d_row_offset; a.idx = d_column_indices;
   a.norm_row = d_src_norm; a.norm_idx = d_dst_norm; a.act = d_act; a.act_scale = act_scale;
@@ -236,12 +320,12 @@ NB_API int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t 
   return launch_spmm<kFusedW, false>(a, vec, as_stream(stream));
 }
 
-NB_API int nb_spmm_csc_fwd_gather_fused(const float *feat, size_t feat_ld, const float *d_cache,
+NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache,
                                         size_t cache_ld, const uint32_t *d_hashmap,
                                         const uint32_t *d_source, float *d_y,
                                         const uint32_t *d_row_indices, const uint32_t *d_column_offset,
                                         const float *d_src_norm, const float *d_dst_norm, uint32_t v,
-                                        uint32_t F, void *stream) {
+                                        uint32_t s, uint32_t e, uint32_t F, void *stream) {
   if (v == 0) return 0;
   NB_REQUIRE(d_source && d_y && d_row_indices && d_column_offset && d_src_norm && d_dst_norm,
              "nb_spmm_csc_fwd_gather_fused: null pointer");
@@ -250,6 +334,26 @@ NB_API int nb_spmm_csc_fwd_gather_fused(const float *feat, size_t feat_ld, const
   NB_REQUIRE(d_hashmap == nullptr || d_cache != nullptr, "nb_spmm_csc_fwd_gather_fused: hashmap without cache");
   NB_REQUIRE(F > 0 && (feat == nullptr || feat_ld >= F) && (d_cache == nullptr || cache_ld >= F),
              "nb_spmm_csc_fwd_gather_fused: bad width or pitch");
+  // Staged path: hits (cache rows, or the table itself when there is no cache) go through the TMA
+  // unit; misses are rows of `feat` that the lanes copy.  Needs scratch for per-edge references.
+  {
+    const float *hit_base = d_hashmap ? d_cache : feat;
+    const size_t hit_ld = d_hashmap ? cache_ld : feat_ld;
+    if (g_staged_spmm && ws != nullptr && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
+      cudaStream_t st = as_stream(stream);
+      WsScope scope(ws);
+      uint32_t *ref = ws->alloc_n<uint32_t>(e);
+      float *w = ws->alloc_n<float>(e);
+      if (!ref || !w) return fail(NB_ERR_NOMEM, "nb_spmm_csc_fwd_gather_fused: workspace arena exhausted");
+      NB_TRY(launch_gather_refs(d_column_offset, d_row_indices, v, e, d_source, d_hashmap, d_hashmap == nullptr,
+                                d_src_norm, d_dst_norm, ref, w, st));
+      TmaSpmmArgs t{};
+      t.x = hit_base; t.x_ld = hit_ld; t.miss = feat; t.miss_ld = feat_ld; t.y = d_y; t.offs = d_column_offset;
+      t.ref = ref; t.w = w; t.n = v; t.F = F; t.act = nullptr; t.act_scale = 1.0f; t.src_rows_hint = s;
+      t.out_vec = pick_vec(F, {}, {d_y});
+      return launch_spmm_tma(t, st);
+    }
+  }
   SpmmArgs a{};
   a.feat = feat; a.feat_ld = feat_ld; a.cache = d_cache; a.cache_ld = cache_ld; a.hashmap = d_hashmap;
   a.source = d_source; a.y = d_y; a.offs = d_column_offset; a.idx = d_row_indices;

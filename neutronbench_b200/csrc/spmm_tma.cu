@@ -1,0 +1,400 @@
+// Aggregation with source rows staged through shared memory by the TMA unit (non-multicast
+// cp.async.bulk global -> shared, completion on an mbarrier).
+//
+// Why: the gather side of the SpMM is a latency problem — a destination has only `fanout` source rows
+// and the address of each row comes out of an index chain.  Loading rows into registers limits the
+// bytes in flight per warp to what the register file can hold.  Here each warp owns a two-stage ring of
+// SEG row slots in shared memory; the lanes issue one bulk copy per source row of the NEXT segment
+// (no registers, no LSU instructions per element), then the warp accumulates the CURRENT segment from
+// shared memory, edge after edge, in the same multiply-then-add order as every other path, so results
+// stay bit-identical.  Per warp up to 2*SEG rows (about 24 KB) are in flight.
+//
+// Requirements checked by the host: row starts 16-byte aligned (base aligned, pitch a multiple of 4
+// floats) and ceil(F/4)*16 bytes readable per row.  Rows flagged as misses (bit 31 of the row
+// reference: features that live in pinned host memory with an arbitrary pitch) are copied by the lanes
+// with ordinary loads into the same slot.
+#include "common.cuh"
+
+namespace nb {
+
+constexpr int kTmaWarps = 8;
+constexpr int kTmaStages = 2;
+constexpr uint32_t kWaitLimit = 1u << 18;   // bounded spin on the mbarrier; then the error flag is set
+
+__device__ unsigned int g_tma_spmm_error = 0;   // 1: an mbarrier wait gave up
+uint64_t g_l2_panel_bytes = 0;                  // working-set target of one column panel (0: no panels)
+int g_l2_prefetch = 0;
+int g_staged_min_width = 256;                   // narrowest row (floats) that takes the staged path                          // 1: prefetch rows into L2 two segments ahead
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-multicast bulk copy, global -> this CTA's shared memory.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Ask L2 to fetch a row ahead of the copy that will stage it (no shared memory is held meanwhile).
+__device__ __forceinline__ void prefetch_l2(const void *src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One warp's walk over its work items, cut into segments of at most `seg` edges.  An item is an
+// (output row, column panel) pair; items are ordered panel-major and dealt round-robin to the warps.
+// The offsets of the item after the current one are loaded when the current item is opened, so
+// opening an item never waits.
+struct SegIter {
+  uint32_t row, panel;             // current item
+  uint32_t ahead_row, ahead_panel; // the item after it
+  uint32_t stride, n, panels;
+  uint32_t pos, end;               // edge range still to emit for the current item
+  uint32_t ahead_pos, ahead_end;   // offsets of the item after it, already requested
+  bool fresh;                      // next segment is the first of its item
+  __device__ void step(uint32_t &r, uint32_t &p) const {
+    r += stride;
+    while (r >= n && p < panels) { r -= n; p++; }
+  }
+  __device__ void prefetch(const uint32_t *__restrict__ offs) {
+    if (ahead_panel < panels) { ahead_pos = __ldg(offs + ahead_row); ahead_end = __ldg(offs + ahead_row + 1); }
+  }
+  __device__ void start(const uint32_t *__restrict__ offs, uint32_t first, uint32_t stride_, uint32_t rows,
+                        uint32_t panels_) {
+    stride = stride_; n = rows; panels = panels_;
+    ahead_row = first; ahead_panel = 0;
+    while (ahead_row >= n && ahead_panel < panels) { ahead_row -= n; ahead_panel++; }
+    ahead_pos = ahead_end = 0;
+    prefetch(offs);
+    advance(offs);
+  }
+  __device__ void advance(const uint32_t *__restrict__ offs) {
+    row = ahead_row; panel = ahead_panel; pos = ahead_pos; end = ahead_end; fresh = true;
+    step(ahead_row, ahead_panel);
+    prefetch(offs);
+  }
+  __device__ bool done() const { return panel >= panels; }
+};
+struct Seg {
+  uint32_t row, panel, begin, cnt;
+  bool first, last, valid;
+};
+// Per-lane operands of one segment: the row reference and what is needed to form the edge weight.
+struct Operands {
+  uint32_t ref;
+  float w_or_nidx;   // explicit weight, or the sqrt-degree factor of the indexed side
+  float nrow;        // sqrt-degree factor of the output row (fused form)
+};
+
+template <int TILES, bool MASK>
+__global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSpmmArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t stage_bytes = a.seg * a.slot_bytes;
+  unsigned char *my_smem = smem_raw + (size_t)warp * kTmaStages * stage_bytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)kTmaWarps * kTmaStages * stage_bytes) +
+                   warp * kTmaStages;
+  const uint32_t bar0 = smem_u32(bars);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kTmaStages; s++) mbar_init(bar0 + 8 * s, 1);
+  }
+  fence_proxy_async();   // make the initialised barriers visible to the async proxy
+  __syncwarp();
+
+  // Work items are (panel, row) pairs, panel-major: all rows of column panel 0 come before panel 1,
+  // so that the source rows touched by one panel stay resident in L2 between their uses.
+  SegIter it;
+  it.start(a.offs, blockIdx.x * kTmaWarps + warp, gridDim.x * kTmaWarps, a.n, a.panels);
+
+
+  auto next_seg = [&]() -> Seg {
+    Seg s{};
+    s.valid = !it.done();
+    if (!s.valid) return s;
+    s.row = it.row;
+    s.panel = it.panel;
+    s.begin = it.pos;
+    s.cnt = min(a.seg, it.end - it.pos);
+    s.first = it.fresh;
+    it.pos += s.cnt;
+    it.fresh = false;
+    s.last = it.pos >= it.end;
+    if (s.last) it.advance(a.offs);
+    return s;
+  };
+
+  // Request a segment's per-edge operands.  Nothing here waits: the values are first used when the
+  // segment's copies are issued, one loop iteration later.
+  auto load_operands = [&](const Seg &s) -> Operands {
+    Operands o{0u, 0.0f, 0.0f};
+    if (s.valid && lane < s.cnt) {
+      const uint32_t j = s.begin + lane;
+      o.ref = __ldg(a.ref + j);
+      if (a.w) o.w_or_nidx = __ldg(a.w + j); else o.nrow = __ldg(a.norm_row + s.row);
+    }
+    return o;
+  };
+
+  // Issue the copies of one segment into `stage`.
+  auto issue = [&](const Seg &s, uint32_t stage, Operands &o) {
+    __syncwarp();   // every lane is done reading the slots that are about to be refilled
+    const bool mine = lane < s.cnt;
+    const bool miss = mine && (o.ref & 0x80000000u);
+    const unsigned hit_mask = __ballot_sync(0xffffffffu, mine && !miss);
+    const unsigned miss_mask = __ballot_sync(0xffffffffu, miss);
+    const uint32_t bar = bar0 + 8 * stage;
+    unsigned char *stage_base = my_smem + (size_t)stage * stage_bytes;
+    const uint32_t col0 = s.panel * a.panel_floats;                       // first column of this panel
+    const uint32_t pbytes = min(a.copy_bytes, (a.fpad - col0) * 4u);    // bytes of one row inside the panel
+    // Slots of this stage were read with ordinary loads (and possibly written by the miss path) two
+    // segments ago; order those accesses before the async-proxy writes that follow.
+    fence_proxy_async();
+    if (lane == 0) mbar_arrive_expect_tx(bar, __popc(hit_mask) * pbytes);
+    __syncwarp();
+    if (mine && !miss)
+      bulk_g2s(smem_u32(stage_base + (size_t)lane * a.slot_bytes), a.x + (size_t)o.ref * a.x_ld + col0, pbytes, bar);
+    if (mine && !a.w) o.w_or_nidx = __ldg(a.norm_idx + o.ref);   // consumed one iteration later
+    // misses: the whole warp copies each flagged row with plain loads (any pitch, any alignment)
+    unsigned mm = miss_mask;
+    while (mm) {
+      const int u = __ffs(mm) - 1;
+      mm &= mm - 1;
+      const uint32_t id = __shfl_sync(0xffffffffu, o.ref, u) & 0x7FFFFFFFu;
+      const float *src = a.miss + (size_t)id * a.miss_ld + col0;
+      float *dst = reinterpret_cast<float *>(stage_base + (size_t)u * a.slot_bytes);
+      const uint32_t width = min(a.panel_floats, a.F - col0);
+      for (uint32_t c = lane; c < width; c += 32) dst[c] = __ldg(src + c);
+    }
+  };
+
+  // L2 prefetch of a segment's rows: issued two iterations before the rows are staged, so that the
+  // DRAM latency is paid while the rows do not yet occupy a shared-memory slot.
+  auto prefetch = [&](const Seg &s, const Operands &o) {
+    if (!s.valid || lane >= s.cnt || (o.ref & 0x80000000u)) return;
+    const uint32_t col0 = s.panel * a.panel_floats;
+    prefetch_l2(a.x + (size_t)o.ref * a.x_ld + col0, min(a.copy_bytes, (a.fpad - col0) * 4u));
+  };
+
+  // Software pipeline over this warp's segments:
+  //   cur  copies in flight into shared memory, consumed in this iteration
+  //   nxt  operands arrived an iteration ago, copies issued now
+  //   far  operands requested now
+  Seg cur = next_seg();
+  Operands o_cur = load_operands(cur);
+  Seg nxt = next_seg();
+  Operands o_nxt = load_operands(nxt);
+  if (cur.valid) issue(cur, 0, o_cur);
+  float acc[TILES][4];
+  uint32_t k = 0;
+  while (cur.valid) {
+    const uint32_t stage = k & 1;
+    if (nxt.valid) issue(nxt, stage ^ 1, o_nxt);
+    Seg far = next_seg();
+    Operands o_far = load_operands(far);
+    if (a.l2_prefetch) prefetch(far, o_far);
+
+    // wait for the current segment's rows (bounded)
+    {
+      const uint32_t bar = bar0 + 8 * stage, parity = (k >> 1) & 1;
+      uint32_t spins = 0;
+      while (!mbar_try_wait(bar, parity)) {
+        if (++spins > kWaitLimit) {
+          if (lane == 0) atomicExch(&g_tma_spmm_error, 1u);
+          // give copies that may still be in flight a second, equally bounded, chance to land
+          for (uint32_t t = 0; t < kWaitLimit && !mbar_try_wait(bar, parity); t++) {}
+          return;
+        }
+      }
+    }
+    __syncwarp();   // also orders the miss path's shared-memory writes before the reads below
+
+    if (cur.first) {
+#pragma unroll
+      for (int t = 0; t < TILES; t++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[t][c] = 0.0f;
+    }
+    // 1 / ((float)sqrt(out_deg[src]) * (float)sqrt(in_deg[dst])) in the fused form
+    const float w_cur = a.w ? o_cur.w_or_nidx : __fdiv_rn(1.0f, __fmul_rn(o_cur.w_or_nidx, o_cur.nrow));
+    const unsigned char *stage_base = my_smem + (size_t)stage * stage_bytes;
+    const uint32_t pcol0 = cur.panel * a.panel_floats;
+    const uint32_t pwidth = min(a.panel_floats, a.F - pcol0);           // valid floats of this panel
+    for (uint32_t u = 0; u < cur.cnt; u++) {
+      const float wu = __shfl_sync(0xffffffffu, w_cur, u);
+      const float4 *row = reinterpret_cast<const float4 *>(stage_base + (size_t)u * a.slot_bytes);
+#pragma unroll
+      for (int t = 0; t < TILES; t++) {
+        const uint32_t q = lane + 32 * t;           // float4 index inside the row
+        if (q * 4 < pwidth) {
+          const float4 v = row[q];
+          acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(v.x, wu));
+          acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(v.y, wu));
+          acc[t][2] = __fadd_rn(acc[t][2], __fmul_rn(v.z, wu));
+          acc[t][3] = __fadd_rn(acc[t][3], __fmul_rn(v.w, wu));
+        }
+      }
+    }
+    if (cur.last) {
+      const uint32_t out_row = cur.row;
+      float *out = a.y + (size_t)out_row * a.F + pcol0;
+      const float *act = MASK ? a.act + (size_t)out_row * a.F + pcol0 : nullptr;
+#pragma unroll
+      for (int t = 0; t < TILES; t++) {
+        const uint32_t col = (lane + 32 * t) * 4;
+        if (col >= pwidth) continue;
+        float r[4] = {acc[t][0], acc[t][1], acc[t][2], acc[t][3]};
+        if (a.out_vec == 4) {
+          if constexpr (MASK) {
+            const float4 m = __ldg(reinterpret_cast<const float4 *>(act + col));
+            r[0] = m.x > 0.0f ? __fmul_rn(r[0], a.act_scale) : 0.0f;
+            r[1] = m.y > 0.0f ? __fmul_rn(r[1], a.act_scale) : 0.0f;
+            r[2] = m.z > 0.0f ? __fmul_rn(r[2], a.act_scale) : 0.0f;
+            r[3] = m.w > 0.0f ? __fmul_rn(r[3], a.act_scale) : 0.0f;
+          }
+          *reinterpret_cast<float4 *>(out + col) = make_float4(r[0], r[1], r[2], r[3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            if (col + c < pwidth) {
+              float val = r[c];
+              if constexpr (MASK) val = __ldg(act + col + c) > 0.0f ? __fmul_rn(val, a.act_scale) : 0.0f;
+              if (a.out_vec != 2) out[col + c] = val;
+              r[c] = val;
+            }
+          }
+          if (a.out_vec == 2) {   // F is even and rows are 8-byte aligned
+            if (col + 1 < pwidth) *reinterpret_cast<float2 *>(out + col) = make_float2(r[0], r[1]);
+            if (col + 3 < pwidth) *reinterpret_cast<float2 *>(out + col + 2) = make_float2(r[2], r[3]);
+          }
+        }
+      }
+    }
+    cur = nxt;
+    o_cur = o_nxt;
+    nxt = far;
+    o_nxt = o_far;
+    k++;
+  }
+}
+
+// ref[j] / w[j] for the gather-fused form: the row reference of edge j is the cache slot of its source
+// (or the global id with bit 31 set when the source is not cached), the weight is the GCN weight.
+__global__ void gather_refs_kernel(const uint32_t *__restrict__ offs, const uint32_t *__restrict__ idx, uint32_t v,
+                                   uint32_t e, const uint32_t *__restrict__ source,
+                                   const uint32_t *__restrict__ hashmap, bool feat_is_hit,
+                                   const float *__restrict__ norm_idx, const float *__restrict__ norm_row,
+                                   uint32_t *__restrict__ ref, float *__restrict__ w) {
+  for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < e; j += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t li = idx[j];
+    const uint32_t g = source[li];
+    const uint32_t slot = hashmap ? hashmap[g] : 0xFFFFFFFFu;
+    ref[j] = slot != 0xFFFFFFFFu ? slot : (feat_is_hit ? g : (g | 0x80000000u));
+    uint32_t lo = 0, hi = v;
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (offs[mid] <= (uint32_t)j) lo = mid; else hi = mid;
+    }
+    w[j] = __fdiv_rn(1.0f, __fmul_rn(norm_idx[li], norm_row[lo]));
+  }
+}
+
+template <int TILES, bool MASK>
+static int launch_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
+  static bool configured = false;   // per instantiation; the attribute is sticky for the process
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(spmm_tma_kernel<TILES, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 200 * 1024));
+    configured = true;
+  }
+  const unsigned need = (unsigned)(((uint64_t)a.n * a.panels + kTmaWarps - 1) / kTmaWarps);
+  const unsigned grid = need < (unsigned)kNumSMs ? need : (unsigned)kNumSMs;
+  spmm_tma_kernel<TILES, MASK><<<grid, kTmaWarps * 32, smem, stream>>>(a);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <bool MASK>
+static int launch_mask(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
+  switch ((a.panel_floats + 127) / 128) {
+    case 1: return launch_tiles<1, MASK>(a, smem, stream);
+    case 2: return launch_tiles<2, MASK>(a, smem, stream);
+    case 3: return launch_tiles<3, MASK>(a, smem, stream);
+    case 4: return launch_tiles<4, MASK>(a, smem, stream);
+    case 5: return launch_tiles<5, MASK>(a, smem, stream);
+    case 6: return launch_tiles<6, MASK>(a, smem, stream);
+    case 7: return launch_tiles<7, MASK>(a, smem, stream);
+    case 8: return launch_tiles<8, MASK>(a, smem, stream);
+    default: return fail(NB_ERR_INVALID, "spmm (staged): feature width above 1024");
+  }
+}
+
+// Staging pays off for wide rows (one bulk copy moves a kilobyte or more); narrow rows are faster with
+// direct vector loads at high occupancy (measured on B200: F = 100..128 direct, F = 602 staged).
+bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F) {
+  if (x == nullptr || F < (uint32_t)g_staged_min_width || F > 1024) return false;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (x_ld & 3) != 0) return false;
+  return (size_t)((F + 3) / 4) * 4 <= x_ld;   // the 16-byte-granular copy stays inside the row pitch
+}
+
+int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
+  if (a.n == 0) return 0;
+  a.fpad = ((a.F + 3) / 4) * 4;
+  a.l2_prefetch = g_l2_prefetch;
+  // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
+  // into panels whose working set fits, and panels are processed one after the other.
+  uint32_t panels = 1;
+  if (a.src_rows_hint > 0 && g_l2_panel_bytes > 0) {
+    const uint64_t working_set = (uint64_t)a.src_rows_hint * a.fpad * 4;
+    panels = (uint32_t)((working_set + g_l2_panel_bytes - 1) / g_l2_panel_bytes);
+    const uint32_t max_panels = (a.fpad + 63) / 64;            // keep copies at 256 bytes or more
+    if (panels > max_panels) panels = max_panels;
+    if (panels < 1) panels = 1;
+  }
+  a.panel_floats = ((a.fpad / 4 + panels - 1) / panels) * 4;   // multiple of 4 floats = 16 bytes
+  a.panels = (a.fpad + a.panel_floats - 1) / a.panel_floats;
+  a.copy_bytes = a.panel_floats * 4;
+  a.slot_bytes = a.copy_bytes;
+  const uint32_t per_warp_budget = 24 * 1024;   // two stages
+  uint32_t seg = per_warp_budget / (kTmaStages * a.slot_bytes);
+  if (seg < 1) seg = 1;
+  if (seg > 32) seg = 32;
+  a.seg = seg;
+  const size_t smem = (size_t)kTmaWarps * kTmaStages * seg * a.slot_bytes + kTmaWarps * kTmaStages * sizeof(uint64_t);
+  if (smem > 200 * 1024) return fail(NB_ERR_INVALID, "spmm (staged): row too wide for the shared-memory ring");
+  if ((uint64_t)a.n * a.panels > 0xFFFFFFFFull) return fail(NB_ERR_INVALID, "spmm (staged): too many work items");
+  return a.act ? launch_mask<true>(a, smem, stream) : launch_mask<false>(a, smem, stream);
+}
+
+int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, uint32_t e, const uint32_t *source,
+                       const uint32_t *hashmap, bool feat_is_hit, const float *norm_idx, const float *norm_row,
+                       uint32_t *ref, float *w, cudaStream_t stream) {
+  if (e == 0) return 0;
+  gather_refs_kernel<<<grid_for(e, 256), 256, 0, stream>>>(offs, idx, v, e, source, hashmap, feat_is_hit, norm_idx,
+                                                          norm_row, ref, w);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+int read_tma_error_flag(unsigned int *value) {
+  NB_CUDA(cudaMemcpyFromSymbol(value, g_tma_spmm_error, sizeof(unsigned int)));
+  return 0;
+}
+
+}  // namespace nb

@@ -197,9 +197,9 @@ class GCN_GPU_NEIGHBOR_impl:
         cache, hm = self.dev_cache_feature, self.dev_cache_node_hashmap
         if self.cfg.fuse_gather:
             self._timed("fwd0_gather_fused", self.agg_bytes_fwd(blk, F, True, hm is not None), lambda: _lib.call(
-                "nb_spmm_csc_fwd_gather_fused", ptr(feat), feat.stride(0), ptr(cache),
+                "nb_spmm_csc_fwd_gather_fused", self.ws.handle, ptr(feat), feat.stride(0), ptr(cache),
                 cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), ptr(Y), ptr(blk.row_indices),
-                ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, F, stream))
+                ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, blk.src_size, blk.e_size, F, stream))
         else:
             X0 = torch.empty((blk.src_size, F), dtype=torch.float32, device=self.device)
             _lib.call("nb_feature_gather", ptr(X0), ptr(feat), feat.stride(0), None, 0, 0, ptr(cache),

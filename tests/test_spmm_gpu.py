@@ -81,8 +81,11 @@ def test_fused_weight_variants_equal_explicit(cuda_device, F):
     np.testing.assert_array_equal(host_f32(dgx).view(np.uint32), ref_b.view(np.uint32))
 
 
+@pytest.mark.parametrize("panel_bytes", [None, 1 << 20, 200_000])
 @pytest.mark.parametrize("F,use_cache", [(602, True), (602, False), (100, True), (128, True)])
-def test_gather_fused_forward_equals_gather_then_spmm(cuda_device, F, use_cache):
+def test_gather_fused_forward_equals_gather_then_spmm(cuda_device, ws, F, use_cache, panel_bytes):
+    """panel_bytes forces the staged kernel to cut rows into 2..many column panels (the cut is a
+    schedule, not arithmetic: the bits must not change)."""
     V = 3000
     blk = _block(V=V)[0]
     rng = np.random.RandomState(11)
@@ -99,11 +102,14 @@ def test_gather_fused_forward_equals_gather_then_spmm(cuda_device, F, use_cache)
     dfeat = dev_f32(feat, d)
     dcache = dev_f32(cache, d) if use_cache else None
     dhm = dev_i32(hm, d) if use_cache else None
-    _lib.call("nb_spmm_csc_fwd_gather_fused", ptr(dfeat), F, ptr(dcache), ld if use_cache else 0, ptr(dhm),
+    old_panel = _lib.load().nb_set_l2_panel_bytes(panel_bytes) if panel_bytes is not None else None
+    _lib.call("nb_spmm_csc_fwd_gather_fused", ws.handle, ptr(dfeat), F, ptr(dcache), ld if use_cache else 0, ptr(dhm),
               ptr(dev_i32(blk.source, d)), ptr(dy), ptr(dev_i32(blk.row_indices, d)),
               ptr(dev_i32(blk.column_offset, d)), ptr(dev_f32(blk.src_norm, d)), ptr(dev_f32(blk.dst_norm, d)),
-              blk.v_size, F, torch.cuda.current_stream().cuda_stream)
+              blk.v_size, blk.src_size, blk.e_size, F, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    if old_panel is not None:
+        _lib.load().nb_set_l2_panel_bytes(old_panel)
     np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref.view(np.uint32))
 
 
@@ -125,9 +131,11 @@ def test_empty_columns_and_empty_block(cuda_device):
     _lib.call("nb_spmm_csc_fwd", 0, 0, 0, 0, 0, 0, 4, st)  # v == 0: nothing to do
 
 
-def test_long_rows_and_unaligned_views(cuda_device):
-    """A hub row of 5000 edges (several 32-edge passes) and an x tensor that starts 4 bytes off a
-    16-byte boundary (vector width must fall back)."""
+@pytest.mark.parametrize("misalign", [1, 0])
+def test_long_rows_and_unaligned_views(cuda_device, misalign):
+    """A hub row of 5000 edges (many segments / 32-edge passes); with misalign=1 the x tensor starts
+    4 bytes off a 16-byte boundary, so the staged path is not applicable and the vector width of the
+    direct-load path must fall back to scalar."""
     rng = np.random.RandomState(5)
     s, F = 700, 128
     lens = np.array([5000, 0, 33, 32, 31, 1], dtype=np.uint32)
@@ -138,9 +146,9 @@ def test_long_rows_and_unaligned_views(cuda_device):
     ref = oracle.spmm_fwd(x, w, ri, co)
     d = cuda_device
     buf = torch.empty(s * F + 1, device=d)
-    xv = buf[1:].view(s, F)
+    xv = buf[misalign: misalign + s * F].view(s, F)
     xv.copy_(dev_f32(x, d))
-    assert xv.data_ptr() % 16 == 4
+    assert xv.data_ptr() % 16 == 4 * misalign
     dy = torch.empty((len(lens), F), device=d)
     _lib.call("nb_spmm_csc_fwd", ptr(xv), ptr(dy), ptr(dev_f32(w, d)), ptr(dev_i32(ri, d)), ptr(dev_i32(co, d)),
               len(lens), F, torch.cuda.current_stream().cuda_stream)
@@ -172,3 +180,31 @@ def test_linearity_at_full_size(cuda_device):
     rhs = agg(x1) + 2 * agg(x2)
     err = (lhs - rhs).abs().max().item() / rhs.abs().max().item()
     assert err < 1e-5, err
+
+
+@pytest.mark.parametrize("F", [16, 100, 128, 256, 1024])
+def test_staged_and_direct_paths_give_identical_bits(cuda_device, F):
+    """The TMA-staged kernel and the direct-load kernel are two schedules of the same arithmetic."""
+    blk = _block(fanouts=(25, 10))[1]
+    rng = np.random.RandomState(F)
+    x = rng.randn(blk.src_size, F).astype(np.float32)
+    d = cuda_device
+    dx, dw = dev_f32(x, d), dev_f32(blk.edge_weight_forward, d)
+    ri, co = dev_i32(blk.row_indices, d), dev_i32(blk.column_offset, d)
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    lib = _lib.load()
+    for staged in (2, 0):
+        old = lib.nb_set_staged_spmm(staged)
+        y = torch.empty((blk.v_size, F), device=d)
+        _lib.call("nb_spmm_csc_fwd", ptr(dx), ptr(y), ptr(dw), ptr(ri), ptr(co), blk.v_size, F, st)
+        torch.cuda.synchronize()
+        lib.nb_set_staged_spmm(1 if old else 0)
+        outs.append(host_f32(y))
+    np.testing.assert_array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    ref = oracle.spmm_fwd(x, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
+    np.testing.assert_array_equal(outs[0].view(np.uint32), ref.view(np.uint32))
+    import ctypes
+    flags = ctypes.c_uint32(7)
+    _lib.call("nb_device_error_flags", ctypes.byref(flags))
+    assert flags.value == 0
