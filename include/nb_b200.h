@@ -114,7 +114,8 @@ int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, c
  * nb_set_staged_spmm(0) forces the direct-load path, 2 stages every width the alignment rules allow,
  * 1 restores the default; returns the previous on/off setting.
  * nb_device_error_flags reads (and so synchronises with) the device-side error word: bit 0 is set
- * when a bounded wait on a copy barrier gave up. */
+ * when a bounded wait on a copy barrier gave up, bit 1 when a wait on a tensor-core completion
+ * barrier gave up. */
 int nb_set_staged_spmm(int enabled);
 /* The staged gather-fused aggregation cuts wide rows into column panels whose distinct source data
  * (s rows x panel width) stays below this many bytes, so that reuse of a source row hits L2
@@ -212,6 +213,9 @@ int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t fea
  *
  * nb_gemm: C[M x N] = op(A) * op(B).  trans_a = 0: A is M x K row-major; 1: A is K x M (A^T used).
  *          trans_b likewise for B (K x N, or N x K when 1).  Supported: NN, TN, NT.
+ *          nb_set_gemm_mode selects the arithmetic: 0 = CUDA cores (fp32 FMA), 1 = tcgen05 tensor cores
+ *          with a three-term TF32 split (fp32-level accuracy), 2 = tcgen05 plain TF32.  Returns the
+ *          previous mode.
  * nb_relu_dropout: z = dropout(relu(z)) in place; keeps element i when the Philox word
  *          (counter (i/4, layer, step, 1), key seed) mapped to [0,1) is >= p, scaling by 1/(1-p).
  * nb_softmax_nll: mean negative log-likelihood of log_softmax(logits) at `label`, its gradient
@@ -220,6 +224,7 @@ int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t fea
  * nb_adam: g = grad + wd*W; M = b1 M + (1-b1) g; V = b2 V + (1-b2) g^2;
  *          W -= alpha * (M/(1-b1_t)) / (sqrt(V/(1-b2_t)) + eps).
  * ---------------------------------------------------------------------------------------------- */
+int nb_set_gemm_mode(int mode);
 int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
             int trans_a, int trans_b, void *stream);
 int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32_t layer, uint32_t step,

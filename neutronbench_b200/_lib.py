@@ -47,6 +47,7 @@ SIGNATURES = {
                                     u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_label_gather": (C.c_int, [i64p, i64p, u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_cache_fill": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_set_gemm_mode": (C.c_int, [C.c_int]),
     "nb_gemm": (C.c_int, [ptr, f32p, f32p, f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, ptr]),
     "nb_relu_dropout": (C.c_int, [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, ptr]),
     "nb_softmax_nll": (C.c_int, [ptr, f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),

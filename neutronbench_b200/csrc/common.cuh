@@ -119,6 +119,10 @@ int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, ui
                        const uint32_t *hashmap, bool feat_is_hit, const float *norm_idx, const float *norm_row,
                        uint32_t *ref, float *w, cudaStream_t stream);
 int read_tma_error_flag(unsigned int *value);
+int read_tc_error_flag(unsigned int *value);
+int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
+                     int trans_a, int trans_b, int mode, cudaStream_t stream);
+extern int g_gemm_mode;    // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
 extern uint64_t g_l2_panel_bytes;
 extern int g_staged_min_width;
 extern int g_staged_spmm;  // 1: use the TMA-staged aggregation where its alignment rules hold

@@ -6,6 +6,8 @@
 
 namespace nb {
 
+int g_gemm_mode = 1;   // tcgen05 with the three-term TF32 split
+
 // ------------------------------------------------------------------------------------ GEMM (SIMT)
 // C[M x N] = op(A) op(B), element access through strides so that NN / TN / NT share one kernel.
 // 64 x 64 x 16 tiles, 256 threads, 4 x 4 outputs per thread.  blockIdx.z walks split-K slices whose
@@ -190,6 +192,7 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
     NB_CUDA(cudaMemsetAsync(d_c, 0, (size_t)(M * N) * sizeof(float), stream));
     return 0;
   }
+  if (g_gemm_mode != 0) return gemm_tensor_core(ws, d_a, d_b, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
   GemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
   g.sa_i = trans_a ? 1 : K;  g.sa_k = trans_a ? M : 1;
@@ -223,6 +226,12 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
     NB_LAUNCH_CHECK();
   }
   return 0;
+}
+
+NB_API int nb_set_gemm_mode(int mode) {
+  const int old = g_gemm_mode;
+  if (mode >= 0 && mode <= 2) g_gemm_mode = mode;
+  return old;
 }
 
 NB_API int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32_t layer, uint32_t step,

@@ -1,0 +1,467 @@
+// fp32 GEMM on the 5th-generation tensor cores (tcgen05.mma, kind::tf32) with fp32-level accuracy.
+//
+//   C[M x N] = op(A) op(B)            NN (Y W), TN (Y^T dZ, split over the long reduction), NT (dZ W^T)
+//
+// Accuracy: every fp32 operand is split as x = hi + lo with hi = x truncated to TF32 (the tensor core
+// drops the low 13 mantissa bits itself) and lo = x - hi (exact).  Three MMAs per K step accumulate
+// hi*hi + hi*lo + lo*hi into the same fp32 TMEM accumulator; the dropped lo*lo term is below 2^-22 of
+// the product.  mode 2 issues only hi*hi (plain TF32).
+//
+// Data path: raw fp32 tiles are copied global -> shared with cp.async straight into the canonical
+// no-swizzle K-major core-matrix layout (8 rows x 16 bytes per core matrix), four stages deep and two
+// chunks ahead of the math; a short pass rewrites each arrived tile as hi in place and lo next to it
+// (the split needs arithmetic, so the TMA unit cannot do it); one elected thread issues tcgen05.mma
+// from shared-memory descriptors; the accumulator lives in tensor memory and is read back with
+// tcgen05.ld (a warp reaches its own 32 TMEM lanes).  A tcgen05.commit mbarrier per stage tells when
+// the MMAs that read it have finished.
+#include "common.cuh"
+
+namespace nb {
+
+constexpr int kTcThreads = 512;   // 16 warps: the staging work is instruction-latency bound, so warps hide it
+constexpr int kBM = 128;           // rows of a C tile = TMEM lanes
+constexpr int kBK = 32;            // K elements per shared-memory chunk (4 MMA K-steps of 8)
+constexpr uint32_t kTcWaitLimit = 1u << 20;
+
+__device__ unsigned int g_tc_gemm_error = 0;
+
+struct TcGemmArgs {
+  const float *a, *b;
+  float *c;                 // output, or split-K partials [splits][M][N]
+  int64_t M, N, K;
+  int64_t a_row, a_k;       // element strides of op(A)(i,k): address = a + i*a_row + k*a_k
+  int64_t b_row, b_k;       // element strides of op(B)^T(j,k): address = b + j*b_row + k*b_k
+  int64_t k_per_split;
+  int a_vec, b_vec;         // widest aligned vector (floats) along the unit-stride dimension
+  int mode;                 // 1: 3xTF32, 2: 1xTF32
+};
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out (the caller records the error and winds down).
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kTcWaitLimit; i++)
+    if (tc_mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices (8 rows x 16 B) adjacent along K
+// are `lbo` bytes apart, 8-row groups along M/N are `sbo` bytes apart.  Bit 46 = descriptor version 1.
+__device__ __forceinline__ uint64_t tc_make_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_split(float x, float &hi, float &lo) {
+  hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+  lo = x - hi;
+}
+
+// Tile layout in shared memory (floats): K-major core matrices (8 rows x 16 B), 8 K-cores per 8-row
+// group.  Consecutive K-cores are 144 bytes apart instead of 128: the 16 bytes of padding put the 8
+// pieces of one tile row on different banks, so that a row can be written by consecutive threads
+// (coalesced global reads) without bank conflicts.  Both strides are descriptor fields (LBO / SBO),
+// so the tensor core reads the padded layout natively.
+constexpr uint32_t kCoreFloats = 36;                   // 128-byte core matrix + 16 bytes of padding
+constexpr uint32_t kGroupFloats = 8 * kCoreFloats;     // 8 K-cores per 8-row group: 1152 bytes
+constexpr uint32_t kLBO = kCoreFloats * 4, kSBO = kGroupFloats * 4;
+__device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t k) {
+  return (r >> 3) * kGroupFloats + (k >> 2) * kCoreFloats + (r & 7) * 4 + (k & 3);
+}
+template <int ROWS>
+struct TileFloats {
+  static constexpr uint32_t value = (ROWS / 8) * kGroupFloats;
+};
+
+constexpr int kStages = 4;        // raw operand stages filled by cp.async, two chunks ahead of the MMAs
+
+__device__ __forceinline__ void cp_async(uint32_t dst, const void *src, int bytes, int valid) {
+  // `valid` bytes are read, the rest of the `bytes`-wide destination is zero-filled
+  if (bytes == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
+  else if (bytes == 8)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Asynchronously copies the ROWS x 32 tile op(X)(row0 + r, k0 + k) = base[(row0+r)*s_row + (k0+k)*s_k]
+// into `tile` (canonical layout), zero outside the matrix.  K unit-stride operands move in pieces of
+// `vec` floats along K; row unit-stride operands (the transposed ones) move element by element, with
+// consecutive threads on consecutive rows so that the global reads coalesce.
+template <int ROWS>
+__device__ __forceinline__ void copy_tile_async(float *tile, const float *__restrict__ base, int64_t s_row,
+                                                int64_t s_k, int64_t row0, int64_t rows_total, int64_t k0,
+                                                int64_t k_end, int vec) {
+  const int tid = threadIdx.x;
+  const uint32_t tile_s = tc_smem_u32(tile);
+  if (s_k == 1) {
+    const int per_row = kBK / vec;                       // pieces per tile row
+    for (int item = tid; item < ROWS * per_row; item += kTcThreads) {
+      const int r = item / per_row, k = (item % per_row) * vec;
+      const int64_t gr = row0 + r, gk = k0 + k;
+      int valid = 0;
+      if (gr < rows_total && gk < k_end) valid = (int)min((int64_t)vec, k_end - gk) * 4;
+      const float *src = valid ? base + gr * s_row + gk : base;
+      cp_async(tile_s + tile_off(r, k) * 4, src, vec * 4, valid);
+    }
+  } else {
+    for (int item = tid; item < ROWS * kBK; item += kTcThreads) {
+      const int r = item % ROWS, k = item / ROWS;
+      const int64_t gr = row0 + r, gk = k0 + k;
+      const int valid = (gr < rows_total && gk < k_end) ? 4 : 0;
+      const float *src = valid ? base + gk * s_k + gr * s_row : base;
+      cp_async(tile_s + tile_off(r, k) * 4, src, 4, valid);
+    }
+  }
+}
+
+// Per-thread copy plan of one operand: the (row, k) pieces a thread moves are the same in every
+// chunk, so the source pointer, the destination offsets and the row predicate are computed once and
+// the main loop only advances the pointer.  item = tid + i*kTcThreads, r = item % ROWS,
+// kidx = item / ROWS = tid/ROWS + i*(kTcThreads/ROWS).
+template <int ROWS>
+struct CopyPlan {
+  const float *src;      // address of this thread's first piece in chunk 0 (row clamped when invalid)
+  int64_t step;          // elements between a thread's consecutive pieces
+  int64_t chunk_step;    // elements between chunks
+  uint32_t dst[ (ROWS * kBK) / kTcThreads > 0 ? (ROWS * kBK) / kTcThreads : 1 ];   // byte offsets in the tile
+  int pieces, bytes, valid;   // valid: bit i set when piece i lies inside the matrix
+
+  __device__ void init(const float *base, int64_t s_row, int64_t s_k, int64_t row0, int64_t rows_total, int64_t k0,
+                       int vec) {
+    const int tid = threadIdx.x;
+    constexpr int NDST = (int)(sizeof(dst) / sizeof(dst[0]));
+    valid = 0;
+    if (s_k == 1) {
+      // K unit-stride: consecutive threads take consecutive pieces of one tile row (coalesced reads);
+      // piece i of a thread is the same k range of a row (kTcThreads / per_row) further down.
+      const int per_row = kBK / vec;
+      const int piece = tid % per_row, r0 = tid / per_row, rstep = kTcThreads / per_row;
+      bytes = vec * 4;
+      pieces = (ROWS * per_row) / kTcThreads;
+      if (pieces < 1) pieces = (tid < ROWS * per_row) ? 1 : 0;
+      src = base + (row0 + r0) * s_row + k0 + piece * vec;
+      step = (int64_t)rstep * s_row;
+#pragma unroll
+      for (int i = 0; i < NDST; i++) {
+        const int r = r0 + i * rstep;
+        dst[i] = tile_off(r, piece * vec) * 4;
+        if (i < pieces && row0 + r < rows_total) valid |= 1 << i;
+      }
+    } else {
+      // row unit-stride (transposed operand): consecutive threads take consecutive rows at one k,
+      // element by element; piece i is KSTEP further along k.
+      const int r = tid % ROWS, kidx0 = tid / ROWS;
+      constexpr int KSTEP = kTcThreads / ROWS;
+      bytes = 4;
+      pieces = (ROWS * kBK) / kTcThreads;
+      if (pieces < 1) pieces = (tid < ROWS * kBK) ? 1 : 0;
+      const bool row_ok = row0 + r < rows_total;
+      src = base + (row_ok ? row0 + r : 0) * s_row + (k0 + kidx0) * s_k;
+      step = (int64_t)KSTEP * s_k;
+#pragma unroll
+      for (int i = 0; i < NDST; i++) {
+        dst[i] = tile_off(r, kidx0 + i * KSTEP) * 4;
+        if (i < pieces && row_ok) valid |= 1 << i;
+      }
+    }
+    chunk_step = (int64_t)kBK * s_k;
+  }
+  // Copies of one full chunk (all 32 k inside the matrix); rows outside the matrix are zero-filled.
+  __device__ __forceinline__ void issue(uint32_t tile_s, int chunk, const float *safe) const {
+    const float *p = src + (int64_t)chunk * chunk_step;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(dst) / sizeof(dst[0])); i++) {
+      if (i < pieces) {
+        const bool ok = (valid >> i) & 1;
+        cp_async(tile_s + dst[i], ok ? p + (int64_t)i * step : safe, bytes, ok ? bytes : 0);
+      }
+    }
+  }
+};
+
+// In place: raw -> hi (low 13 mantissa bits cleared); lo = raw - hi goes to `lo`.
+template <int ROWS>
+__device__ __forceinline__ void split_tile(float *raw, float *lo, bool split) {
+  constexpr int QUADS = ROWS * 8;   // 16-byte pieces (padding between row groups is skipped)
+  for (int q = threadIdx.x; q < QUADS; q += kTcThreads) {
+    const uint32_t off = (q >> 6) * kGroupFloats + ((q & 63) >> 3) * kCoreFloats + (q & 7) * 4;   // 64 quads per group
+    const float4 x = *reinterpret_cast<const float4 *>(raw + off);
+    float h[4], l[4];
+    tc_split(x.x, h[0], l[0]); tc_split(x.y, h[1], l[1]); tc_split(x.z, h[2], l[2]); tc_split(x.w, h[3], l[3]);
+    *reinterpret_cast<float4 *>(raw + off) = make_float4(h[0], h[1], h[2], h[3]);
+    if (split) *reinterpret_cast<float4 *>(lo + off) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs g) {
+  extern __shared__ __align__(1024) unsigned char tc_smem[];
+  constexpr uint32_t A_TILE = TileFloats<kBM>::value;
+  constexpr uint32_t B_TILE = TileFloats<BN>::value;
+  float *a_raw = reinterpret_cast<float *>(tc_smem);                 // [kStages][A_TILE]  (becomes hi)
+  float *b_raw = a_raw + kStages * A_TILE;                           // [kStages][B_TILE]
+  float *a_lo = b_raw + kStages * B_TILE;                            // [2][A_TILE]
+  float *b_lo = a_lo + 2 * A_TILE;                                   // [2][B_TILE]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(b_lo + 2 * B_TILE);  // [kStages]: MMAs of a chunk finished
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kStages);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool split = g.mode == 1;
+  const int64_t row0 = (int64_t)blockIdx.x * kBM, col0 = (int64_t)blockIdx.y * BN;
+  const int64_t k_begin = (int64_t)blockIdx.z * g.k_per_split;
+  const int64_t k_end = min(g.K, k_begin + g.k_per_split);
+  const int nchunks = (int)((k_end - k_begin + kBK - 1) / kBK);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)),
+                 "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; s++) tc_mbar_init(tc_smem_u32(&bars[s]), 1);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  bool ok = true;
+
+  CopyPlan<kBM> plan_a;
+  CopyPlan<BN> plan_b;
+  plan_a.init(g.a, g.a_row, g.a_k, row0, g.M, k_begin, g.a_vec);
+  plan_b.init(g.b, g.b_row, g.b_k, col0, g.N, k_begin, g.b_vec);
+  const int full_chunks = (int)((k_end - k_begin) / kBK);   // chunks without a K tail
+
+  auto start_copy = [&](int chunk) {
+    if (chunk < full_chunks) {
+      const int st = chunk % kStages;
+      plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk, g.a);
+      plan_b.issue(tc_smem_u32(b_raw + st * B_TILE), chunk, g.b);
+    } else if (chunk < nchunks) {   // the one chunk with a K tail: bounds-checked copies
+      const int st = chunk % kStages;
+      const int64_t k0 = k_begin + (int64_t)chunk * kBK;
+      copy_tile_async<kBM>(a_raw + st * A_TILE, g.a, g.a_row, g.a_k, row0, g.M, k0, k_end, g.a_vec);
+      copy_tile_async<BN>(b_raw + st * B_TILE, g.b, g.b_row, g.b_k, col0, g.N, k0, k_end, g.b_vec);
+    }
+    cp_async_commit();   // one group per chunk slot, empty past the end, so that the wait count is constant
+  };
+  start_copy(0);
+  start_copy(1);
+
+  for (int c = 0; c < nchunks; c++) {
+    const int st = c % kStages, lb = c & 1;
+    cp_async_wait<1>();            // this thread's copies of chunk c have landed (chunk c+1 may be in flight)
+    bool mine = true;
+    if (c >= 2) {
+      // MMAs of chunk c-2 done: its lo buffer (same parity) and its raw stage (refilled below) are free.
+      mine = tc_mbar_wait(tc_smem_u32(&bars[(c - 2) % kStages]), ((c - 2) / kStages) & 1);
+    }
+    if (!__syncthreads_and(mine)) { ok = false; break; }   // also: everybody's copies of chunk c are visible
+    start_copy(c + 2);             // into the stage chunk c-2 used
+    split_tile<kBM>(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
+    split_tile<BN>(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t a_h = tc_smem_u32(a_raw + st * A_TILE), a_l = tc_smem_u32(a_lo + lb * A_TILE);
+      const uint32_t b_h = tc_smem_u32(b_raw + st * B_TILE), b_l = tc_smem_u32(b_lo + lb * B_TILE);
+#pragma unroll
+      for (int kk = 0; kk < kBK / 8; kk++) {
+        // one K step = 8 tf32 = two core matrices further along K
+        const uint32_t koff = kk * 2 * kLBO;
+        const uint64_t da_h = tc_make_desc(a_h + koff, kLBO, kSBO), db_h = tc_make_desc(b_h + koff, kLBO, kSBO);
+        tc_mma_tf32(tmem, da_h, db_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+        if (split) {
+          const uint64_t da_l = tc_make_desc(a_l + koff, kLBO, kSBO), db_l = tc_make_desc(b_l + koff, kLBO, kSBO);
+          tc_mma_tf32(tmem, da_h, db_l, idesc, 1u);
+          tc_mma_tf32(tmem, da_l, db_h, idesc, 1u);
+        }
+      }
+      tc_commit(tc_smem_u32(&bars[st]));
+    }
+  }
+  cp_async_wait<0>();   // nothing of ours may still be landing in shared memory when the CTA winds down
+
+  // all MMAs done: the last commit covers every earlier one
+  if (ok && nchunks > 0) {
+    const int last = nchunks - 1;
+    ok = tc_mbar_wait(tc_smem_u32(&bars[last % kStages]), (last / kStages) & 1);
+  }
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) atomicExch(&g_tc_gemm_error, 1u);
+  tc_fence_after();
+
+  if (ok) {
+    // Warp w reads TMEM lanes 32*(w%4)..+31 (the only ones it can reach); warps 0-3 take the left half
+    // of the columns, warps 4-7 the right half.
+    float *out = g.c + (int64_t)blockIdx.z * g.M * g.N;
+    const int quarter = warp & 3, part = warp >> 2;
+    constexpr int CB = BN / 32;                      // 32-column blocks in the tile
+    constexpr int PARTS = kTcThreads / 128;          // groups of four warps sharing the column blocks
+#pragma unroll
+    for (int cbi = 0; cbi < (CB + PARTS - 1) / PARTS; cbi++) {
+      const int cb = cbi * PARTS + part;
+      if (cb >= CB) continue;
+      uint32_t r[32];
+      const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + cb * 32;
+      if (nchunks > 0) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; q++) r[q] = 0u;
+      }
+      // Transpose through shared memory (the operand stages are free by now) so that a warp writes
+      // one C row segment of 128 contiguous bytes per instruction instead of 32 scattered words.
+      float *stage = reinterpret_cast<float *>(tc_smem) + warp * (32 * 33);
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 32; q++) stage[lane * 33 + q] = __uint_as_float(r[q]);
+      __syncwarp();
+      {
+        const int64_t gj = col0 + cb * 32 + lane;
+        for (int rr = 0; rr < 32; rr++) {
+          const int64_t grow = row0 + quarter * 32 + rr;
+          if (grow < g.M && gj < g.N) out[grow * g.N + gj] = stage[rr * 33 + lane];
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+template <int BN>
+static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)((kStages + 2) * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  gemm_tc_kernel<BN><<<grid, kTcThreads, smem, stream>>>(g);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+__global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ c, int64_t mn,
+                                        int splits) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (int64_t)gridDim.x * blockDim.x) {
+    float s = partial[i];
+    for (int z = 1; z < splits; z++) s += partial[(int64_t)z * mn + i];
+    c[i] = s;
+  }
+}
+
+static int vec_of(const float *p, int64_t ld) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  if ((a & 15) == 0 && (ld & 3) == 0) return 4;
+  if ((a & 7) == 0 && (ld & 1) == 0) return 2;
+  return 1;
+}
+
+// Tensor-core GEMM front end; same contract as the CUDA-core path in dense.cu.
+int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
+                     int trans_a, int trans_b, int mode, cudaStream_t stream) {
+  TcGemmArgs g{};
+  g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K; g.mode = mode;
+  // op(A)(i,k): NN/NT -> A[i*K + k];  TN -> A[k*M + i]
+  g.a_row = trans_a ? 1 : K;  g.a_k = trans_a ? M : 1;
+  // op(B)^T(j,k) = op(B)(k,j): NN/TN -> B[k*N + j];  NT -> B[j*K + k]
+  g.b_row = trans_b ? K : 1;  g.b_k = trans_b ? 1 : N;
+  g.a_vec = vec_of(d_a, trans_a ? M : K);
+  g.b_vec = vec_of(d_b, trans_b ? K : N);
+  const int bn = N > 64 ? 128 : (N > 32 ? 64 : 32);
+  const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  int splits = 1;
+  if (tiles < kNumSMs && K >= 8 * kBK) {
+    splits = (int)((kNumSMs + tiles - 1) / tiles);
+    const int64_t max_splits = K / (4 * kBK);
+    if (splits > max_splits) splits = (int)max_splits;
+    if (splits < 1) splits = 1;
+  }
+  g.k_per_split = ((K + splits - 1) / splits + kBK - 1) / kBK * kBK;
+  splits = (int)((K + g.k_per_split - 1) / g.k_per_split);
+  WsScope scope(ws);
+  float *partial = nullptr;
+  if (splits > 1) {
+    NB_REQUIRE(ws != nullptr, "nb_gemm: split-K needs a workspace");
+    partial = ws->alloc_n<float>((size_t)splits * M * N);
+    if (!partial) return fail(NB_ERR_NOMEM, "nb_gemm: workspace arena exhausted");
+  }
+  g.c = splits > 1 ? partial : d_c;
+  dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + bn - 1) / bn), (unsigned)splits);
+  if (grid.y > 65535) return fail(NB_ERR_INVALID, "nb_gemm: N too large for one launch");
+  int st;
+  switch (bn) {
+    case 128: st = launch_tc<128>(g, grid, stream); break;
+    case 64: st = launch_tc<64>(g, grid, stream); break;
+    default: st = launch_tc<32>(g, grid, stream); break;
+  }
+  if (st != 0) return st;
+  if (splits > 1) {
+    tc_splitk_reduce_kernel<<<grid_for(M * N, 256), 256, 0, stream>>>(partial, d_c, M * N, splits);
+    NB_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+int read_tc_error_flag(unsigned int *value) {
+  NB_CUDA(cudaMemcpyFromSymbol(value, g_tc_gemm_error, sizeof(unsigned int)));
+  return 0;
+}
+
+}  // namespace nb

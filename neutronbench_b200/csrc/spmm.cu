@@ -246,9 +246,10 @@ NB_API uint64_t nb_set_l2_panel_bytes(uint64_t bytes) {
 
 NB_API int nb_device_error_flags(uint32_t *flags) {
   NB_REQUIRE(flags != nullptr, "nb_device_error_flags: null pointer");
-  unsigned int v = 0;
+  unsigned int v = 0, t = 0;
   NB_TRY(read_tma_error_flag(&v));
-  *flags = v;
+  NB_TRY(read_tc_error_flag(&t));
+  *flags = (v ? 1u : 0u) | (t ? 2u : 0u);
   return 0;
 }
 

@@ -10,27 +10,43 @@ from neutronbench_b200 import _lib
 from neutronbench_b200.cuda_stream import ptr
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=[1, 0, 2], ids=["tcgen05_3xtf32", "cuda_cores", "tcgen05_tf32"])
+def gemm_mode(request):
+    """Every GEMM test runs on the tensor-core path (default), the CUDA-core path and plain TF32."""
+    lib = _lib.load()
+    old = lib.nb_set_gemm_mode(request.param)
+    yield request.param
+    lib.nb_set_gemm_mode(old)
+    import ctypes
+    flags = ctypes.c_uint32(0)
+    _lib.call("nb_device_error_flags", ctypes.byref(flags))
+    assert flags.value == 0
+
+
 RTOL = 1e-5   # fp32 tolerance of the north star; the GEMMs differ from the oracle only in summation order
 
 
-def _close(a, b, k):
+def _close(a, b, k, mode=1):
     scale = np.abs(b).max() + 1e-30
-    assert np.abs(a - b).max() / scale < RTOL * max(1.0, np.sqrt(k) / 8), (np.abs(a - b).max(), scale)
+    tol = 2e-3 if mode == 2 else RTOL * max(1.0, np.sqrt(k) / 8)   # plain TF32 keeps 10 mantissa bits
+    assert np.abs(a - b).max() / scale < tol, (np.abs(a - b).max(), scale)
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 1, 1), (63, 17, 65), (1024, 128, 41), (3000, 602, 128), (200, 1433, 16)])
-def test_gemm_nn(cuda_device, ws, M, K, N):
+def test_gemm_nn(cuda_device, ws, gemm_mode, M, K, N):
     rng = np.random.RandomState(M + K + N)
     a, b = rng.randn(M, K).astype(np.float32), rng.randn(K, N).astype(np.float32)
     c = torch.empty((M, N), device=cuda_device)
     _lib.call("nb_gemm", ws.handle, ptr(dev_f32(a, cuda_device)), ptr(dev_f32(b, cuda_device)), ptr(c), M, N, K, 0, 0,
               torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    _close(host_f32(c), oracle.gemm_nn(a, b), K)
+    _close(host_f32(c), oracle.gemm_nn(a, b), K, gemm_mode)
 
 
 @pytest.mark.parametrize("M,K,N", [(5000, 602, 128), (1024, 128, 41), (70, 3, 5), (25000, 100, 128)])
-def test_gemm_tn_weight_gradient(cuda_device, ws, M, K, N):
+def test_gemm_tn_weight_gradient(cuda_device, ws, gemm_mode, M, K, N):
     """dW[K x N] = Y^T[K x M] dZ[M x N]; the long reduction over M runs split-K."""
     rng = np.random.RandomState(M + N)
     y, dz = rng.randn(M, K).astype(np.float32), rng.randn(M, N).astype(np.float32)
@@ -38,11 +54,11 @@ def test_gemm_tn_weight_gradient(cuda_device, ws, M, K, N):
     _lib.call("nb_gemm", ws.handle, ptr(dev_f32(y, cuda_device)), ptr(dev_f32(dz, cuda_device)), ptr(c), K, N, M, 1, 0,
               torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    _close(host_f32(c), oracle.gemm_tn(y, dz), M)
+    _close(host_f32(c), oracle.gemm_tn(y, dz), M, gemm_mode)
 
 
 @pytest.mark.parametrize("M,N,K", [(1024, 41, 128), (3000, 128, 128), (7, 5, 3)])
-def test_gemm_nt_input_gradient(cuda_device, ws, M, N, K):
+def test_gemm_nt_input_gradient(cuda_device, ws, gemm_mode, M, N, K):
     """dY[M x K] = dZ[M x N] W^T with W[K x N]."""
     rng = np.random.RandomState(M + N + K)
     dz, w = rng.randn(M, N).astype(np.float32), rng.randn(K, N).astype(np.float32)
@@ -50,7 +66,7 @@ def test_gemm_nt_input_gradient(cuda_device, ws, M, N, K):
     _lib.call("nb_gemm", ws.handle, ptr(dev_f32(dz, cuda_device)), ptr(dev_f32(w, cuda_device)), ptr(c), M, K, N, 0, 1,
               torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    _close(host_f32(c), oracle.gemm_nt(dz, w), N)
+    _close(host_f32(c), oracle.gemm_nt(dz, w), N, gemm_mode)
 
 
 @pytest.mark.parametrize("n,p", [(1, 0.5), (1023, 0.5), (4096, 0.0), (100003, 0.3)])
