@@ -1,0 +1,127 @@
+// Reference-backed oracle: runs the REFERENCE's own code for the sampled mini-batch GCN path and dumps
+// its outputs, so that the plain-C restatement (nts_oracle.c) and the CUDA path can be pinned to them.
+// TEST INFRASTRUCTURE ONLY.  Nothing of the reference is copied: its headers are included in place
+// from the reference tree (-I<reference root>), with single-rank stand-ins for <mpi.h>, <numa.h>,
+// <metis.h> (oracle/shims/) and host-memory stand-ins for the reference's CUDA allocation/copy helpers
+// (oracle/shims/cuda_stubs.cpp), because the reference's CPU path allocates "device" arrays
+// unconditionally (core/ntsSampler.hpp:1098).
+//
+// What runs (all reference code):
+//   FullyRepGraph::ReadRepGraphFromRawFile            core/FullyRepGraph.hpp:485-560
+//   Sampler::sample_one -> init_co, sample_processing, sampCSC::postprocessing,
+//     generate_csr_from_csc, update_degree, compute_weight_forward/backward
+//                                                     core/ntsSampler.hpp:843-1106, core/coocsc.hpp
+//   nts::op::MiniBatchFuseOp::forward / backward      core/ntsMiniBatchGraphOp.hpp:154-244
+//
+// usage: ref_harness <edge_file> <vertices> <seeds.u32> <fanout hop order, comma list> <F> <out_dir>
+// Output: raw little-endian arrays <out_dir>/<name>.bin plus <out_dir>/index.txt (name dtype count).
+#define CUDA_ENABLE 1
+#include "core/neutronstar.hpp"
+
+#include <cstdio>
+#include <fstream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+static std::string g_out;
+static std::ofstream g_index;
+
+template <typename T>
+static void dump(const std::string &name, const char *dtype, const T *data, size_t n) {
+  std::ofstream f(g_out + "/" + name + ".bin", std::ios::binary);
+  f.write(reinterpret_cast<const char *>(data), (std::streamsize)(n * sizeof(T)));
+  g_index << name << " " << dtype << " " << n << "\n";
+}
+
+int main(int argc, char **argv) {
+  if (argc < 7) {
+    fprintf(stderr, "usage: %s edge_file vertices seeds.u32 fanouts F out_dir\n", argv[0]);
+    return 2;
+  }
+  const std::string edge_file = argv[1];
+  const VertexId V = (VertexId)std::stoul(argv[2]);
+  const std::string seeds_file = argv[3];
+  std::vector<int> fanout;
+  {
+    std::stringstream ss(argv[4]);
+    std::string t;
+    while (std::getline(ss, t, ',')) fanout.push_back(std::stoi(t));
+  }
+  const int F = std::stoi(argv[5]);
+  g_out = argv[6];
+  g_index.open(g_out + "/index.txt");
+
+  std::vector<VertexId> seeds;
+  {
+    std::ifstream f(seeds_file, std::ios::binary);
+    VertexId x;
+    while (f.read(reinterpret_cast<char *>(&x), sizeof(x))) seeds.push_back(x);
+  }
+  const long file_bytes = file_size(edge_file.c_str());
+  const EdgeId E = (EdgeId)(file_bytes / (2 * sizeof(VertexId)));
+
+  // A single-rank Graph object with just the fields the sampled path reads.
+  Graph<Empty> *graph = new Graph<Empty>();
+  graph->filename = edge_file;
+  graph->vertices = V;
+  graph->edges = E;
+  graph->partition_offset = new VertexId[2]{0, V};
+  graph->owned_vertices = V;
+  graph->in_degree_for_backward = new VertexId[V]();
+  graph->out_degree_for_backward = new VertexId[V]();
+  graph->gnnctx = new GNNContext();
+  graph->gnnctx->layer_size.assign(fanout.size() + 1, F);
+  graph->gnnctx->fanout = fanout;       // hop order, as the toolkit holds it after its reverse()
+  graph->gnnctx->val_fanout = fanout;
+  graph->config->batch_size = (VertexId)seeds.size();
+  graph->config->batch_type = SEQUENCE;
+  graph->config->sample_rate = -1;
+  graph->config->mini_pull = 1;
+  graph->config->classes = 1;
+  graph->config->threads = 1;   // one sampling thread: the thread-local mt19937(2000) stream is reproducible
+
+  FullyRepGraph *frg = new FullyRepGraph(graph);
+  frg->ReadRepGraphFromRawFile();
+  dump("graph_column_offset", "u32", frg->column_offset, (size_t)V + 1);
+  dump("graph_row_indices", "u32", frg->row_indices, (size_t)E);
+
+  Sampler *sampler = new Sampler(frg, seeds);
+  SampledSubgraph *ssg = sampler->subgraph;
+  sampler->sample_one(ssg, 0, false);   // phase=false: plain fan-out rule, no batch-type special cases
+
+  const int L = (int)fanout.size();
+  for (int l = 0; l < L; l++) {
+    sampCSC *b = ssg->sampled_sgs[l];
+    const std::string p = "block" + std::to_string(l) + "_";
+    VertexId sizes[3] = {b->v_size, b->e_size, b->src_size};
+    dump(p + "sizes", "u32", sizes, 3);
+    dump(p + "destination", "u32", b->destination.data(), b->v_size);
+    dump(p + "source", "u32", b->source.data(), b->src_size);
+    dump(p + "column_offset", "u32", b->column_offset.data(), (size_t)b->v_size + 1);
+    dump(p + "row_indices", "u32", b->row_indices.data(), b->e_size);
+    dump(p + "row_offset", "u32", b->row_offset.data(), (size_t)b->src_size + 1);
+    dump(p + "column_indices", "u32", b->column_indices.data(), b->e_size);
+    dump(p + "edge_weight_forward", "f32", b->edge_weight_forward.data(), b->e_size);
+    dump(p + "edge_weight_backward", "f32", b->edge_weight_backward.data(), b->e_size);
+  }
+
+  // Aggregation through the reference operator on seeded inputs.
+  torch::manual_seed(2000);
+  for (int l = 0; l < L; l++) {
+    sampCSC *b = ssg->sampled_sgs[l];
+    const std::string p = "block" + std::to_string(l) + "_";
+    NtsVar x = torch::randn({(long)b->src_size, (long)F}, torch::kFloat);
+    NtsVar gy = torch::randn({(long)b->v_size, (long)F}, torch::kFloat);
+    nts::op::MiniBatchFuseOp op(ssg, graph, l);
+    NtsVar y = op.forward(x);
+    NtsVar gx = op.backward(gy);
+    dump(p + "x", "f32", x.data_ptr<float>(), (size_t)x.numel());
+    dump(p + "gy", "f32", gy.data_ptr<float>(), (size_t)gy.numel());
+    dump(p + "y", "f32", y.data_ptr<float>(), (size_t)y.numel());
+    dump(p + "gx", "f32", gx.data_ptr<float>(), (size_t)gx.numel());
+  }
+  g_index.close();
+  printf("ref_harness: wrote %s\n", g_out.c_str());
+  return 0;
+}
