@@ -231,6 +231,20 @@ int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32_t laye
                     void *stream);
 int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
                    float *d_dlogits, float *d_stats, void *stream);
+/* No counterpart in the reference.  Same result as nb_softmax_nll, for callers that cannot provide
+ * scratch memory when they call: processes that committed all device memory to their own pool at
+ * start-up, or hosts whose rules forbid any allocation after initialisation.  The per-row scratch
+ * (two floats per row) lives in a fixed 512 KiB device array inside the library image, which every GPU
+ * that loads the library keeps until the process ends.  Limits and rules:
+ *   - B <= 65536 rows; larger batches are refused with NB_ERR_INVALID (use nb_softmax_nll).
+ *   - The call performs no cudaMalloc / cudaFree and uses no workspace.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress with that
+ *     device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ *     (different streams without an ordering between them) corrupt each other's loss.  The array keeps
+ *     the previous call's rows; the kernels rewrite every row they read, so no clearing is required. */
+int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                          float *d_dlogits, float *d_stats, void *stream);
 int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
             float b2, float eps, float wd, float b1_t, float b2_t, void *stream);
 

@@ -51,6 +51,7 @@ SIGNATURES = {
     "nb_gemm": (C.c_int, [ptr, f32p, f32p, f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, ptr]),
     "nb_relu_dropout": (C.c_int, [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, ptr]),
     "nb_softmax_nll": (C.c_int, [ptr, f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
+    "nb_softmax_nll_static": (C.c_int, [f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
     "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
                           C.c_float, C.c_float, C.c_float, ptr]),
 }

@@ -272,3 +272,57 @@ NB_API int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int6
   NB_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------ loss without a workspace
+// Some hosts of this library cannot hand it scratch memory at call time: a serving or training process
+// that gave the whole device to its own pool at start-up (a later cudaMalloc fails or fragments the
+// pool), or a plugin slot whose contract forbids allocation once initialisation is over.  For them the
+// loss is also available with its per-row scratch in a fixed device array that is part of the library
+// image: every GPU that loads the library carries these 512 KiB until the process exits.
+constexpr int64_t kNoAllocMaxRows = 65536;
+static __device__ __align__(256) float g_loss_scratch[2 * kNoAllocMaxRows];   // [row_loss | row_hit]
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *g_loss_scratch_addr[kMaxDevices] = {};   // device address of g_loss_scratch, per device
+}  // namespace
+
+// In host code `g_loss_scratch` names a host-side shadow of the symbol, not device memory, so the
+// device address has to be asked for once per device, with that device current.
+static int loss_scratch_address(float **out) {
+  int dev = -1;
+  NB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return nb::fail(NB_ERR_INVALID, "nb_softmax_nll_static: device index out of range");
+  float *p = __atomic_load_n(&g_loss_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    void *addr = nullptr;
+    NB_CUDA(cudaGetSymbolAddress(&addr, g_loss_scratch));
+    p = static_cast<float *>(addr);
+    __atomic_store_n(&g_loss_scratch_addr[dev], p, __ATOMIC_RELEASE);   // same value from any racing thread
+  }
+  *out = p;
+  return 0;
+}
+
+NB_API int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                                 float *d_dlogits, float *d_stats, void *stream_) {
+  NB_REQUIRE(d_logits && d_label && d_stats, "nb_softmax_nll_static: null pointer");
+  NB_REQUIRE(B > 0 && C > 0, "nb_softmax_nll_static: empty batch or no classes");
+  if (B > kNoAllocMaxRows) {
+    nb::set_error("nb_softmax_nll_static: batch of %lld rows exceeds the built-in scratch of %lld rows; "
+                  "use nb_softmax_nll with a workspace", (long long)B, (long long)kNoAllocMaxRows);
+    return NB_ERR_INVALID;
+  }
+  float *scratch = nullptr;
+  NB_TRY(loss_scratch_address(&scratch));
+  float *row_loss = scratch, *row_hit = scratch + kNoAllocMaxRows;
+  cudaStream_t stream = nb::as_stream(stream_);
+  // Rows 0..B-1 of both halves are fully rewritten below before they are read, so nothing left over
+  // from an earlier call (of any batch size) can leak into this one; no clearing is needed.
+  nb::softmax_nll_rows_kernel<<<nb::grid_for((uint64_t)B * 32, 256), 256, 0, stream>>>(d_logits, d_label, B, C,
+                                                                                    d_dlogits, row_loss, row_hit);
+  NB_LAUNCH_CHECK();
+  nb::loss_reduce_kernel<<<1, 1024, 0, stream>>>(row_loss, row_hit, B, d_stats);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
