@@ -260,8 +260,7 @@ class GCN_GPU_NEIGHBOR_impl:
 
     def Update(self):
         """Gradient SUM over ranks (MPI_SUM in the reference, comm/network.h:189-193) then Adam."""
-        if self.world_size > 1:
-            torch.distributed.all_reduce(self.P.grad, op=torch.distributed.ReduceOp.SUM)
+        sum_gradients(self.P.grad, self.world_size)
         self.P.learn_with_decay_Adam(torch.cuda.current_stream().cuda_stream)
 
     def UpdateZero(self):
@@ -306,6 +305,33 @@ class GCN_GPU_NEIGHBOR_impl:
             batches += 1
         sampler.restart()
         return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
+
+
+def shard_for_rank(ids: np.ndarray, rank: int, world_size: int) -> np.ndarray:
+    """Data parallelism over mini-batches: the (already shuffled) train list is dealt round-robin, so
+    every id belongs to exactly one rank and shard sizes differ by at most one.  (The reference gives
+    each MPI rank the train nodes of its own vertex range, toolkits/GCN_GPU_NEIGHBOR.hpp:1339-1348; with
+    a replicated topology any disjoint cover is equivalent.)"""
+    return ids[rank::world_size]
+
+
+def batches_of(n_ids: int, batch_size: int) -> int:
+    return (n_ids + batch_size - 1) // batch_size
+
+
+def epoch_steps(n_ids_total: int, batch_size: int, world_size: int) -> int:
+    """Steps every rank takes per epoch: the largest shard's batch count.  Ranks whose shard is
+    exhausted earlier still join each step's gradient sum with zeros (UpdateZero,
+    toolkits/GCN_GPU_NEIGHBOR.hpp:309-313), so all ranks issue the same number of collectives."""
+    largest = (n_ids_total + world_size - 1) // world_size
+    return batches_of(largest, batch_size)
+
+
+def sum_gradients(grad: torch.Tensor, world_size: int):
+    """Gradient SUM over ranks (MPI_SUM, comm/network.h:189-193), in place."""
+    if world_size > 1:
+        torch.distributed.all_reduce(grad, op=torch.distributed.ReduceOp.SUM)
+    return grad
 
 
 def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
