@@ -17,6 +17,7 @@
 // Output: raw little-endian arrays <out_dir>/<name>.bin plus <out_dir>/index.txt (name dtype count).
 #define CUDA_ENABLE 1
 #include "core/neutronstar.hpp"
+#include "utils/torch_func.hpp"
 
 #include <cstdio>
 #include <fstream>
@@ -34,7 +35,131 @@ static void dump(const std::string &name, const char *dtype, const T *data, size
   g_index << name << " " << dtype << " " << n << "\n";
 }
 
+// ---------------------------------------------------------------------------------------------
+// bench mode: times the reference's CPU training path on this machine's host cores, batch by batch,
+// with the call sequence of GCN_CPU_NEIGHBOR_impl::Forward (toolkits/GCN_CPU_NEIGHBOR.hpp:300-366):
+// sample_one -> get_feature / get_label -> runGraphOp<MiniBatchFuseOp> + vertexForward per layer ->
+// Loss -> appendNNOp -> self_backward -> all_reduce_to_gradient + learnC2C_with_decay_Adam + next.
+// usage: ref_harness bench <edge_file> <vertices> <feat.f32> <label.i64> <seeds.u32> <fanouts>
+//                          <layers a-b-c> <batch> <warmup batches> <timed batches> <drop> <lr> <wd>
+// prints one line: REFBENCH ms_per_batch=<..> agg_edges_per_batch=<..> omp_threads=<..> batches=<..>
+// ---------------------------------------------------------------------------------------------
+static int bench_main(int argc, char **argv) {
+  if (argc < 15) {
+    fprintf(stderr, "bench: not enough arguments\n");
+    return 2;
+  }
+  const std::string edge_file = argv[2];
+  const VertexId V = (VertexId)std::stoul(argv[3]);
+  const std::string feat_file = argv[4], label_file = argv[5], seeds_file = argv[6];
+  std::vector<int> fanout, sizes;
+  {
+    std::stringstream ss(argv[7]);
+    std::string t;
+    while (std::getline(ss, t, ',')) fanout.push_back(std::stoi(t));
+    std::stringstream s2(argv[8]);
+    while (std::getline(s2, t, '-')) sizes.push_back(std::stoi(t));
+  }
+  const VertexId batch = (VertexId)std::stoul(argv[9]);
+  const int warm = std::stoi(argv[10]), timed = std::stoi(argv[11]);
+  const float drop = std::stof(argv[12]), lr = std::stof(argv[13]), wd = std::stof(argv[14]);
+  const int L = (int)fanout.size();
+
+  std::vector<VertexId> seeds;
+  {
+    std::ifstream f(seeds_file, std::ios::binary);
+    VertexId x;
+    while (f.read(reinterpret_cast<char *>(&x), sizeof(x))) seeds.push_back(x);
+  }
+  const EdgeId E = (EdgeId)(file_size(edge_file.c_str()) / (2 * sizeof(VertexId)));
+  Graph<Empty> *graph = new Graph<Empty>();
+  graph->filename = edge_file;
+  graph->vertices = V;
+  graph->edges = E;
+  graph->partition_offset = new VertexId[2]{0, V};
+  graph->owned_vertices = V;
+  graph->in_degree_for_backward = new VertexId[V]();
+  graph->out_degree_for_backward = new VertexId[V]();
+  graph->gnnctx = new GNNContext();
+  graph->gnnctx->layer_size = sizes;
+  graph->gnnctx->fanout = fanout;
+  graph->gnnctx->val_fanout = fanout;
+  graph->config->batch_size = batch;
+  graph->config->batch_type = SEQUENCE;
+  graph->config->sample_rate = -1;
+  graph->config->mini_pull = 1;
+  graph->config->classes = 1;
+
+  FullyRepGraph *frg = new FullyRepGraph(graph);
+  frg->ReadRepGraphFromRawFile();
+  Sampler *sampler = new Sampler(frg, seeds);
+  SampledSubgraph *ssg = sampler->subgraph;
+
+  const long F0 = sizes[0];
+  NtsVar F = torch::empty({(long)V, F0}, torch::kFloat);
+  {
+    std::ifstream f(feat_file, std::ios::binary);
+    f.read(reinterpret_cast<char *>(F.data_ptr<float>()), (std::streamsize)((size_t)V * F0 * sizeof(float)));
+  }
+  NtsVar labels = torch::empty({(long)V}, torch::kLong);
+  {
+    std::ifstream f(label_file, std::ios::binary);
+    f.read(reinterpret_cast<char *>(labels.data_ptr<long>()), (std::streamsize)((size_t)V * sizeof(long)));
+  }
+  torch::manual_seed(2000);
+  std::vector<Parameter *> P;
+  for (int i = 0; i < L; i++) P.push_back(new Parameter(sizes[i], sizes[i + 1], lr, 0.9, 0.999, 1e-9, wd));
+  nts::ctx::NtsContext *ctx = new nts::ctx::NtsContext();
+  ctx->train();
+  std::vector<NtsVar> X(L + 1);
+  int cur_layer = 0;
+  auto vertexForward = [&](NtsVar &n_i) -> NtsVar {
+    if (cur_layer == L - 1) return P[cur_layer]->forward(n_i);
+    return torch::dropout(torch::relu(P[cur_layer]->forward(n_i)), drop, true);
+  };
+
+  double total = 0;
+  uint64_t edges = 0;
+  int done = 0;
+  for (int b = 0; b < warm + timed && sampler->sample_not_finished(); b++) {
+    const double t0 = get_time();
+    for (auto p : P) p->zero_grad();
+    sampler->sample_one(ssg, 0, false);
+    X[0] = nts::op::get_feature(ssg->sampled_sgs[0]->src().data(), ssg->sampled_sgs[0]->src_size, F, graph);
+    NtsVar target = nts::op::get_label(ssg->sampled_sgs.back()->dst().data(), ssg->sampled_sgs.back()->v_size, labels,
+                                       graph);
+    for (int l = 0; l < L; l++) {
+      cur_layer = l;
+      NtsVar Y = ctx->runGraphOp<nts::op::MiniBatchFuseOp>(ssg, graph, l, X[l]);
+      X[l + 1] = ctx->runVertexForward([&](NtsVar n_i) { return vertexForward(n_i); }, Y);
+    }
+    auto loss = Loss(X[L], target, true);
+    volatile float lv = loss.item<float>();
+    (void)lv;
+    ctx->appendNNOp(X[L], loss);
+    ctx->self_backward(false);
+    for (auto p : P) {
+      p->all_reduce_to_gradient(p->W.grad());
+      p->learnC2C_with_decay_Adam();
+      p->next();
+    }
+    const double dt = get_time() - t0;
+    if (b >= warm) {
+      total += dt;
+      done++;
+      for (int l = 0; l < L; l++) edges += ssg->sampled_sgs[l]->e_size;
+      for (int l = 1; l < L; l++) edges += ssg->sampled_sgs[l]->e_size;
+    }
+  }
+  printf("REFBENCH ms_per_batch=%.4f agg_edges_per_batch=%.1f omp_threads=%d batches=%d\n",
+         done ? 1e3 * total / done : 0.0, done ? (double)edges / done : 0.0,
+         std::max(1, numa_num_configured_cpus() / 2 - 1), done);
+  fflush(stdout);
+  _exit(0);   // the reference's destructors free members they never initialised
+}
+
 int main(int argc, char **argv) {
+  if (argc > 1 && std::string(argv[1]) == "bench") return bench_main(argc, argv);
   if (argc < 7) {
     fprintf(stderr, "usage: %s edge_file vertices seeds.u32 fanouts F out_dir\n", argv[0]);
     return 2;
