@@ -125,6 +125,7 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
 extern int g_gemm_mode;    // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
 extern uint64_t g_l2_panel_bytes;
 extern int g_staged_min_width;
+extern int g_spmm_ring;
 extern int g_staged_spmm;  // 1: use the TMA-staged aggregation where its alignment rules hold
 
 // Scoped mark/release so that a call's scratch is returned to the arena when it ends.

@@ -46,6 +46,40 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
   }
 }
 
+// Warp per destination for fanouts up to 32: lane t makes draw t of the destination's Philox stream,
+// the Floyd duplicate rule is resolved in draw order with ballots, and the lanes fetch the chosen
+// neighbours together.  Produces exactly what sample_hop_kernel produces.
+__global__ void sample_hop_warp_kernel(const uint64_t *__restrict__ g_co, const uint32_t *__restrict__ g_ri,
+                                       const uint32_t *__restrict__ dst, uint32_t v, int fanout,
+                                       const uint32_t *__restrict__ column_offset, uint32_t seed_lo,
+                                       uint32_t seed_hi, uint32_t hop, uint32_t *__restrict__ row_indices) {
+  const unsigned lane = threadIdx.x & 31;
+  const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < v; i += warps) {
+    const uint32_t d = dst[i];
+    const uint64_t base = g_co[d];
+    const uint32_t deg = (uint32_t)(g_co[d + 1] - base);
+    const uint32_t pos = column_offset[i];
+    if (deg <= (uint32_t)fanout) {
+      for (uint32_t j = lane; j < deg; j += 32) row_indices[pos + j] = g_ri[base + j];
+      continue;
+    }
+    const uint32_t k = (uint32_t)fanout;      // <= 32
+    uint32_t chosen = 0xFFFFFFFFu;
+    if (lane < k) {
+      uint32_t r[4];
+      philox4x32_10(lane >> 2, (uint32_t)i, hop, 0u, seed_lo, seed_hi, r);
+      chosen = __umulhi(r[lane & 3], deg - k + lane + 1);   // candidate of draw `lane`: uniform in [0, j]
+    }
+    for (uint32_t t = 1; t < k; t++) {
+      const uint32_t c = __shfl_sync(0xffffffffu, chosen, t);
+      const unsigned dup = __ballot_sync(0xffffffffu, lane < t && chosen == c);
+      if (dup && lane == t) chosen = deg - k + t;           // Floyd: a repeated candidate yields j itself
+    }
+    if (lane < k) row_indices[pos + lane] = g_ri[base + chosen];
+  }
+}
+
 // ------------------------------------------------------------------------------------ graph CSC
 __global__ void edge_degree_kernel(const uint32_t *__restrict__ edges, uint64_t E, uint32_t V, uint32_t *in_deg,
                                    uint32_t *out_deg, uint32_t *err) {
@@ -162,9 +196,15 @@ NB_API int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *
   NB_REQUIRE(d_graph_column_offset && d_graph_row_indices && d_dst && d_column_offset && d_row_indices,
              "nb_sample_hop: null pointer");
   NB_REQUIRE(fanout != 0, "nb_sample_hop: fanout must be positive, or negative for all neighbours");
-  sample_hop_kernel<<<grid_for(v, 128), 128, 0, as_stream(stream_)>>>(
-      d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, (uint32_t)seed,
-      (uint32_t)(seed >> 32), hop, d_row_indices);
+  if (fanout > 0 && fanout <= 32) {
+    sample_hop_warp_kernel<<<grid_for((uint64_t)v * 32, 256), 256, 0, as_stream(stream_)>>>(
+        d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, (uint32_t)seed,
+        (uint32_t)(seed >> 32), hop, d_row_indices);
+  } else {
+    sample_hop_kernel<<<grid_for(v, 128), 128, 0, as_stream(stream_)>>>(
+        d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, (uint32_t)seed,
+        (uint32_t)(seed >> 32), hop, d_row_indices);
+  }
   NB_LAUNCH_CHECK();
   return 0;
 }

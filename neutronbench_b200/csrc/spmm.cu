@@ -233,8 +233,8 @@ using namespace nb;
 NB_API int nb_set_staged_spmm(int enabled) {
   const int old = g_staged_spmm;
   g_staged_spmm = enabled ? 1 : 0;
-  if (enabled > 1) g_staged_min_width = 1;   // 2: stage every width the alignment rules allow
-  else g_staged_min_width = 256;
+  g_staged_min_width = (enabled == 2 || enabled == 4) ? 1 : 256;   // 2, 4: stage every allowed width
+  g_spmm_ring = (enabled == 3 || enabled == 4) ? 0 : 1;            // 3, 4: two-stage segment kernel, no ring
   return old;
 }
 

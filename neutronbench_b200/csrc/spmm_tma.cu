@@ -24,6 +24,7 @@ constexpr uint32_t kWaitLimit = 1u << 18;   // bounded spin on the mbarrier; the
 __device__ unsigned int g_tma_spmm_error = 0;   // 1: an mbarrier wait gave up
 uint64_t g_l2_panel_bytes = 0;                  // working-set target of one column panel (0: no panels)
 int g_l2_prefetch = 0;
+int g_spmm_ring = 1;                             // 1: per-edge ring variant when rows are not cut into panels
 int g_staged_min_width = 256;                   // narrowest row (floats) that takes the staged path                          // 1: prefetch rows into L2 two segments ahead
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -294,6 +295,160 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Ring variant: a warp owns a CONTIGUOUS range of output rows, hence a contiguous range of edges,
+// and streams those edges through a ring of R row slots in shared memory, one mbarrier per slot.
+// A slot is refilled (edge j + R) as soon as edge j has been accumulated, so R - 1 of the R slots are
+// in flight at any time instead of one stage out of two.  16 warps per CTA share the SM's shared
+// memory (about 12 KB each).  Arithmetic and order are those of every other path.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRingWarps = 16;
+
+template <int TILES, bool MASK>
+__global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const TmaSpmmArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t R = a.seg;                                   // slots per warp
+  unsigned char *my_smem = smem_raw + (size_t)warp * R * a.slot_bytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)kRingWarps * R * a.slot_bytes) + warp * R;
+  const uint32_t bar0 = smem_u32(bars);
+  if (lane < R) mbar_init(bar0 + 8 * lane, 1);
+  fence_proxy_async();
+  __syncwarp();
+
+  // rows of this warp: an equal share of the rows, contiguous
+  const uint32_t total_warps = gridDim.x * kRingWarps;
+  const uint32_t gw = blockIdx.x * kRingWarps + warp;
+  const uint32_t per = (a.n + total_warps - 1) / total_warps;
+  const uint32_t r_begin = min(a.n, gw * per), r_end = min(a.n, r_begin + per);
+  if (r_begin >= r_end) return;
+  const uint32_t j0 = __ldg(a.offs + r_begin), j1 = __ldg(a.offs + r_end);
+
+  // operand windows of 32 edges aligned to j0: `cur` holds the window being consumed, `nxt` the next
+  auto load_ref = [&](uint32_t wbase) -> uint32_t { const uint32_t j = wbase + lane; return j < j1 ? __ldg(a.ref + j) : 0u; };
+  auto load_w = [&](uint32_t wbase, uint32_t ref) -> float {
+    const uint32_t j = wbase + lane;
+    if (j >= j1) return 0.0f;
+    return a.w ? __ldg(a.w + j) : __ldg(a.norm_idx + ref);    // fused form: factor of the indexed side
+  };
+  uint32_t win = j0;                                          // base of the consume window
+  uint32_t ref_cur = load_ref(win), ref_nxt = load_ref(win + 32);
+  float w_cur = load_w(win, ref_cur), w_nxt = load_w(win + 32, ref_nxt);
+
+  // issue the copy of edge j (j0 <= j < j1) into its slot; executed by the whole warp
+  auto issue = [&](uint32_t j) {
+    const uint32_t slot = (j - j0) % R;
+    const bool in_cur = j < win + 32;
+    const uint32_t ref = __shfl_sync(0xffffffffu, in_cur ? ref_cur : ref_nxt, (j - j0) & 31);
+    const uint32_t bar = bar0 + 8 * slot;
+    unsigned char *dst = my_smem + (size_t)slot * a.slot_bytes;
+    if (ref & 0x80000000u) {        // miss: lanes copy the row; the barrier still gets its arrival
+      const float *src = a.miss + (size_t)(ref & 0x7FFFFFFFu) * a.miss_ld;
+      for (uint32_t c = lane; c < a.F; c += 32) reinterpret_cast<float *>(dst)[c] = __ldg(src + c);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_expect_tx(bar, 0);
+    } else if (lane == 0) {
+      mbar_arrive_expect_tx(bar, a.copy_bytes);
+      bulk_g2s(smem_u32(dst), a.x + (size_t)ref * a.x_ld, a.copy_bytes, bar);
+    }
+  };
+
+  // prologue: fill the ring
+  const uint32_t n_edges = j1 - j0;
+  for (uint32_t t = 0; t < min(R, n_edges); t++) issue(j0 + t);
+
+  // row bookkeeping: lane holds the end offset of row rw_base + lane
+  uint32_t rw_base = r_begin;
+  uint32_t rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
+  uint32_t row = r_begin;
+  uint32_t row_end = __shfl_sync(0xffffffffu, rend, 0);
+  float acc[TILES][4];
+#pragma unroll
+  for (int t = 0; t < TILES; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+  float nrow = a.w ? 0.0f : __ldg(a.norm_row + row);
+
+  auto finish_row = [&]() {      // write the accumulated row, move to the next one
+    float *out = a.y + (size_t)row * a.F;
+    const float *act = MASK ? a.act + (size_t)row * a.F : nullptr;
+#pragma unroll
+    for (int t = 0; t < TILES; t++) {
+      const uint32_t col = (lane + 32 * t) * 4;
+      if (col < a.F) {
+        float r[4] = {acc[t][0], acc[t][1], acc[t][2], acc[t][3]};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          if (col + c < a.F) {
+            if constexpr (MASK) r[c] = __ldg(act + col + c) > 0.0f ? __fmul_rn(r[c], a.act_scale) : 0.0f;
+          }
+        }
+        if (a.out_vec == 4) {
+          *reinterpret_cast<float4 *>(out + col) = make_float4(r[0], r[1], r[2], r[3]);
+        } else if (a.out_vec == 2) {
+          if (col + 1 < a.F) *reinterpret_cast<float2 *>(out + col) = make_float2(r[0], r[1]);
+          if (col + 3 < a.F) *reinterpret_cast<float2 *>(out + col + 2) = make_float2(r[2], r[3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; c++)
+            if (col + c < a.F) out[col + c] = r[c];
+        }
+      }
+      acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    }
+    row++;
+    if (row < r_end) {
+      if (row - rw_base >= 32) {
+        rw_base = row;
+        rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
+      }
+      row_end = __shfl_sync(0xffffffffu, rend, row - rw_base);
+      if (!a.w) nrow = __ldg(a.norm_row + row);
+    }
+  };
+
+  for (uint32_t j = j0; j < j1; j++) {
+    while (j == row_end && row < r_end) finish_row();        // rows without (more) edges
+    if (j - win >= 32) {                                      // consume window moves on; fetch the one after
+      win += 32;
+      ref_cur = ref_nxt; w_cur = w_nxt;
+      ref_nxt = load_ref(win + 32);
+      w_nxt = load_w(win + 32, ref_nxt);
+    }
+    const uint32_t slot = (j - j0) % R;
+    {
+      const uint32_t bar = bar0 + 8 * slot, parity = ((j - j0) / R) & 1;
+      uint32_t spins = 0;
+      while (!mbar_try_wait(bar, parity)) {
+        if (++spins > kWaitLimit) {
+          if (lane == 0) atomicExch(&g_tma_spmm_error, 1u);
+          for (uint32_t t = 0; t < kWaitLimit && !mbar_try_wait(bar, parity); t++) {}
+          return;
+        }
+      }
+    }
+    __syncwarp();
+    float wu = __shfl_sync(0xffffffffu, w_cur, (j - j0) & 31);
+    if (!a.w) wu = __fdiv_rn(1.0f, __fmul_rn(wu, nrow));      // 1 / (sqrt(deg_src) * sqrt(deg_dst))
+    const float4 *rowp = reinterpret_cast<const float4 *>(my_smem + (size_t)slot * a.slot_bytes);
+#pragma unroll
+    for (int t = 0; t < TILES; t++) {
+      const uint32_t q = lane + 32 * t;
+      if (q * 4 < a.F) {
+        const float4 v = rowp[q];
+        acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(v.x, wu));
+        acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(v.y, wu));
+        acc[t][2] = __fadd_rn(acc[t][2], __fmul_rn(v.z, wu));
+        acc[t][3] = __fadd_rn(acc[t][3], __fmul_rn(v.w, wu));
+      }
+    }
+    if (j + R < j1) {
+      __syncwarp();            // every lane has read the slot
+      fence_proxy_async();     // order those reads before the async-proxy refill
+      issue(j + R);
+    }
+  }
+  while (row < r_end) finish_row();
+}
+
 // ref[j] / w[j] for the gather-fused form: the row reference of edge j is the cache slot of its source
 // (or the global id with bit 31 set when the source is not cached), the weight is the GCN weight.
 __global__ void gather_refs_kernel(const uint32_t *__restrict__ offs, const uint32_t *__restrict__ idx, uint32_t v,
@@ -328,6 +483,37 @@ static int launch_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) 
   spmm_tma_kernel<TILES, MASK><<<grid, kTmaWarps * 32, smem, stream>>>(a);
   NB_LAUNCH_CHECK();
   return 0;
+}
+
+template <int TILES, bool MASK>
+static int launch_ring_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(spmm_ring_kernel<TILES, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 220 * 1024));
+    configured = true;
+  }
+  // enough CTAs that every warp gets at least a few rows, at most one CTA per SM
+  const unsigned want = (a.n + kRingWarps * 4 - 1) / (kRingWarps * 4);
+  const unsigned grid = want < (unsigned)kNumSMs ? (want ? want : 1) : (unsigned)kNumSMs;
+  spmm_ring_kernel<TILES, MASK><<<grid, kRingWarps * 32, smem, stream>>>(a);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <bool MASK>
+static int launch_ring(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
+  switch ((a.F + 127) / 128) {
+    case 1: return launch_ring_tiles<1, MASK>(a, smem, stream);
+    case 2: return launch_ring_tiles<2, MASK>(a, smem, stream);
+    case 3: return launch_ring_tiles<3, MASK>(a, smem, stream);
+    case 4: return launch_ring_tiles<4, MASK>(a, smem, stream);
+    case 5: return launch_ring_tiles<5, MASK>(a, smem, stream);
+    case 6: return launch_ring_tiles<6, MASK>(a, smem, stream);
+    case 7: return launch_ring_tiles<7, MASK>(a, smem, stream);
+    case 8: return launch_ring_tiles<8, MASK>(a, smem, stream);
+    default: return fail(NB_ERR_INVALID, "spmm (ring): feature width above 1024");
+  }
 }
 
 template <bool MASK>
@@ -366,6 +552,17 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
     const uint32_t max_panels = (a.fpad + 63) / 64;            // keep copies at 256 bytes or more
     if (panels > max_panels) panels = max_panels;
     if (panels < 1) panels = 1;
+  }
+  if (panels == 1 && g_spmm_ring) {
+    // ring variant: whole rows, per-warp ring of R slots out of about 13.5 KB
+    a.panels = 1; a.panel_floats = a.fpad; a.copy_bytes = a.fpad * 4; a.slot_bytes = a.copy_bytes;
+    uint32_t R = (13 * 1024 + 512) / a.slot_bytes;
+    if (R > 16) R = 16;
+    if (R >= 2) {
+      a.seg = R;
+      const size_t smem = (size_t)kRingWarps * R * a.slot_bytes + (size_t)kRingWarps * R * sizeof(uint64_t);
+      return a.act ? launch_ring<true>(a, smem, stream) : launch_ring<false>(a, smem, stream);
+    }
   }
   a.panel_floats = ((a.fpad / 4 + panels - 1) / panels) * 4;   // multiple of 4 floats = 16 bytes
   a.panels = (a.fpad + a.panel_floats - 1) / a.panel_floats;

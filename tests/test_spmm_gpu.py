@@ -194,7 +194,7 @@ def test_staged_and_direct_paths_give_identical_bits(cuda_device, F):
     st = torch.cuda.current_stream().cuda_stream
     outs = []
     lib = _lib.load()
-    for staged in (2, 0):
+    for staged in (2, 4, 0):    # ring kernel, two-stage segment kernel, direct loads
         old = lib.nb_set_staged_spmm(staged)
         y = torch.empty((blk.v_size, F), device=d)
         _lib.call("nb_spmm_csc_fwd", ptr(dx), ptr(y), ptr(dw), ptr(ri), ptr(co), blk.v_size, F, st)
@@ -202,6 +202,7 @@ def test_staged_and_direct_paths_give_identical_bits(cuda_device, F):
         lib.nb_set_staged_spmm(1 if old else 0)
         outs.append(host_f32(y))
     np.testing.assert_array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    np.testing.assert_array_equal(outs[0].view(np.uint32), outs[2].view(np.uint32))
     ref = oracle.spmm_fwd(x, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
     np.testing.assert_array_equal(outs[0].view(np.uint32), ref.view(np.uint32))
     import ctypes
