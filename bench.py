@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--cpu-batches", type=int, default=3, help="batches timed for the CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-gather", action="store_true")
+    ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
 
@@ -271,6 +272,7 @@ def main():
         "l2_policy": "inputs larger than L2 (feature store >> 126 MB, each step touches a new random subset)",
         "parallelism": f"dp{world}",
         "fuse_gather": cfg.fuse_gather,
+        "step": "python (one call per kernel family)" if args.python_step else "native (nb_gcn_step)",
     }
 
     if args.impl == "reference":
@@ -287,7 +289,7 @@ def main():
         print(json.dumps(line))
         return 0
 
-    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world)
+    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world, use_engine=not args.python_step)
     tk.init_cache()
     del feat_dev
     # this rank's share of the shuffled train list: contiguous shard (data parallel over mini-batches)
@@ -310,17 +312,19 @@ def main():
         smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
         if staged:
             smp.stage_seeds_on_device()
+        clocks = ClockSampler(local_rank)
+        if rank == 0 and record_events:
+            clocks.start()           # nvidia-smi needs ~0.1 s to produce its first sample: start before warm-up
         for _ in range(W):
             tk.train_step(smp)
             if not staged:
                 tk.read_stats()
         barrier()
         tk.agg_edges_fwd = tk.agg_edges_bwd = 0
-        tk.events = [] if record_events else None
+        tk.events = [] if (record_events and not tk.use_engine) else None
+        if record_events and tk.use_engine:
+            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
         launches0 = _lib.load().nb_launch_count()
-        clocks = ClockSampler(local_rank)
-        if rank == 0 and record_events:
-            clocks.start()
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
@@ -336,6 +340,12 @@ def main():
         edges = tk.agg_edges_fwd + tk.agg_edges_bwd
         ev = tk.events
         tk.events = None
+        if record_events and tk.use_engine:
+            import ctypes
+            a_ms, a_b, a_n = ctypes.c_double(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
+            _lib.call("nb_gcn_read_timing", tk._ensure_engine(), ctypes.byref(a_ms), ctypes.byref(a_b), ctypes.byref(a_n))
+            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 0)
+            ev = ("engine", a_ms.value, int(a_b.value), int(a_n.value))
         return ms, edges, launches, clk, ev
 
     ms_a, edges_a, launches, clk, events = run(staged=True, record_events=True)
@@ -359,8 +369,13 @@ def main():
     edges_a, edges_b = reduce_sum(edges_a), reduce_sum(edges_b)
 
     # roofline of the aggregation kernels from the events recorded inside the timed region
-    agg_ms = sum(s.elapsed_time(e) for (_, _, s, e) in events)
-    agg_bytes = sum(b for (_, b, _, _) in events)
+    if isinstance(events, tuple):      # native step: totals measured by the library's own CUDA events
+        _, agg_ms, agg_bytes, agg_launches = events
+        events = []
+    else:
+        agg_ms = sum(s.elapsed_time(e) for (_, _, s, e) in events)
+        agg_bytes = sum(b for (_, b, _, _) in events)
+        agg_launches = len(events)
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         peak = float(json.load(open(peaks_path))["hbm_gbs"])
@@ -376,7 +391,7 @@ def main():
         d[2] += 1
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": peak_src, "kernel": "spmm_rows_kernel (all aggregation launches)",
-                "launches": len(events), "avg_launch_ms": agg_ms / max(len(events), 1),
+                "launches": agg_launches, "avg_launch_ms": agg_ms / max(agg_launches, 1),
                 "per_call": {k: {"GBps": v[0] / (v[1] * 1e-3) / 1e9 if v[1] > 0 else 0.0, "ms_avg": v[1] / v[2],
                                  "bytes_avg": v[0] / v[2]} for k, v in per_kernel.items()}}
 

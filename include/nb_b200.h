@@ -249,6 +249,55 @@ int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t
 int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
             float b2, float eps, float wd, float b1_t, float b2_t, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Whole training step in one call: the body of the batch loop of
+ * GCN_GPU_NEIGHBOR_impl::zerocopy_version (toolkits/GCN_GPU_NEIGHBOR.hpp:604-713) — sample_one,
+ * feature / label gather, per layer runGraphOp<SingleGPUSampleGraphOp> + vertexForward, Loss,
+ * self_backward (core/ntsContext.hpp:285-366; the input-side block is not back-propagated) — issued
+ * from native code on the caller's stream, with every per-step buffer taken from the workspace arena
+ * (which the call resets first).  The caller owns the graph, the feature store, the labels and the
+ * flat parameter buffers; nb_gcn_update applies Adam (Parameter::learnC2G_with_decay_Adam + next,
+ * core/NtsScheduler.hpp:794-811, 700-711) to the gradient that nb_gcn_step left in d_grad, so that a
+ * data-parallel caller can sum d_grad over ranks in between.
+ * ---------------------------------------------------------------------------------------------- */
+#define NB_MAX_LAYERS 8
+typedef struct nb_gcn_config {
+  uint32_t num_layers;                      /* L: number of GCN layers = number of hops            */
+  uint32_t layer_size[NB_MAX_LAYERS + 1];   /* LAYERS a-b-c                                         */
+  int32_t fanout[NB_MAX_LAYERS];            /* hop order, seeds first; negative = all neighbours    */
+  uint32_t num_vertices;
+  float learn_rate, weight_decay, drop_rate, beta1, beta2, epsilon;
+  uint64_t seed;
+  int fuse_gather;                          /* layer 0 aggregates straight from the feature store   */
+  const uint64_t *d_graph_column_offset;    /* whole-graph CSC                                      */
+  const uint32_t *d_graph_row_indices;
+  const float *feat;   size_t feat_ld;      /* feature table (device or mapped pinned host), may be NULL when all rows are cached */
+  const float *d_cache; size_t cache_ld;    /* GPU feature cache and its slot map, or NULL          */
+  const uint32_t *d_hashmap;
+  const int64_t *d_label;                   /* one label per vertex                                 */
+  float *d_W, *d_grad, *d_M, *d_V;          /* flat parameter bucket, sum of layer_size[l]*layer_size[l+1] floats each */
+} nb_gcn_config;
+
+typedef struct nb_gcn_step_info {
+  uint32_t v[NB_MAX_LAYERS], s[NB_MAX_LAYERS], e[NB_MAX_LAYERS];   /* block sizes, index 0 = input side */
+  uint64_t agg_bytes;                        /* algorithmic bytes of the step's aggregation launches */
+} nb_gcn_step_info;
+
+typedef struct nb_gcn nb_gcn;
+int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws);
+int nb_gcn_destroy(nb_gcn *g);
+/* One batch.  d_seeds: n_seeds vertex ids on the device.  train != 0: dropout on, gradient of the
+ * weights left in d_grad; train == 0: forward and loss only.  d_stats[0] = mean loss, d_stats[1] =
+ * number of correct argmax predictions (device).  info (nullable, host) receives the block sizes. */
+int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
+                nb_gcn_step_info *info, void *stream);
+int nb_gcn_update(nb_gcn *g, void *stream);
+/* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
+ * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
+ * algorithmic bytes and the launch count since timing was switched on (or last read). */
+int nb_gcn_set_timing(nb_gcn *g, int enabled);
+int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t *agg_launches);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,27 @@ u64p = C.c_void_p
 i64p = C.c_void_p
 ptr = C.c_void_p
 
+NB_MAX_LAYERS = 8
+
+
+class GcnConfig(C.Structure):
+    """struct nb_gcn_config (include/nb_b200.h)."""
+    _fields_ = [("num_layers", C.c_uint32), ("layer_size", C.c_uint32 * (NB_MAX_LAYERS + 1)),
+                ("fanout", C.c_int32 * NB_MAX_LAYERS), ("num_vertices", C.c_uint32),
+                ("learn_rate", C.c_float), ("weight_decay", C.c_float), ("drop_rate", C.c_float),
+                ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("seed", C.c_uint64),
+                ("fuse_gather", C.c_int), ("d_graph_column_offset", C.c_void_p), ("d_graph_row_indices", C.c_void_p),
+                ("feat", C.c_void_p), ("feat_ld", C.c_size_t), ("d_cache", C.c_void_p), ("cache_ld", C.c_size_t),
+                ("d_hashmap", C.c_void_p), ("d_label", C.c_void_p), ("d_W", C.c_void_p), ("d_grad", C.c_void_p),
+                ("d_M", C.c_void_p), ("d_V", C.c_void_p)]
+
+
+class GcnStepInfo(C.Structure):
+    """struct nb_gcn_step_info (include/nb_b200.h)."""
+    _fields_ = [("v", C.c_uint32 * NB_MAX_LAYERS), ("s", C.c_uint32 * NB_MAX_LAYERS),
+                ("e", C.c_uint32 * NB_MAX_LAYERS), ("agg_bytes", C.c_uint64)]
+
+
 # name -> (restype, argtypes); mirrors include/nb_b200.h one to one.
 SIGNATURES = {
     "nb_last_error": (C.c_char_p, []),
@@ -52,6 +73,12 @@ SIGNATURES = {
     "nb_relu_dropout": (C.c_int, [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, ptr]),
     "nb_softmax_nll": (C.c_int, [ptr, f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
     "nb_softmax_nll_static": (C.c_int, [f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
+    "nb_gcn_create": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(GcnConfig), ptr]),
+    "nb_gcn_destroy": (C.c_int, [ptr]),
+    "nb_gcn_step": (C.c_int, [ptr, u32p, C.c_uint32, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
+    "nb_gcn_update": (C.c_int, [ptr] * 2),
+    "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
+    "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
                           C.c_float, C.c_float, C.c_float, ptr]),
 }

@@ -1,0 +1,244 @@
+// Whole training step issued from native code: the batch-loop body of the reference toolkit
+// (toolkits/GCN_GPU_NEIGHBOR.hpp:604-713) as a sequence of this library's kernels on one stream.
+// No kernels of its own: it exists so that a step costs one host call and no per-step allocations.
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+struct nb_gcn {
+  nb_gcn_config cfg;
+  nb_ws *ws;
+  uint32_t draws;      // sample_one calls so far: part of the Philox counter of the sampler
+  uint32_t steps;      // optimizer steps so far: part of the Philox counter of the dropout mask
+  float beta1_t, beta2_t;
+  size_t w_off[NB_MAX_LAYERS + 1];
+  // optional timing of the aggregation launches with CUDA events on the step's stream
+  bool timing = false;
+  std::vector<cudaEvent_t> ev_pool;   // pairs: start, stop
+  size_t ev_used = 0;
+  uint64_t timed_bytes = 0;
+};
+
+namespace {
+
+struct Block {
+  uint32_t v, s, e;
+  uint32_t *destination, *source, *column_offset, *row_indices, *row_offset, *column_indices;
+  float *src_norm, *dst_norm;
+};
+
+template <typename T>
+int arena(nb_ws *ws, size_t n, T **out) {
+  *out = ws->alloc_n<T>(n ? n : 1);
+  if (!*out) return nb::fail(NB_ERR_NOMEM, "nb_gcn_step: workspace arena exhausted");
+  return 0;
+}
+
+uint64_t bytes_fwd(const Block &b, uint32_t F, bool gather, bool cached) {
+  uint64_t x = 4ull * F * (b.s + b.v) + 4ull * b.e + 4ull * (b.v + 1) + 4ull * (b.s + b.v);
+  if (gather) x += 4ull * b.s + (cached ? 4ull * b.s : 0);
+  return x;
+}
+uint64_t bytes_bwd(const Block &b, uint32_t F) {
+  return 4ull * F * (b.v + b.s) + 4ull * b.e + 4ull * (b.s + 1) + 4ull * (b.s + b.v) + 4ull * F * b.s;
+}
+
+// Brackets one aggregation launch with events when timing is on.
+struct AggTimer {
+  nb_gcn *g;
+  cudaStream_t st;
+  bool on;
+  AggTimer(nb_gcn *g_, void *stream, uint64_t bytes) : g(g_), st(nb::as_stream(stream)), on(g_->timing) {
+    if (!on) return;
+    if (g->ev_used + 2 > g->ev_pool.size()) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { on = false; return; }
+      g->ev_pool.push_back(a);
+      g->ev_pool.push_back(b);
+    }
+    cudaEventRecord(g->ev_pool[g->ev_used], st);
+    g->timed_bytes += bytes;
+  }
+  ~AggTimer() {
+    if (!on) return;
+    cudaEventRecord(g->ev_pool[g->ev_used + 1], st);
+    g->ev_used += 2;
+  }
+};
+
+}  // namespace
+
+NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
+  NB_REQUIRE(out && cfg && ws, "nb_gcn_create: null pointer");
+  NB_REQUIRE(cfg->num_layers >= 1 && cfg->num_layers <= NB_MAX_LAYERS, "nb_gcn_create: 1..8 layers");
+  NB_REQUIRE(cfg->d_graph_column_offset && cfg->d_graph_row_indices && cfg->d_label, "nb_gcn_create: null graph or labels");
+  NB_REQUIRE(cfg->d_W && cfg->d_grad && cfg->d_M && cfg->d_V, "nb_gcn_create: null parameter buffers");
+  NB_REQUIRE(cfg->feat || (cfg->d_cache && cfg->d_hashmap), "nb_gcn_create: no feature store");
+  NB_REQUIRE(cfg->drop_rate >= 0.0f && cfg->drop_rate < 1.0f, "nb_gcn_create: drop rate must be in [0,1)");
+  for (uint32_t l = 0; l <= cfg->num_layers; l++) NB_REQUIRE(cfg->layer_size[l] > 0, "nb_gcn_create: zero layer width");
+  for (uint32_t l = 0; l < cfg->num_layers; l++) NB_REQUIRE(cfg->fanout[l] != 0, "nb_gcn_create: zero fanout");
+  nb_gcn *g = new (std::nothrow) nb_gcn();
+  if (!g) return nb::fail(NB_ERR_NOMEM, "nb_gcn_create: out of host memory");
+  g->cfg = *cfg;
+  g->ws = ws;
+  g->draws = 0;
+  g->steps = 0;
+  g->beta1_t = cfg->beta1;
+  g->beta2_t = cfg->beta2;
+  g->w_off[0] = 0;
+  for (uint32_t l = 0; l < cfg->num_layers; l++)
+    g->w_off[l + 1] = g->w_off[l] + (size_t)cfg->layer_size[l] * cfg->layer_size[l + 1];
+  *out = g;
+  return 0;
+}
+
+NB_API int nb_gcn_destroy(nb_gcn *g) {
+  if (g) for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
+  delete g;
+  return 0;
+}
+
+NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
+  NB_REQUIRE(g != nullptr, "nb_gcn_set_timing: null pointer");
+  g->timing = enabled != 0;
+  g->ev_used = 0;
+  g->timed_bytes = 0;
+  return 0;
+}
+
+NB_API int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t *agg_launches) {
+  NB_REQUIRE(g && agg_ms && agg_bytes && agg_launches, "nb_gcn_read_timing: null pointer");
+  double total = 0.0;
+  for (size_t i = 0; i + 1 < g->ev_used; i += 2) {
+    NB_CUDA(cudaEventSynchronize(g->ev_pool[i + 1]));
+    float ms = 0.0f;
+    NB_CUDA(cudaEventElapsedTime(&ms, g->ev_pool[i], g->ev_pool[i + 1]));
+    total += ms;
+  }
+  *agg_ms = total;
+  *agg_bytes = g->timed_bytes;
+  *agg_launches = g->ev_used / 2;
+  g->ev_used = 0;
+  g->timed_bytes = 0;
+  return 0;
+}
+
+NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
+                       nb_gcn_step_info *info, void *stream) {
+  NB_REQUIRE(g && d_seeds && d_stats, "nb_gcn_step: null pointer");
+  NB_REQUIRE(n_seeds > 0, "nb_gcn_step: empty batch");
+  const nb_gcn_config &c = g->cfg;
+  const uint32_t L = c.num_layers;
+  nb_ws *ws = g->ws;
+  ws->used = 0;   // everything of the previous step is dead; later kernels are stream-ordered after its users
+
+  // ---- sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106)
+  Block hops[NB_MAX_LAYERS];
+  const uint32_t *dst = d_seeds;
+  uint32_t v = n_seeds;
+  for (uint32_t h = 0; h < L; h++) {
+    Block &b = hops[h];
+    b.v = v;
+    b.destination = const_cast<uint32_t *>(dst);
+    NB_TRY(arena(ws, (size_t)v + 1, &b.column_offset));
+    NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
+    NB_TRY(arena(ws, b.e, &b.row_indices));
+    NB_TRY(nb_sample_hop(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, c.fanout[h], b.column_offset, c.seed,
+                         (g->draws << 8) | h, b.row_indices, stream));
+    const size_t cap = b.e < c.num_vertices ? (b.e ? b.e : 1) : c.num_vertices;
+    NB_TRY(arena(ws, cap, &b.source));
+    NB_TRY(arena(ws, cap + 1, &b.row_offset));
+    NB_TRY(arena(ws, b.e, &b.column_indices));
+    NB_TRY(arena(ws, cap, &b.src_norm));
+    NB_TRY(arena(ws, v, &b.dst_norm));
+    NB_TRY(nb_block_build(ws, c.num_vertices, b.row_indices, b.column_offset, v, b.e, b.source, &b.s, b.row_offset,
+                          b.column_indices, b.src_norm, b.dst_norm, nullptr, nullptr, stream));
+    dst = b.source;
+    v = b.s;
+  }
+  g->draws++;
+  Block blk[NB_MAX_LAYERS];   // index 0 = input side (core/ntsSampler.hpp:1088)
+  for (uint32_t l = 0; l < L; l++) blk[l] = hops[L - 1 - l];
+  uint64_t agg_bytes = 0;
+
+  // ---- forward
+  const float p = train ? c.drop_rate : 0.0f;
+  const float scale = p > 0.0f ? 1.0f / (1.0f - p) : 1.0f;
+  float *Y[NB_MAX_LAYERS], *X[NB_MAX_LAYERS + 1];
+  X[0] = nullptr;
+  for (uint32_t l = 0; l < L; l++) {
+    const Block &b = blk[l];
+    const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
+    NB_TRY(arena(ws, (size_t)b.v * Fi, &Y[l]));
+    if (l == 0) {
+      if (c.fuse_gather) {
+        AggTimer t(g, stream, bytes_fwd(b, Fi, true, c.d_hashmap != nullptr));
+        NB_TRY(nb_spmm_csc_fwd_gather_fused(ws, c.feat, c.feat_ld, c.d_cache, c.cache_ld, c.d_hashmap, b.source, Y[0],
+                                            b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, b.s, b.e, Fi,
+                                            stream));
+        agg_bytes += bytes_fwd(b, Fi, true, c.d_hashmap != nullptr);
+      } else {
+        NB_TRY(arena(ws, (size_t)b.s * Fi, &X[0]));
+        NB_TRY(nb_feature_gather(X[0], c.feat, c.feat_ld, nullptr, 0, 0, c.d_cache, c.cache_ld, c.d_hashmap, b.source,
+                                 b.s, Fi, stream));
+        AggTimer t(g, stream, bytes_fwd(b, Fi, false, false));
+        NB_TRY(nb_spmm_csc_fwd_fused(X[0], Y[0], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi,
+                                     stream));
+        agg_bytes += bytes_fwd(b, Fi, false, false);
+      }
+    } else {
+      AggTimer t(g, stream, bytes_fwd(b, Fi, false, false));
+      NB_TRY(nb_spmm_csc_fwd_fused(X[l], Y[l], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi, stream));
+      agg_bytes += bytes_fwd(b, Fi, false, false);
+    }
+    NB_TRY(arena(ws, (size_t)b.v * Fo, &X[l + 1]));
+    NB_TRY(nb_gemm(ws, Y[l], c.d_W + g->w_off[l], X[l + 1], b.v, Fo, Fi, 0, 0, stream));
+    if (l + 1 < L) NB_TRY(nb_relu_dropout(X[l + 1], (int64_t)b.v * Fo, p, c.seed, l, g->steps, stream));
+  }
+
+  // ---- loss (utils/torch_func.hpp:67-82)
+  const Block &last = blk[L - 1];
+  const int64_t B = last.v, C = c.layer_size[L];
+  int64_t *lab;
+  NB_TRY(arena(ws, (size_t)B, &lab));
+  NB_TRY(nb_label_gather(lab, c.d_label, last.destination, last.v, 1, stream));
+  float *dZ = nullptr;
+  if (train) NB_TRY(arena(ws, (size_t)(B * C), &dZ));
+  NB_TRY(nb_softmax_nll(ws, X[L], lab, B, C, dZ, d_stats, stream));
+
+  // ---- backward: dW_l = Y_l^T dZ_l; dY_l = dZ_l W_l^T; dZ_{l-1} = (A_l^T dY_l) masked by X_l > 0
+  if (train) {
+    for (int l = (int)L - 1; l >= 0; l--) {
+      const Block &b = blk[l];
+      const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
+      NB_TRY(nb_gemm(ws, Y[l], dZ, c.d_grad + g->w_off[l], Fi, Fo, b.v, 1, 0, stream));
+      if (l == 0) break;   // the input-side block is never back-propagated (core/ntsContext.hpp:292)
+      float *dY, *dX;
+      NB_TRY(arena(ws, (size_t)b.v * Fi, &dY));
+      NB_TRY(nb_gemm(ws, dZ, c.d_W + g->w_off[l], dY, b.v, Fi, Fo, 0, 1, stream));
+      NB_TRY(arena(ws, (size_t)b.s * Fi, &dX));
+      AggTimer t(g, stream, bytes_bwd(b, Fi));
+      NB_TRY(nb_spmm_csr_bwd_fused(dY, dX, b.row_offset, b.column_indices, b.src_norm, b.dst_norm, X[l], scale, b.s, Fi,
+                                   stream));
+      agg_bytes += bytes_bwd(b, Fi);
+      dZ = dX;
+    }
+  }
+  if (info) {
+    for (uint32_t l = 0; l < L; l++) { info->v[l] = blk[l].v; info->s[l] = blk[l].s; info->e[l] = blk[l].e; }
+    info->agg_bytes = agg_bytes;
+  }
+  return 0;
+}
+
+NB_API int nb_gcn_update(nb_gcn *g, void *stream) {
+  NB_REQUIRE(g != nullptr, "nb_gcn_update: null pointer");
+  const nb_gcn_config &c = g->cfg;
+  NB_TRY(nb_adam(c.d_W, c.d_grad, c.d_M, c.d_V, (int64_t)g->w_off[c.num_layers], c.learn_rate, c.beta1, c.beta2,
+                 c.epsilon, c.weight_decay, g->beta1_t, g->beta2_t, stream));
+  g->beta1_t *= c.beta1;   // Parameter::next (core/NtsScheduler.hpp:700-711)
+  g->beta2_t *= c.beta2;
+  g->steps++;
+  return 0;
+}

@@ -226,22 +226,26 @@ class Sampler:
         self._pinned_seeds[:n].copy_(torch.from_numpy(seeds.view(np.int32)))
         return self._pinned_seeds[:n].to(self.whole_graph.device, non_blocking=True)
 
+    def next_seeds(self):
+        """Seeds of the next batch as a device tensor, and their number; advances work_offset
+        (the last batch of an epoch is short, core/ntsSampler.hpp:846)."""
+        assert self.work_offset < self.work_range[1]
+        actl = min(self.batch_size, self.work_range[1] - self.work_offset)
+        lo = self.work_offset
+        self.work_offset += actl
+        if self._dev_nids is not None:
+            return self._dev_nids[lo: lo + actl], actl
+        return self._seeds_to_device(self.sample_nids[lo: lo + actl]), actl
+
     def sample_one(self, ssg: Optional[SampledSubgraph] = None, raw_edges: Optional[list] = None) -> SampledSubgraph:
         """One batch: per hop, column offsets, sampling, dedup/reindex, CSR, weights
         (core/ntsSampler.hpp:843-1106).  ``raw_edges`` (list per hop of device int32 tensors of global
         source ids laid out by the hop's column offsets) replaces the Philox sampler with an externally
         supplied edge list — the form in which parity with the reference is defined."""
         ssg = self.subgraph if ssg is None else ssg
-        assert self.work_offset < self.work_range[1]
-        actl = min(self.batch_size, self.work_range[1] - self.work_offset)
-        seeds = self.sample_nids[self.work_offset: self.work_offset + actl]
-        self.work_offset += actl
+        dst, actl = self.next_seeds()
         g = self.whole_graph
         stream = torch.cuda.current_stream().cuda_stream
-        if self._dev_nids is not None:
-            dst = self._dev_nids[self.work_offset - actl: self.work_offset]
-        else:
-            dst = self._seeds_to_device(seeds)
         v = actl
         blocks = []
         for hop in range(self.layers):

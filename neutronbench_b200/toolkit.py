@@ -111,7 +111,7 @@ class GCN_GPU_NEIGHBOR_impl:
     """Trainer with the reference toolkit's structure (init_nn / Forward / Update / run)."""
 
     def __init__(self, graph: FullyRepGraph, datum: GNNDatum, cfg: GCNConfig, ws: Optional[Workspace] = None,
-                 rank: int = 0, world_size: int = 1):
+                 rank: int = 0, world_size: int = 1, use_engine: bool = True):
         self.graph = graph
         self.datum = datum
         self.cfg = cfg
@@ -133,6 +133,12 @@ class GCN_GPU_NEIGHBOR_impl:
         self.agg_edges_fwd = 0
         self.agg_edges_bwd = 0
         self.events = None  # when a list: (name, algorithmic bytes, start event, end event) per aggregation
+        # use_engine: a batch is one native call (nb_gcn_step) instead of one Python call per kernel family;
+        # both issue the same kernels in the same order and give identical results.
+        self.use_engine = use_engine
+        self._engine = None
+        self._engine_cfg = None
+        self.last_info = None
 
     def _timed(self, name: str, nbytes: int, fn):
         """Runs fn(); with self.events set, brackets it with CUDA events on the current stream."""
@@ -258,10 +264,59 @@ class GCN_GPU_NEIGHBOR_impl:
             self.agg_edges_bwd += blk.e_size
             dZ = dX
 
+    # ------------------------------------------------------------------ native step (nb_gcn_*)
+    def _ensure_engine(self):
+        if self._engine is not None:
+            return self._engine
+        import ctypes as C
+        c = self.cfg
+        ec = _lib.GcnConfig()
+        ec.num_layers = self.layers
+        for i, w in enumerate(c.layers):
+            ec.layer_size[i] = int(w)
+        for i, f in enumerate(c.fanout):
+            ec.fanout[i] = int(f)
+        ec.num_vertices = self.graph.global_vertices
+        ec.learn_rate, ec.weight_decay, ec.drop_rate = c.learn_rate, c.weight_decay, c.drop_rate
+        ec.beta1, ec.beta2, ec.epsilon = c.beta1, c.beta2, c.epsilon
+        ec.seed = c.seed
+        ec.fuse_gather = 1 if c.fuse_gather else 0
+        ec.d_graph_column_offset = ptr(self.graph.column_offset)
+        ec.d_graph_row_indices = ptr(self.graph.row_indices)
+        feat = self.datum.local_feature
+        ec.feat, ec.feat_ld = ptr(feat), feat.stride(0)
+        if self.dev_cache_feature is not None:
+            ec.d_cache, ec.cache_ld = ptr(self.dev_cache_feature), self.dev_cache_feature.stride(0)
+            ec.d_hashmap = ptr(self.dev_cache_node_hashmap)
+        ec.d_label = ptr(self.datum.local_label)
+        ec.d_W, ec.d_grad, ec.d_M, ec.d_V = ptr(self.P.W), ptr(self.P.grad), ptr(self.P.M), ptr(self.P.V)
+        handle = C.c_void_p()
+        _lib.call("nb_gcn_create", C.byref(handle), C.byref(ec), self.ws.handle)
+        self._engine, self._engine_cfg = handle, ec
+        return handle
+
+    def engine_step(self, sampler: Sampler, train: bool = True):
+        """One batch through nb_gcn_step; leaves loss/hits in self.stats and dW in P.grad."""
+        import ctypes as C
+        eng = self._ensure_engine()
+        seeds, n = sampler.next_seeds()
+        info = _lib.GcnStepInfo()
+        _lib.call("nb_gcn_step", eng, ptr(seeds), n, 1 if train else 0, ptr(self.stats), C.byref(info),
+                  torch.cuda.current_stream().cuda_stream)
+        L = self.layers
+        self.agg_edges_fwd += sum(info.e[l] for l in range(L))
+        if train:
+            self.agg_edges_bwd += sum(info.e[l] for l in range(1, L))
+        self.last_info = info
+        return info
+
     def Update(self):
         """Gradient SUM over ranks (MPI_SUM in the reference, comm/network.h:189-193) then Adam."""
         sum_gradients(self.P.grad, self.world_size)
-        self.P.learn_with_decay_Adam(torch.cuda.current_stream().cuda_stream)
+        if self.use_engine:
+            _lib.call("nb_gcn_update", self._ensure_engine(), torch.cuda.current_stream().cuda_stream)
+        else:
+            self.P.learn_with_decay_Adam(torch.cuda.current_stream().cuda_stream)
 
     def UpdateZero(self):
         """A rank that ran out of batches still joins the collective with zeros
@@ -270,8 +325,10 @@ class GCN_GPU_NEIGHBOR_impl:
         self.Update()
 
     def train_step(self, sampler: Sampler):
-        ssg = sampler.sample_one()
-        self.forward_backward(ssg, train=True)
+        if self.use_engine:
+            self.engine_step(sampler, train=True)
+        else:
+            self.forward_backward(sampler.sample_one(), train=True)
         self.Update()
         self.step_count += 1
 
@@ -293,15 +350,20 @@ class GCN_GPU_NEIGHBOR_impl:
         while sampler.sample_not_finished():
             if max_batches is not None and batches >= max_batches:
                 break
-            ssg = sampler.sample_one()
-            self.forward_backward(ssg, train=train)
+            if self.use_engine:
+                info = self.engine_step(sampler, train=train)
+                batch_nodes = info.v[self.layers - 1]
+            else:
+                ssg = sampler.sample_one()
+                self.forward_backward(ssg, train=train)
+                batch_nodes = ssg.sampled_sgs[self.layers - 1].v_size
             if train:
                 self.Update()
                 self.step_count += 1
             loss, hits = self.read_stats()
             loss_epoch += loss
             correct += hits
-            nodes += ssg.sampled_sgs[self.layers - 1].v_size
+            nodes += batch_nodes
             batches += 1
         sampler.restart()
         return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
@@ -346,4 +408,12 @@ def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
     block = 8 * words + 16 * min(num_vertices, e_max) + 8 * e_max
     widest = max(cfg.layers[i] * cfg.layers[i + 1] for i in range(len(cfg.layers) - 1))
     splitk = 4 * widest * 320
-    return int(block + splitk + (64 << 20))
+    # per-step activations and gradients when a whole step lives in the arena (nb_gcn_step)
+    v, acts = cfg.batch_size, 0
+    for i, f in enumerate(cfg.fanout):
+        layer = len(cfg.fanout) - 1 - i                      # hop i feeds GCN layer L-1-i
+        width = max(cfg.layers[layer], cfg.layers[layer + 1])
+        acts += 6 * 4 * v * width
+        v = min(num_vertices, v * (f if f > 0 else 64))
+    acts += 4 * v * cfg.layers[0]                            # gathered input rows when the gather is not fused
+    return int(block + splitk + acts + (64 << 20))

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _setup(cuda_device, V=4000, E=60000, F=100, hidden=32, classes=7, fanout=(10, 5), batch=256, drop=0.5,
-           cache_rate=0.0, fuse=True, layers=None):
+           cache_rate=0.0, fuse=True, layers=None, use_engine=True):
     edges, co, ri = small_graph(V, E, seed=6)
     rng = np.random.RandomState(0)
     feat = rng.randn(V, F).astype(np.float32)
@@ -26,7 +26,7 @@ def _setup(cuda_device, V=4000, E=60000, F=100, hidden=32, classes=7, fanout=(10
     g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
     datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device),
                      np.zeros(V, np.int32))
-    tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg)
+    tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg, use_engine=use_engine)
     tk.init_cache()
     ref = oracle.GCN(sizes, tk.P.W.cpu().numpy(), cfg.learn_rate, cfg.weight_decay, drop, cfg.seed)
     return edges, co, ri, feat, label, cfg, g, tk, ref
@@ -34,10 +34,11 @@ def _setup(cuda_device, V=4000, E=60000, F=100, hidden=32, classes=7, fanout=(10
 
 @pytest.mark.parametrize("fanout,drop,cache_rate,fuse", [((10, 5), 0.5, 0.0, True), ((10, 5), 0.0, 0.3, True),
                                                          ((5, 4, 3), 0.5, 1.0, False), ((5, 4, 3), 0.2, 0.0, True)])
-def test_loss_curve_matches_oracle_over_5_epochs(cuda_device, fanout, drop, cache_rate, fuse):
+@pytest.mark.parametrize("use_engine", [True, False], ids=["native_step", "python_step"])
+def test_loss_curve_matches_oracle_over_5_epochs(cuda_device, fanout, drop, cache_rate, fuse, use_engine):
     V = 4000
     edges, co, ri, feat, label, cfg, g, tk, ref = _setup(cuda_device, V=V, fanout=fanout, drop=drop,
-                                                         cache_rate=cache_rate, fuse=fuse)
+                                                         cache_rate=cache_rate, fuse=fuse, use_engine=use_engine)
     train_ids = np.arange(0, 1200, dtype=np.uint32)
     smp = Sampler(g, train_ids, fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
     rng_gpu, rng_cpu = np.random.RandomState(2000), np.random.RandomState(2000)
@@ -94,3 +95,20 @@ def test_eval_forward_has_no_side_effects(cuda_device):
     acc, loss, batches = tk.Forward(smp, train=False)
     assert batches == 1 and np.isfinite(loss) and 0.0 <= acc <= 1.0
     assert torch.equal(w0, tk.P.W)
+
+
+def test_native_step_and_python_step_are_the_same_computation(cuda_device):
+    """nb_gcn_step issues the kernels the Python mirror issues, in the same order: after three
+    optimizer steps the weights are identical bit for bit."""
+    outs = []
+    for use_engine in (True, False):
+        edges, co, ri, feat, label, cfg, g, tk, ref = _setup(cuda_device, fanout=(5, 4, 3), drop=0.3, cache_rate=0.4,
+                                                             use_engine=use_engine)
+        smp = Sampler(g, np.arange(700, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                      with_edge_weights=False)
+        for _ in range(3):
+            tk.train_step(smp)
+        loss, hits = tk.read_stats()
+        outs.append((tk.P.W.cpu().numpy().copy(), loss, hits))
+    np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
+    assert outs[0][1] == outs[1][1] and outs[0][2] == outs[1][2]
