@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-gather", action="store_true")
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
+    ap.add_argument("--pipelines", type=int, default=2,
+                    help="PIPELINES of the reference's cfg: 2 = sample batch i+1 while batch i trains, 1 = plain loop")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
 
@@ -272,7 +274,10 @@ def main():
         "l2_policy": "inputs larger than L2 (feature store >> 126 MB, each step touches a new random subset)",
         "parallelism": f"dp{world}",
         "fuse_gather": cfg.fuse_gather,
-        "step": "python (one call per kernel family)" if args.python_step else "native (nb_gcn_step)",
+        "step": "python (one call per kernel family)" if args.python_step else
+                ("native (nb_gcn_sample on a second stream overlapping nb_gcn_compute)" if args.pipelines > 1
+                 else "native (nb_gcn_step)"),
+        "pipelines": 1 if args.python_step else max(1, args.pipelines),
     }
 
     if args.impl == "reference":
@@ -289,6 +294,7 @@ def main():
         print(json.dumps(line))
         return 0
 
+    cfg.pipelines = 1 if args.python_step else max(1, args.pipelines)
     tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world, use_engine=not args.python_step)
     tk.init_cache()
     del feat_dev
@@ -315,10 +321,17 @@ def main():
         clocks = ClockSampler(local_rank)
         if rank == 0 and record_events:
             clocks.start()           # nvidia-smi needs ~0.1 s to produce its first sample: start before warm-up
-        for _ in range(W):
-            tk.train_step(smp)
-            if not staged:
-                tk.read_stats()
+        def steps(n):
+            if cfg.pipelines > 1:
+                done = tk.run_pipelined(smp, max_batches=n, train=True, read_back=not staged)[3]
+                assert done == n
+                return
+            for _ in range(n):
+                tk.train_step(smp)
+                if not staged:
+                    tk.read_stats()
+
+        steps(W)
         barrier()
         tk.agg_edges_fwd = tk.agg_edges_bwd = 0
         tk.events = [] if (record_events and not tk.use_engine) else None
@@ -328,10 +341,7 @@ def main():
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
-        for _ in range(K):
-            tk.train_step(smp)
-            if not staged:
-                tk.read_stats()
+        steps(K)
         t1.record()
         barrier()
         ms = t0.elapsed_time(t1)

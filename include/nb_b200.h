@@ -215,8 +215,9 @@ int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t fea
  * nb_gemm: C[M x N] = op(A) * op(B).  trans_a = 0: A is M x K row-major; 1: A is K x M (A^T used).
  *          trans_b likewise for B (K x N, or N x K when 1).  Supported: NN, TN, NT.
  *          nb_set_gemm_mode selects the arithmetic: 0 = CUDA cores (fp32 FMA), 1 = tcgen05 tensor cores
- *          with a three-term TF32 split (fp32-level accuracy), 2 = tcgen05 plain TF32.  Returns the
- *          previous mode.
+ *          with a three-term TF32 split (fp32-level accuracy), 2 = tcgen05 plain TF32.  Products below
+ *          about 40 MFLOP run on the CUDA cores in every mode (faster there); 17 / 18 are modes 1 / 2
+ *          with that shortcut off.  Returns the previous mode.
  * nb_relu_dropout: z = dropout(relu(z)) in place; keeps element i when the Philox word
  *          (counter (i/4, layer, step, 1), key seed) mapped to [0,1) is >= p, scaling by 1/(1-p).
  * nb_softmax_nll: mean negative log-likelihood of log_softmax(logits) at `label`, its gradient
@@ -292,6 +293,23 @@ int nb_gcn_destroy(nb_gcn *g);
 int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
                 nb_gcn_step_info *info, void *stream);
 int nb_gcn_update(nb_gcn *g, void *stream);
+/* The same step in two halves, so that sampling batch i+1 overlaps the training of batch i — the
+ * reference's pipelined batch loop (pipeline_version, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, where each
+ * pipeline thread owns its SampledSubgraph and three streams).  A nb_gcn_batch is one SampledSubgraph
+ * whose arrays live in a workspace of its own (not the model's).
+ *   nb_gcn_sample  draws the batch on `stream` (d_seeds: device or pinned host memory, copied into the
+ *                  batch); it synchronises that stream for the block sizes, and first waits for the
+ *                  compute call that last used this batch.
+ *   nb_gcn_compute makes `stream` wait for the batch's sampling, then runs forward, loss and backward
+ *                  exactly as nb_gcn_step; it never blocks the host.
+ * Batches must be sampled in the order they are trained on (the sampler stream position advances per
+ * nb_gcn_sample); results are bit-identical to nb_gcn_step on the same sequence of batches. */
+typedef struct nb_gcn_batch nb_gcn_batch;
+int nb_gcn_batch_create(nb_gcn_batch **out, nb_ws *ws);
+int nb_gcn_batch_destroy(nb_gcn_batch *batch);
+int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
+int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
+                   void *stream);
 /* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
  * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
  * algorithmic bytes and the launch count since timing was switched on (or last read). */

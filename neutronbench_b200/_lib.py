@@ -77,6 +77,10 @@ SIGNATURES = {
     "nb_gcn_destroy": (C.c_int, [ptr]),
     "nb_gcn_step": (C.c_int, [ptr, u32p, C.c_uint32, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_update": (C.c_int, [ptr] * 2),
+    "nb_gcn_batch_create": (C.c_int, [C.POINTER(C.c_void_p), ptr]),
+    "nb_gcn_batch_destroy": (C.c_int, [ptr]),
+    "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
+    "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,

@@ -7,6 +7,7 @@
 namespace nb {
 
 int g_gemm_mode = 1;   // tcgen05 with the three-term TF32 split
+int g_gemm_force_tc = 0;   // 1: send even tiny products to the tensor-core kernel (tests)
 
 // ------------------------------------------------------------------------------------ GEMM (SIMT)
 // C[M x N] = op(A) op(B), element access through strides so that NN / TN / NT share one kernel.
@@ -192,7 +193,11 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
     NB_CUDA(cudaMemsetAsync(d_c, 0, (size_t)(M * N) * sizeof(float), stream));
     return 0;
   }
-  if (g_gemm_mode != 0) return gemm_tensor_core(ws, d_a, d_b, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
+  // Small products (the output layer and its gradients) finish sooner on the CUDA cores than the
+  // tensor-core kernel takes to set up its pipeline (TMEM allocation, 200 KB of staging buffers).
+  const bool tiny = 2.0 * (double)M * (double)N * (double)K < 4.0e7 && g_gemm_force_tc == 0;
+  if (g_gemm_mode != 0 && !tiny)
+    return gemm_tensor_core(ws, d_a, d_b, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
   GemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
   g.sa_i = trans_a ? 1 : K;  g.sa_k = trans_a ? M : 1;
@@ -230,7 +235,8 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
 
 NB_API int nb_set_gemm_mode(int mode) {
   const int old = g_gemm_mode;
-  if (mode >= 0 && mode <= 2) g_gemm_mode = mode;
+  if (mode >= 0 && mode <= 2) { g_gemm_mode = mode; g_gemm_force_tc = 0; }
+  if (mode >= 16 && mode <= 18) { g_gemm_mode = mode - 16; g_gemm_force_tc = 1; }   // 17 / 18: tensor cores for every size
   return old;
 }
 

@@ -6,9 +6,26 @@
 
 #include "common.cuh"
 
+struct BlockArrays {
+  uint32_t v, s, e;
+  uint32_t *destination, *source, *column_offset, *row_indices, *row_offset, *column_indices;
+  float *src_norm, *dst_norm;
+};
+
+// One sampled subgraph (SampledSubgraph, core/ntsSampler.hpp:843-1106): its arrays live in the arena of `ws`.
+struct nb_gcn_batch {
+  nb_ws *ws = nullptr;
+  uint32_t layers = 0;
+  BlockArrays blk[NB_MAX_LAYERS];   // index 0 = input side (core/ntsSampler.hpp:1088)
+  cudaEvent_t sampled = nullptr;    // recorded when the last sampling kernel is enqueued
+  cudaEvent_t consumed = nullptr;   // recorded after the last kernel that reads the arrays
+  bool in_use = false;              // a compute call has been enqueued since the last sample call
+};
+
 struct nb_gcn {
   nb_gcn_config cfg;
   nb_ws *ws;
+  nb_gcn_batch own;    // the batch nb_gcn_step samples into: shares `ws` with the activations
   uint32_t draws;      // sample_one calls so far: part of the Philox counter of the sampler
   uint32_t steps;      // optimizer steps so far: part of the Philox counter of the dropout mask
   float beta1_t, beta2_t;
@@ -22,11 +39,7 @@ struct nb_gcn {
 
 namespace {
 
-struct Block {
-  uint32_t v, s, e;
-  uint32_t *destination, *source, *column_offset, *row_indices, *row_offset, *column_indices;
-  float *src_norm, *dst_norm;
-};
+using Block = BlockArrays;
 
 template <typename T>
 int arena(nb_ws *ws, size_t n, T **out) {
@@ -82,6 +95,7 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   if (!g) return nb::fail(NB_ERR_NOMEM, "nb_gcn_create: out of host memory");
   g->cfg = *cfg;
   g->ws = ws;
+  g->own.ws = ws;
   g->draws = 0;
   g->steps = 0;
   g->beta1_t = cfg->beta1;
@@ -94,7 +108,11 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
 }
 
 NB_API int nb_gcn_destroy(nb_gcn *g) {
-  if (g) for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
+  if (g) {
+    for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
+    if (g->own.sampled) cudaEventDestroy(g->own.sampled);
+    if (g->own.consumed) cudaEventDestroy(g->own.consumed);
+  }
   delete g;
   return 0;
 }
@@ -124,18 +142,31 @@ NB_API int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, ui
   return 0;
 }
 
-NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
-                       nb_gcn_step_info *info, void *stream) {
-  NB_REQUIRE(g && d_seeds && d_stats, "nb_gcn_step: null pointer");
-  NB_REQUIRE(n_seeds > 0, "nb_gcn_step: empty batch");
+namespace {
+
+int ensure_events(nb_gcn_batch *bt) {
+  if (!bt->sampled) NB_CUDA(cudaEventCreateWithFlags(&bt->sampled, cudaEventDisableTiming));
+  if (!bt->consumed) NB_CUDA(cudaEventCreateWithFlags(&bt->consumed, cudaEventDisableTiming));
+  return 0;
+}
+
+// sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106).
+int sample_into(nb_gcn *g, nb_gcn_batch *bt, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
   const nb_gcn_config &c = g->cfg;
   const uint32_t L = c.num_layers;
-  nb_ws *ws = g->ws;
-  ws->used = 0;   // everything of the previous step is dead; later kernels are stream-ordered after its users
-
-  // ---- sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106)
+  nb_ws *ws = bt->ws;
+  NB_TRY(ensure_events(bt));
+  if (bt->in_use) {   // the arrays of the batch sampled here before may still be read by a compute call
+    NB_CUDA(cudaEventSynchronize(bt->consumed));
+    bt->in_use = false;
+  }
+  ws->used = 0;
+  // The batch keeps its own copy of the seeds: the caller may reuse its buffer for the next batch at once.
+  uint32_t *seeds;
+  NB_TRY(arena(ws, n_seeds, &seeds));
+  NB_CUDA(cudaMemcpyAsync(seeds, d_seeds, 4ull * n_seeds, cudaMemcpyDefault, nb::as_stream(stream)));
   Block hops[NB_MAX_LAYERS];
-  const uint32_t *dst = d_seeds;
+  const uint32_t *dst = seeds;
   uint32_t v = n_seeds;
   for (uint32_t h = 0; h < L; h++) {
     Block &b = hops[h];
@@ -158,8 +189,22 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
     v = b.s;
   }
   g->draws++;
-  Block blk[NB_MAX_LAYERS];   // index 0 = input side (core/ntsSampler.hpp:1088)
-  for (uint32_t l = 0; l < L; l++) blk[l] = hops[L - 1 - l];
+  bt->layers = L;
+  for (uint32_t l = 0; l < L; l++) bt->blk[l] = hops[L - 1 - l];
+  NB_CUDA(cudaEventRecord(bt->sampled, nb::as_stream(stream)));
+  return 0;
+}
+
+int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_step_info *info, void *stream) {
+  const nb_gcn_config &c = g->cfg;
+  const uint32_t L = c.num_layers;
+  NB_REQUIRE(bt->layers == L && bt->sampled, "nb_gcn_compute: the batch holds no sampled subgraph of this model");
+  nb_ws *ws = g->ws;
+  if (bt->ws != ws) {
+    ws->used = 0;   // activations of the previous step are dead; later kernels are stream-ordered after its users
+    NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), bt->sampled, 0));
+  }
+  const Block *blk = bt->blk;
   uint64_t agg_bytes = 0;
 
   // ---- forward
@@ -229,7 +274,51 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
     for (uint32_t l = 0; l < L; l++) { info->v[l] = blk[l].v; info->s[l] = blk[l].s; info->e[l] = blk[l].e; }
     info->agg_bytes = agg_bytes;
   }
+  NB_CUDA(cudaEventRecord(bt->consumed, nb::as_stream(stream)));
+  bt->in_use = true;
   return 0;
+}
+
+}  // namespace
+
+NB_API int nb_gcn_batch_create(nb_gcn_batch **out, nb_ws *ws) {
+  NB_REQUIRE(out && ws, "nb_gcn_batch_create: null pointer");
+  nb_gcn_batch *bt = new (std::nothrow) nb_gcn_batch();
+  if (!bt) return nb::fail(NB_ERR_NOMEM, "nb_gcn_batch_create: out of host memory");
+  bt->ws = ws;
+  *out = bt;
+  return 0;
+}
+
+NB_API int nb_gcn_batch_destroy(nb_gcn_batch *bt) {
+  if (bt) {
+    if (bt->sampled) cudaEventDestroy(bt->sampled);
+    if (bt->consumed) cudaEventDestroy(bt->consumed);
+  }
+  delete bt;
+  return 0;
+}
+
+NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
+  NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample: null pointer");
+  NB_REQUIRE(n_seeds > 0, "nb_gcn_sample: empty batch");
+  NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample: a batch needs a workspace of its own, not the model's");
+  return sample_into(g, batch, d_seeds, n_seeds, stream);
+}
+
+NB_API int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
+                          void *stream) {
+  NB_REQUIRE(g && batch && d_stats, "nb_gcn_compute: null pointer");
+  return compute_from(g, batch, train, d_stats, info, stream);
+}
+
+NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
+                       nb_gcn_step_info *info, void *stream) {
+  NB_REQUIRE(g && d_seeds && d_stats, "nb_gcn_step: null pointer");
+  NB_REQUIRE(n_seeds > 0, "nb_gcn_step: empty batch");
+  g->own.in_use = false;   // same stream and same arena: stream order alone protects the arrays
+  NB_TRY(sample_into(g, &g->own, d_seeds, n_seeds, stream));
+  return compute_from(g, &g->own, train, d_stats, info, stream);
 }
 
 NB_API int nb_gcn_update(nb_gcn *g, void *stream) {

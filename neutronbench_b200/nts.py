@@ -201,7 +201,7 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     cfg = GCNConfig(layers=layers, fanout=info.fanout_hop_order(), val_fanout=info.val_fanout_hop_order(),
                     batch_size=info.batch_size, learn_rate=info.learn_rate, weight_decay=info.weight_decay,
                     drop_rate=info.drop_rate, cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate,
-                    cache_policy=info.cache_policy or "degree")
+                    cache_policy=info.cache_policy or "degree", pipelines=max(1, int(info.pipelines)))
     feature = torch.from_numpy(feat)
     feature = feature.to(dev) if cache_rate >= 1.0 else feature.pin_memory()
     datum = GNNDatum(feature, torch.from_numpy(label).to(dev), mask)

@@ -41,6 +41,7 @@ class GCNConfig:
     beta1: float = 0.9
     beta2: float = 0.999
     epsilon: float = 1e-9                         # toolkits/GCN_GPU_NEIGHBOR.hpp:217
+    pipelines: int = 1                            # PIPELINES > 1: sampling of batch i+1 overlaps training of batch i
 
 
 class Parameter:
@@ -139,6 +140,11 @@ class GCN_GPU_NEIGHBOR_impl:
         self._engine = None
         self._engine_cfg = None
         self.last_info = None
+        # pipelined batch loop (pipeline_version, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505): two sampled
+        # subgraphs in flight, sampling on a stream of its own
+        self._batches = None
+        self._batch_ws = None
+        self._sample_stream = None
 
     def _timed(self, name: str, nbytes: int, fn):
         """Runs fn(); with self.events set, brackets it with CUDA events on the current stream."""
@@ -310,6 +316,78 @@ class GCN_GPU_NEIGHBOR_impl:
         self.last_info = info
         return info
 
+    # ------------------------------------------------------------------ pipelined halves of the native step
+    def _ensure_pipeline(self):
+        if self._batches is not None:
+            return
+        import ctypes as C
+        self._sample_stream = torch.cuda.Stream(device=self.device)
+        self._batch_ws = [Workspace(default_workspace_bytes(self.graph.global_vertices, self.cfg)) for _ in range(2)]
+        self._batches = []
+        for w in self._batch_ws:
+            h = C.c_void_p()
+            _lib.call("nb_gcn_batch_create", C.byref(h), w.handle)
+            self._batches.append(h)
+
+    def sample_batch(self, sampler: Sampler, slot: int):
+        """nb_gcn_sample of the sampler's next batch into subgraph `slot`, on the sampling stream."""
+        self._ensure_pipeline()
+        with torch.cuda.stream(self._sample_stream):
+            seeds, n = sampler.next_seeds()
+            _lib.call("nb_gcn_sample", self._ensure_engine(), self._batches[slot], ptr(seeds), n,
+                      self._sample_stream.cuda_stream)
+        return n
+
+    def compute_batch(self, slot: int, train: bool = True):
+        """nb_gcn_compute on subgraph `slot`, on the current stream; never blocks the host."""
+        import ctypes as C
+        info = _lib.GcnStepInfo()
+        _lib.call("nb_gcn_compute", self._ensure_engine(), self._batches[slot], 1 if train else 0, ptr(self.stats),
+                  C.byref(info), torch.cuda.current_stream().cuda_stream)
+        L = self.layers
+        self.agg_edges_fwd += sum(info.e[l] for l in range(L))
+        if train:
+            self.agg_edges_bwd += sum(info.e[l] for l in range(1, L))
+        self.last_info = info
+        return info
+
+    def run_pipelined(self, sampler: Sampler, max_batches: Optional[int] = None, train: bool = True,
+                      on_batch=None, read_back: bool = True):
+        """Batch loop with the next batch's sampling issued while the current batch trains.  The order of
+        batches, sampler draws and optimizer steps is that of the plain loop, so results are identical.
+        Returns (correct, nodes, loss sum, batches); with read_back False no statistics are read."""
+        assert self.use_engine, "the pipelined loop runs on the native step"
+        correct = nodes = batches = 0
+        loss_sum = 0.0
+        if not sampler.sample_not_finished() or (max_batches is not None and max_batches <= 0):
+            return correct, nodes, loss_sum, batches
+        self.sample_batch(sampler, 0)
+        slot = 0
+        while True:
+            info = self.compute_batch(slot, train=train)
+            if train:
+                self.Update()
+                self.step_count += 1
+            if read_back:   # asynchronous copy now, read after the next batch has been sampled
+                self._stats_host.copy_(self.stats, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record()
+            batches += 1
+            more = sampler.sample_not_finished() and (max_batches is None or batches < max_batches)
+            if more:
+                self.sample_batch(sampler, slot ^ 1)
+            if read_back:
+                done.synchronize()
+                loss_sum += float(self._stats_host[0])
+                correct += int(self._stats_host[1])
+            nodes += info.v[self.layers - 1]
+            if on_batch is not None:
+                on_batch(batches)
+            if not more:
+                break
+            slot ^= 1
+        return correct, nodes, loss_sum, batches
+
     def Update(self):
         """Gradient SUM over ranks (MPI_SUM in the reference, comm/network.h:189-193) then Adam."""
         sum_gradients(self.P.grad, self.world_size)
@@ -345,12 +423,19 @@ class GCN_GPU_NEIGHBOR_impl:
         toolkits/GCN_GPU_NEIGHBOR.hpp:604-800).  Returns (accuracy, mean loss, batches)."""
         if rng is not None:
             sampler.shuffle(rng)
+        # the native step samples with the training fan-out and sizes its arenas for the training batch
+        native = (self.use_engine and list(sampler.fanout) == list(self.cfg.fanout)
+                  and sampler.batch_size <= self.cfg.batch_size)
+        if native and self.cfg.pipelines > 1:
+            correct, nodes, loss_epoch, batches = self.run_pipelined(sampler, max_batches, train=train)
+            sampler.restart()
+            return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
         correct = nodes = batches = 0
         loss_epoch = 0.0
         while sampler.sample_not_finished():
             if max_batches is not None and batches >= max_batches:
                 break
-            if self.use_engine:
+            if native:
                 info = self.engine_step(sampler, train=train)
                 batch_nodes = info.v[self.layers - 1]
             else:

@@ -12,7 +12,7 @@ from neutronbench_b200.cuda_stream import ptr
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 0, 2], ids=["tcgen05_3xtf32", "cuda_cores", "tcgen05_tf32"])
+@pytest.fixture(params=[17, 0, 18, 1], ids=["tcgen05_3xtf32", "cuda_cores", "tcgen05_tf32", "default"])
 def gemm_mode(request):
     """Every GEMM test runs on the tensor-core path (default), the CUDA-core path and plain TF32."""
     lib = _lib.load()
@@ -30,7 +30,7 @@ RTOL = 1e-5   # fp32 tolerance of the north star; the GEMMs differ from the orac
 
 def _close(a, b, k, mode=1):
     scale = np.abs(b).max() + 1e-30
-    tol = 2e-3 if mode == 2 else RTOL * max(1.0, np.sqrt(k) / 8)   # plain TF32 keeps 10 mantissa bits
+    tol = 2e-3 if mode == 18 else RTOL * max(1.0, np.sqrt(k) / 8)   # plain TF32 keeps 10 mantissa bits
     assert np.abs(a - b).max() / scale < tol, (np.abs(a - b).max(), scale)
 
 

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _setup(cuda_device, V=4000, E=60000, F=100, hidden=32, classes=7, fanout=(10, 5), batch=256, drop=0.5,
-           cache_rate=0.0, fuse=True, layers=None, use_engine=True):
+           cache_rate=0.0, fuse=True, layers=None, use_engine=True, pipelines=1):
     edges, co, ri = small_graph(V, E, seed=6)
     rng = np.random.RandomState(0)
     feat = rng.randn(V, F).astype(np.float32)
@@ -22,7 +22,7 @@ def _setup(cuda_device, V=4000, E=60000, F=100, hidden=32, classes=7, fanout=(10
     sizes = layers or [F] + [hidden] * (len(fanout) - 1) + [classes]
     cfg = GCNConfig(layers=sizes, fanout=fanout, batch_size=batch, drop_rate=drop, learn_rate=0.01,
                     weight_decay=0.0001, cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate,
-                    fuse_gather=fuse, seed=2000)
+                    fuse_gather=fuse, seed=2000, pipelines=pipelines)
     g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
     datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device),
                      np.zeros(V, np.int32))
@@ -112,3 +112,28 @@ def test_native_step_and_python_step_are_the_same_computation(cuda_device):
         outs.append((tk.P.W.cpu().numpy().copy(), loss, hits))
     np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
     assert outs[0][1] == outs[1][1] and outs[0][2] == outs[1][2]
+
+
+@pytest.mark.parametrize("staged", [False, True], ids=["host_seeds", "device_seeds"])
+def test_pipelined_loop_equals_plain_loop(cuda_device, staged):
+    """Sampling batch i+1 on a second stream while batch i trains (nb_gcn_sample / nb_gcn_compute)
+    changes no result: per-epoch loss and accuracy and the final weights are bit-identical."""
+    outs = []
+    for pipelines in (1, 2):
+        edges, co, ri, feat, label, cfg, g, tk, ref = _setup(cuda_device, fanout=(10, 5), drop=0.5, cache_rate=0.3,
+                                                             pipelines=pipelines)
+        smp = Sampler(g, np.arange(1100, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                      with_edge_weights=False)
+        rng = np.random.RandomState(11)
+        curve = []
+        for _ in range(3):
+            if staged:
+                smp.shuffle(rng)
+                smp.stage_seeds_on_device()
+                curve.append(tk.Forward(smp, train=True))
+            else:
+                curve.append(tk.Forward(smp, rng=rng, train=True))
+        outs.append((tk.P.W.cpu().numpy().copy(), curve))
+    np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
+    assert outs[0][1] == outs[1][1]
+    assert outs[0][1][0][2] == 5
