@@ -310,6 +310,11 @@ int nb_gcn_batch_destroy(nb_gcn_batch *batch);
 int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
 int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
                    void *stream);
+/* nb_gcn_sample on a thread of the library (started at the first call, joined by nb_gcn_destroy), so that the
+ * caller's thread is free to enqueue the training of the previous batch meanwhile; requests run in the order
+ * they were made.  d_seeds must stay valid until the batch has been sampled.  nb_gcn_compute on the batch blocks
+ * until then and returns the sampling's error, if any.  nb_gcn_batch_destroy: only after that. */
+int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
 /* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
  * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
  * algorithmic bytes and the launch count since timing was switched on (or last read). */

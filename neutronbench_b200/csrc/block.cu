@@ -8,6 +8,7 @@
 //                   core/coocsc.hpp:293-298); here rows are filled with atomic cursors and then each
 //                   row is sorted — equal keys are indistinguishable, so the result is unique.
 #include "common.cuh"
+#include "scan.cuh"
 
 namespace nb {
 
@@ -32,8 +33,18 @@ __global__ void popc_words_kernel(const uint32_t *__restrict__ bitmap, uint32_t 
     counts[w] = __popc(bitmap[w]);
 }
 
+// Scan input produced on the fly: the population count of bitmap word i.
+struct ScanLoadPopc {
+  const uint32_t *bitmap;
+  __device__ __forceinline__ uint32_t operator()(uint64_t i) const { return __popc(bitmap[i]); }
+};
+
+// Also clears the CSR row counters (zero_n entries) that the next kernel accumulates into.
 __global__ void emit_source_kernel(const uint32_t *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
-                                   uint64_t words, uint32_t *__restrict__ source) {
+                                   uint64_t words, uint32_t *__restrict__ source, uint32_t *__restrict__ zero,
+                                   uint64_t zero_n) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += (uint64_t)gridDim.x * blockDim.x)
+    zero[i] = 0u;
   for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words; w += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t word = bitmap[w];
     uint32_t p = prefix[w];
@@ -60,9 +71,19 @@ __global__ void remap_count_kernel(uint32_t *row_indices, uint32_t e, const uint
 }
 
 // ------------------------------------------------------------------------------------ norms
-__global__ void sqrt_degree_kernel(const uint32_t *__restrict__ offsets, uint32_t n, float *__restrict__ norm) {
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
-    norm[i] = (float)sqrt((double)(offsets[i + 1] - offsets[i]));  // (float)std::sqrt(int), core/ntsBaseOp.hpp:183-186
+// Both degree factors of a block and the fill cursors (a copy of the row offsets) in one pass.
+__global__ void degree_norms_kernel(const uint32_t *__restrict__ row_offset, uint32_t s, float *__restrict__ src_norm,
+                                    uint32_t *__restrict__ cursor, const uint32_t *__restrict__ column_offset,
+                                    uint32_t v, float *__restrict__ dst_norm) {
+  const uint64_t n = s > v ? s : v;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    if (i < s) {
+      const uint32_t lo = row_offset[i];
+      src_norm[i] = (float)sqrt((double)(row_offset[i + 1] - lo));
+      if (cursor) cursor[i] = lo;
+    }
+    if (i < v) dst_norm[i] = (float)sqrt((double)(column_offset[i + 1] - column_offset[i]));
+  }
 }
 
 // Index of the segment that holds position j: largest i with offsets[i] <= j (offsets ascending, n+1 entries).
@@ -239,20 +260,24 @@ NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indi
   WsScope scope(ws);
 
   const uint64_t words = ((uint64_t)num_vertices + 31) / 32;
-  uint32_t *bitmap = ws->alloc_n<uint32_t>(words);
+  uint32_t *bitmap = ws->alloc_n<uint32_t>(words + 4);   // + flags, cleared by the same memset
   uint32_t *prefix = ws->alloc_n<uint32_t>(words + 1);
-  uint32_t *flags = ws->alloc_n<uint32_t>(4);  // [0] error, [1] long-row count
-  if (!bitmap || !prefix || !flags) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
-  NB_CUDA(cudaMemsetAsync(bitmap, 0, words * sizeof(uint32_t), stream));
-  NB_CUDA(cudaMemsetAsync(flags, 0, 4 * sizeof(uint32_t), stream));
+  if (!bitmap || !prefix) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
+  uint32_t *flags = bitmap + words;  // [0] error, [1] long-row count
+  NB_CUDA(cudaMemsetAsync(bitmap, 0, (words + 4) * sizeof(uint32_t), stream));
 
   if (e > 0) {
     mark_bitmap_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_row_indices, e, num_vertices, bitmap, flags);
     NB_LAUNCH_CHECK();
   }
-  popc_words_kernel<<<grid_for(words, kThreads), kThreads, 0, stream>>>(bitmap, prefix, words);
-  NB_LAUNCH_CHECK();
-  NB_TRY(exclusive_scan_u32(ws, prefix, prefix, words, true, stream));
+  if (words <= kSingleBlockScanMax) {   // popcount and scan in one launch
+    scan_single_block<uint32_t, ScanLoadPopc><<<1, 1024, 0, stream>>>(ScanLoadPopc{bitmap}, prefix, words, true);
+    NB_LAUNCH_CHECK();
+  } else {
+    popc_words_kernel<<<grid_for(words, kThreads), kThreads, 0, stream>>>(bitmap, prefix, words);
+    NB_LAUNCH_CHECK();
+    NB_TRY(exclusive_scan_u32(ws, prefix, prefix, words, true, stream));
+  }
   NB_CUDA(cudaMemcpyAsync(ws->mailbox, prefix + words, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 1, flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
   NB_CUDA(cudaStreamSynchronize(stream));
@@ -260,31 +285,30 @@ NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indi
   if (ws->mailbox[1] != 0) return fail(NB_ERR_INVALID, "nb_block_build: a source id is >= num_vertices");
   *src_size = s;
 
-  emit_source_kernel<<<grid_for(words, kThreads), kThreads, 0, stream>>>(bitmap, prefix, words, d_source);
-  NB_LAUNCH_CHECK();
-
   // CSR: count -> scan -> fill -> sort rows
-  NB_CUDA(cudaMemsetAsync(d_row_offset, 0, ((size_t)s + 1) * sizeof(uint32_t), stream));
+  emit_source_kernel<<<grid_for(words > s ? words : s + 1, kThreads), kThreads, 0, stream>>>(
+      bitmap, prefix, words, d_source, d_row_offset, (uint64_t)s + 1);
+  NB_LAUNCH_CHECK();
   if (e > 0) {
     remap_count_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_row_indices, e, bitmap, prefix,
                                                                        num_vertices, d_row_offset);
     NB_LAUNCH_CHECK();
   }
   NB_TRY(exclusive_scan_u32(ws, d_row_offset, d_row_offset, s, true, stream));
-  if (s > 0) {
-    sqrt_degree_kernel<<<grid_for(s, kThreads), kThreads, 0, stream>>>(d_row_offset, s, d_src_norm);
-    NB_LAUNCH_CHECK();
+  uint32_t *cursor = nullptr;
+  if (e > 0) {
+    cursor = ws->alloc_n<uint32_t>((size_t)s + 1);
+    if (!cursor) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
   }
-  if (v > 0) {
-    sqrt_degree_kernel<<<grid_for(v, kThreads), kThreads, 0, stream>>>(d_column_offset, v, d_dst_norm);
+  if (s > 0 || v > 0) {
+    degree_norms_kernel<<<grid_for(s > v ? s : v, kThreads), kThreads, 0, stream>>>(d_row_offset, s, d_src_norm, cursor,
+                                                                                d_column_offset, v, d_dst_norm);
     NB_LAUNCH_CHECK();
   }
   if (e > 0) {
-    uint32_t *cursor = ws->alloc_n<uint32_t>((size_t)s + 1);
     uint32_t *long_rows = ws->alloc_n<uint32_t>((size_t)e / 32 + 1);
     uint32_t *scratch = ws->alloc_n<uint32_t>(e);
-    if (!cursor || !long_rows || !scratch) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
-    NB_CUDA(cudaMemcpyAsync(cursor, d_row_offset, (size_t)s * sizeof(uint32_t), cudaMemcpyDeviceToDevice, stream));
+    if (!long_rows || !scratch) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
     csr_fill_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_column_offset, d_row_indices, v, e, cursor,
                                                                     d_column_indices, d_src_norm, d_dst_norm, d_w_fwd);
     NB_LAUNCH_CHECK();

@@ -2,6 +2,7 @@
 #include <stdarg.h>
 
 #include "common.cuh"
+#include "scan.cuh"
 
 namespace nb {
 
@@ -20,39 +21,6 @@ void set_error(const char *fmt, ...) {
 // No inter-block waiting, so there is nothing that can spin.  Traffic: reads the input twice and
 // writes the output once (12 bytes per element for u32 -> u32).
 // ---------------------------------------------------------------------------------------------
-constexpr int kScanThreads = 256;
-constexpr int kScanItems = 8;
-constexpr int kScanTile = kScanThreads * kScanItems;
-
-template <typename T>
-__device__ __forceinline__ T block_exclusive_scan(T val, T *total, T *smem /* 32 entries */) {
-  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  T incl = val;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    T n = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= (unsigned)o) incl += n;
-  }
-  if (lane == 31) smem[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    T w = (lane < (blockDim.x >> 5)) ? smem[lane] : (T)0;
-    T wi = w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      T n = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= (unsigned)o) wi += n;
-    }
-    smem[lane] = wi - w;  // exclusive prefix of the warp totals
-    if (lane == 31) smem[32] = wi;
-  }
-  __syncthreads();
-  T res = smem[warp] + incl - val;
-  *total = smem[32];
-  __syncthreads();
-  return res;
-}
-
 template <typename TOut>
 __global__ void __launch_bounds__(kScanThreads) scan_tile_sums(const uint32_t *__restrict__ in,
                                                                TOut *__restrict__ tile_sums, uint64_t n) {
@@ -105,35 +73,6 @@ __global__ void __launch_bounds__(kScanThreads) scan_tiles(const uint32_t *in, T
   }
 }
 
-// Small inputs (the per-hop arrays of a sampled block): one block walks the array in chunks of
-// 1024 x 8 with a running carry.  One launch instead of three; the array is read once.
-template <typename TOut>
-__global__ void __launch_bounds__(1024) scan_single_block(const uint32_t *in, TOut *out, uint64_t n, bool write_total) {
-  __shared__ TOut smem[33];
-  TOut carry = 0;
-  for (uint64_t start = 0; start < n; start += 1024 * kScanItems) {
-    const uint64_t base = start + (uint64_t)threadIdx.x * kScanItems;
-    uint32_t v[kScanItems];
-    TOut sum = 0;
-#pragma unroll
-    for (int k = 0; k < kScanItems; k++) {
-      v[k] = (base + k < n) ? in[base + k] : 0u;
-      sum += v[k];
-    }
-    TOut total;
-    TOut ex = block_exclusive_scan<TOut>(sum, &total, smem) + carry;
-#pragma unroll
-    for (int k = 0; k < kScanItems; k++) {
-      if (base + k < n) out[base + k] = ex;
-      ex += v[k];
-    }
-    carry += total;
-  }
-  if (write_total && threadIdx.x == 0) out[n] = carry;
-}
-
-constexpr uint64_t kSingleBlockScanMax = 1u << 17;
-
 template <typename TOut>
 static int scan_impl(nb_ws *ws, const uint32_t *d_in, TOut *d_out, uint64_t n, bool write_total,
                      cudaStream_t stream) {
@@ -142,7 +81,7 @@ static int scan_impl(nb_ws *ws, const uint32_t *d_in, TOut *d_out, uint64_t n, b
     return 0;
   }
   if (n <= kSingleBlockScanMax) {
-    scan_single_block<TOut><<<1, 1024, 0, stream>>>(d_in, d_out, n, write_total);
+    scan_single_block<TOut, ScanLoadArray><<<1, 1024, 0, stream>>>(ScanLoadArray{d_in}, d_out, n, write_total);
     NB_LAUNCH_CHECK();
     return 0;
   }

@@ -1,7 +1,12 @@
 // Whole training step issued from native code: the batch-loop body of the reference toolkit
 // (toolkits/GCN_GPU_NEIGHBOR.hpp:604-713) as a sequence of this library's kernels on one stream.
 // No kernels of its own: it exists so that a step costs one host call and no per-step allocations.
+#include <condition_variable>
+#include <deque>
+#include <mutex>
 #include <new>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -20,6 +25,17 @@ struct nb_gcn_batch {
   cudaEvent_t sampled = nullptr;    // recorded when the last sampling kernel is enqueued
   cudaEvent_t consumed = nullptr;   // recorded after the last kernel that reads the arrays
   bool in_use = false;              // a compute call has been enqueued since the last sample call
+  // nb_gcn_sample_async: set under the model's mutex
+  bool pending = false;             // queued or being sampled by the sampler thread
+  int status = 0;                   // result of that sampling
+  std::string error;
+};
+
+struct SampleJob {
+  nb_gcn_batch *batch;
+  const uint32_t *seeds;
+  uint32_t n;
+  void *stream;
 };
 
 struct nb_gcn {
@@ -35,6 +51,14 @@ struct nb_gcn {
   std::vector<cudaEvent_t> ev_pool;   // pairs: start, stop
   size_t ev_used = 0;
   uint64_t timed_bytes = 0;
+  // sampler thread (one of the reference's pipeline threads, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, reduced to
+  // the part that blocks on the device): started by the first nb_gcn_sample_async
+  int device = 0;
+  std::thread sampler;
+  std::mutex mu;
+  std::condition_variable cv_job, cv_done;
+  std::deque<SampleJob> jobs;
+  bool stop = false;
 };
 
 namespace {
@@ -96,6 +120,7 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   g->cfg = *cfg;
   g->ws = ws;
   g->own.ws = ws;
+  NB_CUDA(cudaGetDevice(&g->device));
   g->draws = 0;
   g->steps = 0;
   g->beta1_t = cfg->beta1;
@@ -109,6 +134,14 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
 
 NB_API int nb_gcn_destroy(nb_gcn *g) {
   if (g) {
+    if (g->sampler.joinable()) {
+      {
+        std::lock_guard<std::mutex> lk(g->mu);
+        g->stop = true;
+      }
+      g->cv_job.notify_all();
+      g->sampler.join();
+    }
     for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
     if (g->own.sampled) cudaEventDestroy(g->own.sampled);
     if (g->own.consumed) cudaEventDestroy(g->own.consumed);
@@ -279,6 +312,36 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   return 0;
 }
 
+// Blocks until the sampler thread has finished with `bt`; returns the sampling's status.
+int wait_sampled(nb_gcn *g, nb_gcn_batch *bt) {
+  std::unique_lock<std::mutex> lk(g->mu);
+  g->cv_done.wait(lk, [&] { return !bt->pending; });
+  if (bt->status != 0) return nb::fail((nb_status)bt->status, bt->error.c_str());
+  return 0;
+}
+
+void sampler_main(nb_gcn *g) {
+  cudaSetDevice(g->device);
+  for (;;) {
+    SampleJob job;
+    {
+      std::unique_lock<std::mutex> lk(g->mu);
+      g->cv_job.wait(lk, [&] { return g->stop || !g->jobs.empty(); });
+      if (g->jobs.empty()) return;   // stop requested and nothing left to do
+      job = g->jobs.front();
+      g->jobs.pop_front();
+    }
+    const int st = sample_into(g, job.batch, job.seeds, job.n, job.stream);
+    {
+      std::lock_guard<std::mutex> lk(g->mu);
+      job.batch->status = st;
+      job.batch->error = st ? nb_last_error() : "";
+      job.batch->pending = false;
+    }
+    g->cv_done.notify_all();
+  }
+}
+
 }  // namespace
 
 NB_API int nb_gcn_batch_create(nb_gcn_batch **out, nb_ws *ws) {
@@ -303,12 +366,41 @@ NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds
   NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample: null pointer");
   NB_REQUIRE(n_seeds > 0, "nb_gcn_sample: empty batch");
   NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample: a batch needs a workspace of its own, not the model's");
+  {
+    std::unique_lock<std::mutex> lk(g->mu);   // keep the order of sampler draws: let queued batches go first
+    g->cv_done.wait(lk, [&] {
+      if (batch->pending) return false;
+      return g->jobs.empty();
+    });
+  }
   return sample_into(g, batch, d_seeds, n_seeds, stream);
+}
+
+NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds,
+                               void *stream) {
+  NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample_async: null pointer");
+  NB_REQUIRE(n_seeds > 0, "nb_gcn_sample_async: empty batch");
+  NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample_async: a batch needs a workspace of its own, not the model's");
+  std::lock_guard<std::mutex> lk(g->mu);
+  NB_REQUIRE(!batch->pending, "nb_gcn_sample_async: this batch is still being sampled");
+  if (!g->sampler.joinable()) {
+    try {
+      g->sampler = std::thread(sampler_main, g);
+    } catch (...) {
+      return nb::fail(NB_ERR_NOMEM, "nb_gcn_sample_async: cannot start the sampler thread");
+    }
+  }
+  batch->pending = true;
+  batch->status = 0;
+  g->jobs.push_back(SampleJob{batch, d_seeds, n_seeds, stream});
+  g->cv_job.notify_one();
+  return 0;
 }
 
 NB_API int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
                           void *stream) {
   NB_REQUIRE(g && batch && d_stats, "nb_gcn_compute: null pointer");
+  NB_TRY(wait_sampled(g, batch));
   return compute_from(g, batch, train, d_stats, info, stream);
 }
 

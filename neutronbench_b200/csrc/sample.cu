@@ -1,5 +1,6 @@
 // Fan-out neighbour sampling of one hop and the whole-graph CSC build.
 #include "common.cuh"
+#include "scan.cuh"
 #include "philox.cuh"
 
 namespace nb {
@@ -15,6 +16,18 @@ __global__ void hop_counts_kernel(const uint64_t *__restrict__ g_co, const uint3
     counts[i] = (uint32_t)((fanout < 0 || deg < (uint64_t)fanout) ? deg : (uint64_t)fanout);
   }
 }
+
+// The same count as a scan input, so that small hops need one launch for counts and offsets.
+struct ScanLoadHopCount {
+  const uint64_t *g_co;
+  const uint32_t *dst;
+  int fanout;
+  __device__ __forceinline__ uint32_t operator()(uint64_t i) const {
+    const uint32_t d = dst[i];
+    const uint64_t deg = g_co[d + 1] - g_co[d];
+    return (uint32_t)((fanout < 0 || deg < (uint64_t)fanout) ? deg : (uint64_t)fanout);
+  }
+};
 
 // One thread per destination.  deg <= fanout: copy the column.  Otherwise Floyd's algorithm picks
 // `fanout` distinct positions; the chosen positions are parked in the output slots (read back by the
@@ -177,12 +190,18 @@ NB_API int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offse
   NB_REQUIRE(v == 0 || d_dst, "nb_sample_hop_offsets: null destination list");
   NB_REQUIRE(fanout != 0, "nb_sample_hop_offsets: fanout must be positive, or negative for all neighbours");
   cudaStream_t stream = as_stream(stream_);
-  if (v > 0) {
-    hop_counts_kernel<<<grid_for(v, kThreads), kThreads, 0, stream>>>(d_graph_column_offset, d_dst, v, fanout,
-                                                                     d_column_offset);
+  if (v > 0 && v <= kSingleBlockScanMax) {
+    scan_single_block<uint32_t, ScanLoadHopCount><<<1, 1024, 0, stream>>>(
+        ScanLoadHopCount{d_graph_column_offset, d_dst, fanout}, d_column_offset, v, true);
     NB_LAUNCH_CHECK();
+  } else {
+    if (v > 0) {
+      hop_counts_kernel<<<grid_for(v, kThreads), kThreads, 0, stream>>>(d_graph_column_offset, d_dst, v, fanout,
+                                                                       d_column_offset);
+      NB_LAUNCH_CHECK();
+    }
+    NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   }
-  NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 2, d_column_offset + v, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
   NB_CUDA(cudaStreamSynchronize(stream));
   *e_size = ws->mailbox[2];

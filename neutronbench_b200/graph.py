@@ -237,6 +237,19 @@ class Sampler:
             return self._dev_nids[lo: lo + actl], actl
         return self._seeds_to_device(self.sample_nids[lo: lo + actl]), actl
 
+    def next_seeds_into(self, pinned: torch.Tensor):
+        """Like next_seeds, for a caller that hands the seeds to a library thread: a slice of the staged
+        device list, or (host seeds) a copy in the caller's pinned int32 buffer, which the library reads
+        itself.  Returns (tensor whose data_ptr() holds the seeds, count)."""
+        assert self.work_offset < self.work_range[1]
+        actl = min(self.batch_size, self.work_range[1] - self.work_offset)
+        lo = self.work_offset
+        self.work_offset += actl
+        if self._dev_nids is not None:
+            return self._dev_nids[lo: lo + actl], actl
+        pinned[:actl].copy_(torch.from_numpy(self.sample_nids[lo: lo + actl].view(np.int32)))
+        return pinned[:actl], actl
+
     def sample_one(self, ssg: Optional[SampledSubgraph] = None, raw_edges: Optional[list] = None) -> SampledSubgraph:
         """One batch: per hop, column offsets, sampling, dedup/reindex, CSR, weights
         (core/ntsSampler.hpp:843-1106).  ``raw_edges`` (list per hop of device int32 tensors of global

@@ -323,6 +323,9 @@ class GCN_GPU_NEIGHBOR_impl:
         import ctypes as C
         self._sample_stream = torch.cuda.Stream(device=self.device)
         self._batch_ws = [Workspace(default_workspace_bytes(self.graph.global_vertices, self.cfg)) for _ in range(2)]
+        self._slot_seeds = [torch.empty(self.cfg.batch_size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._slot_refs = [None, None]
+        self._stats_ring = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._batches = []
         for w in self._batch_ws:
             h = C.c_void_p()
@@ -330,12 +333,13 @@ class GCN_GPU_NEIGHBOR_impl:
             self._batches.append(h)
 
     def sample_batch(self, sampler: Sampler, slot: int):
-        """nb_gcn_sample of the sampler's next batch into subgraph `slot`, on the sampling stream."""
+        """Asks the library's sampler thread (nb_gcn_sample_async) to draw the sampler's next batch into
+        subgraph `slot` on the sampling stream; returns at once.  compute_batch(slot) waits for it."""
         self._ensure_pipeline()
-        with torch.cuda.stream(self._sample_stream):
-            seeds, n = sampler.next_seeds()
-            _lib.call("nb_gcn_sample", self._ensure_engine(), self._batches[slot], ptr(seeds), n,
-                      self._sample_stream.cuda_stream)
+        seeds, n = sampler.next_seeds_into(self._slot_seeds[slot])
+        self._slot_refs[slot] = seeds   # keeps a staged device slice alive until the batch is computed
+        _lib.call("nb_gcn_sample_async", self._ensure_engine(), self._batches[slot], ptr(seeds), n,
+                  self._sample_stream.cuda_stream)
         return n
 
     def compute_batch(self, slot: int, train: bool = True):
@@ -362,30 +366,38 @@ class GCN_GPU_NEIGHBOR_impl:
         if not sampler.sample_not_finished() or (max_batches is not None and max_batches <= 0):
             return correct, nodes, loss_sum, batches
         self.sample_batch(sampler, 0)
-        slot = 0
+        slot, issued = 0, 1
+        pending_read = None
         while True:
+            more = sampler.sample_not_finished() and (max_batches is None or issued < max_batches)
+            if more:   # the sampler thread draws batch i+1 while this thread enqueues batch i
+                self.sample_batch(sampler, slot ^ 1)
+                issued += 1
             info = self.compute_batch(slot, train=train)
             if train:
                 self.Update()
                 self.step_count += 1
-            if read_back:   # asynchronous copy now, read after the next batch has been sampled
-                self._stats_host.copy_(self.stats, non_blocking=True)
-                done = torch.cuda.Event()
-                done.record()
+            if read_back:   # copy now, read one batch later: the host never waits for the batch it just enqueued
+                if pending_read is not None:
+                    pending_read[1].synchronize()
+                    loss_sum += float(pending_read[0][0])
+                    correct += int(pending_read[0][1])
+                host = self._stats_ring[batches & 1]
+                host.copy_(self.stats, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                pending_read = (host, ev)
             batches += 1
-            more = sampler.sample_not_finished() and (max_batches is None or batches < max_batches)
-            if more:
-                self.sample_batch(sampler, slot ^ 1)
-            if read_back:
-                done.synchronize()
-                loss_sum += float(self._stats_host[0])
-                correct += int(self._stats_host[1])
             nodes += info.v[self.layers - 1]
             if on_batch is not None:
                 on_batch(batches)
             if not more:
                 break
             slot ^= 1
+        if pending_read is not None:
+            pending_read[1].synchronize()
+            loss_sum += float(pending_read[0][0])
+            correct += int(pending_read[0][1])
         return correct, nodes, loss_sum, batches
 
     def Update(self):
