@@ -18,9 +18,10 @@
 
 namespace nb {
 
-constexpr int kTcThreads = 512;   // 16 warps: the staging work is instruction-latency bound, so warps hide it
+constexpr int kTcThreads = 256;   // two CTAs share an SM: one stages operands while the other waits on its MMAs
 constexpr int kBM = 128;           // rows of a C tile = TMEM lanes
-constexpr int kBK = 32;            // K elements per shared-memory chunk (4 MMA K-steps of 8)
+constexpr int kBK = 16;            // K elements per shared-memory chunk (2 MMA K-steps of 8)
+constexpr int kCtasPerSM = 2;      // 108 KB of shared memory and 128 TMEM columns per CTA
 constexpr uint32_t kTcWaitLimit = 1u << 20;
 
 __device__ unsigned int g_tc_gemm_error = 0;
@@ -57,14 +58,15 @@ __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-// Shared-memory matrix descriptor, K-major, no swizzle: core matrices (8 rows x 16 B) adjacent along K
-// are `lbo` bytes apart, 8-row groups along M/N are `sbo` bytes apart.  Bit 46 = descriptor version 1.
-__device__ __forceinline__ uint64_t tc_make_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor: start address, the two strides (see the tile layouts below), bit 46 =
+// descriptor version 1, bits 61-63 = layout type.
+__device__ __forceinline__ uint64_t tc_make_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
   d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
+  d |= (uint64_t)(layout & 7) << 61;   // 0: no swizzle, 1: 128-byte swizzle with 32-byte atoms
   return d;
 }
 
@@ -87,29 +89,62 @@ __device__ __forceinline__ void tc_split(float x, float &hi, float &lo) {
   lo = x - hi;
 }
 
-// Tile layout in shared memory (floats): K-major core matrices (8 rows x 16 B), 8 K-cores per 8-row
-// group.  Consecutive K-cores are 144 bytes apart instead of 128: the 16 bytes of padding put the 8
-// pieces of one tile row on different banks, so that a row can be written by consecutive threads
-// (coalesced global reads) without bank conflicts.  Both strides are descriptor fields (LBO / SBO),
-// so the tensor core reads the padded layout natively.
-constexpr uint32_t kCoreFloats = 36;                   // 128-byte core matrix + 16 bytes of padding
-constexpr uint32_t kGroupFloats = 8 * kCoreFloats;     // 8 K-cores per 8-row group: 1152 bytes
-constexpr uint32_t kLBO = kCoreFloats * 4, kSBO = kGroupFloats * 4;
+// Tile layouts in shared memory (floats).  A tile holds ROWS rows (M or N index) by kBK reduction elements.
+//
+//   K-major   (the operand is contiguous along K in global memory): no swizzle; core matrices of 8 rows x
+//             4 k (16 bytes per row).  K-cores of a row group are 144 bytes apart (LBO), 8-row groups
+//             kKCores*144 bytes (SBO).  The 16 bytes of padding per core put the pieces that consecutive
+//             threads write on different banks.
+//   MN-major  (the operand is contiguous along its row index: a transposed operand).  For kind::tf32 the
+//             tensor core reads MN-major operands only in the "128-byte swizzle with 32-byte atoms" mode
+//             (descriptor layout type 1): a line is 32 rows (128 bytes) of one k; four lines (k & 3) form
+//             a 512-byte atom inside which the 32-byte quarter (row >> 3) & 3 of a line is stored at
+//             quarter ^ (k & 3).  Atoms of consecutive k groups are SBO = 512 bytes apart, 32-row blocks
+//             LBO = kBK/4 * 512 bytes.  Measured on the device with a selector matrix, not taken from a
+//             manual.  A quarter-warp writes one whole 128-byte line, so there are no bank conflicts.
+//
+// Strides and the swizzle mode are descriptor fields, so the transposed operands need no transposition
+// pass: rows are copied with 16-byte pieces along their contiguous direction either way.
+constexpr uint32_t kCoreFloats = 36;                   // K-major: 128-byte core matrix + 16 bytes of padding
+constexpr uint32_t kKCores = kBK / 4;                  // K-major core matrices along K per chunk
+constexpr uint32_t kGroupFloats = kKCores * kCoreFloats;
+constexpr uint32_t kMnAtomFloats = 128;                // MN-major: 4 k x 32 rows
+constexpr uint32_t kMnBlockFloats = (kBK / 4) * kMnAtomFloats;   // one 32-row block of a chunk
+
+template <bool MN>
 __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t k) {
+  if (MN)
+    return (r >> 5) * kMnBlockFloats + (k >> 2) * kMnAtomFloats + (k & 3) * 32 + ((((r >> 3) & 3) ^ (k & 3)) << 3) + (r & 7);
   return (r >> 3) * kGroupFloats + (k >> 2) * kCoreFloats + (r & 7) * 4 + (k & 3);
 }
+// float offset of 16-byte piece q of a tile, q in [0, ROWS * kBK / 4): any order that covers the data
+template <bool MN>
+__device__ __forceinline__ uint32_t quad_off(uint32_t q) {
+  if (MN) return q * 4;   // the MN-major tile is dense
+  constexpr uint32_t PER_GROUP = 8 * kKCores;
+  return (q / PER_GROUP) * kGroupFloats + ((q % PER_GROUP) >> 3) * kCoreFloats + (q & 7) * 4;
+}
 template <int ROWS>
-struct TileFloats {
-  static constexpr uint32_t value = (ROWS / 8) * kGroupFloats;
+struct TileFloats {   // the K-major tile is the larger of the two; rounded up to 1 KB so that every tile of a
+                      // stage ring keeps the alignment the swizzle pattern is defined on
+  static constexpr uint32_t value = (((ROWS / 8) * kGroupFloats) + 255) / 256 * 256;
+};
+template <bool MN> struct DescStride {};
+template <> struct DescStride<false> {
+  static constexpr uint32_t lbo = kCoreFloats * 4, sbo = kGroupFloats * 4, kstep = 2 * kCoreFloats * 4, layout = 0;
+};
+template <> struct DescStride<true> {
+  static constexpr uint32_t lbo = kMnBlockFloats * 4, sbo = kMnAtomFloats * 4, kstep = 2 * kMnAtomFloats * 4, layout = 1;
 };
 
 constexpr int kStages = 4;        // raw operand stages filled by cp.async, two chunks ahead of the MMAs
 
-__device__ __forceinline__ void cp_async(uint32_t dst, const void *src, int bytes, int valid) {
-  // `valid` bytes are read, the rest of the `bytes`-wide destination is zero-filled
-  if (bytes == 16)
+template <int BYTES>
+__device__ __forceinline__ void cp_async(uint32_t dst, const void *src, int valid) {
+  // `valid` bytes are read, the rest of the BYTES-wide destination is zero-filled
+  if (BYTES == 16)
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
-  else if (bytes == 8)
+  else if (BYTES == 8)
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
   else
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid) : "memory");
@@ -118,118 +153,119 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Asynchronously copies the ROWS x 32 tile op(X)(row0 + r, k0 + k) = base[(row0+r)*s_row + (k0+k)*s_k]
-// into `tile` (canonical layout), zero outside the matrix.  K unit-stride operands move in pieces of
-// `vec` floats along K; row unit-stride operands (the transposed ones) move element by element, with
-// consecutive threads on consecutive rows so that the global reads coalesce.
-template <int ROWS>
-__device__ __forceinline__ void copy_tile_async(float *tile, const float *__restrict__ base, int64_t s_row,
-                                                int64_t s_k, int64_t row0, int64_t rows_total, int64_t k0,
-                                                int64_t k_end, int vec) {
-  const int tid = threadIdx.x;
-  const uint32_t tile_s = tc_smem_u32(tile);
-  if (s_k == 1) {
-    const int per_row = kBK / vec;                       // pieces per tile row
-    for (int item = tid; item < ROWS * per_row; item += kTcThreads) {
-      const int r = item / per_row, k = (item % per_row) * vec;
-      const int64_t gr = row0 + r, gk = k0 + k;
-      int valid = 0;
-      if (gr < rows_total && gk < k_end) valid = (int)min((int64_t)vec, k_end - gk) * 4;
-      const float *src = valid ? base + gr * s_row + gk : base;
-      cp_async(tile_s + tile_off(r, k) * 4, src, vec * 4, valid);
-    }
-  } else {
-    for (int item = tid; item < ROWS * kBK; item += kTcThreads) {
-      const int r = item % ROWS, k = item / ROWS;
-      const int64_t gr = row0 + r, gk = k0 + k;
-      const int valid = (gr < rows_total && gk < k_end) ? 4 : 0;
-      const float *src = valid ? base + gk * s_k + gr * s_row : base;
-      cp_async(tile_s + tile_off(r, k) * 4, src, 4, valid);
-    }
-  }
-}
-
-// Per-thread copy plan of one operand: the (row, k) pieces a thread moves are the same in every
-// chunk, so the source pointer, the destination offsets and the row predicate are computed once and
-// the main loop only advances the pointer.  item = tid + i*kTcThreads, r = item % ROWS,
-// kidx = item / ROWS = tid/ROWS + i*(kTcThreads/ROWS).
-template <int ROWS>
+// Per-thread copy plan of one operand.  A tile is moved in pieces of `vec` floats along the operand's
+// contiguous direction; piece `item` = tid + i * kTcThreads of every chunk is the same (row, k) place, so
+// the source pointer, the destination offsets and the bounds predicate are computed once and the main
+// loop only advances the pointer.
+//   K-major:  piece = item % (kBK/vec) along k, row = item / (kBK/vec)
+//   MN-major: piece = item % (ROWS/vec) along the rows, k = item / (ROWS/vec)
+// The pitch of a dense row-major operand equals its extent along the contiguous direction and is a
+// multiple of `vec`, so a piece never straddles the matrix edge.
+template <int ROWS, bool MN>
 struct CopyPlan {
-  const float *src;      // address of this thread's first piece in chunk 0 (row clamped when invalid)
-  int64_t step;          // elements between a thread's consecutive pieces
-  int64_t chunk_step;    // elements between chunks
-  uint32_t dst[ (ROWS * kBK) / kTcThreads > 0 ? (ROWS * kBK) / kTcThreads : 1 ];   // byte offsets in the tile
-  int pieces, bytes, valid;   // valid: bit i set when piece i lies inside the matrix
+  static constexpr int kMaxPieces = (ROWS * kBK) / kTcThreads > 0 ? (ROWS * kBK) / kTcThreads : 1;   // at vec = 1
+  const float *src;        // this thread's first piece in chunk 0 (clamped into the matrix when out of range)
+  int64_t step;            // elements between a thread's consecutive pieces
+  int64_t chunk_step;      // elements between chunks
+  uint32_t dst[kMaxPieces];   // byte offsets in the tile
+  int vec, pieces, valid;  // valid: bit i set when piece i lies inside the matrix rows
+  // for the bounds-checked tail chunk
+  int64_t s_row, s_k, row0, rows_total;
+  const float *base;
 
-  __device__ void init(const float *base, int64_t s_row, int64_t s_k, int64_t row0, int64_t rows_total, int64_t k0,
-                       int vec) {
+  __device__ void init(const float *base_, int64_t s_row_, int64_t s_k_, int64_t row0_, int64_t rows_total_,
+                       int64_t k0, int vec_) {
+    base = base_; s_row = s_row_; s_k = s_k_; row0 = row0_; rows_total = rows_total_; vec = vec_;
     const int tid = threadIdx.x;
-    constexpr int NDST = (int)(sizeof(dst) / sizeof(dst[0]));
     valid = 0;
-    if (s_k == 1) {
-      // K unit-stride: consecutive threads take consecutive pieces of one tile row (coalesced reads);
-      // piece i of a thread is the same k range of a row (kTcThreads / per_row) further down.
-      const int per_row = kBK / vec;
-      const int piece = tid % per_row, r0 = tid / per_row, rstep = kTcThreads / per_row;
-      bytes = vec * 4;
-      pieces = (ROWS * per_row) / kTcThreads;
-      if (pieces < 1) pieces = (tid < ROWS * per_row) ? 1 : 0;
-      src = base + (row0 + r0) * s_row + k0 + piece * vec;
-      step = (int64_t)rstep * s_row;
+    const int per_line = (MN ? ROWS : kBK) / vec;           // pieces along the contiguous direction
+    const int total = (ROWS * kBK) / vec;
+    pieces = total / kTcThreads;
+    if (pieces < 1) pieces = tid < total ? 1 : 0;
+    const int piece = tid % per_line, line0 = tid / per_line;
+    const int lstep = kTcThreads / per_line > 0 ? kTcThreads / per_line : 1;
+    if (MN) {
+      const int r = piece * vec;                            // row within the tile, k = line
+      const bool row_ok = row0 + r < rows_total;
+      src = base + (k0 + line0) * s_k + (row_ok ? row0 + r : 0);
+      step = (int64_t)lstep * s_k;
 #pragma unroll
-      for (int i = 0; i < NDST; i++) {
-        const int r = r0 + i * rstep;
-        dst[i] = tile_off(r, piece * vec) * 4;
-        if (i < pieces && row0 + r < rows_total) valid |= 1 << i;
+      for (int i = 0; i < kMaxPieces; i++) {
+        dst[i] = tile_off<true>(r, line0 + i * lstep) * 4;
+        if (i < pieces && row_ok) valid |= 1 << i;
       }
     } else {
-      // row unit-stride (transposed operand): consecutive threads take consecutive rows at one k,
-      // element by element; piece i is KSTEP further along k.
-      const int r = tid % ROWS, kidx0 = tid / ROWS;
-      constexpr int KSTEP = kTcThreads / ROWS;
-      bytes = 4;
-      pieces = (ROWS * kBK) / kTcThreads;
-      if (pieces < 1) pieces = (tid < ROWS * kBK) ? 1 : 0;
-      const bool row_ok = row0 + r < rows_total;
-      src = base + (row_ok ? row0 + r : 0) * s_row + (k0 + kidx0) * s_k;
-      step = (int64_t)KSTEP * s_k;
+      const int k = piece * vec;                            // k within the chunk, row = line
+      src = base + (row0 + line0) * s_row + k0 + k;
+      step = (int64_t)lstep * s_row;
 #pragma unroll
-      for (int i = 0; i < NDST; i++) {
-        dst[i] = tile_off(r, kidx0 + i * KSTEP) * 4;
-        if (i < pieces && row_ok) valid |= 1 << i;
+      for (int i = 0; i < kMaxPieces; i++) {
+        const int r = line0 + i * lstep;
+        dst[i] = tile_off<false>(r < ROWS ? r : 0, k) * 4;
+        if (i < pieces && row0 + r < rows_total) valid |= 1 << i;
       }
     }
     chunk_step = (int64_t)kBK * s_k;
   }
-  // Copies of one full chunk (all 32 k inside the matrix); rows outside the matrix are zero-filled.
-  __device__ __forceinline__ void issue(uint32_t tile_s, int chunk, const float *safe) const {
-    const float *p = src + (int64_t)chunk * chunk_step;
+
+  template <int VEC>
+  __device__ __forceinline__ void issue_vec(uint32_t tile_s, const float *p) const {
+    constexpr int N = kMaxPieces / VEC > 0 ? kMaxPieces / VEC : 1;   // pieces per thread at this width
 #pragma unroll
-    for (int i = 0; i < (int)(sizeof(dst) / sizeof(dst[0])); i++) {
-      if (i < pieces) {
+    for (int i = 0; i < N; i++) {
+      if (N > 1 || i < pieces) {
         const bool ok = (valid >> i) & 1;
-        cp_async(tile_s + dst[i], ok ? p + (int64_t)i * step : safe, bytes, ok ? bytes : 0);
+        cp_async<VEC * 4>(tile_s + dst[i], ok ? p + (int64_t)i * step : base, ok ? VEC * 4 : 0);
       }
+    }
+  }
+  // Copies of one full chunk (all kBK reduction elements inside the matrix); rows outside are zero-filled.
+  __device__ __forceinline__ void issue(uint32_t tile_s, int chunk) const {
+    const float *p = src + (int64_t)chunk * chunk_step;
+    if (vec == 4) issue_vec<4>(tile_s, p);
+    else if (vec == 2) issue_vec<2>(tile_s, p);
+    else issue_vec<1>(tile_s, p);
+  }
+  // The one chunk with a K tail: element by element with bounds checks.
+  __device__ void issue_tail(uint32_t tile_s, int64_t k0, int64_t k_end) const {
+    for (int item = threadIdx.x; item < ROWS * kBK; item += kTcThreads) {
+      const int r = MN ? item % ROWS : item / kBK, k = MN ? item / ROWS : item % kBK;
+      const int64_t gr = row0 + r, gk = k0 + k;
+      const bool ok = gr < rows_total && gk < k_end;
+      cp_async<4>(tile_s + tile_off<MN>(r, k) * 4, ok ? base + gr * s_row + gk * s_k : base, ok ? 4 : 0);
     }
   }
 };
 
-// In place: raw -> hi (low 13 mantissa bits cleared); lo = raw - hi goes to `lo`.
-template <int ROWS>
-__device__ __forceinline__ void split_tile(float *raw, float *lo, bool split) {
-  constexpr int QUADS = ROWS * 8;   // 16-byte pieces (padding between row groups is skipped)
-  for (int q = threadIdx.x; q < QUADS; q += kTcThreads) {
-    const uint32_t off = (q >> 6) * kGroupFloats + ((q & 63) >> 3) * kCoreFloats + (q & 7) * 4;   // 64 quads per group
-    const float4 x = *reinterpret_cast<const float4 *>(raw + off);
-    float h[4], l[4];
-    tc_split(x.x, h[0], l[0]); tc_split(x.y, h[1], l[1]); tc_split(x.z, h[2], l[2]); tc_split(x.w, h[3], l[3]);
-    *reinterpret_cast<float4 *>(raw + off) = make_float4(h[0], h[1], h[2], h[3]);
-    if (split) *reinterpret_cast<float4 *>(lo + off) = make_float4(l[0], l[1], l[2], l[3]);
+// In place: raw -> hi (low 13 mantissa bits cleared); lo = raw - hi goes to `lo`.  Works piece by piece on
+// the same offsets in both buffers, so it does not care which layout the tile has.
+template <int ROWS, bool MN>
+struct SplitPlan {
+  static constexpr int QUADS = ROWS * kBK / 4;
+  static constexpr int N = (QUADS + kTcThreads - 1) / kTcThreads;
+  uint32_t off[N];
+  __device__ void init() {
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+      const int q = threadIdx.x + i * kTcThreads;
+      off[i] = q < QUADS ? quad_off<MN>(q) : 0xFFFFFFFFu;
+    }
   }
-}
+  __device__ __forceinline__ void run(float *raw, float *lo, bool split) const {
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+      if (off[i] == 0xFFFFFFFFu) continue;
+      const float4 x = *reinterpret_cast<const float4 *>(raw + off[i]);
+      float h[4], l[4];
+      tc_split(x.x, h[0], l[0]); tc_split(x.y, h[1], l[1]); tc_split(x.z, h[2], l[2]); tc_split(x.w, h[3], l[3]);
+      *reinterpret_cast<float4 *>(raw + off[i]) = make_float4(h[0], h[1], h[2], h[3]);
+      if (split) *reinterpret_cast<float4 *>(lo + off[i]) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+  }
+};
 
-template <int BN>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs g) {
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const TcGemmArgs g) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   constexpr uint32_t A_TILE = TileFloats<kBM>::value;
   constexpr uint32_t B_TILE = TileFloats<BN>::value;
@@ -262,26 +298,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  // instruction descriptor: D = F32, A = B = TF32, bit 15 / 16 = A / B is MN-major, N = BN, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   bool ok = true;
 
-  CopyPlan<kBM> plan_a;
-  CopyPlan<BN> plan_b;
+  CopyPlan<kBM, A_MN> plan_a;
+  CopyPlan<BN, B_MN> plan_b;
   plan_a.init(g.a, g.a_row, g.a_k, row0, g.M, k_begin, g.a_vec);
   plan_b.init(g.b, g.b_row, g.b_k, col0, g.N, k_begin, g.b_vec);
+  SplitPlan<kBM, A_MN> split_a;
+  SplitPlan<BN, B_MN> split_b;
+  split_a.init();
+  split_b.init();
   const int full_chunks = (int)((k_end - k_begin) / kBK);   // chunks without a K tail
 
   auto start_copy = [&](int chunk) {
     if (chunk < full_chunks) {
       const int st = chunk % kStages;
-      plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk, g.a);
-      plan_b.issue(tc_smem_u32(b_raw + st * B_TILE), chunk, g.b);
+      plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk);
+      plan_b.issue(tc_smem_u32(b_raw + st * B_TILE), chunk);
     } else if (chunk < nchunks) {   // the one chunk with a K tail: bounds-checked copies
       const int st = chunk % kStages;
       const int64_t k0 = k_begin + (int64_t)chunk * kBK;
-      copy_tile_async<kBM>(a_raw + st * A_TILE, g.a, g.a_row, g.a_k, row0, g.M, k0, k_end, g.a_vec);
-      copy_tile_async<BN>(b_raw + st * B_TILE, g.b, g.b_row, g.b_k, col0, g.N, k0, k_end, g.b_vec);
+      plan_a.issue_tail(tc_smem_u32(a_raw + st * A_TILE), k0, k_end);
+      plan_b.issue_tail(tc_smem_u32(b_raw + st * B_TILE), k0, k_end);
     }
     cp_async_commit();   // one group per chunk slot, empty past the end, so that the wait count is constant
   };
@@ -298,8 +339,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs
     }
     if (!__syncthreads_and(mine)) { ok = false; break; }   // also: everybody's copies of chunk c are visible
     start_copy(c + 2);             // into the stage chunk c-2 used
-    split_tile<kBM>(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
-    split_tile<BN>(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
+    split_a.run(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
+    split_b.run(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
     tc_fence_before();
     __syncthreads();
@@ -309,12 +350,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs
       const uint32_t b_h = tc_smem_u32(b_raw + st * B_TILE), b_l = tc_smem_u32(b_lo + lb * B_TILE);
 #pragma unroll
       for (int kk = 0; kk < kBK / 8; kk++) {
-        // one K step = 8 tf32 = two core matrices further along K
-        const uint32_t koff = kk * 2 * kLBO;
-        const uint64_t da_h = tc_make_desc(a_h + koff, kLBO, kSBO), db_h = tc_make_desc(b_h + koff, kLBO, kSBO);
+        // one K step = 8 tf32: two K-major core matrices, or one MN-major core matrix, further along K
+        using SA = DescStride<A_MN>;
+        using SB = DescStride<B_MN>;
+        const uint32_t ka = kk * SA::kstep, kb = kk * SB::kstep;
+        const uint64_t da_h = tc_make_desc(a_h + ka, SA::lbo, SA::sbo, SA::layout);
+        const uint64_t db_h = tc_make_desc(b_h + kb, SB::lbo, SB::sbo, SB::layout);
         tc_mma_tf32(tmem, da_h, db_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
         if (split) {
-          const uint64_t da_l = tc_make_desc(a_l + koff, kLBO, kSBO), db_l = tc_make_desc(b_l + koff, kLBO, kSBO);
+          const uint64_t da_l = tc_make_desc(a_l + ka, SA::lbo, SA::sbo, SA::layout);
+          const uint64_t db_l = tc_make_desc(b_l + kb, SB::lbo, SB::sbo, SB::layout);
           tc_mma_tf32(tmem, da_h, db_l, idesc, 1u);
           tc_mma_tf32(tmem, da_l, db_h, idesc, 1u);
         }
@@ -384,15 +429,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const TcGemmArgs
   }
 }
 
-template <int BN>
+template <int BN, bool A_MN, bool B_MN>
 static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   constexpr size_t smem = (size_t)((kStages + 2) * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
   static bool configured = false;
   if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  gemm_tc_kernel<BN><<<grid, kTcThreads, smem, stream>>>(g);
+  gemm_tc_kernel<BN, A_MN, B_MN><<<grid, kTcThreads, smem, stream>>>(g);
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -404,6 +449,16 @@ __global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float
     for (int z = 1; z < splits; z++) s += partial[(int64_t)z * mn + i];
     c[i] = s;
   }
+}
+
+// The three operand layouts of the GCN step: Y W (B transposed in memory relative to K-major), Y^T dZ
+// (both), dZ W^T (neither).
+template <int BN>
+static int launch_layout(const TcGemmArgs &g, int trans_a, int trans_b, dim3 grid, cudaStream_t stream) {
+  if (!trans_a && !trans_b) return launch_tc<BN, false, true>(g, grid, stream);
+  if (trans_a && !trans_b) return launch_tc<BN, true, true>(g, grid, stream);
+  if (!trans_a && trans_b) return launch_tc<BN, false, false>(g, grid, stream);
+  return launch_tc<BN, true, false>(g, grid, stream);
 }
 
 static int vec_of(const float *p, int64_t ld) {
@@ -427,9 +482,10 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
   const int bn = N > 64 ? 128 : (N > 32 ? 64 : 32);
   const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   int splits = 1;
-  if (tiles < kNumSMs && K >= 8 * kBK) {
-    splits = (int)((kNumSMs + tiles - 1) / tiles);
-    const int64_t max_splits = K / (4 * kBK);
+  const int64_t slots = (int64_t)kNumSMs * kCtasPerSM;   // CTAs resident at once
+  if (tiles < slots && K >= 256) {
+    splits = (int)(slots / tiles);
+    const int64_t max_splits = K / 128;
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
   }
@@ -447,9 +503,9 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
   if (grid.y > 65535) return fail(NB_ERR_INVALID, "nb_gemm: N too large for one launch");
   int st;
   switch (bn) {
-    case 128: st = launch_tc<128>(g, grid, stream); break;
-    case 64: st = launch_tc<64>(g, grid, stream); break;
-    default: st = launch_tc<32>(g, grid, stream); break;
+    case 128: st = launch_layout<128>(g, trans_a, trans_b, grid, stream); break;
+    case 64: st = launch_layout<64>(g, trans_a, trans_b, grid, stream); break;
+    default: st = launch_layout<32>(g, trans_a, trans_b, grid, stream); break;
   }
   if (st != 0) return st;
   if (splits > 1) {
