@@ -315,6 +315,11 @@ int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb
  * they were made.  d_seeds must stay valid until the batch has been sampled.  nb_gcn_compute on the batch blocks
  * until then and returns the sampling's error, if any.  nb_gcn_batch_destroy: only after that. */
 int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
+/* Number of library threads that serve nb_gcn_sample_async (default 1, at most 8).  With more than one,
+ * several batches are drawn at the same time, each on the stream its request named (use one stream per
+ * batch); every request takes its place in the sampler's sequence of draws when it is made, so results do
+ * not depend on the number of threads. */
+int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
 /* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
  * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
  * algorithmic bytes and the launch count since timing was switched on (or last read). */

@@ -81,6 +81,7 @@ SIGNATURES = {
     "nb_gcn_batch_destroy": (C.c_int, [ptr]),
     "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
     "nb_gcn_sample_async": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
+    "nb_gcn_set_sampler_threads": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),

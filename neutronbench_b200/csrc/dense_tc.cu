@@ -14,6 +14,7 @@
 // from shared-memory descriptors; the accumulator lives in tensor memory and is read back with
 // tcgen05.ld (a warp reaches its own 32 TMEM lanes).  A tcgen05.commit mbarrier per stage tells when
 // the MMAs that read it have finished.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace nb {
@@ -35,6 +36,7 @@ struct TcGemmArgs {
   int64_t k_per_split;
   int a_vec, b_vec;         // widest aligned vector (floats) along the unit-stride dimension
   int mode;                 // 1: 3xTF32, 2: 1xTF32
+  int debug;
 };
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -314,6 +316,7 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
   const int full_chunks = (int)((k_end - k_begin) / kBK);   // chunks without a K tail
 
   auto start_copy = [&](int chunk) {
+    if (g.debug & 4) { cp_async_commit(); return; }
     if (chunk < full_chunks) {
       const int st = chunk % kStages;
       plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk);
@@ -326,6 +329,22 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
     }
     cp_async_commit();   // one group per chunk slot, empty past the end, so that the wait count is constant
   };
+  // A K-major operand is read 64 bytes per row and chunk; left alone, DRAM serves those as scattered
+  // short bursts.  Every kPrefetchChunks chunks one thread per row asks L2 for the row's next
+  // kPrefetchChunks * 64 bytes in whole lines, so DRAM sees long bursts and the chunk copies hit L2.
+  constexpr int kPrefetchChunks = 8;
+  auto prefetch_rows = [&](int chunk_lo) {
+    if (A_MN || tid >= kBM || row0 + tid >= g.M) return;
+    const int64_t k_lo = k_begin + (int64_t)chunk_lo * kBK;
+    const int64_t k_hi = min(k_end, k_lo + (int64_t)kPrefetchChunks * kBK);
+    if (k_lo >= k_hi) return;
+    const char *row = reinterpret_cast<const char *>(g.a + (row0 + tid) * g.a_row);
+    const char *lo = reinterpret_cast<const char *>(reinterpret_cast<uintptr_t>(row + k_lo * 4) & ~(uintptr_t)127);
+    const char *hi = row + k_hi * 4;
+    for (const char *q = lo; q < hi; q += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+  };
+  prefetch_rows(0);
+  prefetch_rows(kPrefetchChunks);
   start_copy(0);
   start_copy(1);
 
@@ -333,18 +352,21 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
     const int st = c % kStages, lb = c & 1;
     cp_async_wait<1>();            // this thread's copies of chunk c have landed (chunk c+1 may be in flight)
     bool mine = true;
-    if (c >= 2) {
+    if (c >= 2 && !(g.debug & 2)) {
       // MMAs of chunk c-2 done: its lo buffer (same parity) and its raw stage (refilled below) are free.
       mine = tc_mbar_wait(tc_smem_u32(&bars[(c - 2) % kStages]), ((c - 2) / kStages) & 1);
     }
     if (!__syncthreads_and(mine)) { ok = false; break; }   // also: everybody's copies of chunk c are visible
     start_copy(c + 2);             // into the stage chunk c-2 used
-    split_a.run(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
-    split_b.run(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
+    if (c % kPrefetchChunks == 0) prefetch_rows(c + 2 * kPrefetchChunks);
+    if (!(g.debug & 1)) {
+      split_a.run(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
+      split_b.run(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && !(g.debug & 2)) {
       tc_fence_after();
       const uint32_t a_h = tc_smem_u32(a_raw + st * A_TILE), a_l = tc_smem_u32(a_lo + lb * A_TILE);
       const uint32_t b_h = tc_smem_u32(b_raw + st * B_TILE), b_l = tc_smem_u32(b_lo + lb * B_TILE);
@@ -370,7 +392,7 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
   cp_async_wait<0>();   // nothing of ours may still be landing in shared memory when the CTA winds down
 
   // all MMAs done: the last commit covers every earlier one
-  if (ok && nchunks > 0) {
+  if (ok && nchunks > 0 && !(g.debug & 2)) {
     const int last = nchunks - 1;
     ok = tc_mbar_wait(tc_smem_u32(&bars[last % kStages]), (last / kStages) & 1);
   }
@@ -489,6 +511,8 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
   }
+  if (getenv("NB_TC_SPLITS")) splits = atoi(getenv("NB_TC_SPLITS"));
+  g.debug = getenv("NB_TC_DEBUG") ? atoi(getenv("NB_TC_DEBUG")) : 0;
   g.k_per_split = ((K + splits - 1) / splits + kBK - 1) / kBK * kBK;
   splits = (int)((K + g.k_per_split - 1) / g.k_per_split);
   WsScope scope(ws);

@@ -32,6 +32,7 @@ struct nb_gcn_batch {
 };
 
 struct SampleJob {
+  uint32_t draw;        // position of this batch in the sampler's stream of draws
   nb_gcn_batch *batch;
   const uint32_t *seeds;
   uint32_t n;
@@ -54,7 +55,8 @@ struct nb_gcn {
   // sampler thread (one of the reference's pipeline threads, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, reduced to
   // the part that blocks on the device): started by the first nb_gcn_sample_async
   int device = 0;
-  std::thread sampler;
+  std::vector<std::thread> samplers;
+  int sampler_threads = 1;
   std::mutex mu;
   std::condition_variable cv_job, cv_done;
   std::deque<SampleJob> jobs;
@@ -134,13 +136,13 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
 
 NB_API int nb_gcn_destroy(nb_gcn *g) {
   if (g) {
-    if (g->sampler.joinable()) {
+    if (!g->samplers.empty()) {
       {
         std::lock_guard<std::mutex> lk(g->mu);
         g->stop = true;
       }
       g->cv_job.notify_all();
-      g->sampler.join();
+      for (std::thread &t : g->samplers) t.join();
     }
     for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
     if (g->own.sampled) cudaEventDestroy(g->own.sampled);
@@ -184,7 +186,7 @@ int ensure_events(nb_gcn_batch *bt) {
 }
 
 // sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106).
-int sample_into(nb_gcn *g, nb_gcn_batch *bt, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
+int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
   const nb_gcn_config &c = g->cfg;
   const uint32_t L = c.num_layers;
   nb_ws *ws = bt->ws;
@@ -209,7 +211,7 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, const uint32_t *d_seeds, uint32_t n
     NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
     NB_TRY(arena(ws, b.e, &b.row_indices));
     NB_TRY(nb_sample_hop(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, c.fanout[h], b.column_offset, c.seed,
-                         (g->draws << 8) | h, b.row_indices, stream));
+                         (draw << 8) | h, b.row_indices, stream));
     const size_t cap = b.e < c.num_vertices ? (b.e ? b.e : 1) : c.num_vertices;
     NB_TRY(arena(ws, cap, &b.source));
     NB_TRY(arena(ws, cap + 1, &b.row_offset));
@@ -221,7 +223,6 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, const uint32_t *d_seeds, uint32_t n
     dst = b.source;
     v = b.s;
   }
-  g->draws++;
   bt->layers = L;
   for (uint32_t l = 0; l < L; l++) bt->blk[l] = hops[L - 1 - l];
   NB_CUDA(cudaEventRecord(bt->sampled, nb::as_stream(stream)));
@@ -331,7 +332,7 @@ void sampler_main(nb_gcn *g) {
       job = g->jobs.front();
       g->jobs.pop_front();
     }
-    const int st = sample_into(g, job.batch, job.seeds, job.n, job.stream);
+    const int st = sample_into(g, job.batch, job.draw, job.seeds, job.n, job.stream);
     {
       std::lock_guard<std::mutex> lk(g->mu);
       job.batch->status = st;
@@ -366,14 +367,13 @@ NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds
   NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample: null pointer");
   NB_REQUIRE(n_seeds > 0, "nb_gcn_sample: empty batch");
   NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample: a batch needs a workspace of its own, not the model's");
+  uint32_t draw;
   {
-    std::unique_lock<std::mutex> lk(g->mu);   // keep the order of sampler draws: let queued batches go first
-    g->cv_done.wait(lk, [&] {
-      if (batch->pending) return false;
-      return g->jobs.empty();
-    });
+    std::unique_lock<std::mutex> lk(g->mu);
+    g->cv_done.wait(lk, [&] { return !batch->pending; });
+    draw = g->draws++;
   }
-  return sample_into(g, batch, d_seeds, n_seeds, stream);
+  return sample_into(g, batch, draw, d_seeds, n_seeds, stream);
 }
 
 NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds,
@@ -383,17 +383,27 @@ NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d
   NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample_async: a batch needs a workspace of its own, not the model's");
   std::lock_guard<std::mutex> lk(g->mu);
   NB_REQUIRE(!batch->pending, "nb_gcn_sample_async: this batch is still being sampled");
-  if (!g->sampler.joinable()) {
+  while ((int)g->samplers.size() < g->sampler_threads) {
     try {
-      g->sampler = std::thread(sampler_main, g);
+      g->samplers.emplace_back(sampler_main, g);
     } catch (...) {
-      return nb::fail(NB_ERR_NOMEM, "nb_gcn_sample_async: cannot start the sampler thread");
+      if (g->samplers.empty()) return nb::fail(NB_ERR_NOMEM, "nb_gcn_sample_async: cannot start a sampler thread");
+      break;
     }
   }
   batch->pending = true;
   batch->status = 0;
-  g->jobs.push_back(SampleJob{batch, d_seeds, n_seeds, stream});
+  g->jobs.push_back(SampleJob{g->draws++, batch, d_seeds, n_seeds, stream});
   g->cv_job.notify_one();
+  return 0;
+}
+
+NB_API int nb_gcn_set_sampler_threads(nb_gcn *g, int threads) {
+  NB_REQUIRE(g != nullptr, "nb_gcn_set_sampler_threads: null pointer");
+  NB_REQUIRE(threads >= 1 && threads <= 8, "nb_gcn_set_sampler_threads: 1..8 threads");
+  std::lock_guard<std::mutex> lk(g->mu);
+  NB_REQUIRE((int)g->samplers.size() <= threads, "nb_gcn_set_sampler_threads: threads cannot be taken away");
+  g->sampler_threads = threads;
   return 0;
 }
 
@@ -409,7 +419,12 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
   NB_REQUIRE(g && d_seeds && d_stats, "nb_gcn_step: null pointer");
   NB_REQUIRE(n_seeds > 0, "nb_gcn_step: empty batch");
   g->own.in_use = false;   // same stream and same arena: stream order alone protects the arrays
-  NB_TRY(sample_into(g, &g->own, d_seeds, n_seeds, stream));
+  uint32_t draw;
+  {
+    std::lock_guard<std::mutex> lk(g->mu);
+    draw = g->draws++;
+  }
+  NB_TRY(sample_into(g, &g->own, draw, d_seeds, n_seeds, stream));
   return compute_from(g, &g->own, train, d_stats, info, stream);
 }
 

@@ -190,7 +190,7 @@ NB_API int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offse
   NB_REQUIRE(v == 0 || d_dst, "nb_sample_hop_offsets: null destination list");
   NB_REQUIRE(fanout != 0, "nb_sample_hop_offsets: fanout must be positive, or negative for all neighbours");
   cudaStream_t stream = as_stream(stream_);
-  if (v > 0 && v <= kSingleBlockScanMax) {
+  if (v > 0 && v <= kSingleBlockGatherScanMax) {
     scan_single_block<uint32_t, ScanLoadHopCount><<<1, 1024, 0, stream>>>(
         ScanLoadHopCount{d_graph_column_offset, d_dst, fanout}, d_column_offset, v, true);
     NB_LAUNCH_CHECK();

@@ -144,7 +144,7 @@ class GCN_GPU_NEIGHBOR_impl:
         # subgraphs in flight, sampling on a stream of its own
         self._batches = None
         self._batch_ws = None
-        self._sample_stream = None
+        self._sample_streams = None
 
     def _timed(self, name: str, nbytes: int, fn):
         """Runs fn(); with self.events set, brackets it with CUDA events on the current stream."""
@@ -318,19 +318,23 @@ class GCN_GPU_NEIGHBOR_impl:
 
     # ------------------------------------------------------------------ pipelined halves of the native step
     def _ensure_pipeline(self):
+        """PIPELINES = P keeps P sampled subgraphs in flight: one training, P-1 being drawn, each by a
+        library thread on a stream of its own."""
         if self._batches is not None:
             return
         import ctypes as C
-        self._sample_stream = torch.cuda.Stream(device=self.device)
-        self._batch_ws = [Workspace(default_workspace_bytes(self.graph.global_vertices, self.cfg)) for _ in range(2)]
-        self._slot_seeds = [torch.empty(self.cfg.batch_size, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self._slot_refs = [None, None]
+        slots = max(2, int(self.cfg.pipelines))
+        self._sample_streams = [torch.cuda.Stream(device=self.device) for _ in range(slots)]
+        self._batch_ws = [Workspace(default_workspace_bytes(self.graph.global_vertices, self.cfg)) for _ in range(slots)]
+        self._slot_seeds = [torch.empty(self.cfg.batch_size, dtype=torch.int32).pin_memory() for _ in range(slots)]
+        self._slot_refs = [None] * slots
         self._stats_ring = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._batches = []
         for w in self._batch_ws:
             h = C.c_void_p()
             _lib.call("nb_gcn_batch_create", C.byref(h), w.handle)
             self._batches.append(h)
+        _lib.call("nb_gcn_set_sampler_threads", self._ensure_engine(), slots - 1)
 
     def sample_batch(self, sampler: Sampler, slot: int):
         """Asks the library's sampler thread (nb_gcn_sample_async) to draw the sampler's next batch into
@@ -339,7 +343,7 @@ class GCN_GPU_NEIGHBOR_impl:
         seeds, n = sampler.next_seeds_into(self._slot_seeds[slot])
         self._slot_refs[slot] = seeds   # keeps a staged device slice alive until the batch is computed
         _lib.call("nb_gcn_sample_async", self._ensure_engine(), self._batches[slot], ptr(seeds), n,
-                  self._sample_stream.cuda_stream)
+                  self._sample_streams[slot].cuda_stream)
         return n
 
     def compute_batch(self, slot: int, train: bool = True):
@@ -365,13 +369,21 @@ class GCN_GPU_NEIGHBOR_impl:
         loss_sum = 0.0
         if not sampler.sample_not_finished() or (max_batches is not None and max_batches <= 0):
             return correct, nodes, loss_sum, batches
-        self.sample_batch(sampler, 0)
-        slot, issued = 0, 1
+        self._ensure_pipeline()
+        slots = len(self._batches)
+
+        def more_to_issue():
+            return sampler.sample_not_finished() and (max_batches is None or issued < max_batches)
+
+        issued = 0
+        while issued < slots - 1 and more_to_issue():   # fill the pipeline
+            self.sample_batch(sampler, issued % slots)
+            issued += 1
+        slot = 0
         pending_read = None
         while True:
-            more = sampler.sample_not_finished() and (max_batches is None or issued < max_batches)
-            if more:   # the sampler thread draws batch i+1 while this thread enqueues batch i
-                self.sample_batch(sampler, slot ^ 1)
+            if more_to_issue():   # the sampler threads draw ahead while this thread enqueues batch i
+                self.sample_batch(sampler, issued % slots)
                 issued += 1
             info = self.compute_batch(slot, train=train)
             if train:
@@ -391,9 +403,9 @@ class GCN_GPU_NEIGHBOR_impl:
             nodes += info.v[self.layers - 1]
             if on_batch is not None:
                 on_batch(batches)
-            if not more:
+            if batches >= issued:
                 break
-            slot ^= 1
+            slot = (slot + 1) % slots
         if pending_read is not None:
             pending_read[1].synchronize()
             loss_sum += float(pending_read[0][0])
