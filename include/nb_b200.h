@@ -325,6 +325,9 @@ int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
  * algorithmic bytes and the launch count since timing was switched on (or last read). */
 int nb_gcn_set_timing(nb_gcn *g, int enabled);
 int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t *agg_launches);
+/* The same, split in two classes: [0] the layer-0 forward aggregation (the launch that reads the feature rows,
+ * the dominant kernel of a step), [1] all other aggregation launches. */
+int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]);
 
 #ifdef __cplusplus
 }

@@ -85,6 +85,7 @@ SIGNATURES = {
     "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "nb_gcn_read_timing_by_class": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
                           C.c_float, C.c_float, C.c_float, ptr]),
 }

@@ -52,6 +52,8 @@ struct nb_gcn {
   std::vector<cudaEvent_t> ev_pool;   // pairs: start, stop
   size_t ev_used = 0;
   uint64_t timed_bytes = 0;
+  std::vector<int> ev_class;         // per pair: 0 = layer-0 forward aggregation, 1 = any other aggregation
+  std::vector<uint64_t> ev_bytes;
   // sampler thread (one of the reference's pipeline threads, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, reduced to
   // the part that blocks on the device): started by the first nb_gcn_sample_async
   int device = 0;
@@ -88,7 +90,7 @@ struct AggTimer {
   nb_gcn *g;
   cudaStream_t st;
   bool on;
-  AggTimer(nb_gcn *g_, void *stream, uint64_t bytes) : g(g_), st(nb::as_stream(stream)), on(g_->timing) {
+  AggTimer(nb_gcn *g_, void *stream, uint64_t bytes, int cls = 1) : g(g_), st(nb::as_stream(stream)), on(g_->timing) {
     if (!on) return;
     if (g->ev_used + 2 > g->ev_pool.size()) {
       cudaEvent_t a, b;
@@ -98,6 +100,8 @@ struct AggTimer {
     }
     cudaEventRecord(g->ev_pool[g->ev_used], st);
     g->timed_bytes += bytes;
+    g->ev_class.push_back(cls);
+    g->ev_bytes.push_back(bytes);
   }
   ~AggTimer() {
     if (!on) return;
@@ -157,23 +161,38 @@ NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
   g->timing = enabled != 0;
   g->ev_used = 0;
   g->timed_bytes = 0;
+  g->ev_class.clear();
+  g->ev_bytes.clear();
+  return 0;
+}
+
+NB_API int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]) {
+  NB_REQUIRE(g && ms && bytes && launches, "nb_gcn_read_timing_by_class: null pointer");
+  for (int k = 0; k < 2; k++) { ms[k] = 0.0; bytes[k] = 0; launches[k] = 0; }
+  for (size_t i = 0; i + 1 < g->ev_used; i += 2) {
+    NB_CUDA(cudaEventSynchronize(g->ev_pool[i + 1]));
+    float t = 0.0f;
+    NB_CUDA(cudaEventElapsedTime(&t, g->ev_pool[i], g->ev_pool[i + 1]));
+    const int k = g->ev_class[i / 2] == 0 ? 0 : 1;
+    ms[k] += t;
+    bytes[k] += g->ev_bytes[i / 2];
+    launches[k]++;
+  }
+  g->ev_used = 0;
+  g->timed_bytes = 0;
+  g->ev_class.clear();
+  g->ev_bytes.clear();
   return 0;
 }
 
 NB_API int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t *agg_launches) {
   NB_REQUIRE(g && agg_ms && agg_bytes && agg_launches, "nb_gcn_read_timing: null pointer");
-  double total = 0.0;
-  for (size_t i = 0; i + 1 < g->ev_used; i += 2) {
-    NB_CUDA(cudaEventSynchronize(g->ev_pool[i + 1]));
-    float ms = 0.0f;
-    NB_CUDA(cudaEventElapsedTime(&ms, g->ev_pool[i], g->ev_pool[i + 1]));
-    total += ms;
-  }
-  *agg_ms = total;
-  *agg_bytes = g->timed_bytes;
-  *agg_launches = g->ev_used / 2;
-  g->ev_used = 0;
-  g->timed_bytes = 0;
+  double ms[2];
+  uint64_t bytes[2], launches[2];
+  NB_TRY(nb_gcn_read_timing_by_class(g, ms, bytes, launches));
+  *agg_ms = ms[0] + ms[1];
+  *agg_bytes = bytes[0] + bytes[1];
+  *agg_launches = launches[0] + launches[1];
   return 0;
 }
 
@@ -252,7 +271,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
     NB_TRY(arena(ws, (size_t)b.v * Fi, &Y[l]));
     if (l == 0) {
       if (c.fuse_gather) {
-        AggTimer t(g, stream, bytes_fwd(b, Fi, true, c.d_hashmap != nullptr));
+        AggTimer t(g, stream, bytes_fwd(b, Fi, true, c.d_hashmap != nullptr), 0);
         NB_TRY(nb_spmm_csc_fwd_gather_fused(ws, c.feat, c.feat_ld, c.d_cache, c.cache_ld, c.d_hashmap, b.source, Y[0],
                                             b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, b.s, b.e, Fi,
                                             stream));
@@ -261,7 +280,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
         NB_TRY(arena(ws, (size_t)b.s * Fi, &X[0]));
         NB_TRY(nb_feature_gather(X[0], c.feat, c.feat_ld, nullptr, 0, 0, c.d_cache, c.cache_ld, c.d_hashmap, b.source,
                                  b.s, Fi, stream));
-        AggTimer t(g, stream, bytes_fwd(b, Fi, false, false));
+        AggTimer t(g, stream, bytes_fwd(b, Fi, false, false), 0);
         NB_TRY(nb_spmm_csc_fwd_fused(X[0], Y[0], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi,
                                      stream));
         agg_bytes += bytes_fwd(b, Fi, false, false);

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(1024) scan_single_block(Load load, TOut *out, 
 
 // One block walks 8192 elements per round trip through its barrier: beyond a few rounds the three-launch
 // scan (all SMs) is faster.  Fused producers that read scattered memory per element get a lower limit.
-constexpr uint64_t kSingleBlockScanMax = 1u << 15;
+constexpr uint64_t kSingleBlockScanMax = 1u << 13;
 constexpr uint64_t kSingleBlockGatherScanMax = 1u << 12;
 
 }  // namespace nb
