@@ -206,6 +206,10 @@ int nb_label_gather(int64_t *d_lab, const int64_t *d_label, const uint32_t *d_ds
                     uint32_t label_size, void *stream);
 int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t feat_ld,
                   const uint32_t *d_hashmap, uint32_t num_vertices, uint32_t F, void *stream);
+/* d_counts[id] += 1 for every id of the list: the per-node sampling frequency that CACHE_POLICY:sample ranks
+ * nodes by (cache_sample, toolkits/GCN_GPU_NEIGHBOR.hpp:974-999, counts every block's source list over one
+ * dry-run epoch).  d_counts: num_vertices words, zeroed by the caller before the first call. */
+int nb_count_ids(const uint32_t *d_ids, uint64_t n, uint32_t num_vertices, uint32_t *d_counts, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Dense layer, loss, optimizer (the libtorch calls of vertexForward / Loss / Parameter,
@@ -320,6 +324,9 @@ int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds,
  * batch); every request takes its place in the sampler's sequence of draws when it is made, so results do
  * not depend on the number of threads. */
 int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
+/* nb_count_ids over the source list of every block of a sampled batch (one step of the dry-run epoch of
+ * CACHE_POLICY:sample); waits for the batch's sampling like nb_gcn_compute. */
+int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_counts, void *stream);
 /* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
  * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
  * algorithmic bytes and the launch count since timing was switched on (or last read). */

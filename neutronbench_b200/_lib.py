@@ -68,6 +68,7 @@ SIGNATURES = {
                                     u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_label_gather": (C.c_int, [i64p, i64p, u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_cache_fill": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_count_ids": (C.c_int, [u32p, C.c_uint64, C.c_uint32, u32p, ptr]),
     "nb_set_gemm_mode": (C.c_int, [C.c_int]),
     "nb_gemm": (C.c_int, [ptr, f32p, f32p, f32p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, ptr]),
     "nb_relu_dropout": (C.c_int, [f32p, C.c_int64, C.c_float, C.c_uint64, C.c_uint32, C.c_uint32, ptr]),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "nb_gcn_batch_destroy": (C.c_int, [ptr]),
     "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
     "nb_gcn_sample_async": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
+    "nb_gcn_count_sources": (C.c_int, [ptr, ptr, u32p, ptr]),
     "nb_gcn_set_sampler_threads": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),

@@ -417,6 +417,18 @@ NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d
   return 0;
 }
 
+NB_API int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_counts, void *stream) {
+  NB_REQUIRE(g && batch && d_counts, "nb_gcn_count_sources: null pointer");
+  NB_TRY(wait_sampled(g, batch));
+  NB_REQUIRE(batch->layers == g->cfg.num_layers && batch->sampled, "nb_gcn_count_sources: the batch holds no sampled subgraph");
+  if (batch->ws != g->ws) NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), batch->sampled, 0));
+  for (uint32_t l = 0; l < batch->layers; l++)
+    NB_TRY(nb_count_ids(batch->blk[l].source, batch->blk[l].s, g->cfg.num_vertices, d_counts, stream));
+  NB_CUDA(cudaEventRecord(batch->consumed, nb::as_stream(stream)));
+  batch->in_use = true;
+  return 0;
+}
+
 NB_API int nb_gcn_set_sampler_threads(nb_gcn *g, int threads) {
   NB_REQUIRE(g != nullptr, "nb_gcn_set_sampler_threads: null pointer");
   NB_REQUIRE(threads >= 1 && threads <= 8, "nb_gcn_set_sampler_threads: 1..8 threads");

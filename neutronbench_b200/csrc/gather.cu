@@ -96,6 +96,14 @@ __global__ void __launch_bounds__(kWarps * 32) cache_fill_kernel(float *cache, s
   }
 }
 
+// counts[id] += 1 for every id of the list (ids outside the graph are skipped)
+__global__ void count_ids_kernel(const uint32_t *__restrict__ ids, uint64_t n, uint32_t V, uint32_t *counts) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t g = ids[i];
+    if (g < V) atomicAdd(&counts[g], 1u);
+  }
+}
+
 static inline bool aligned_to(const void *p, size_t bytes) {
   return p == nullptr || (reinterpret_cast<uintptr_t>(p) % bytes) == 0;
 }
@@ -153,6 +161,14 @@ NB_API int nb_label_gather(int64_t *d_lab, const int64_t *d_label, const uint32_
   NB_REQUIRE(label_size > 0, "nb_label_gather: label_size is zero");
   label_gather_kernel<<<grid_for((uint64_t)n * label_size, 256), 256, 0, as_stream(stream)>>>(d_lab, d_label, d_dst,
                                                                                              n, label_size);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+NB_API int nb_count_ids(const uint32_t *d_ids, uint64_t n, uint32_t num_vertices, uint32_t *d_counts, void *stream) {
+  if (n == 0) return 0;
+  NB_REQUIRE(d_ids && d_counts, "nb_count_ids: null pointer");
+  nb::count_ids_kernel<<<nb::grid_for(n, 256), 256, 0, nb::as_stream(stream)>>>(d_ids, n, num_vertices, d_counts);
   NB_LAUNCH_CHECK();
   return 0;
 }

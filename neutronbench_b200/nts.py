@@ -197,19 +197,25 @@ def run(cfg_path: str, out=sys.stdout) -> float:
         feat, label, mask = random_generate(V, layers[0], layers[-1])
     else:
         feat, label, mask = read_feature_label_mask(info.feature_file, info.label_file, info.mask_file, V, layers[0])
-    cache_rate = info.cache_rate if info.cache_type == "rate" else 0.0
+    cache_type = info.cache_type or "none"
+    cache_rate = info.cache_rate if cache_type in ("rate", "random") else 0.0
+    if cache_type in ("rate", "random") and cache_rate <= 0:
+        cache_type = "none"
     cfg = GCNConfig(layers=layers, fanout=info.fanout_hop_order(), val_fanout=info.val_fanout_hop_order(),
                     batch_size=info.batch_size, learn_rate=info.learn_rate, weight_decay=info.weight_decay,
-                    drop_rate=info.drop_rate, cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate,
+                    drop_rate=info.drop_rate, cache_type=cache_type, cache_rate=cache_rate,
                     cache_policy=info.cache_policy or "degree", pipelines=max(1, int(info.pipelines)))
     feature = torch.from_numpy(feat)
+    # the table stays in pinned host memory (zero-copy misses) unless every row is cached on the GPU anyway
     feature = feature.to(dev) if cache_rate >= 1.0 else feature.pin_memory()
     datum = GNNDatum(feature, torch.from_numpy(label).to(dev), mask)
     tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg)
-    tk.init_cache()
     ids = [np.nonzero(mask == k)[0].astype(np.uint32) for k in (0, 1, 2)]
     print("label rate: %.3f, train/val/test: (%d/%d/%d)" % (sum(map(len, ids)) / V, *map(len, ids)), file=out)
     train = Sampler(graph, ids[0], cfg.fanout, cfg.batch_size, tk.ws, with_edge_weights=False)
+    tk.init_cache(train)   # CACHE_POLICY:sample runs its dry-run epoch on the training sampler
+    if tk.cache_node_num:
+        print("cache_node_num %d (%.3f)" % (tk.cache_node_num, tk.cache_node_num / V), file=out)
     # validation / test: one full batch each with the validation fanout (toolkits/...:1381-1392)
     evals = [Sampler(graph, ids[k], cfg.val_fanout, max(len(ids[k]), 1), tk.ws, full_batch=True,
                      with_edge_weights=False) if len(ids[k]) else None for k in (1, 2)]

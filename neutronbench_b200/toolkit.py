@@ -96,16 +96,47 @@ class GNNDatum:
         self.local_mask = mask        # 0 train, 1 val, 2 test (core/ntsDataloador.hpp:318-330)
 
 
-def cache_slots_by_degree(out_degree: np.ndarray, cache_num: int) -> np.ndarray:
-    """cache_high_degree + mark_cache_node (toolkits/GCN_GPU_NEIGHBOR.hpp:919-943): nodes ordered by
-    descending out degree take slots 0..cache_num-1, all others 0xFFFFFFFF.  std::sort leaves equal
-    degrees in unspecified order; here ties go by ascending id."""
-    V = len(out_degree)
-    order = np.lexsort((np.arange(V, dtype=np.int64), -out_degree.astype(np.int64)))
+def cache_slots_by_key(key: np.ndarray, cache_num: int) -> np.ndarray:
+    """mark_cache_node after a descending sort by `key` (toolkits/GCN_GPU_NEIGHBOR.hpp:930-943): the first
+    cache_num nodes of the order take slots 0..cache_num-1, all others 0xFFFFFFFF.  The reference's
+    std::sort leaves equal keys in unspecified order; here ties go by ascending id."""
+    V = len(key)
+    order = np.lexsort((np.arange(V, dtype=np.int64), -key.astype(np.int64)))
     hashmap = np.full(V, 0xFFFFFFFF, dtype=np.uint32)
     cache_num = min(int(cache_num), V)
     hashmap[order[:cache_num]] = np.arange(cache_num, dtype=np.uint32)
     return hashmap
+
+
+def cache_slots_by_degree(out_degree: np.ndarray, cache_num: int) -> np.ndarray:
+    """CACHE_POLICY:degree — cache_high_degree (toolkits/GCN_GPU_NEIGHBOR.hpp:958-967)."""
+    return cache_slots_by_key(out_degree, cache_num)
+
+
+def cache_slots_by_sample_count(sample_count: np.ndarray, cache_num: int) -> np.ndarray:
+    """CACHE_POLICY:sample — cache_sample (toolkits/GCN_GPU_NEIGHBOR.hpp:974-999): nodes ordered by how often
+    they appeared as a block source during one dry-run epoch of the training sampler."""
+    return cache_slots_by_key(sample_count, cache_num)
+
+
+def cache_slots_random(num_vertices: int, cache_num: int, seed: int) -> np.ndarray:
+    """CACHE_POLICY:random — cache_random_node (toolkits/GCN_GPU_NEIGHBOR.hpp:969-972): a seeded shuffle of
+    the node ids; the first cache_num take the slots.  (The reference shuffles with its own seeded
+    generator; only the distribution, a uniform random subset, is matched.)"""
+    order = np.random.RandomState(seed).permutation(num_vertices)
+    hashmap = np.full(num_vertices, 0xFFFFFFFF, dtype=np.uint32)
+    cache_num = min(int(cache_num), num_vertices)
+    hashmap[order[:cache_num]] = np.arange(cache_num, dtype=np.uint32)
+    return hashmap
+
+
+def cache_nodes_for_memory(free_bytes: int, feature_size: int, num_vertices: int, reserve_mb: int = 100) -> int:
+    """CACHE_TYPE:gpu_memory sizing (toolkits/GCN_GPU_NEIGHBOR.hpp:1427-1441): the memory left after a dry
+    run, minus 100 MB, divided by the bytes of one feature row."""
+    free_mb = free_bytes / (1024.0 * 1024.0) - reserve_mb
+    if free_mb <= 0:
+        return 0
+    return int(min(num_vertices, free_mb * 1024 * 1024 / 4 / feature_size))
 
 
 class GCN_GPU_NEIGHBOR_impl:
@@ -174,16 +205,38 @@ class GCN_GPU_NEIGHBOR_impl:
         return 4 * F * (v + s) + 4 * e + 4 * (s + 1) + 4 * (s + v) + (4 * F * s if masked else 0)
 
     # ------------------------------------------------------------------ cache (toolkits/...:899-999, 1214-1243)
-    def determine_cache_node_idx(self, node_nums: int):
+    def sample_counts(self, train_sampler: Sampler) -> np.ndarray:
+        """Dry-run epoch of cache_sample (toolkits/GCN_GPU_NEIGHBOR.hpp:974-999): how often every node is a
+        source of a sampled block.  The sampler is restarted afterwards; the draws are not replayed by
+        training (the reference also trains on fresh draws)."""
+        V = self.graph.global_vertices
+        counts = torch.zeros(V, dtype=torch.int32, device=self.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        while train_sampler.sample_not_finished():
+            ssg = train_sampler.sample_one()
+            for blk in ssg.sampled_sgs:
+                _lib.call("nb_count_ids", ptr(blk.source), blk.src_size, V, ptr(counts), stream)
+        train_sampler.restart()
+        return counts.cpu().numpy().view(np.uint32)
+
+    def determine_cache_node_idx(self, node_nums: int, train_sampler: Optional[Sampler] = None):
         V = self.graph.global_vertices
         node_nums = min(int(node_nums), V)
         self.cache_node_num = node_nums
         if node_nums == 0:
             return
-        assert self.cfg.cache_policy == "degree", "only CACHE_POLICY:degree is built"
-        out_deg = self.graph.out_degree.cpu().numpy().astype(np.uint32)
-        out_deg = np.maximum(out_deg, 1)  # generate_backward_structure clamp, core/graph.hpp:3983-3986
-        hashmap = cache_slots_by_degree(out_deg, node_nums)
+        policy = self.cfg.cache_policy
+        if policy == "degree":
+            out_deg = self.graph.out_degree.cpu().numpy().astype(np.uint32)
+            out_deg = np.maximum(out_deg, 1)  # generate_backward_structure clamp, core/graph.hpp:3983-3986
+            hashmap = cache_slots_by_degree(out_deg, node_nums)
+        elif policy == "sample":
+            assert train_sampler is not None, "CACHE_POLICY:sample needs the training sampler for its dry run"
+            hashmap = cache_slots_by_sample_count(self.sample_counts(train_sampler), node_nums)
+        elif policy == "random":
+            hashmap = cache_slots_random(V, node_nums, self.cfg.seed)
+        else:
+            raise ValueError(f"cache_policy {policy!r} is not one of degree | sample | random")
         self.dev_cache_node_hashmap = torch.from_numpy(hashmap.view(np.int32)).to(self.device)
         F = self.cfg.layers[0]
         ld = (F + 3) // 4 * 4  # private layout: rows padded to 16 bytes so that 128-bit loads apply
@@ -191,14 +244,26 @@ class GCN_GPU_NEIGHBOR_impl:
         feat = self.datum.local_feature
         _lib.call("nb_cache_fill", ptr(self.dev_cache_feature), ld, ptr(feat), feat.stride(0),
                   ptr(self.dev_cache_node_hashmap), V, F, torch.cuda.current_stream().cuda_stream)
+        assert self._engine is None, "the feature cache must be set up before the first native step"
 
-    def init_cache(self):
+    def init_cache(self, train_sampler: Optional[Sampler] = None):
+        """CACHE_TYPE handling of run() (toolkits/GCN_GPU_NEIGHBOR.hpp:1426-1454)."""
         c = self.cfg
-        if c.cache_type == "rate":
+        V = self.graph.global_vertices
+        if c.cache_type in ("rate", "random"):
             assert 0.0 <= c.cache_rate <= 1.0
-            self.determine_cache_node_idx(int(self.graph.global_vertices * c.cache_rate))
+            self.determine_cache_node_idx(int(V * c.cache_rate), train_sampler)
+        elif c.cache_type == "gpu_memory":
+            # The reference trains one dry-run epoch to learn libtorch's peak memory.  Here every per-step
+            # buffer comes from arenas of fixed size, so it is enough to create them (and the sampling
+            # slots of the pipelined loop) before asking the driver how much memory is left.
+            reserve = [Workspace(default_workspace_bytes(V, c)) for _ in range(max(2, c.pipelines) if c.pipelines > 1 else 0)]
+            torch.cuda.synchronize()
+            free_bytes, _total = torch.cuda.mem_get_info(self.device)
+            del reserve
+            self.determine_cache_node_idx(cache_nodes_for_memory(free_bytes, c.layers[0], V), train_sampler)
         elif c.cache_type != "none":
-            raise NotImplementedError(f"cache_type {c.cache_type}")
+            raise ValueError(f"cache_type {c.cache_type!r} is not one of none | rate | random | gpu_memory")
 
     # ------------------------------------------------------------------ one step
     def _aggregate0(self, ssg: SampledSubgraph, stream: int) -> torch.Tensor:

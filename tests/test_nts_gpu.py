@@ -10,7 +10,11 @@ from neutronbench_b200.nts import run
 pytestmark = pytest.mark.gpu
 
 
-def test_cfg_driven_training_learns(tmp_path, cuda_device):
+@pytest.mark.parametrize("cache,pipelines", [("CACHE_TYPE:rate\nCACHE_RATE:0.3\nCACHE_POLICY:degree", 1),
+                                             ("CACHE_TYPE:rate\nCACHE_RATE:0.25\nCACHE_POLICY:sample", 2),
+                                             ("CACHE_TYPE:gpu_memory\nCACHE_POLICY:random", 3)],
+                         ids=["rate_degree", "rate_sample_pipelined", "gpu_memory_random_pipelined"])
+def test_cfg_driven_training_learns(tmp_path, cuda_device, cache, pipelines):
     V, F, C = 1500, 16, 4
     rng = np.random.RandomState(0)
     label = rng.randint(0, C, V)
@@ -39,8 +43,8 @@ def test_cfg_driven_training_learns(tmp_path, cuda_device):
     cfg = tmp_path / "toy.cfg"
     cfg.write_text(f"ALGORITHM:GCNNEIGHBORGPU\nVERTICES:{V}\nLAYERS:{F}-32-{C}\nFANOUT:5,10\nVALFANOUT:5,10\n"
                    f"BATCH_SIZE:256\nBATCH_TYPE:shuffle\nEPOCHS:8\nEDGE_FILE:{base}.edge\nFEATURE_FILE:{base}.feat\n"
-                   f"LABEL_FILE:{base}.label\nMASK_FILE:{base}.mask\nMODE:zerocopy\nCACHE_TYPE:rate\nCACHE_RATE:0.3\n"
-                   f"CACHE_POLICY:degree\nLEARN_RATE:0.01\nWEIGHT_DECAY:0.0001\nDROP_RATE:0.1\nBATCH_NORM:0\n")
+                   f"LABEL_FILE:{base}.label\nMASK_FILE:{base}.mask\nMODE:zerocopy\n{cache}\nPIPELINES:{pipelines}\n"
+                   f"LEARN_RATE:0.01\nWEIGHT_DECAY:0.0001\nDROP_RATE:0.1\nBATCH_NORM:0\n")
     out = io.StringIO()
     best = run(str(cfg), out=out)
     lines = [l for l in out.getvalue().splitlines() if l.startswith("Epoch")]
