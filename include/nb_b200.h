@@ -167,6 +167,13 @@ int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices,
 int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offset, const uint32_t *d_dst,
                           uint32_t v, int fanout, uint32_t *d_column_offset, uint32_t *e_size,
                           void *stream);
+/* SAMPLE_RATE mode of the training sampler (core/ntsSampler.hpp:901-912): the count of destination i is
+ * max(int(deg * sample_rate), min(lower_fanout, deg)) instead of min(deg, fanout).  nb_sample_hop takes its
+ * counts from the offsets, so it follows with fanout = -1; subsets of more than 128 positions are drawn
+ * by selection sampling (one Philox draw per neighbour, counter word 3 = 2) instead of Floyd's algorithm. */
+int nb_sample_hop_offsets_rate(nb_ws *ws, const uint64_t *d_graph_column_offset, const uint32_t *d_dst,
+                               uint32_t v, float sample_rate, int lower_fanout, uint32_t *d_column_offset,
+                               uint32_t *e_size, void *stream);
 int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices,
                   const uint32_t *d_dst, uint32_t v, int fanout, const uint32_t *d_column_offset,
                   uint64_t seed, uint32_t hop, uint32_t *d_row_indices, void *stream);
@@ -281,6 +288,8 @@ typedef struct nb_gcn_config {
   const uint32_t *d_hashmap;
   const int64_t *d_label;                   /* one label per vertex                                 */
   float *d_W, *d_grad, *d_M, *d_V;          /* flat parameter bucket, sum of layer_size[l]*layer_size[l+1] floats each */
+  float sample_rate;                        /* SAMPLE_RATE > 0: training batches use nb_sample_hop_offsets_rate */
+  int32_t lower_fanout;                     /* LOWER_FANOUT of that mode                             */
 } nb_gcn_config;
 
 typedef struct nb_gcn_step_info {
@@ -302,7 +311,7 @@ int nb_gcn_update(nb_gcn *g, void *stream);
  * pipeline thread owns its SampledSubgraph and three streams).  A nb_gcn_batch is one SampledSubgraph
  * whose arrays live in a workspace of its own (not the model's).
  *   nb_gcn_sample  draws the batch on `stream` (d_seeds: device or pinned host memory, copied into the
- *                  batch); it synchronises that stream for the block sizes, and first waits for the
+ *                  batch; train != 0 selects the training sampler's SAMPLE_RATE mode when configured); it synchronises that stream for the block sizes, and first waits for the
  *                  compute call that last used this batch.
  *   nb_gcn_compute makes `stream` wait for the batch's sampling, then runs forward, loss and backward
  *                  exactly as nb_gcn_step; it never blocks the host.
@@ -311,14 +320,16 @@ int nb_gcn_update(nb_gcn *g, void *stream);
 typedef struct nb_gcn_batch nb_gcn_batch;
 int nb_gcn_batch_create(nb_gcn_batch **out, nb_ws *ws);
 int nb_gcn_batch_destroy(nb_gcn_batch *batch);
-int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
+int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, int train,
+                  void *stream);
 int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
                    void *stream);
 /* nb_gcn_sample on a thread of the library (started at the first call, joined by nb_gcn_destroy), so that the
  * caller's thread is free to enqueue the training of the previous batch meanwhile; requests run in the order
  * they were made.  d_seeds must stay valid until the batch has been sampled.  nb_gcn_compute on the batch blocks
  * until then and returns the sampling's error, if any.  nb_gcn_batch_destroy: only after that. */
-int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream);
+int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, int train,
+                        void *stream);
 /* Number of library threads that serve nb_gcn_sample_async (default 1, at most 8).  With more than one,
  * several batches are drawn at the same time, each on the stream its request named (use one stream per
  * batch); every request takes its place in the sampler's sequence of draws when it is made, so results do

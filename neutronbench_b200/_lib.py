@@ -30,7 +30,7 @@ class GcnConfig(C.Structure):
                 ("fuse_gather", C.c_int), ("d_graph_column_offset", C.c_void_p), ("d_graph_row_indices", C.c_void_p),
                 ("feat", C.c_void_p), ("feat_ld", C.c_size_t), ("d_cache", C.c_void_p), ("cache_ld", C.c_size_t),
                 ("d_hashmap", C.c_void_p), ("d_label", C.c_void_p), ("d_W", C.c_void_p), ("d_grad", C.c_void_p),
-                ("d_M", C.c_void_p), ("d_V", C.c_void_p)]
+                ("d_M", C.c_void_p), ("d_V", C.c_void_p), ("sample_rate", C.c_float), ("lower_fanout", C.c_int32)]
 
 
 class GcnStepInfo(C.Structure):
@@ -62,6 +62,8 @@ SIGNATURES = {
     "nb_block_build": (C.c_int, [ptr, C.c_uint32, u32p, u32p, C.c_uint32, C.c_uint32, u32p,
                                  C.POINTER(C.c_uint32), u32p, u32p, f32p, f32p, f32p, f32p, ptr]),
     "nb_sample_hop_offsets": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_int, u32p, C.POINTER(C.c_uint32), ptr]),
+    "nb_sample_hop_offsets_rate": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_float, C.c_int, u32p,
+                                             C.POINTER(C.c_uint32), ptr]),
     "nb_sample_hop": (C.c_int, [u64p, u32p, u32p, C.c_uint32, C.c_int, u32p, C.c_uint64, C.c_uint32, u32p, ptr]),
     "nb_graph_build_csc": (C.c_int, [ptr, u32p, C.c_uint64, C.c_uint32, u64p, u32p, u32p, u32p, ptr]),
     "nb_feature_gather": (C.c_int, [f32p, f32p, C.c_size_t, ptr, C.c_uint32, C.c_uint32, f32p, C.c_size_t, u32p,
@@ -80,8 +82,8 @@ SIGNATURES = {
     "nb_gcn_update": (C.c_int, [ptr] * 2),
     "nb_gcn_batch_create": (C.c_int, [C.POINTER(C.c_void_p), ptr]),
     "nb_gcn_batch_destroy": (C.c_int, [ptr]),
-    "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
-    "nb_gcn_sample_async": (C.c_int, [ptr, ptr, u32p, C.c_uint32, ptr]),
+    "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.c_int, ptr]),
+    "nb_gcn_sample_async": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.c_int, ptr]),
     "nb_gcn_count_sources": (C.c_int, [ptr, ptr, u32p, ptr]),
     "nb_gcn_set_sampler_threads": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),

@@ -32,6 +32,7 @@ struct nb_gcn_batch {
 };
 
 struct SampleJob {
+  int train;
   uint32_t draw;        // position of this batch in the sampler's stream of draws
   nb_gcn_batch *batch;
   const uint32_t *seeds;
@@ -119,6 +120,8 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   NB_REQUIRE(cfg->d_W && cfg->d_grad && cfg->d_M && cfg->d_V, "nb_gcn_create: null parameter buffers");
   NB_REQUIRE(cfg->feat || (cfg->d_cache && cfg->d_hashmap), "nb_gcn_create: no feature store");
   NB_REQUIRE(cfg->drop_rate >= 0.0f && cfg->drop_rate < 1.0f, "nb_gcn_create: drop rate must be in [0,1)");
+  NB_REQUIRE(cfg->sample_rate >= 0.0f && cfg->sample_rate <= 1.0f && cfg->lower_fanout >= 0,
+             "nb_gcn_create: sample rate must be in [0,1] and the lower fan-out non-negative");
   for (uint32_t l = 0; l <= cfg->num_layers; l++) NB_REQUIRE(cfg->layer_size[l] > 0, "nb_gcn_create: zero layer width");
   for (uint32_t l = 0; l < cfg->num_layers; l++) NB_REQUIRE(cfg->fanout[l] != 0, "nb_gcn_create: zero fanout");
   nb_gcn *g = new (std::nothrow) nb_gcn();
@@ -205,7 +208,8 @@ int ensure_events(nb_gcn_batch *bt) {
 }
 
 // sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106).
-int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
+int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_seeds, uint32_t n_seeds, int train,
+                void *stream) {
   const nb_gcn_config &c = g->cfg;
   const uint32_t L = c.num_layers;
   nb_ws *ws = bt->ws;
@@ -227,9 +231,14 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
     b.v = v;
     b.destination = const_cast<uint32_t *>(dst);
     NB_TRY(arena(ws, (size_t)v + 1, &b.column_offset));
-    NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
+    const bool by_rate = train && c.sample_rate > 0.0f;   // core/ntsSampler.hpp:901-912
+    if (by_rate)
+      NB_TRY(nb_sample_hop_offsets_rate(ws, c.d_graph_column_offset, dst, v, c.sample_rate, c.lower_fanout,
+                                        b.column_offset, &b.e, stream));
+    else
+      NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
     NB_TRY(arena(ws, b.e, &b.row_indices));
-    NB_TRY(nb_sample_hop(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, c.fanout[h], b.column_offset, c.seed,
+    NB_TRY(nb_sample_hop(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, by_rate ? -1 : c.fanout[h], b.column_offset, c.seed,
                          (draw << 8) | h, b.row_indices, stream));
     const size_t cap = b.e < c.num_vertices ? (b.e ? b.e : 1) : c.num_vertices;
     NB_TRY(arena(ws, cap, &b.source));
@@ -351,7 +360,7 @@ void sampler_main(nb_gcn *g) {
       job = g->jobs.front();
       g->jobs.pop_front();
     }
-    const int st = sample_into(g, job.batch, job.draw, job.seeds, job.n, job.stream);
+    const int st = sample_into(g, job.batch, job.draw, job.seeds, job.n, job.train, job.stream);
     {
       std::lock_guard<std::mutex> lk(g->mu);
       job.batch->status = st;
@@ -382,7 +391,8 @@ NB_API int nb_gcn_batch_destroy(nb_gcn_batch *bt) {
   return 0;
 }
 
-NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, void *stream) {
+NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, int train,
+                         void *stream) {
   NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample: null pointer");
   NB_REQUIRE(n_seeds > 0, "nb_gcn_sample: empty batch");
   NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample: a batch needs a workspace of its own, not the model's");
@@ -392,10 +402,10 @@ NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds
     g->cv_done.wait(lk, [&] { return !batch->pending; });
     draw = g->draws++;
   }
-  return sample_into(g, batch, draw, d_seeds, n_seeds, stream);
+  return sample_into(g, batch, draw, d_seeds, n_seeds, train, stream);
 }
 
-NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds,
+NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, int train,
                                void *stream) {
   NB_REQUIRE(g && batch && d_seeds, "nb_gcn_sample_async: null pointer");
   NB_REQUIRE(n_seeds > 0, "nb_gcn_sample_async: empty batch");
@@ -412,7 +422,7 @@ NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d
   }
   batch->pending = true;
   batch->status = 0;
-  g->jobs.push_back(SampleJob{g->draws++, batch, d_seeds, n_seeds, stream});
+  g->jobs.push_back(SampleJob{train, g->draws++, batch, d_seeds, n_seeds, stream});
   g->cv_job.notify_one();
   return 0;
 }
@@ -455,7 +465,7 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
     std::lock_guard<std::mutex> lk(g->mu);
     draw = g->draws++;
   }
-  NB_TRY(sample_into(g, &g->own, draw, d_seeds, n_seeds, stream));
+  NB_TRY(sample_into(g, &g->own, draw, d_seeds, n_seeds, train, stream));
   return compute_from(g, &g->own, train, d_stats, info, stream);
 }
 

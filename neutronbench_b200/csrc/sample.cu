@@ -29,6 +29,25 @@ struct ScanLoadHopCount {
   }
 };
 
+constexpr uint32_t kFloydMax = 128;   // Floyd's duplicate test is quadratic in the subset size
+
+// count[i] = max(int(deg * rate), min(lower, deg))  — SAMPLE_RATE mode, core/ntsSampler.hpp:901-912
+__device__ __forceinline__ uint32_t rate_count(uint64_t deg64, float rate, int lower) {
+  const int deg = (int)deg64;
+  const int lo = lower < deg ? lower : deg;
+  const int by_rate = (int)__fmul_rn((float)deg, rate);
+  int k = by_rate > lo ? by_rate : lo;
+  k = k > deg ? deg : k;
+  return (uint32_t)(k < 0 ? 0 : k);
+}
+__global__ void hop_counts_rate_kernel(const uint64_t *__restrict__ g_co, const uint32_t *__restrict__ dst, uint32_t v,
+                                       float rate, int lower, uint32_t *__restrict__ counts) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t d = dst[i];
+    counts[i] = rate_count(g_co[d + 1] - g_co[d], rate, lower);
+  }
+}
+
 // One thread per destination.  deg <= fanout: copy the column.  Otherwise Floyd's algorithm picks
 // `fanout` distinct positions; the chosen positions are parked in the output slots (read back by the
 // same thread for the membership test) and then replaced by the neighbour ids.
@@ -42,11 +61,21 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
     const uint32_t deg = (uint32_t)(g_co[d + 1] - base);
     const uint32_t pos = column_offset[i];
     const uint32_t k = column_offset[i + 1] - pos;
-    if (fanout < 0 || deg <= (uint32_t)fanout) {
+    if (k >= deg) {   // the counts already carry the fan-out rule: nothing to choose
       for (uint32_t j = 0; j < deg; j++) row_indices[pos + j] = g_ri[base + j];
       continue;
     }
     uint32_t r[4];
+    if (k > kFloydMax) {
+      // Large subsets (SAMPLE_RATE on hub vertices): selection sampling, one draw per neighbour in column
+      // order (stream tag 2 in the fourth counter word); picks exactly k, in ascending position.
+      uint32_t m = 0;
+      for (uint32_t j = 0; j < deg && m < k; j++) {
+        if ((j & 3) == 0) philox4x32_10(j >> 2, (uint32_t)i, hop, 2u, seed_lo, seed_hi, r);
+        if (__umulhi(r[j & 3], deg - j) < k - m) row_indices[pos + m++] = g_ri[base + j];
+      }
+      continue;
+    }
     for (uint32_t t = 0; t < k; t++) {
       if ((t & 3) == 0) philox4x32_10(t >> 2, (uint32_t)i, hop, 0u, seed_lo, seed_hi, r);
       const uint32_t j = deg - k + t;
@@ -202,6 +231,26 @@ NB_API int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offse
     }
     NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   }
+  NB_CUDA(cudaMemcpyAsync(ws->mailbox + 2, d_column_offset + v, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
+  NB_CUDA(cudaStreamSynchronize(stream));
+  *e_size = ws->mailbox[2];
+  return 0;
+}
+
+NB_API int nb_sample_hop_offsets_rate(nb_ws *ws, const uint64_t *d_graph_column_offset, const uint32_t *d_dst, uint32_t v,
+                                      float sample_rate, int lower_fanout, uint32_t *d_column_offset, uint32_t *e_size,
+                                      void *stream_) {
+  NB_REQUIRE(ws && d_graph_column_offset && d_column_offset && e_size, "nb_sample_hop_offsets_rate: null pointer");
+  NB_REQUIRE(v == 0 || d_dst, "nb_sample_hop_offsets_rate: null destination list");
+  NB_REQUIRE(sample_rate > 0.0f && sample_rate <= 1.0f, "nb_sample_hop_offsets_rate: sample rate must be in (0, 1]");
+  NB_REQUIRE(lower_fanout >= 0, "nb_sample_hop_offsets_rate: negative lower fan-out");
+  cudaStream_t stream = as_stream(stream_);
+  if (v > 0) {
+    hop_counts_rate_kernel<<<grid_for(v, kThreads), kThreads, 0, stream>>>(d_graph_column_offset, d_dst, v, sample_rate,
+                                                                          lower_fanout, d_column_offset);
+    NB_LAUNCH_CHECK();
+  }
+  NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 2, d_column_offset + v, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
   NB_CUDA(cudaStreamSynchronize(stream));
   *e_size = ws->mailbox[2];

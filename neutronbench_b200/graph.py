@@ -167,8 +167,17 @@ class Sampler:
     """
 
     def __init__(self, whole_graph: FullyRepGraph, index: Sequence[int], fanout: Sequence[int], batch_size: int,
-                 ws: Workspace, full_batch: bool = False, seed: int = 2000, with_edge_weights: bool = True):
+                 ws: Workspace, full_batch: bool = False, seed: int = 2000, with_edge_weights: bool = True,
+                 sample_rate: float = 0.0, lower_fanout: int = 0):
         self.whole_graph = whole_graph
+        # SAMPLE_RATE > 0: the training sampler takes max(int(deg * rate), min(lower_fanout, deg)) neighbours
+        # per destination instead of min(deg, fanout) (core/ntsSampler.hpp:901-912)
+        self.sample_rate = float(sample_rate)
+        self.lower_fanout = int(lower_fanout)
+        # BATCH_TYPE:random — every training batch is a fresh uniform subset of the seed list instead of
+        # the next slice of it (sampCSC::random_batch, core/coocsc.hpp:488-499)
+        self.random_batches = False
+        self._batch_rng = np.random.RandomState(int(seed))
         self.sample_nids = np.asarray(index, dtype=np.uint32).copy()
         self.fanout = list(fanout)
         self.layers = len(self.fanout)
@@ -226,31 +235,39 @@ class Sampler:
         self._pinned_seeds[:n].copy_(torch.from_numpy(seeds.view(np.int32)))
         return self._pinned_seeds[:n].to(self.whole_graph.device, non_blocking=True)
 
-    def next_seeds(self):
-        """Seeds of the next batch as a device tensor, and their number; advances work_offset
-        (the last batch of an epoch is short, core/ntsSampler.hpp:846)."""
+    def _next_seed_ids(self):
+        """Host view of the next batch's seeds (None when they are a slice of the staged device list);
+        advances work_offset (the last batch of an epoch is short, core/ntsSampler.hpp:846)."""
         assert self.work_offset < self.work_range[1]
         actl = min(self.batch_size, self.work_range[1] - self.work_offset)
         lo = self.work_offset
         self.work_offset += actl
+        if self.random_batches:
+            pick = self._batch_rng.choice(len(self.sample_nids), size=actl, replace=False)
+            return self.sample_nids[pick], lo, actl
         if self._dev_nids is not None:
+            return None, lo, actl
+        return self.sample_nids[lo: lo + actl], lo, actl
+
+    def next_seeds(self):
+        """Seeds of the next batch as a device tensor, and their number."""
+        host, lo, actl = self._next_seed_ids()
+        if host is None:
             return self._dev_nids[lo: lo + actl], actl
-        return self._seeds_to_device(self.sample_nids[lo: lo + actl]), actl
+        return self._seeds_to_device(host), actl
 
     def next_seeds_into(self, pinned: torch.Tensor):
         """Like next_seeds, for a caller that hands the seeds to a library thread: a slice of the staged
         device list, or (host seeds) a copy in the caller's pinned int32 buffer, which the library reads
         itself.  Returns (tensor whose data_ptr() holds the seeds, count)."""
-        assert self.work_offset < self.work_range[1]
-        actl = min(self.batch_size, self.work_range[1] - self.work_offset)
-        lo = self.work_offset
-        self.work_offset += actl
-        if self._dev_nids is not None:
+        host, lo, actl = self._next_seed_ids()
+        if host is None:
             return self._dev_nids[lo: lo + actl], actl
-        pinned[:actl].copy_(torch.from_numpy(self.sample_nids[lo: lo + actl].view(np.int32)))
+        pinned[:actl].copy_(torch.from_numpy(np.ascontiguousarray(host).view(np.int32)))
         return pinned[:actl], actl
 
-    def sample_one(self, ssg: Optional[SampledSubgraph] = None, raw_edges: Optional[list] = None) -> SampledSubgraph:
+    def sample_one(self, ssg: Optional[SampledSubgraph] = None, raw_edges: Optional[list] = None,
+                   phase: bool = True) -> SampledSubgraph:
         """One batch: per hop, column offsets, sampling, dedup/reindex, CSR, weights
         (core/ntsSampler.hpp:843-1106).  ``raw_edges`` (list per hop of device int32 tensors of global
         source ids laid out by the hop's column offsets) replaces the Philox sampler with an externally
@@ -264,8 +281,13 @@ class Sampler:
         for hop in range(self.layers):
             co = _i32(v + 1, g.device)
             e = C.c_uint32(0)
-            _lib.call("nb_sample_hop_offsets", self.ws.handle, ptr(g.column_offset), ptr(dst), v,
-                      int(self.fanout[hop]), ptr(co), C.byref(e), stream)
+            by_rate = phase and self.sample_rate > 0
+            if by_rate:
+                _lib.call("nb_sample_hop_offsets_rate", self.ws.handle, ptr(g.column_offset), ptr(dst), v,
+                          self.sample_rate, self.lower_fanout, ptr(co), C.byref(e), stream)
+            else:
+                _lib.call("nb_sample_hop_offsets", self.ws.handle, ptr(g.column_offset), ptr(dst), v,
+                          int(self.fanout[hop]), ptr(co), C.byref(e), stream)
             e = int(e.value)
             if raw_edges is not None:
                 ri = raw_edges[hop].clone()
@@ -274,7 +296,7 @@ class Sampler:
                 ri = _i32(max(e, 1), g.device)
                 hop_key = (self.draws << 8) | hop
                 _lib.call("nb_sample_hop", ptr(g.column_offset), ptr(g.row_indices), ptr(dst), v,
-                          int(self.fanout[hop]), ptr(co), self.seed, hop_key, ptr(ri), stream)
+                          -1 if by_rate else int(self.fanout[hop]), ptr(co), self.seed, hop_key, ptr(ri), stream)
             blk = build_block(self.ws, g.global_vertices, dst, co, ri, v, e, self.with_edge_weights, stream)
             blocks.append(blk)
             dst = blk.source

@@ -12,6 +12,7 @@ are the reference's: binary .edge (u32 src, u32 dst pairs), text .feat ("id f0 .
 """
 from __future__ import annotations
 
+import os
 import sys
 import time
 from dataclasses import dataclass, field
@@ -60,6 +61,9 @@ class InputInfo:
     cache_policy: str = "degree"
     cache_rate: float = 0.0
     pipelines: int = 1
+    sample_rate: float = -1.0
+    lower_fanout: int = 0
+    del_frac: float = 0.0
     mini_pull: int = 1
     run_time: float = -1.0
     runs: int = 1
@@ -79,6 +83,7 @@ class InputInfo:
             "CACHE_TYPE": ("cache_type", str), "CACHE_POLICY": ("cache_policy", str),
             "CACHE_RATE": ("cache_rate", float), "PIPELINES": ("pipelines", int), "MINI_PULL": ("mini_pull", int),
             "RUN_TIME": ("run_time", float), "RUNS": ("runs", int), "THREADS": ("threads", int),
+            "SAMPLE_RATE": ("sample_rate", float), "LOWER_FANOUT": ("lower_fanout", int), "DEL_FRAC": ("del_frac", float),
         }
         for line in open(path):
             line = line.rstrip("\n").rstrip("\r")
@@ -121,11 +126,20 @@ class InputInfo:
         return list(reversed(self._fanout(s)))
 
 
-def read_feature_label_mask(feature_file: str, label_file: str, mask_file: str, vertices: int, feat_dim: int):
-    """GNNDatum::readFeature_Label_Mask (core/ntsDataloador.hpp:264-330), single label per node."""
+def feature_sidecar_path(feature_file: str, vertices: int, feat_dim: int) -> str:
+    return f"{feature_file}.{vertices}x{feat_dim}.f32"
+
+
+def read_feature(feature_file: str, vertices: int, feat_dim: int, use_sidecar: bool = True) -> np.ndarray:
+    """The `.feat` text table ("id v0 v1 ..." per line, core/ntsDataloador.hpp:264-300) as float32
+    [vertices x feat_dim].  Parsing the text dominates start-up on large datasets, so the parsed table is
+    kept beside the text file as raw little-endian float32 (`<file>.<V>x<F>.f32`) and read from there
+    while it is at least as new as the text; a directory that cannot be written is not an error."""
+    side = feature_sidecar_path(feature_file, vertices, feat_dim)
+    if use_sidecar and os.path.exists(side) and os.path.getmtime(side) >= os.path.getmtime(feature_file) \
+            and os.path.getsize(side) == 4 * vertices * feat_dim:
+        return np.fromfile(side, dtype="<f4").reshape(vertices, feat_dim)
     feat = np.zeros((vertices, feat_dim), dtype=np.float32)
-    label = np.zeros(vertices, dtype=np.int64)
-    mask = np.full(vertices, 3, dtype=np.int32)
     with open(feature_file) as ff:
         for line in ff:
             parts = line.split()
@@ -134,6 +148,21 @@ def read_feature_label_mask(feature_file: str, label_file: str, mask_file: str, 
             vid = int(parts[0])
             if 0 <= vid < vertices:
                 feat[vid, :] = np.asarray(parts[1:1 + feat_dim], dtype=np.float32)
+    if use_sidecar:
+        try:
+            tmp = side + ".tmp%d" % os.getpid()
+            feat.astype("<f4").tofile(tmp)
+            os.replace(tmp, side)
+        except OSError:
+            pass
+    return feat
+
+
+def read_feature_label_mask(feature_file: str, label_file: str, mask_file: str, vertices: int, feat_dim: int):
+    """GNNDatum::readFeature_Label_Mask (core/ntsDataloador.hpp:264-330), single label per node."""
+    feat = read_feature(feature_file, vertices, feat_dim)
+    label = np.zeros(vertices, dtype=np.int64)
+    mask = np.full(vertices, 3, dtype=np.int32)
     with open(label_file) as lf:
         for line in lf:
             parts = line.split()
@@ -176,6 +205,7 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     Returns the best validation accuracy."""
     import torch
     from . import FullyRepGraph, GCN_GPU_NEIGHBOR_impl, GCNConfig, GNNDatum, Sampler, Workspace
+    from .toolkit import drop_train_ids_by_degree
 
     info = InputInfo().readFromCfgFile(cfg_path)
     if info.algorithm != "GCNNEIGHBORGPU":
@@ -204,7 +234,8 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     cfg = GCNConfig(layers=layers, fanout=info.fanout_hop_order(), val_fanout=info.val_fanout_hop_order(),
                     batch_size=info.batch_size, learn_rate=info.learn_rate, weight_decay=info.weight_decay,
                     drop_rate=info.drop_rate, cache_type=cache_type, cache_rate=cache_rate,
-                    cache_policy=info.cache_policy or "degree", pipelines=max(1, int(info.pipelines)))
+                    cache_policy=info.cache_policy or "degree", pipelines=max(1, int(info.pipelines)),
+                    sample_rate=max(0.0, info.sample_rate), lower_fanout=max(0, info.lower_fanout))
     feature = torch.from_numpy(feat)
     # the table stays in pinned host memory (zero-copy misses) unless every row is cached on the GPU anyway
     feature = feature.to(dev) if cache_rate >= 1.0 else feature.pin_memory()
@@ -212,7 +243,15 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg)
     ids = [np.nonzero(mask == k)[0].astype(np.uint32) for k in (0, 1, 2)]
     print("label rate: %.3f, train/val/test: (%d/%d/%d)" % (sum(map(len, ids)) / V, *map(len, ids)), file=out)
-    train = Sampler(graph, ids[0], cfg.fanout, cfg.batch_size, tk.ws, with_edge_weights=False)
+    if info.batch_type == "metis":
+        raise ValueError("BATCH_TYPE:metis needs the METIS library, which this build does not link")
+    if info.batch_type not in ("shuffle", "sequence", "random", "dellow", "delhigh"):
+        raise ValueError(f"BATCH_TYPE {info.batch_type!r} is not one of shuffle | sequence | random | dellow | delhigh")
+    in_deg = np.diff(graph.column_offset.cpu().numpy().astype(np.int64))
+    train_ids = drop_train_ids_by_degree(ids[0], in_deg, info.batch_type, info.del_frac)
+    train = Sampler(graph, train_ids, cfg.fanout, cfg.batch_size, tk.ws, with_edge_weights=False,
+                    sample_rate=cfg.sample_rate, lower_fanout=cfg.lower_fanout)
+    train.random_batches = info.batch_type == "random"
     tk.init_cache(train)   # CACHE_POLICY:sample runs its dry-run epoch on the training sampler
     if tk.cache_node_num:
         print("cache_node_num %d (%.3f)" % (tk.cache_node_num, tk.cache_node_num / V), file=out)
@@ -225,7 +264,8 @@ def run(cfg_path: str, out=sys.stdout) -> float:
         if info.run_time > 0 and run_time >= info.run_time:
             break
         t0 = time.time()
-        train_acc, train_loss, _ = tk.Forward(train, rng=rng if info.batch_type == "shuffle" else None, train=True)
+        # every batch type but "sequence" reshuffles the seed list per epoch (toolkits/GCN_GPU_NEIGHBOR.hpp:741-745)
+        train_acc, train_loss, _ = tk.Forward(train, rng=rng if info.batch_type != "sequence" else None, train=True)
         torch.cuda.synchronize()
         train_time = time.time() - t0
         run_time += train_time

@@ -42,6 +42,8 @@ class GCNConfig:
     beta2: float = 0.999
     epsilon: float = 1e-9                         # toolkits/GCN_GPU_NEIGHBOR.hpp:217
     pipelines: int = 1                            # PIPELINES > 1: sampling of batch i+1 overlaps training of batch i
+    sample_rate: float = 0.0                      # SAMPLE_RATE > 0: degree-proportional fan-out for training batches
+    lower_fanout: int = 0                         # LOWER_FANOUT of that mode
 
 
 class Parameter:
@@ -352,6 +354,7 @@ class GCN_GPU_NEIGHBOR_impl:
         ec.beta1, ec.beta2, ec.epsilon = c.beta1, c.beta2, c.epsilon
         ec.seed = c.seed
         ec.fuse_gather = 1 if c.fuse_gather else 0
+        ec.sample_rate, ec.lower_fanout = float(c.sample_rate), int(c.lower_fanout)
         ec.d_graph_column_offset = ptr(self.graph.column_offset)
         ec.d_graph_row_indices = ptr(self.graph.row_indices)
         feat = self.datum.local_feature
@@ -401,13 +404,13 @@ class GCN_GPU_NEIGHBOR_impl:
             self._batches.append(h)
         _lib.call("nb_gcn_set_sampler_threads", self._ensure_engine(), slots - 1)
 
-    def sample_batch(self, sampler: Sampler, slot: int):
+    def sample_batch(self, sampler: Sampler, slot: int, train: bool = True):
         """Asks the library's sampler thread (nb_gcn_sample_async) to draw the sampler's next batch into
         subgraph `slot` on the sampling stream; returns at once.  compute_batch(slot) waits for it."""
         self._ensure_pipeline()
         seeds, n = sampler.next_seeds_into(self._slot_seeds[slot])
         self._slot_refs[slot] = seeds   # keeps a staged device slice alive until the batch is computed
-        _lib.call("nb_gcn_sample_async", self._ensure_engine(), self._batches[slot], ptr(seeds), n,
+        _lib.call("nb_gcn_sample_async", self._ensure_engine(), self._batches[slot], ptr(seeds), n, 1 if train else 0,
                   self._sample_streams[slot].cuda_stream)
         return n
 
@@ -442,13 +445,13 @@ class GCN_GPU_NEIGHBOR_impl:
 
         issued = 0
         while issued < slots - 1 and more_to_issue():   # fill the pipeline
-            self.sample_batch(sampler, issued % slots)
+            self.sample_batch(sampler, issued % slots, train)
             issued += 1
         slot = 0
         pending_read = None
         while True:
             if more_to_issue():   # the sampler threads draw ahead while this thread enqueues batch i
-                self.sample_batch(sampler, issued % slots)
+                self.sample_batch(sampler, issued % slots, train)
                 issued += 1
             info = self.compute_batch(slot, train=train)
             if train:
@@ -514,7 +517,8 @@ class GCN_GPU_NEIGHBOR_impl:
             sampler.shuffle(rng)
         # the native step samples with the training fan-out and sizes its arenas for the training batch
         native = (self.use_engine and list(sampler.fanout) == list(self.cfg.fanout)
-                  and sampler.batch_size <= self.cfg.batch_size)
+                  and sampler.batch_size <= self.cfg.batch_size
+                  and (not train or (sampler.sample_rate, sampler.lower_fanout) == (self.cfg.sample_rate, self.cfg.lower_fanout)))
         if native and self.cfg.pipelines > 1:
             correct, nodes, loss_epoch, batches = self.run_pipelined(sampler, max_batches, train=train)
             sampler.restart()
@@ -528,7 +532,7 @@ class GCN_GPU_NEIGHBOR_impl:
                 info = self.engine_step(sampler, train=train)
                 batch_nodes = info.v[self.layers - 1]
             else:
-                ssg = sampler.sample_one()
+                ssg = sampler.sample_one(phase=train)
                 self.forward_backward(ssg, train=train)
                 batch_nodes = ssg.sampled_sgs[self.layers - 1].v_size
             if train:
@@ -541,6 +545,20 @@ class GCN_GPU_NEIGHBOR_impl:
             batches += 1
         sampler.restart()
         return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
+
+
+def drop_train_ids_by_degree(train_ids: np.ndarray, in_degree: np.ndarray, batch_type: str, del_frac: float) -> np.ndarray:
+    """BATCH_TYPE:dellow | delhigh with DEL_FRAC (toolkits/GCN_GPU_NEIGHBOR.hpp:1365-1377): the training ids are
+    sorted by in-degree — descending for delhigh, ascending for dellow — and the last DEL_FRAC of that order
+    is dropped, so delhigh keeps the high-degree end and dellow the low-degree end, as the reference's code
+    does.  Equal degrees are ordered by id (std::sort leaves them unspecified)."""
+    if batch_type not in ("dellow", "delhigh"):
+        return train_ids
+    deg = in_degree[train_ids].astype(np.int64)
+    key = -deg if batch_type == "delhigh" else deg
+    order = np.lexsort((train_ids.astype(np.int64), key))
+    keep = int(len(train_ids) * (1 - del_frac))
+    return train_ids[order[:keep]]
 
 
 def shard_for_rank(ids: np.ndarray, rank: int, world_size: int) -> np.ndarray:
@@ -575,6 +593,8 @@ def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
     v = cfg.batch_size
     e_max = 0
     for f in cfg.fanout:
+        if cfg.sample_rate > 0:   # degree-proportional counts have no fan-out bound: allow for hub-heavy batches
+            f = max(f if f > 0 else 64, 4 * cfg.lower_fanout, 64)
         e = v * (f if f > 0 else 64)
         e_max = max(e_max, e)
         v = min(num_vertices, e)

@@ -78,6 +78,25 @@ ORC_API vid_t orc_init_co(const uint64_t *g_column_offset, const vid_t *dst, vid
   return off;
 }
 
+/* SAMPLE_RATE mode of the training sampler (core/ntsSampler.hpp:901-912): per destination
+ * max(int(nbrs * sample_rate), min(lower_fanout, nbrs)); the product is a float multiply truncated to int. */
+ORC_API vid_t orc_init_co_rate(const uint64_t *g_column_offset, const vid_t *dst, vid_t v, float sample_rate,
+                               int lower_fanout, vid_t *column_offset /*v+1*/) {
+  vid_t off = 0;
+  for (vid_t i = 0; i < v; i++) {
+    column_offset[i] = off;
+    int nbrs = (int)(g_column_offset[dst[i] + 1] - g_column_offset[dst[i]]);
+    int lower = lower_fanout < nbrs ? lower_fanout : nbrs;
+    int by_rate = (int)((float)nbrs * sample_rate);
+    int k = by_rate > lower ? by_rate : lower;
+    if (k > nbrs) k = nbrs;
+    if (k < 0) k = 0;
+    off += (vid_t)k;
+  }
+  column_offset[v] = off;
+  return off;
+}
+
 /* --------------------------------------------------------------------------------------------
  * Counter-based random numbers: Philox4x32-10 (Salmon et al., SC'11), the published algorithm.
  * The reference draws from a thread-local std::mt19937(2000) under OpenMP (utils/rand.hpp:6-13), so
@@ -119,6 +138,7 @@ static inline uint32_t bounded(uint32_t r, uint32_t n) { return (uint32_t)(((uin
  * Philox(counter = (draw/4, local dst index, hop, 0), key = (seed_lo, seed_hi)); position t of the
  * subset uses draw t.  Within a column the order is Floyd's insertion order.
  * ------------------------------------------------------------------------------------------ */
+#define ORC_FLOYD_MAX 128u
 ORC_API void orc_sample_hop(const uint64_t *g_column_offset, const vid_t *g_row_indices,
                             const vid_t *dst, vid_t v, int fanout, const vid_t *column_offset,
                             uint64_t seed, uint32_t hop, vid_t *row_indices /*e, global ids*/) {
@@ -127,8 +147,19 @@ ORC_API void orc_sample_hop(const uint64_t *g_column_offset, const vid_t *g_row_
     uint32_t deg = (uint32_t)(g_column_offset[dst[i] + 1] - base);
     vid_t pos = column_offset[i];
     uint32_t k = column_offset[i + 1] - pos;
-    if (fanout < 0 || deg <= (uint32_t)fanout) {
+    (void)fanout;   /* the counts in column_offset already carry the fan-out rule */
+    if (k >= deg) {
       for (uint32_t j = 0; j < deg; j++) row_indices[pos + j] = g_row_indices[base + j];
+      continue;
+    }
+    if (k > ORC_FLOYD_MAX) {
+      /* Large subsets (SAMPLE_RATE on hub vertices): selection sampling, one draw per neighbour in
+       * column order, stream tag 2 in the fourth counter word; picks exactly k, ascending positions. */
+      uint32_t r[4], m = 0;
+      for (uint32_t j = 0; j < deg && m < k; j++) {
+        if ((j & 3) == 0) philox4x32_10(j >> 2, i, hop, 2, (uint32_t)seed, (uint32_t)(seed >> 32), r);
+        if (bounded(r[j & 3], deg - j) < k - m) row_indices[pos + m++] = g_row_indices[base + j];
+      }
       continue;
     }
     uint32_t *chosen = (uint32_t *)malloc(sizeof(uint32_t) * k);

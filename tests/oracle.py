@@ -21,6 +21,7 @@ def lib():
             subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "liboracle.so"])
         _lib = C.CDLL(_SO)
         _lib.orc_init_co.restype = C.c_uint32
+        _lib.orc_init_co_rate.restype = C.c_uint32
         _lib.orc_dedup_reindex.restype = C.c_uint32
         _lib.orc_softmax_nll.restype = C.c_float
         _lib.orc_num_threads.restype = C.c_int
@@ -52,6 +53,14 @@ def init_co(g_co, dst, fanout):
     dst = np.ascontiguousarray(dst, dtype=np.uint32)
     co = np.zeros(len(dst) + 1, dtype=np.uint32)
     e = lib().orc_init_co(_p(g_co), _p(dst), C.c_uint32(len(dst)), C.c_int(fanout), _p(co))
+    return co, int(e)
+
+
+def init_co_rate(g_co, dst, sample_rate, lower_fanout):
+    dst = np.ascontiguousarray(dst, dtype=np.uint32)
+    co = np.zeros(len(dst) + 1, dtype=np.uint32)
+    e = lib().orc_init_co_rate(_p(g_co), _p(dst), C.c_uint32(len(dst)), C.c_float(sample_rate), C.c_int(lower_fanout),
+                               _p(co))
     return co, int(e)
 
 
@@ -111,13 +120,14 @@ def build_block(V, dst, co, ri_global):
     return b
 
 
-def sample_batch(g_co, g_ri, V, seeds, fanouts, seed, draw=0, raw=None):
+def sample_batch(g_co, g_ri, V, seeds, fanouts, seed, draw=0, raw=None, sample_rate=0.0, lower_fanout=0):
     """Sampler::sample_one (core/ntsSampler.hpp:843-1106): blocks returned input side first.
-    ``raw`` (list per hop) injects externally sampled global edge lists."""
+    ``raw`` (list per hop) injects externally sampled global edge lists; sample_rate > 0 selects the
+    degree-proportional counts of the training sampler."""
     dst = np.ascontiguousarray(seeds, dtype=np.uint32)
     blocks, raws = [], []
     for hop, f in enumerate(fanouts):
-        co, e = init_co(g_co, dst, f)
+        co, e = init_co_rate(g_co, dst, sample_rate, lower_fanout) if sample_rate > 0 else init_co(g_co, dst, f)
         rg = raw[hop] if raw is not None else sample_hop(g_co, g_ri, dst, f, co, seed, (draw << 8) | hop)
         raws.append(np.array(rg, dtype=np.uint32, copy=True))
         b = build_block(V, dst, co, rg)

@@ -54,3 +54,27 @@ def test_epoch_line_is_parseable_by_the_reference_scraper():
     assert _parse_num(line, "val_acc") == 0.625
     assert _parse_num(line, "train_time") == 0.321
     assert _parse_num(line, "gcn_run_time") == 3.21
+
+
+def test_feature_sidecar_round_trip(tmp_path):
+    from neutronbench_b200.nts import feature_sidecar_path, read_feature
+    V, F = 40, 5
+    rng = np.random.RandomState(0)
+    feat = rng.randn(V, F).astype(np.float32)
+    path = tmp_path / "toy.feat"
+    with open(path, "w") as f:
+        for i in rng.permutation(V):                      # any line order; ids outside the graph are ignored
+            f.write(f"{i} " + " ".join(repr(float(x)) for x in feat[i]) + "\n")
+        f.write(f"{V + 3} " + " ".join("1.0" for _ in range(F)) + "\n")
+    first = read_feature(str(path), V, F)
+    np.testing.assert_array_equal(first, feat)
+    side = feature_sidecar_path(str(path), V, F)
+    import os
+    assert os.path.getsize(side) == 4 * V * F
+    np.testing.assert_array_equal(read_feature(str(path), V, F), feat)          # second read: from the side-car
+    np.testing.assert_array_equal(np.fromfile(side, dtype="<f4").reshape(V, F), feat)
+    # a stale or wrong-sized side-car is not trusted
+    with open(side, "wb") as f:
+        f.write(b"\0" * 12)
+    np.testing.assert_array_equal(read_feature(str(path), V, F), feat)
+    np.testing.assert_array_equal(read_feature(str(path), V, F, use_sidecar=False), feat)

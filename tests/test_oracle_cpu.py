@@ -159,3 +159,47 @@ def test_label_and_feature_gather():
     np.testing.assert_array_equal(oracle.feature_gather(feat, src), feat[src])
     lab = rng.randint(0, 5, 50).astype(np.int64)
     np.testing.assert_array_equal(oracle.label_gather(lab, src), lab[src])
+
+
+def test_sample_rate_counts_and_large_subsets():
+    """SAMPLE_RATE mode (core/ntsSampler.hpp:901-912): per destination max(int(deg * rate), min(lower, deg));
+    subsets above 128 positions are drawn by selection sampling and are still exact-size, distinct and
+    inside the neighbourhood."""
+    rng = np.random.RandomState(4)
+    V = 600
+    hub = np.stack([rng.randint(0, V, 900), np.zeros(900, np.int64)], axis=1)          # vertex 0: in-degree ~900
+    rest = np.stack([rng.randint(0, V, 6000), rng.randint(0, V, 6000)], axis=1)
+    edges = np.concatenate([hub, rest]).astype(np.uint32)
+    co, ri = oracle.build_csc(edges, V)
+    deg = np.diff(co.astype(np.int64))
+    dst = np.array([0, 5, 17, 300, 599, 5], dtype=np.uint32)
+    for rate, lower in ((0.5, 3), (0.05, 8), (1.0, 1)):
+        offs, e = oracle.init_co_rate(co, dst, rate, lower)
+        want = np.maximum((deg[dst].astype(np.float32) * np.float32(rate)).astype(np.int64), np.minimum(lower, deg[dst]))
+        np.testing.assert_array_equal(np.diff(offs.astype(np.int64)), want)
+        assert e == want.sum()
+        picked = oracle.sample_hop(co, ri, dst, -1, offs, 99, 3)
+        for i, d in enumerate(dst):
+            mine = picked[offs[i]: offs[i + 1]]
+            nbrs = ri[co[d]: co[d + 1]]
+            # a sample is a sub-multiset of the column: no neighbour position is used twice
+            cnt_m = np.bincount(mine, minlength=V)
+            cnt_n = np.bincount(nbrs, minlength=V)
+            assert (cnt_m <= cnt_n).all() and len(mine) == want[i]
+    offs, _ = oracle.init_co_rate(co, dst, 0.5, 3)
+    assert offs[1] - offs[0] > 128                       # the hub takes the selection-sampling path
+    a = oracle.sample_hop(co, ri, dst, -1, offs, 99, 3)
+    b = oracle.sample_hop(co, ri, dst, -1, offs, 100, 3)
+    assert not np.array_equal(a, b)                      # the seed matters
+
+
+def test_drop_train_ids_by_degree_follows_the_reference_code():
+    from neutronbench_b200 import drop_train_ids_by_degree
+    in_deg = np.array([5, 1, 9, 3, 7, 2, 8, 4], dtype=np.int64)
+    ids = np.arange(8, dtype=np.uint32)
+    np.testing.assert_array_equal(drop_train_ids_by_degree(ids, in_deg, "shuffle", 0.5), ids)
+    # delhigh: descending order, last quarter dropped -> the two lowest-degree ids go
+    np.testing.assert_array_equal(drop_train_ids_by_degree(ids, in_deg, "delhigh", 0.25), [2, 6, 4, 0, 7, 3])
+    # dellow: ascending order, last quarter dropped -> the two highest-degree ids go
+    np.testing.assert_array_equal(drop_train_ids_by_degree(ids, in_deg, "dellow", 0.25), [1, 5, 3, 7, 0, 4])
+    assert len(drop_train_ids_by_degree(ids, in_deg, "dellow", 1.0)) == 0

@@ -57,3 +57,49 @@ def test_structure_and_uniformity(cuda_device, ws):
     chi2 = ((picked - expected) ** 2 / expected).sum()
     assert chi2 < 80.0, chi2          # 39 degrees of freedom: 99.99 % quantile is about 79
     assert picked.min() > 0
+
+
+@pytest.mark.parametrize("rate,lower", [(0.5, 3), (0.1, 6), (1.0, 1)])
+def test_sample_rate_mode_matches_oracle(cuda_device, ws, rate, lower):
+    """SAMPLE_RATE / LOWER_FANOUT (core/ntsSampler.hpp:901-912): counts, Floyd draws for small subsets and
+    selection sampling for subsets above 128 positions (a hub with ~900 in-neighbours) equal the oracle's."""
+    V = 2500
+    rng = np.random.RandomState(8)
+    hub = np.stack([rng.randint(0, V, 900), np.zeros(900, np.int64)], axis=1)
+    edges = np.concatenate([hub, small_graph(V, 30000, seed=2)[0].astype(np.int64)]).astype(np.uint32)
+    co, ri = oracle.build_csc(edges, V)
+    seeds = np.concatenate([[0], rng.choice(np.arange(1, V), 149, replace=False)]).astype(np.uint32)
+    g = FullyRepGraph(dev_i64(co, cuda_device), dev_i32(ri, cuda_device), V)
+    smp = Sampler(g, seeds, (4, 4), batch_size=100, ws=ws, seed=77, sample_rate=rate, lower_fanout=lower)
+    draw = 0
+    while smp.sample_not_finished():
+        lo = smp.work_offset
+        ssg = smp.sample_one(phase=True)
+        ref, _ = oracle.sample_batch(co, ri, V, seeds[lo: lo + 100], [4, 4], seed=77, draw=draw, sample_rate=rate,
+                                     lower_fanout=lower)
+        for dev_blk, ref_blk in zip(ssg.sampled_sgs, ref):
+            assert_block_equal(dev_blk, ref_blk)
+        draw += 1
+    # outside the training phase the fan-out rule applies again
+    smp.restart()
+    ssg = smp.sample_one(phase=False)
+    ref, _ = oracle.sample_batch(co, ri, V, seeds[:100], [4, 4], seed=77, draw=draw)
+    for dev_blk, ref_blk in zip(ssg.sampled_sgs, ref):
+        assert_block_equal(dev_blk, ref_blk)
+
+
+def test_random_batches_are_fresh_uniform_subsets(cuda_device, ws):
+    V = 3000
+    edges, co, ri = small_graph(V, 30000, seed=5)
+    ids = np.arange(100, 1100, dtype=np.uint32)
+    g = FullyRepGraph(dev_i64(co, cuda_device), dev_i32(ri, cuda_device), V)
+    smp = Sampler(g, ids, (3,), batch_size=256, ws=ws, seed=5)
+    smp.random_batches = True
+    seen = []
+    while smp.sample_not_finished():
+        d, n = smp.next_seeds()
+        got = host_u32(d)[:n]
+        assert len(np.unique(got)) == n and np.isin(got, ids).all()     # distinct members of the seed list
+        seen.append(got)
+    assert [len(s) for s in seen] == [256, 256, 256, 232]                # batch sizes as in the plain loop
+    assert len(np.intersect1d(seen[0], seen[1])) > 0                     # batches are drawn independently

@@ -138,3 +138,35 @@ def test_pipelined_loop_equals_plain_loop(cuda_device, staged):
         np.testing.assert_array_equal(outs[0][0].view(np.uint32), other[0].view(np.uint32))
         assert outs[0][1] == other[1]
     assert outs[0][1][0][2] == 5
+
+
+def test_sample_rate_training_matches_oracle(cuda_device):
+    """The native step with SAMPLE_RATE set draws degree-proportional neighbourhoods for training batches
+    (and only for those): loss curve equal to the oracle's on the same draws, pipelined."""
+    V, fanout = 4000, (10, 5)
+    edges, co, ri = small_graph(V, 60000, seed=6)
+    rng = np.random.RandomState(0)
+    feat = rng.randn(V, 40).astype(np.float32)
+    label = rng.randint(0, 6, size=V).astype(np.int64)
+    sizes = [40, 24, 6]
+    cfg = GCNConfig(layers=sizes, fanout=fanout, batch_size=200, drop_rate=0.2, seed=2000, pipelines=2,
+                    sample_rate=0.3, lower_fanout=2)
+    g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
+    datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device), np.zeros(V, np.int32))
+    tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg)
+    ref = oracle.GCN(sizes, tk.P.W.cpu().numpy(), cfg.learn_rate, cfg.weight_decay, cfg.drop_rate, cfg.seed)
+    ids = np.arange(0, 1000, dtype=np.uint32)
+    smp = Sampler(g, ids, fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False,
+                  sample_rate=cfg.sample_rate, lower_fanout=cfg.lower_fanout)
+    draw = 0
+    for epoch in range(2):
+        acc, loss, batches = tk.Forward(smp, train=True)
+        ref_loss = 0.0
+        for lo in range(0, len(ids), cfg.batch_size):
+            blocks, _ = oracle.sample_batch(co, ri, V, ids[lo: lo + cfg.batch_size], list(fanout), cfg.seed, draw,
+                                            sample_rate=cfg.sample_rate, lower_fanout=cfg.lower_fanout)
+            l, c, _, _ = ref.train_step(blocks, feat, label)
+            ref_loss += l
+            draw += 1
+        assert batches == 5 and abs(loss - ref_loss / batches) < 1e-3
+    assert np.abs(tk.P.W.cpu().numpy() - ref.W).max() < 1e-3
