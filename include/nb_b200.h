@@ -258,6 +258,13 @@ int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_label, int
  *     the previous call's rows; the kernels rewrite every row they read, so no clearing is required. */
 int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
                           float *d_dlogits, float *d_stats, void *stream);
+/* Multi-label loss and F1 counters (CLASSES > 1; Loss with onelabel = false and f1_score,
+ * utils/torch_func.hpp:31-75): loss = mean over B*C of binary_cross_entropy(sigmoid(z), y) with libtorch's
+ * clamp of each log at -100; d_dlogits (nullable) = its gradient; d_label: B x C, zero / non-zero.
+ * d_stats (device, 4 floats) = {mean loss, predicted-and-true, predicted (sigmoid > 0.5), true}; the batch's
+ * F1 is 2PR/(P+R) with P = stats[1]/stats[2], R = stats[1]/stats[3], and 0 when stats[1] or stats[2] is 0. */
+int nb_sigmoid_bce(nb_ws *ws, const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                   float *d_dlogits, float *d_stats, void *stream);
 int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
             float b2, float eps, float wd, float b1_t, float b2_t, void *stream);
 
@@ -290,6 +297,8 @@ typedef struct nb_gcn_config {
   float *d_W, *d_grad, *d_M, *d_V;          /* flat parameter bucket, sum of layer_size[l]*layer_size[l+1] floats each */
   float sample_rate;                        /* SAMPLE_RATE > 0: training batches use nb_sample_hop_offsets_rate */
   int32_t lower_fanout;                     /* LOWER_FANOUT of that mode                             */
+  uint32_t classes;                         /* CLASSES: 0 or 1 = one label per vertex (NLL loss); > 1 = that many
+                                               zero/non-zero labels per vertex in d_label (BCE loss, 4 stats)  */
 } nb_gcn_config;
 
 typedef struct nb_gcn_step_info {
@@ -302,7 +311,7 @@ int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws);
 int nb_gcn_destroy(nb_gcn *g);
 /* One batch.  d_seeds: n_seeds vertex ids on the device.  train != 0: dropout on, gradient of the
  * weights left in d_grad; train == 0: forward and loss only.  d_stats[0] = mean loss, d_stats[1] =
- * number of correct argmax predictions (device).  info (nullable, host) receives the block sizes. */
+ * number of correct argmax predictions (device; with classes > 1 the four values of nb_sigmoid_bce).  info (nullable, host) receives the block sizes. */
 int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
                 nb_gcn_step_info *info, void *stream);
 int nb_gcn_update(nb_gcn *g, void *stream);

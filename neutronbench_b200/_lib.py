@@ -30,7 +30,8 @@ class GcnConfig(C.Structure):
                 ("fuse_gather", C.c_int), ("d_graph_column_offset", C.c_void_p), ("d_graph_row_indices", C.c_void_p),
                 ("feat", C.c_void_p), ("feat_ld", C.c_size_t), ("d_cache", C.c_void_p), ("cache_ld", C.c_size_t),
                 ("d_hashmap", C.c_void_p), ("d_label", C.c_void_p), ("d_W", C.c_void_p), ("d_grad", C.c_void_p),
-                ("d_M", C.c_void_p), ("d_V", C.c_void_p), ("sample_rate", C.c_float), ("lower_fanout", C.c_int32)]
+                ("d_M", C.c_void_p), ("d_V", C.c_void_p), ("sample_rate", C.c_float), ("lower_fanout", C.c_int32),
+                ("classes", C.c_uint32)]
 
 
 class GcnStepInfo(C.Structure):
@@ -90,6 +91,7 @@ SIGNATURES = {
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_gcn_read_timing_by_class": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "nb_sigmoid_bce": (C.c_int, [ptr, f32p, i64p, C.c_int64, C.c_int64, f32p, f32p, ptr]),
     "nb_adam": (C.c_int, [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
                           C.c_float, C.c_float, C.c_float, ptr]),
 }

@@ -162,6 +162,66 @@ __global__ void __launch_bounds__(1024) loss_reduce_kernel(const float *__restri
   if (threadIdx.x == 0) { stats[0] = sl[0] / (float)B; stats[1] = sh[0]; }
 }
 
+// Multi-label loss (CLASSES > 1): one warp per row; per row the BCE sum and the three F1 counters.
+__global__ void sigmoid_bce_rows_kernel(const float *__restrict__ logits, const int64_t *__restrict__ label, int64_t B,
+                                        int64_t C, float *dlogits, float4 *row_part) {
+  const unsigned lane = threadIdx.x & 31;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const float inv_n = 1.0f / ((float)B * (float)C);
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < B; i += warps) {
+    float loss = 0.0f, tp = 0.0f, pre = 0.0f, tru = 0.0f;
+    for (int64_t c = lane; c < C; c += 32) {
+      const float z = logits[i * C + c];
+      const float p = 1.0f / (1.0f + expf(-z));
+      const bool y = label[i * C + c] != 0;
+      const float lp = fmaxf(logf(p), -100.0f), lq = fmaxf(logf(1.0f - p), -100.0f);
+      loss -= y ? lp : lq;
+      const bool pred = p > 0.5f;
+      tp += (pred && y) ? 1.0f : 0.0f;
+      pre += pred ? 1.0f : 0.0f;
+      tru += y ? 1.0f : 0.0f;
+      if (dlogits) {
+        const float den = fmaxf((1.0f - p) * p, 1e-12f);
+        dlogits[i * C + c] = (p - (y ? 1.0f : 0.0f)) / den * (p * (1.0f - p)) * inv_n;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      loss += __shfl_xor_sync(0xffffffffu, loss, o);
+      tp += __shfl_xor_sync(0xffffffffu, tp, o);
+      pre += __shfl_xor_sync(0xffffffffu, pre, o);
+      tru += __shfl_xor_sync(0xffffffffu, tru, o);
+    }
+    if (lane == 0) row_part[i] = make_float4(loss, tp, pre, tru);
+  }
+}
+
+// Fixed-shape reduction of the row partials: stats = {mean loss, predicted-and-true, predicted, true}.
+__global__ void __launch_bounds__(1024) bce_reduce_kernel(const float4 *__restrict__ row_part, int64_t B, int64_t C,
+                                                          float *stats) {
+  __shared__ float4 sm[1024];
+  float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int64_t i = threadIdx.x; i < B; i += 1024) {
+    const float4 r = row_part[i];
+    a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
+  }
+  sm[threadIdx.x] = a;
+  __syncthreads();
+  for (int o = 512; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      float4 x = sm[threadIdx.x];
+      const float4 y = sm[threadIdx.x + o];
+      x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+      sm[threadIdx.x] = x;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    stats[0] = sm[0].x / ((float)B * (float)C);
+    stats[1] = sm[0].y; stats[2] = sm[0].z; stats[3] = sm[0].w;
+  }
+}
+
 // ------------------------------------------------------------------------------------ Adam
 __global__ void adam_kernel(float *W, const float *__restrict__ grad, float *M, float *V, int64_t n, float alpha,
                             float b1, float b2, float eps, float wd, float c1, float c2) {
@@ -265,6 +325,23 @@ NB_API int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_lab
                                                                                row_loss, row_hit);
   NB_LAUNCH_CHECK();
   loss_reduce_kernel<<<1, 1024, 0, stream>>>(row_loss, row_hit, B, d_stats);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+NB_API int nb_sigmoid_bce(nb_ws *ws, const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
+                          float *d_dlogits, float *d_stats, void *stream_) {
+  NB_REQUIRE(ws && d_logits && d_label && d_stats, "nb_sigmoid_bce: null pointer");
+  NB_REQUIRE(B > 0 && C > 0, "nb_sigmoid_bce: empty batch or no classes");
+  NB_REQUIRE((double)B * (double)C < 16777216.0, "nb_sigmoid_bce: more than 2^24 label slots in one batch");
+  cudaStream_t stream = as_stream(stream_);
+  WsScope scope(ws);
+  float4 *row_part = ws->alloc_n<float4>((size_t)B);
+  if (!row_part) return fail(NB_ERR_NOMEM, "nb_sigmoid_bce: workspace arena exhausted");
+  sigmoid_bce_rows_kernel<<<grid_for((uint64_t)B * 32, 256), 256, 0, stream>>>(d_logits, d_label, B, C, d_dlogits,
+                                                                               row_part);
+  NB_LAUNCH_CHECK();
+  bce_reduce_kernel<<<1, 1024, 0, stream>>>(row_part, B, C, d_stats);
   NB_LAUNCH_CHECK();
   return 0;
 }

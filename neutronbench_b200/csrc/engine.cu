@@ -120,6 +120,8 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   NB_REQUIRE(cfg->d_W && cfg->d_grad && cfg->d_M && cfg->d_V, "nb_gcn_create: null parameter buffers");
   NB_REQUIRE(cfg->feat || (cfg->d_cache && cfg->d_hashmap), "nb_gcn_create: no feature store");
   NB_REQUIRE(cfg->drop_rate >= 0.0f && cfg->drop_rate < 1.0f, "nb_gcn_create: drop rate must be in [0,1)");
+  NB_REQUIRE(cfg->classes <= 1 || cfg->classes == cfg->layer_size[cfg->num_layers],
+             "nb_gcn_create: with classes > 1 the last layer must have one output per class");
   NB_REQUIRE(cfg->sample_rate >= 0.0f && cfg->sample_rate <= 1.0f && cfg->lower_fanout >= 0,
              "nb_gcn_create: sample rate must be in [0,1] and the lower fan-out non-negative");
   for (uint32_t l = 0; l <= cfg->num_layers; l++) NB_REQUIRE(cfg->layer_size[l] > 0, "nb_gcn_create: zero layer width");
@@ -307,12 +309,16 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   // ---- loss (utils/torch_func.hpp:67-82)
   const Block &last = blk[L - 1];
   const int64_t B = last.v, C = c.layer_size[L];
+  const bool multi = c.classes > 1;   // CLASSES > 1: C labels per vertex, BCE loss (utils/torch_func.hpp:67-75)
   int64_t *lab;
-  NB_TRY(arena(ws, (size_t)B, &lab));
-  NB_TRY(nb_label_gather(lab, c.d_label, last.destination, last.v, 1, stream));
+  NB_TRY(arena(ws, (size_t)(multi ? B * C : B), &lab));
+  NB_TRY(nb_label_gather(lab, c.d_label, last.destination, last.v, multi ? (uint32_t)C : 1u, stream));
   float *dZ = nullptr;
   if (train) NB_TRY(arena(ws, (size_t)(B * C), &dZ));
-  NB_TRY(nb_softmax_nll(ws, X[L], lab, B, C, dZ, d_stats, stream));
+  if (multi)
+    NB_TRY(nb_sigmoid_bce(ws, X[L], lab, B, C, dZ, d_stats, stream));
+  else
+    NB_TRY(nb_softmax_nll(ws, X[L], lab, B, C, dZ, d_stats, stream));
 
   // ---- backward: dW_l = Y_l^T dZ_l; dY_l = dZ_l W_l^T; dZ_{l-1} = (A_l^T dY_l) masked by X_l > 0
   if (train) {

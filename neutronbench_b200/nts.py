@@ -158,16 +158,24 @@ def read_feature(feature_file: str, vertices: int, feat_dim: int, use_sidecar: b
     return feat
 
 
-def read_feature_label_mask(feature_file: str, label_file: str, mask_file: str, vertices: int, feat_dim: int):
-    """GNNDatum::readFeature_Label_Mask (core/ntsDataloador.hpp:264-330), single label per node."""
+def read_feature_label_mask(feature_file: str, label_file: str, mask_file: str, vertices: int, feat_dim: int,
+                            classes: int = 1):
+    """GNNDatum::readFeature_Label_Mask (core/ntsDataloador.hpp:264-330).  Label lines are "id label", or with
+    CLASSES > 1 "id count idx_1 ... idx_count" (the set labels of a multi-hot row, :304-312)."""
     feat = read_feature(feature_file, vertices, feat_dim)
-    label = np.zeros(vertices, dtype=np.int64)
+    label = np.zeros((vertices, classes), dtype=np.int64) if classes > 1 else np.zeros(vertices, dtype=np.int64)
     mask = np.full(vertices, 3, dtype=np.int32)
     with open(label_file) as lf:
         for line in lf:
             parts = line.split()
             if len(parts) >= 2 and 0 <= int(parts[0]) < vertices:
-                label[int(parts[0])] = int(parts[1])
+                if classes > 1:
+                    n = int(parts[1])
+                    for idx in parts[2: 2 + n]:
+                        if 0 <= int(idx) < classes:
+                            label[int(parts[0]), int(idx)] = 1
+                else:
+                    label[int(parts[0])] = int(parts[1])
     code = {"train": 0, "eval": 1, "val": 1, "test": 2}
     with open(mask_file) as mf:
         for line in mf:
@@ -213,8 +221,9 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     if info.batch_norm:
         raise SystemExit("BATCH_NORM:1 is not supported on the GPU path (the reference keeps its BatchNorm modules on "
                          "the CPU, toolkits/GCN_GPU_NEIGHBOR.hpp:242-246); use BATCH_NORM:0")
-    if info.classes != 1:
-        raise SystemExit("multi-label training (CLASSES > 1) is not built")
+    classes = max(1, int(info.classes))
+    if classes > 1 and classes != info.layers()[-1]:
+        raise SystemExit("CLASSES > 1 needs a last layer with one output per class")
     assert torch.cuda.is_available(), "nts needs a CUDA device; there is no CPU fallback"
     dev = torch.device("cuda", torch.cuda.current_device())
     layers = info.layers()
@@ -225,8 +234,11 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     del edges
     if info.feature_file == "random":
         feat, label, mask = random_generate(V, layers[0], layers[-1])
+        if classes > 1:   # one random label per node, as a multi-hot row
+            label = np.eye(classes, dtype=np.int64)[label]
     else:
-        feat, label, mask = read_feature_label_mask(info.feature_file, info.label_file, info.mask_file, V, layers[0])
+        feat, label, mask = read_feature_label_mask(info.feature_file, info.label_file, info.mask_file, V, layers[0],
+                                                    classes)
     cache_type = info.cache_type or "none"
     cache_rate = info.cache_rate if cache_type in ("rate", "random") else 0.0
     if cache_type in ("rate", "random") and cache_rate <= 0:
@@ -235,7 +247,7 @@ def run(cfg_path: str, out=sys.stdout) -> float:
                     batch_size=info.batch_size, learn_rate=info.learn_rate, weight_decay=info.weight_decay,
                     drop_rate=info.drop_rate, cache_type=cache_type, cache_rate=cache_rate,
                     cache_policy=info.cache_policy or "degree", pipelines=max(1, int(info.pipelines)),
-                    sample_rate=max(0.0, info.sample_rate), lower_fanout=max(0, info.lower_fanout))
+                    sample_rate=max(0.0, info.sample_rate), lower_fanout=max(0, info.lower_fanout), classes=classes)
     feature = torch.from_numpy(feat)
     # the table stays in pinned host memory (zero-copy misses) unless every row is cached on the GPU anyway
     feature = feature.to(dev) if cache_rate >= 1.0 else feature.pin_memory()

@@ -158,8 +158,13 @@ class GCN_GPU_NEIGHBOR_impl:
         gen = torch.Generator().manual_seed(cfg.seed)
         self.P = Parameter(cfg.layers, cfg, self.device, gen)
         self.step_count = 0
-        self.stats = torch.zeros(2, dtype=torch.float32, device=self.device)
-        self._stats_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        # (loss, hits) for one label per node; (loss, predicted-and-true, predicted, true) with CLASSES > 1
+        self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self._stats_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+        self.multi_label = int(cfg.classes) > 1
+        if self.multi_label:
+            assert int(cfg.classes) == int(cfg.layers[-1]), "CLASSES > 1 needs one output per class"
+            assert datum.local_label.dim() == 2 and datum.local_label.size(1) == int(cfg.classes)
         self.dev_cache_feature = None
         self.dev_cache_node_hashmap = None
         self.cache_node_num = 0
@@ -315,10 +320,15 @@ class GCN_GPU_NEIGHBOR_impl:
             X.append(z)
         last = ssg.sampled_sgs[L - 1]
         B, C = last.v_size, c.layers[L]
-        lab = torch.empty(B, dtype=torch.int64, device=self.device)
-        _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(last.destination), B, 1, stream)
         dZ = torch.empty((B, C), dtype=torch.float32, device=self.device) if train else None
-        _lib.call("nb_softmax_nll", wsh, ptr(X[L]), ptr(lab), B, C, ptr(dZ), ptr(self.stats), stream)
+        if self.multi_label:   # Loss(..., onelabel=false), utils/torch_func.hpp:67-75
+            lab = torch.empty((B, C), dtype=torch.int64, device=self.device)
+            _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(last.destination), B, C, stream)
+            _lib.call("nb_sigmoid_bce", wsh, ptr(X[L]), ptr(lab), B, C, ptr(dZ), ptr(self.stats), stream)
+        else:
+            lab = torch.empty(B, dtype=torch.int64, device=self.device)
+            _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(last.destination), B, 1, stream)
+            _lib.call("nb_softmax_nll", wsh, ptr(X[L]), ptr(lab), B, C, ptr(dZ), ptr(self.stats), stream)
         self.agg_edges_fwd += sum(b.e_size for b in ssg.sampled_sgs)
         if not train:
             return
@@ -355,6 +365,7 @@ class GCN_GPU_NEIGHBOR_impl:
         ec.seed = c.seed
         ec.fuse_gather = 1 if c.fuse_gather else 0
         ec.sample_rate, ec.lower_fanout = float(c.sample_rate), int(c.lower_fanout)
+        ec.classes = int(c.classes)
         ec.d_graph_column_offset = ptr(self.graph.column_offset)
         ec.d_graph_row_indices = ptr(self.graph.row_indices)
         feat = self.datum.local_feature
@@ -396,7 +407,7 @@ class GCN_GPU_NEIGHBOR_impl:
         self._batch_ws = [Workspace(default_workspace_bytes(self.graph.global_vertices, self.cfg)) for _ in range(slots)]
         self._slot_seeds = [torch.empty(self.cfg.batch_size, dtype=torch.int32).pin_memory() for _ in range(slots)]
         self._slot_refs = [None] * slots
-        self._stats_ring = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._stats_ring = [torch.zeros(4, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._batches = []
         for w in self._batch_ws:
             h = C.c_void_p()
@@ -460,8 +471,9 @@ class GCN_GPU_NEIGHBOR_impl:
             if read_back:   # copy now, read one batch later: the host never waits for the batch it just enqueued
                 if pending_read is not None:
                     pending_read[1].synchronize()
-                    loss_sum += float(pending_read[0][0])
-                    correct += int(pending_read[0][1])
+                    loss, score = self._loss_and_score(pending_read[0])
+                    loss_sum += loss
+                    correct += score
                 host = self._stats_ring[batches & 1]
                 host.copy_(self.stats, non_blocking=True)
                 ev = torch.cuda.Event()
@@ -476,8 +488,9 @@ class GCN_GPU_NEIGHBOR_impl:
             slot = (slot + 1) % slots
         if pending_read is not None:
             pending_read[1].synchronize()
-            loss_sum += float(pending_read[0][0])
-            correct += int(pending_read[0][1])
+            loss, score = self._loss_and_score(pending_read[0])
+            loss_sum += loss
+            correct += score
         return correct, nodes, loss_sum, batches
 
     def Update(self):
@@ -502,12 +515,24 @@ class GCN_GPU_NEIGHBOR_impl:
         self.Update()
         self.step_count += 1
 
+    def _loss_and_score(self, host: torch.Tensor):
+        """(loss, hits) of a batch, or with CLASSES > 1 (loss, F1 of the batch) as f1_score computes it
+        (utils/torch_func.hpp:31-60)."""
+        loss = float(host[0])
+        if not self.multi_label:
+            return loss, int(host[1])
+        true_p, all_pre, all_true = float(host[1]), float(host[2]), float(host[3])
+        if true_p == 0 or all_pre == 0:
+            return loss, 0.0
+        precision, recall = np.float32(true_p) / np.float32(all_pre), np.float32(true_p) / np.float32(all_true)
+        return loss, float(np.float32(2) * precision * recall / (precision + recall))
+
     def read_stats(self):
-        """Device -> host read of (loss, hits) of the last batch; the only host sync of a step besides
-        the size read-backs of the block builder."""
+        """Device -> host read of (loss, hits) — (loss, F1) with CLASSES > 1 — of the last batch; the only
+        host sync of a step besides the size read-backs of the block builder."""
         self._stats_host.copy_(self.stats, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return float(self._stats_host[0]), int(self._stats_host[1])
+        return self._loss_and_score(self._stats_host)
 
     def Forward(self, sampler: Sampler, rng: Optional[np.random.RandomState] = None, train: bool = True,
                 max_batches: Optional[int] = None):
@@ -522,7 +547,7 @@ class GCN_GPU_NEIGHBOR_impl:
         if native and self.cfg.pipelines > 1:
             correct, nodes, loss_epoch, batches = self.run_pipelined(sampler, max_batches, train=train)
             sampler.restart()
-            return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
+            return self._epoch_accuracy(correct, nodes, batches), loss_epoch / max(batches, 1), batches
         correct = nodes = batches = 0
         loss_epoch = 0.0
         while sampler.sample_not_finished():
@@ -544,7 +569,14 @@ class GCN_GPU_NEIGHBOR_impl:
             nodes += batch_nodes
             batches += 1
         sampler.restart()
-        return (correct / max(nodes, 1)), loss_epoch / max(batches, 1), batches
+        return self._epoch_accuracy(correct, nodes, batches), loss_epoch / max(batches, 1), batches
+
+    def _epoch_accuracy(self, score_sum, nodes: int, batches: int) -> float:
+        """correct / nodes, or the mean of the batches' F1 with CLASSES > 1
+        (toolkits/GCN_GPU_NEIGHBOR.hpp:783-793)."""
+        if self.multi_label:
+            return score_sum / max(batches, 1)
+        return score_sum / max(nodes, 1)
 
 
 def drop_train_ids_by_degree(train_ids: np.ndarray, in_degree: np.ndarray, batch_type: str, del_frac: float) -> np.ndarray:

@@ -445,6 +445,40 @@ ORC_API float orc_softmax_nll(const float *logits, const int64_t *label, int64_t
   return (float)(loss / (double)B);
 }
 
+/* Multi-label loss and F1 counters (CLASSES > 1): Loss = binary_cross_entropy(sigmoid(z), y), mean over all
+ * B*C elements with each log clamped at -100 (utils/torch_func.hpp:67-75; the clamp is libtorch's);
+ * dlogits follows libtorch's backward pair: (p - y) / max((1 - p) p, 1e-12) * p (1 - p) / (B*C).
+ * counters (utils/torch_func.hpp:31-60, f1_score): [0] predicted-and-true, [1] predicted (sigmoid > 0.5),
+ * [2] true labels.  label: B x C, zero / non-zero.  Returns the mean loss. */
+ORC_API float orc_sigmoid_bce(const float *logits, const int64_t *label, int64_t B, int64_t C, float *dlogits,
+                              int64_t counters[3]) {
+  double loss = 0.0;
+  int64_t tp = 0, pre = 0, tru = 0;
+  const double n = (double)B * (double)C;
+  for (int64_t i = 0; i < B * C; i++) {
+    /* the sigmoid is an fp32 tensor in the reference: it saturates to exactly 0 or 1 beyond |z| of about 17,
+     * which is what brings the clamp into play */
+    const float pf = 1.0f / (1.0f + expf(-logits[i]));
+    const double p = (double)pf;
+    const double y = label[i] != 0 ? 1.0 : 0.0;
+    double lp = log(p), lq = log((double)(1.0f - pf));
+    if (lp < -100.0) lp = -100.0;
+    if (lq < -100.0) lq = -100.0;
+    loss += -(y * lp + (1.0 - y) * lq);
+    const int pred = pf > 0.5f;
+    tp += (pred && label[i] != 0);
+    pre += pred;
+    tru += (label[i] != 0);
+    if (dlogits) {
+      double den = (double)(1.0f - pf) * p;
+      if (den < 1e-12) den = 1e-12;
+      dlogits[i] = (float)((p - y) / den * (p * (double)(1.0f - pf)) / n);
+    }
+  }
+  if (counters) { counters[0] = tp; counters[1] = pre; counters[2] = tru; }
+  return (float)(loss / n);
+}
+
 /* --------------------------------------------------------------------------------------------
  * a13 Adam with weight decay, as Parameter::learnC2G_with_decay_Adam
  * (core/NtsScheduler.hpp:794-811) followed by next() (:700-711):

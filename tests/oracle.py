@@ -228,6 +228,28 @@ def softmax_nll(logits, label):
     return float(loss), d, int(correct.value)
 
 
+def sigmoid_bce(logits, label):
+    """Multi-label loss: (mean loss, dlogits, (predicted-and-true, predicted, true))."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    label = np.ascontiguousarray(label, dtype=np.int64)
+    B, Cn = logits.shape
+    d = np.zeros((B, Cn), dtype=np.float32)
+    counters = (C.c_int64 * 3)()
+    fn = lib().orc_sigmoid_bce
+    fn.restype = C.c_float
+    loss = fn(_p(logits), _p(label), C.c_int64(B), C.c_int64(Cn), _p(d), counters)
+    return float(loss), d, tuple(int(x) for x in counters)
+
+
+def f1_of(counters):
+    """f1_score of one batch (utils/torch_func.hpp:31-60) from its three counters, in float32."""
+    tp, pre, tru = counters
+    if tp == 0 or pre == 0:
+        return 0.0
+    precision, recall = np.float32(tp) / np.float32(pre), np.float32(tp) / np.float32(tru)
+    return float(np.float32(2) * precision * recall / (precision + recall))
+
+
 def adam(W, grad, M, V, alpha, b1, b2, eps, wd, b1_t, b2_t):
     lib().orc_adam(_p(W), _p(grad), _p(M), _p(V), C.c_int64(W.size), C.c_float(alpha), C.c_float(b1), C.c_float(b2),
                    C.c_float(eps), C.c_float(wd), C.c_float(b1_t), C.c_float(b2_t))
@@ -244,7 +266,9 @@ class GCN:
     """CPU restatement of one GCN_CPU_NEIGHBOR / GCN_GPU_NEIGHBOR training step on given blocks
     (toolkits/GCN_CPU_NEIGHBOR.hpp:225-427): forward, loss, backward, Adam."""
 
-    def __init__(self, layer_sizes, W_flat, lr, wd, drop, seed, b1=0.9, b2=0.999, eps=1e-9, blas=False):
+    def __init__(self, layer_sizes, W_flat, lr, wd, drop, seed, b1=0.9, b2=0.999, eps=1e-9, blas=False,
+                 multi_label=False):
+        self.multi_label = multi_label   # CLASSES > 1: BCE loss; `correct` of train_step is then the batch's F1
         # blas=True routes the dense products through numpy's BLAS (the stand-in for libtorch's CPU mm
         # when the oracle is timed as the host baseline); blas=False uses the plain-C loops.
         self.blas = blas
@@ -279,8 +303,13 @@ class GCN:
             if l < L - 1:
                 z = relu_dropout(z, p, self.seed, l, self.step)
             X.append(z)
-        lab = label_gather(labels, blocks[L - 1].destination)
-        loss, dZ, correct = softmax_nll(X[L], lab)
+        if self.multi_label:
+            lab = label_gather(labels, blocks[L - 1].destination, label_size=labels.shape[1])
+            loss, dZ, counters = sigmoid_bce(X[L], lab.reshape(-1, labels.shape[1]))
+            correct = f1_of(counters)
+        else:
+            lab = label_gather(labels, blocks[L - 1].destination)
+            loss, dZ, correct = softmax_nll(X[L], lab)
         if train:
             for l in range(L - 1, -1, -1):
                 b = blocks[l]

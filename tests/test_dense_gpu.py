@@ -117,3 +117,27 @@ def test_adam_bit_exact_over_steps(cuda_device):
     np.testing.assert_array_equal(host_f32(dW).view(np.uint32), W.view(np.uint32))
     np.testing.assert_array_equal(host_f32(dM).view(np.uint32), M.view(np.uint32))
     np.testing.assert_array_equal(host_f32(dV).view(np.uint32), V.view(np.uint32))
+
+
+@pytest.mark.parametrize("B,C", [(1, 1), (37, 11), (1024, 121), (300, 33)])
+def test_sigmoid_bce_matches_oracle(cuda_device, ws, B, C):
+    """Multi-label loss, gradient and F1 counters (CLASSES > 1) against the oracle; the counters are exact."""
+    rng = np.random.RandomState(B + C)
+    z = (rng.randn(B, C) * 3).astype(np.float32)
+    z.flat[0] = 110.0
+    y = (rng.rand(B, C) < 0.25).astype(np.int64)
+    y.flat[0] = 0
+    loss, d_ref, counters = oracle.sigmoid_bce(z, y)
+    dz = torch.full((B, C), float("nan"), device=cuda_device)
+    stats = torch.zeros(4, device=cuda_device)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.call("nb_sigmoid_bce", ws.handle, ptr(dev_f32(z, cuda_device)), ptr(dev_i64(y, cuda_device)), B, C, ptr(dz),
+              ptr(stats), st)
+    s = stats.cpu().numpy()
+    assert abs(s[0] - loss) <= 2e-5 * max(1.0, abs(loss))
+    assert (int(s[1]), int(s[2]), int(s[3])) == counters
+    np.testing.assert_allclose(dz.cpu().numpy(), d_ref, rtol=2e-4, atol=1e-9)
+    # forward only: no gradient buffer
+    _lib.call("nb_sigmoid_bce", ws.handle, ptr(dev_f32(z, cuda_device)), ptr(dev_i64(y, cuda_device)), B, C, None,
+              ptr(stats), st)
+    assert abs(float(stats[0]) - loss) <= 2e-5 * max(1.0, abs(loss))

@@ -78,3 +78,19 @@ def test_feature_sidecar_round_trip(tmp_path):
         f.write(b"\0" * 12)
     np.testing.assert_array_equal(read_feature(str(path), V, F), feat)
     np.testing.assert_array_equal(read_feature(str(path), V, F, use_sidecar=False), feat)
+
+
+def test_multi_label_file_format(tmp_path):
+    """CLASSES > 1: label lines are "id count idx..." and become multi-hot rows (core/ntsDataloador.hpp:304-312)."""
+    V, F, C = 6, 2, 5
+    (tmp_path / "f").write_text("".join(f"{i} 0.5 1.5\n" for i in range(V)))
+    (tmp_path / "l").write_text("0 2 1 4\n1 0\n2 1 0\n3 3 0 2 4\n5 1 3\n")
+    (tmp_path / "m").write_text("".join(f"{i} train\n" for i in range(V)))
+    feat, label, mask = read_feature_label_mask(str(tmp_path / "f"), str(tmp_path / "l"), str(tmp_path / "m"), V, F, C)
+    want = np.zeros((V, C), np.int64)
+    want[0, [1, 4]] = 1
+    want[2, 0] = 1
+    want[3, [0, 2, 4]] = 1
+    want[5, 3] = 1
+    np.testing.assert_array_equal(label, want)
+    assert feat.shape == (V, F) and (mask == 0).all()

@@ -203,3 +203,29 @@ def test_drop_train_ids_by_degree_follows_the_reference_code():
     # dellow: ascending order, last quarter dropped -> the two highest-degree ids go
     np.testing.assert_array_equal(drop_train_ids_by_degree(ids, in_deg, "dellow", 0.25), [1, 5, 3, 7, 0, 4])
     assert len(drop_train_ids_by_degree(ids, in_deg, "dellow", 1.0)) == 0
+
+
+def test_sigmoid_bce_oracle_equals_libtorch():
+    """The multi-label loss of the reference is libtorch's binary_cross_entropy(sigmoid(z), y)
+    (utils/torch_func.hpp:67-75); the oracle restates it and is checked here against torch itself,
+    including logits large enough to reach the log clamp at -100."""
+    import torch
+    rng = np.random.RandomState(2)
+    B, Cn = 37, 11
+    z = (rng.randn(B, Cn) * 4).astype(np.float32)
+    z[0, 0], z[0, 1], z[1, 0] = 120.0, -120.0, 30.0
+    y = (rng.rand(B, Cn) < 0.3).astype(np.int64)
+    y[0, 0], y[0, 1] = 0, 1                                   # confidently wrong: clamped logs
+    loss, d, counters = oracle.sigmoid_bce(z, y)
+    zt = torch.tensor(z, requires_grad=True)
+    lt = torch.nn.functional.binary_cross_entropy(torch.sigmoid(zt), torch.tensor(y, dtype=torch.float32))
+    lt.backward()
+    assert abs(loss - float(lt.detach())) < 1e-5 * max(1.0, abs(float(lt.detach())))
+    np.testing.assert_allclose(d, zt.grad.numpy(), rtol=1e-4, atol=1e-8)
+    pred = (torch.sigmoid(torch.tensor(z)) > 0.5).numpy()
+    assert counters == (int((pred & (y != 0)).sum()), int(pred.sum()), int((y != 0).sum()))
+    # f1_score of the reference (utils/torch_func.hpp:31-60) on the same batch
+    tp, pre, tru = counters
+    f1 = 2 * (tp / pre) * (tp / tru) / (tp / pre + tp / tru)
+    assert abs(oracle.f1_of(counters) - f1) < 1e-6
+    assert oracle.f1_of((0, 5, 9)) == 0.0 and oracle.f1_of((0, 0, 9)) == 0.0

@@ -170,3 +170,44 @@ def test_sample_rate_training_matches_oracle(cuda_device):
             draw += 1
         assert batches == 5 and abs(loss - ref_loss / batches) < 1e-3
     assert np.abs(tk.P.W.cpu().numpy() - ref.W).max() < 1e-3
+
+
+@pytest.mark.parametrize("pipelines", [1, 2], ids=["plain", "pipelined"])
+def test_multi_label_training_matches_oracle(cuda_device, pipelines):
+    """CLASSES > 1: BCE loss and per-batch F1 (utils/torch_func.hpp:31-75) through the native step."""
+    V, fanout, classes = 3000, (8, 4), 9
+    edges, co, ri = small_graph(V, 40000, seed=3)
+    rng = np.random.RandomState(0)
+    feat = rng.randn(V, 30).astype(np.float32)
+    label = (rng.rand(V, classes) < 0.3).astype(np.int64)
+    sizes = [30, 16, classes]
+    cfg = GCNConfig(layers=sizes, fanout=fanout, batch_size=150, drop_rate=0.1, seed=2000, pipelines=pipelines,
+                    classes=classes)
+    g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
+    datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device), np.zeros(V, np.int32))
+    tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg)
+    ref = oracle.GCN(sizes, tk.P.W.cpu().numpy(), cfg.learn_rate, cfg.weight_decay, cfg.drop_rate, cfg.seed,
+                     multi_label=True)
+    ids = np.arange(0, 700, dtype=np.uint32)
+    smp = Sampler(g, ids, fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
+    draw = 0
+    for epoch in range(3):
+        f1, loss, batches = tk.Forward(smp, train=True)
+        ref_loss = ref_f1 = 0.0
+        for lo in range(0, len(ids), cfg.batch_size):
+            blocks, _ = oracle.sample_batch(co, ri, V, ids[lo: lo + cfg.batch_size], list(fanout), cfg.seed, draw)
+            l, f, _, _ = ref.train_step(blocks, feat, label)
+            ref_loss += l
+            ref_f1 += f
+            draw += 1
+        assert batches == 5
+        assert abs(loss - ref_loss / batches) < 1e-3
+        assert abs(f1 - ref_f1 / batches) < 0.02
+    assert np.abs(tk.P.W.cpu().numpy() - ref.W).max() < 1e-3
+    # the Python mirror of the step gives the same numbers as the native one
+    tk2 = GCN_GPU_NEIGHBOR_impl(g, datum, cfg, use_engine=False)
+    tk3 = GCN_GPU_NEIGHBOR_impl(g, datum, GCNConfig(**{**cfg.__dict__, "pipelines": 1}))
+    for t in (tk2, tk3):
+        s2 = Sampler(g, ids, fanout, cfg.batch_size, t.ws, seed=cfg.seed, with_edge_weights=False)
+        t.Forward(s2, train=True)
+    np.testing.assert_array_equal(tk2.P.W.cpu().numpy().view(np.uint32), tk3.P.W.cpu().numpy().view(np.uint32))
