@@ -19,7 +19,8 @@
 
 namespace nb {
 
-constexpr int kTcThreads = 256;   // two CTAs share an SM: one stages operands while the other waits on its MMAs
+// Threads per CTA (template parameter T of the kernel): 256 when the grid can put two CTAs on every SM (one stages
+// operands while the other waits on its MMAs), 512 when a single wave leaves one CTA per SM.
 constexpr int kBM = 128;           // rows of a C tile = TMEM lanes
 constexpr int kBK = 16;            // K elements per shared-memory chunk (2 MMA K-steps of 8)
 constexpr int kCtasPerSM = 2;      // 108 KB of shared memory and 128 TMEM columns per CTA
@@ -156,16 +157,16 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Per-thread copy plan of one operand.  A tile is moved in pieces of `vec` floats along the operand's
-// contiguous direction; piece `item` = tid + i * kTcThreads of every chunk is the same (row, k) place, so
+// contiguous direction; piece `item` = tid + i * T (T threads per CTA) of every chunk is the same (row, k) place, so
 // the source pointer, the destination offsets and the bounds predicate are computed once and the main
 // loop only advances the pointer.
 //   K-major:  piece = item % (kBK/vec) along k, row = item / (kBK/vec)
 //   MN-major: piece = item % (ROWS/vec) along the rows, k = item / (ROWS/vec)
 // The pitch of a dense row-major operand equals its extent along the contiguous direction and is a
 // multiple of `vec`, so a piece never straddles the matrix edge.
-template <int ROWS, bool MN>
+template <int ROWS, bool MN, int T>
 struct CopyPlan {
-  static constexpr int kMaxPieces = (ROWS * kBK) / kTcThreads > 0 ? (ROWS * kBK) / kTcThreads : 1;   // at vec = 1
+  static constexpr int kMaxPieces = (ROWS * kBK) / T > 0 ? (ROWS * kBK) / T : 1;   // at vec = 1
   const float *src;        // this thread's first piece in chunk 0 (clamped into the matrix when out of range)
   int64_t step;            // elements between a thread's consecutive pieces
   int64_t chunk_step;      // elements between chunks
@@ -182,10 +183,10 @@ struct CopyPlan {
     valid = 0;
     const int per_line = (MN ? ROWS : kBK) / vec;           // pieces along the contiguous direction
     const int total = (ROWS * kBK) / vec;
-    pieces = total / kTcThreads;
+    pieces = total / T;
     if (pieces < 1) pieces = tid < total ? 1 : 0;
     const int piece = tid % per_line, line0 = tid / per_line;
-    const int lstep = kTcThreads / per_line > 0 ? kTcThreads / per_line : 1;
+    const int lstep = T / per_line > 0 ? T / per_line : 1;
     if (MN) {
       const int r = piece * vec;                            // row within the tile, k = line
       const bool row_ok = row0 + r < rows_total;
@@ -230,7 +231,7 @@ struct CopyPlan {
   }
   // The one chunk with a K tail: element by element with bounds checks.
   __device__ void issue_tail(uint32_t tile_s, int64_t k0, int64_t k_end) const {
-    for (int item = threadIdx.x; item < ROWS * kBK; item += kTcThreads) {
+    for (int item = threadIdx.x; item < ROWS * kBK; item += T) {
       const int r = MN ? item % ROWS : item / kBK, k = MN ? item / ROWS : item % kBK;
       const int64_t gr = row0 + r, gk = k0 + k;
       const bool ok = gr < rows_total && gk < k_end;
@@ -241,15 +242,15 @@ struct CopyPlan {
 
 // In place: raw -> hi (low 13 mantissa bits cleared); lo = raw - hi goes to `lo`.  Works piece by piece on
 // the same offsets in both buffers, so it does not care which layout the tile has.
-template <int ROWS, bool MN>
+template <int ROWS, bool MN, int T>
 struct SplitPlan {
   static constexpr int QUADS = ROWS * kBK / 4;
-  static constexpr int N = (QUADS + kTcThreads - 1) / kTcThreads;
+  static constexpr int N = (QUADS + T - 1) / T;
   uint32_t off[N];
   __device__ void init() {
 #pragma unroll
     for (int i = 0; i < N; i++) {
-      const int q = threadIdx.x + i * kTcThreads;
+      const int q = threadIdx.x + i * T;
       off[i] = q < QUADS ? quad_off<MN>(q) : 0xFFFFFFFFu;
     }
   }
@@ -266,8 +267,8 @@ struct SplitPlan {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const TcGemmArgs g) {
+template <int BN, bool A_MN, bool B_MN, int T>
+__global__ void __launch_bounds__(T, T == 256 ? kCtasPerSM : 1) gemm_tc_kernel(const TcGemmArgs g) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   constexpr uint32_t A_TILE = TileFloats<kBM>::value;
   constexpr uint32_t B_TILE = TileFloats<BN>::value;
@@ -305,12 +306,12 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
                          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   bool ok = true;
 
-  CopyPlan<kBM, A_MN> plan_a;
-  CopyPlan<BN, B_MN> plan_b;
+  CopyPlan<kBM, A_MN, T> plan_a;
+  CopyPlan<BN, B_MN, T> plan_b;
   plan_a.init(g.a, g.a_row, g.a_k, row0, g.M, k_begin, g.a_vec);
   plan_b.init(g.b, g.b_row, g.b_k, col0, g.N, k_begin, g.b_vec);
-  SplitPlan<kBM, A_MN> split_a;
-  SplitPlan<BN, B_MN> split_b;
+  SplitPlan<kBM, A_MN, T> split_a;
+  SplitPlan<BN, B_MN, T> split_b;
   split_a.init();
   split_b.init();
   const int full_chunks = (int)((k_end - k_begin) / kBK);   // chunks without a K tail
@@ -406,7 +407,7 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
     float *out = g.c + (int64_t)blockIdx.z * g.M * g.N;
     const int quarter = warp & 3, part = warp >> 2;
     constexpr int CB = BN / 32;                      // 32-column blocks in the tile
-    constexpr int PARTS = kTcThreads / 128;          // groups of four warps sharing the column blocks
+    constexpr int PARTS = T / 128;                   // groups of four warps sharing the column blocks
 #pragma unroll
     for (int cbi = 0; cbi < (CB + PARTS - 1) / PARTS; cbi++) {
       const int cb = cbi * PARTS + part;
@@ -451,15 +452,15 @@ __global__ void __launch_bounds__(kTcThreads, kCtasPerSM) gemm_tc_kernel(const T
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
+template <int BN, bool A_MN, bool B_MN, int T>
+static int launch_tc_t(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   constexpr size_t smem = (size_t)((kStages + 2) * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
   static bool configured = false;
   if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  gemm_tc_kernel<BN, A_MN, B_MN><<<grid, kTcThreads, smem, stream>>>(g);
+  gemm_tc_kernel<BN, A_MN, B_MN, T><<<grid, T, smem, stream>>>(g);
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -471,6 +472,16 @@ __global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float
     for (int z = 1; z < splits; z++) s += partial[(int64_t)z * mn + i];
     c[i] = s;
   }
+}
+
+// 512 threads when every CTA has an SM to itself (more warps to hide the staging latency), 256 otherwise.
+template <int BN, bool A_MN, bool B_MN>
+static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
+  const int64_t ctas = (int64_t)grid.x * grid.y * grid.z;
+  int threads = ctas <= kNumSMs ? 512 : 256;
+  if (getenv("NB_TC_THREADS")) threads = atoi(getenv("NB_TC_THREADS"));
+  if (threads == 512) return launch_tc_t<BN, A_MN, B_MN, 512>(g, grid, stream);
+  return launch_tc_t<BN, A_MN, B_MN, 256>(g, grid, stream);
 }
 
 // The three operand layouts of the GCN step: Y W (B transposed in memory relative to K-major), Y^T dZ
