@@ -100,6 +100,7 @@ struct TmaSpmmArgs {
   const float *miss;       // base of rows whose reference has bit 31 set (copied by the lanes), or null
   size_t miss_ld;
   float *y;                // n x F output
+  size_t y_ld;             // pitch of y in floats (0 = F)
   const uint32_t *offs;    // n + 1 offsets
   const uint32_t *ref;     // per edge: row reference
   const float *w;          // per edge weight, or null to form it from the two factors below
@@ -120,8 +121,21 @@ int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, ui
                        uint32_t *ref, float *w, cudaStream_t stream);
 int read_tma_error_flag(unsigned int *value);
 int read_tc_error_flag(unsigned int *value);
-int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
-                     int trans_a, int trans_b, int mode, cudaStream_t stream);
+int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
+                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream);
+int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M, int64_t N,
+            int64_t K, int trans_a, int trans_b, cudaStream_t stream);
+bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K);
+bool tma_gemm_applicable(const float *d_a, int64_t lda, const float *d_b, int64_t ldb);
+int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *c, int64_t M, int64_t N,
+                    int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
+                    cudaStream_t stream);
+int read_tma_gemm_error_flag(unsigned int *value);
+int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache, size_t cache_ld,
+                                 const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
+                                 const uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                                 const float *d_src_norm, const float *d_dst_norm, uint32_t v, uint32_t s, uint32_t e,
+                                 uint32_t F, void *stream);
 extern int g_gemm_mode;    // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
 extern uint64_t g_l2_panel_bytes;
 extern int g_staged_min_width;

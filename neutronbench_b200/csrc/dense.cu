@@ -244,24 +244,36 @@ using namespace nb;
 
 NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
                    int trans_a, int trans_b, void *stream_) {
+  return nb::gemm_ld(ws, d_a, trans_a ? M : K, d_b, trans_b ? K : N, d_c, M, N, K, trans_a, trans_b, as_stream(stream_));
+}
+
+namespace nb {
+
+bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K) {
+  const bool tiny = 2.0 * (double)M * (double)N * (double)K < 4.0e7 && g_gemm_force_tc == 0;
+  return g_gemm_mode != 0 && !tiny;
+}
+
+// nb_gemm with operand pitches (floats): A is stored with pitch lda >= its row length, B with ldb; C is dense.
+int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M, int64_t N,
+            int64_t K, int trans_a, int trans_b, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NB_REQUIRE(d_a && d_b && d_c, "nb_gemm: null pointer");
   NB_REQUIRE(M > 0 && N > 0 && K >= 0, "nb_gemm: negative dimension");
   NB_REQUIRE(!(trans_a && trans_b), "nb_gemm: TT is not supported");
-  cudaStream_t stream = as_stream(stream_);
+  NB_REQUIRE(lda >= (trans_a ? M : K) && ldb >= (trans_b ? K : N), "nb_gemm: pitch shorter than a row");
   if (K == 0) {
     NB_CUDA(cudaMemsetAsync(d_c, 0, (size_t)(M * N) * sizeof(float), stream));
     return 0;
   }
   // Small products (the output layer and its gradients) finish sooner on the CUDA cores than the
   // tensor-core kernel takes to set up its pipeline (TMEM allocation, 200 KB of staging buffers).
-  const bool tiny = 2.0 * (double)M * (double)N * (double)K < 4.0e7 && g_gemm_force_tc == 0;
-  if (g_gemm_mode != 0 && !tiny)
-    return gemm_tensor_core(ws, d_a, d_b, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
+  if (gemm_uses_tensor_cores(M, N, K))
+    return gemm_tensor_core(ws, d_a, lda, d_b, ldb, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
   GemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
-  g.sa_i = trans_a ? 1 : K;  g.sa_k = trans_a ? M : 1;
-  g.sb_k = trans_b ? 1 : N;  g.sb_j = trans_b ? K : 1;
+  g.sa_i = trans_a ? 1 : lda;  g.sa_k = trans_a ? lda : 1;
+  g.sb_k = trans_b ? 1 : ldb;  g.sb_j = trans_b ? ldb : 1;
   const int64_t tiles = ((M + kTM - 1) / kTM) * ((N + kTN - 1) / kTN);
   int splits = 1;
   if (tiles < 2 * kNumSMs && K >= 4 * kTK * 8) {
@@ -292,6 +304,8 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
   }
   return 0;
 }
+
+}  // namespace nb
 
 NB_API int nb_set_gemm_mode(int mode) {
   const int old = g_gemm_mode;

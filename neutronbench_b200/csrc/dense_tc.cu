@@ -16,81 +16,11 @@
 // the MMAs that read it have finished.
 #include <cstdlib>
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace nb {
 
-// Threads per CTA (template parameter T of the kernel): 256 when the grid can put two CTAs on every SM (one stages
-// operands while the other waits on its MMAs), 512 when a single wave leaves one CTA per SM.
-constexpr int kBM = 128;           // rows of a C tile = TMEM lanes
-constexpr int kBK = 16;            // K elements per shared-memory chunk (2 MMA K-steps of 8)
-constexpr int kCtasPerSM = 2;      // 108 KB of shared memory and 128 TMEM columns per CTA
-constexpr uint32_t kTcWaitLimit = 1u << 20;
-
 __device__ unsigned int g_tc_gemm_error = 0;
-
-struct TcGemmArgs {
-  const float *a, *b;
-  float *c;                 // output, or split-K partials [splits][M][N]
-  int64_t M, N, K;
-  int64_t a_row, a_k;       // element strides of op(A)(i,k): address = a + i*a_row + k*a_k
-  int64_t b_row, b_k;       // element strides of op(B)^T(j,k): address = b + j*b_row + k*b_k
-  int64_t k_per_split;
-  int a_vec, b_vec;         // widest aligned vector (floats) along the unit-stride dimension
-  int mode;                 // 1: 3xTF32, 2: 1xTF32
-  int debug;
-};
-
-__device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the limit ran out (the caller records the error and winds down).
-__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kTcWaitLimit; i++)
-    if (tc_mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-
-// Shared-memory matrix descriptor: start address, the two strides (see the tile layouts below), bit 46 =
-// descriptor version 1, bits 61-63 = layout type.
-__device__ __forceinline__ uint64_t tc_make_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo, uint32_t layout = 0) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)(layout & 7) << 61;   // 0: no swizzle, 1: 128-byte swizzle with 32-byte atoms
-  return d;
-}
-
-__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_split(float x, float &hi, float &lo) {
-  hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-  lo = x - hi;
-}
 
 // Tile layouts in shared memory (floats).  A tile holds ROWS rows (M or N index) by kBK reduction elements.
 //
@@ -140,7 +70,6 @@ template <> struct DescStride<true> {
   static constexpr uint32_t lbo = kMnBlockFloats * 4, sbo = kMnAtomFloats * 4, kstep = 2 * kMnAtomFloats * 4, layout = 1;
 };
 
-constexpr int kStages = 4;        // raw operand stages filled by cp.async, two chunks ahead of the MMAs
 
 template <int BYTES>
 __device__ __forceinline__ void cp_async(uint32_t dst, const void *src, int valid) {
@@ -229,6 +158,51 @@ struct CopyPlan {
     else if (vec == 2) issue_vec<2>(tile_s, p);
     else issue_vec<1>(tile_s, p);
   }
+  // hi/lo split of exactly the pieces this thread copied (after its own cp.async.wait_group): raw -> hi in
+  // place, lo = raw - hi into the same offsets of `lo`.  No other thread's data is touched, so the staging
+  // threads need no barrier among themselves.  Zero-filled pieces are processed too (lo must be zero there).
+  template <int VEC>
+  __device__ __forceinline__ void split_vec(unsigned char *raw, unsigned char *lo, bool split) const {
+    constexpr int N = kMaxPieces / VEC > 0 ? kMaxPieces / VEC : 1;
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+      if (N > 1 || i < pieces) {
+        float x[VEC], h[VEC], l[VEC];
+        if (VEC == 4) *reinterpret_cast<float4 *>(x) = *reinterpret_cast<const float4 *>(raw + dst[i]);
+        else if (VEC == 2) *reinterpret_cast<float2 *>(x) = *reinterpret_cast<const float2 *>(raw + dst[i]);
+        else x[0] = *reinterpret_cast<const float *>(raw + dst[i]);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) tc_split(x[e], h[e], l[e]);
+        if (VEC == 4) {
+          *reinterpret_cast<float4 *>(raw + dst[i]) = *reinterpret_cast<float4 *>(h);
+          if (split) *reinterpret_cast<float4 *>(lo + dst[i]) = *reinterpret_cast<float4 *>(l);
+        } else if (VEC == 2) {
+          *reinterpret_cast<float2 *>(raw + dst[i]) = *reinterpret_cast<float2 *>(h);
+          if (split) *reinterpret_cast<float2 *>(lo + dst[i]) = *reinterpret_cast<float2 *>(l);
+        } else {
+          *reinterpret_cast<float *>(raw + dst[i]) = h[0];
+          if (split) *reinterpret_cast<float *>(lo + dst[i]) = l[0];
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ void split_own(float *raw, float *lo, bool split) const {
+    unsigned char *r = reinterpret_cast<unsigned char *>(raw), *l = reinterpret_cast<unsigned char *>(lo);
+    if (vec == 4) split_vec<4>(r, l, split);
+    else if (vec == 2) split_vec<2>(r, l, split);
+    else split_vec<1>(r, l, split);
+  }
+  // The same for the tail chunk, whose elements were copied one by one by issue_tail.
+  __device__ void split_tail(float *raw, float *lo, bool split) const {
+    for (int item = threadIdx.x; item < ROWS * kBK; item += T) {
+      const int r = MN ? item % ROWS : item / kBK, k = MN ? item / ROWS : item % kBK;
+      const uint32_t off = tile_off<MN>(r, k);
+      float h, l;
+      tc_split(raw[off], h, l);
+      raw[off] = h;
+      if (split) lo[off] = l;
+    }
+  }
   // The one chunk with a K tail: element by element with bounds checks.
   __device__ void issue_tail(uint32_t tile_s, int64_t k0, int64_t k_end) const {
     for (int item = threadIdx.x; item < ROWS * kBK; item += T) {
@@ -267,19 +241,30 @@ struct SplitPlan {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN, int T>
-__global__ void __launch_bounds__(T, T == 256 ? kCtasPerSM : 1) gemm_tc_kernel(const TcGemmArgs g) {
+// Warp-specialised main loop.  NS staging threads (256, or 512 when the CTA has an SM to itself) copy and split operand tiles; one more warp only
+// issues MMAs.  The two sides meet through mbarriers alone:
+//   full[s]  (count = staging threads) a staging thread arrives once its own pieces of the chunk in stage s are
+//            copied, split and fenced towards the tensor core's proxy;
+//   empty[s] (count = 1) tcgen05.commit arrives when the MMAs that read stage s have finished.
+// A staging thread splits exactly the pieces it copied itself, so it waits only for its own cp.async group
+// and never for another staging thread: there is no block-wide barrier in the loop, and the latency of
+// issuing MMAs is off the staging path.
+template <int BN, bool A_MN, bool B_MN, int S, int NS>
+__global__ void __launch_bounds__(NS + 32, S <= 3 ? kCtasPerSM : 1) gemm_tc_kernel(const TcGemmArgs g) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
+  constexpr int T = NS;   // staging threads; one more warp issues the MMAs
   constexpr uint32_t A_TILE = TileFloats<kBM>::value;
   constexpr uint32_t B_TILE = TileFloats<BN>::value;
-  float *a_raw = reinterpret_cast<float *>(tc_smem);                 // [kStages][A_TILE]  (becomes hi)
-  float *b_raw = a_raw + kStages * A_TILE;                           // [kStages][B_TILE]
-  float *a_lo = b_raw + kStages * B_TILE;                            // [2][A_TILE]
-  float *b_lo = a_lo + 2 * A_TILE;                                   // [2][B_TILE]
-  uint64_t *bars = reinterpret_cast<uint64_t *>(b_lo + 2 * B_TILE);  // [kStages]: MMAs of a chunk finished
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kStages);
+  float *a_raw = reinterpret_cast<float *>(tc_smem);                 // [S][A_TILE]  (becomes hi)
+  float *b_raw = a_raw + S * A_TILE;                                 // [S][B_TILE]
+  float *a_lo = b_raw + S * B_TILE;                                  // [S][A_TILE]
+  float *b_lo = a_lo + S * A_TILE;                                   // [S][B_TILE]
+  uint64_t *full = reinterpret_cast<uint64_t *>(b_lo + S * B_TILE);  // [S]
+  uint64_t *empty = full + S;                                        // [S]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(empty + S);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_stager = tid < T;
   const bool split = g.mode == 1;
   const int64_t row0 = (int64_t)blockIdx.x * kBM, col0 = (int64_t)blockIdx.y * BN;
   const int64_t k_begin = (int64_t)blockIdx.z * g.k_per_split;
@@ -293,7 +278,10 @@ __global__ void __launch_bounds__(T, T == 256 ? kCtasPerSM : 1) gemm_tc_kernel(c
   }
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kStages; s++) tc_mbar_init(tc_smem_u32(&bars[s]), 1);
+    for (int s = 0; s < S; s++) {
+      tc_mbar_init(tc_smem_u32(&full[s]), T);
+      tc_mbar_init(tc_smem_u32(&empty[s]), 1);
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   tc_fence_before();
@@ -305,103 +293,113 @@ __global__ void __launch_bounds__(T, T == 256 ? kCtasPerSM : 1) gemm_tc_kernel(c
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   bool ok = true;
-
-  CopyPlan<kBM, A_MN, T> plan_a;
-  CopyPlan<BN, B_MN, T> plan_b;
-  plan_a.init(g.a, g.a_row, g.a_k, row0, g.M, k_begin, g.a_vec);
-  plan_b.init(g.b, g.b_row, g.b_k, col0, g.N, k_begin, g.b_vec);
-  SplitPlan<kBM, A_MN, T> split_a;
-  SplitPlan<BN, B_MN, T> split_b;
-  split_a.init();
-  split_b.init();
   const int full_chunks = (int)((k_end - k_begin) / kBK);   // chunks without a K tail
 
-  auto start_copy = [&](int chunk) {
-    if (g.debug & 4) { cp_async_commit(); return; }
-    if (chunk < full_chunks) {
-      const int st = chunk % kStages;
-      plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk);
-      plan_b.issue(tc_smem_u32(b_raw + st * B_TILE), chunk);
-    } else if (chunk < nchunks) {   // the one chunk with a K tail: bounds-checked copies
-      const int st = chunk % kStages;
-      const int64_t k0 = k_begin + (int64_t)chunk * kBK;
-      plan_a.issue_tail(tc_smem_u32(a_raw + st * A_TILE), k0, k_end);
-      plan_b.issue_tail(tc_smem_u32(b_raw + st * B_TILE), k0, k_end);
-    }
-    cp_async_commit();   // one group per chunk slot, empty past the end, so that the wait count is constant
-  };
-  // A K-major operand is read 64 bytes per row and chunk; left alone, DRAM serves those as scattered
-  // short bursts.  Every kPrefetchChunks chunks one thread per row asks L2 for the row's next
-  // kPrefetchChunks * 64 bytes in whole lines, so DRAM sees long bursts and the chunk copies hit L2.
-  constexpr int kPrefetchChunks = 8;
-  auto prefetch_rows = [&](int chunk_lo) {
-    if (A_MN || tid >= kBM || row0 + tid >= g.M) return;
-    const int64_t k_lo = k_begin + (int64_t)chunk_lo * kBK;
-    const int64_t k_hi = min(k_end, k_lo + (int64_t)kPrefetchChunks * kBK);
-    if (k_lo >= k_hi) return;
-    const char *row = reinterpret_cast<const char *>(g.a + (row0 + tid) * g.a_row);
-    const char *lo = reinterpret_cast<const char *>(reinterpret_cast<uintptr_t>(row + k_lo * 4) & ~(uintptr_t)127);
-    const char *hi = row + k_hi * 4;
-    for (const char *q = lo; q < hi; q += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
-  };
-  prefetch_rows(0);
-  prefetch_rows(kPrefetchChunks);
-  start_copy(0);
-  start_copy(1);
+  if (is_stager) {
+    CopyPlan<kBM, A_MN, T> plan_a;
+    CopyPlan<BN, B_MN, T> plan_b;
+    plan_a.init(g.a, g.a_row, g.a_k, row0, g.M, k_begin, g.a_vec);
+    plan_b.init(g.b, g.b_row, g.b_k, col0, g.N, k_begin, g.b_vec);
 
-  for (int c = 0; c < nchunks; c++) {
-    const int st = c % kStages, lb = c & 1;
-    cp_async_wait<1>();            // this thread's copies of chunk c have landed (chunk c+1 may be in flight)
-    bool mine = true;
-    if (c >= 2 && !(g.debug & 2)) {
-      // MMAs of chunk c-2 done: its lo buffer (same parity) and its raw stage (refilled below) are free.
-      mine = tc_mbar_wait(tc_smem_u32(&bars[(c - 2) % kStages]), ((c - 2) / kStages) & 1);
-    }
-    if (!__syncthreads_and(mine)) { ok = false; break; }   // also: everybody's copies of chunk c are visible
-    start_copy(c + 2);             // into the stage chunk c-2 used
-    if (c % kPrefetchChunks == 0) prefetch_rows(c + 2 * kPrefetchChunks);
-    if (!(g.debug & 1)) {
-      split_a.run(a_raw + st * A_TILE, a_lo + lb * A_TILE, split);
-      split_b.run(b_raw + st * B_TILE, b_lo + lb * B_TILE, split);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && !(g.debug & 2)) {
-      tc_fence_after();
-      const uint32_t a_h = tc_smem_u32(a_raw + st * A_TILE), a_l = tc_smem_u32(a_lo + lb * A_TILE);
-      const uint32_t b_h = tc_smem_u32(b_raw + st * B_TILE), b_l = tc_smem_u32(b_lo + lb * B_TILE);
-#pragma unroll
-      for (int kk = 0; kk < kBK / 8; kk++) {
-        // one K step = 8 tf32: two K-major core matrices, or one MN-major core matrix, further along K
-        using SA = DescStride<A_MN>;
-        using SB = DescStride<B_MN>;
-        const uint32_t ka = kk * SA::kstep, kb = kk * SB::kstep;
-        const uint64_t da_h = tc_make_desc(a_h + ka, SA::lbo, SA::sbo, SA::layout);
-        const uint64_t db_h = tc_make_desc(b_h + kb, SB::lbo, SB::sbo, SB::layout);
-        tc_mma_tf32(tmem, da_h, db_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
-        if (split) {
-          const uint64_t da_l = tc_make_desc(a_l + ka, SA::lbo, SA::sbo, SA::layout);
-          const uint64_t db_l = tc_make_desc(b_l + kb, SB::lbo, SB::sbo, SB::layout);
-          tc_mma_tf32(tmem, da_h, db_l, idesc, 1u);
-          tc_mma_tf32(tmem, da_l, db_h, idesc, 1u);
+    // A K-major operand is read 64 bytes per row and chunk; every kPrefetchChunks chunks one thread per row
+    // asks L2 for the row's next kPrefetchChunks * 64 bytes in whole lines, so that DRAM sees long bursts.
+    constexpr int kPrefetchChunks = 8;
+    auto prefetch_rows = [&](int chunk_lo) {
+      if (A_MN || tid >= kBM || row0 + tid >= g.M) return;
+      const int64_t k_lo = k_begin + (int64_t)chunk_lo * kBK;
+      const int64_t k_hi = min(k_end, k_lo + (int64_t)kPrefetchChunks * kBK);
+      if (k_lo >= k_hi) return;
+      const char *row = reinterpret_cast<const char *>(g.a + (row0 + tid) * g.a_row);
+      const char *lo = reinterpret_cast<const char *>(reinterpret_cast<uintptr_t>(row + k_lo * 4) & ~(uintptr_t)127);
+      const char *hi = row + k_hi * 4;
+      for (const char *q = lo; q < hi; q += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+    };
+    // copies of chunk `chunk` into its stage; one cp.async group per call, empty past the end, so that the
+    // wait count below is a constant
+    auto start_copy = [&](int chunk) {
+      if (chunk < nchunks) {
+        const int st = chunk % S;
+        if (chunk >= S) {   // the stage is being reused: the MMAs of chunk - S must have finished reading it
+          if (!tc_mbar_wait(tc_smem_u32(&empty[st]), ((chunk / S) - 1) & 1)) ok = false;
+        }
+        if (ok) {
+          if (chunk < full_chunks) {
+            plan_a.issue(tc_smem_u32(a_raw + st * A_TILE), chunk);
+            plan_b.issue(tc_smem_u32(b_raw + st * B_TILE), chunk);
+          } else {
+            const int64_t k0 = k_begin + (int64_t)chunk * kBK;
+            plan_a.issue_tail(tc_smem_u32(a_raw + st * A_TILE), k0, k_end);
+            plan_b.issue_tail(tc_smem_u32(b_raw + st * B_TILE), k0, k_end);
+          }
         }
       }
-      tc_commit(tc_smem_u32(&bars[st]));
+      cp_async_commit();
+    };
+    // Chunks in flight ahead of the one being split.  Refilling the stage of chunk c-1 would wait for MMAs
+    // that have only just been issued, so with four or more stages the copy goes S-2 chunks ahead (into the
+    // stage chunk c-2 used); three stages (two CTAs per SM, which cover for each other) leave one.
+    constexpr int kAhead = S >= 4 ? S - 2 : 1;
+    prefetch_rows(0);
+    prefetch_rows(kPrefetchChunks);
+#pragma unroll
+    for (int c = 0; c < kAhead; c++) start_copy(c);
+    for (int c = 0; c < nchunks && ok; c++) {
+      const int st = c % S;
+      start_copy(c + kAhead);                 // into a stage whose MMAs are done (waits for them if not)
+      if (c % kPrefetchChunks == 0) prefetch_rows(c + 2 * kPrefetchChunks);
+      cp_async_wait<kAhead>();                // this thread's copies of chunk c have landed
+      if (c < full_chunks) {
+        plan_a.split_own(a_raw + st * A_TILE, a_lo + st * A_TILE, split);
+        plan_b.split_own(b_raw + st * B_TILE, b_lo + st * B_TILE, split);
+      } else {
+        plan_a.split_tail(a_raw + st * A_TILE, a_lo + st * A_TILE, split);
+        plan_b.split_tail(b_raw + st * B_TILE, b_lo + st * B_TILE, split);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&full[st])) : "memory");
+    }
+    cp_async_wait<0>();   // nothing of ours may still be landing in shared memory when the CTA winds down
+  } else {
+    // MMA warp: waits for a full stage, issues its MMAs from one lane, commits to the stage's empty barrier
+    for (int c = 0; c < nchunks; c++) {
+      const int st = c % S;
+      if (!tc_mbar_wait(tc_smem_u32(&full[st]), (c / S) & 1)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t a_h = tc_smem_u32(a_raw + st * A_TILE), a_l = tc_smem_u32(a_lo + st * A_TILE);
+        const uint32_t b_h = tc_smem_u32(b_raw + st * B_TILE), b_l = tc_smem_u32(b_lo + st * B_TILE);
+#pragma unroll
+        for (int kk = 0; kk < kBK / 8; kk++) {
+          // one K step = 8 tf32: two K-major core matrices, or one MN-major core matrix, further along K
+          using SA = DescStride<A_MN>;
+          using SB = DescStride<B_MN>;
+          const uint32_t ka = kk * SA::kstep, kb = kk * SB::kstep;
+          const uint64_t da_h = tc_make_desc(a_h + ka, SA::lbo, SA::sbo, SA::layout);
+          const uint64_t db_h = tc_make_desc(b_h + kb, SB::lbo, SB::sbo, SB::layout);
+          tc_mma_tf32(tmem, da_h, db_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+          if (split) {
+            const uint64_t da_l = tc_make_desc(a_l + ka, SA::lbo, SA::sbo, SA::layout);
+            const uint64_t db_l = tc_make_desc(b_l + kb, SB::lbo, SB::sbo, SB::layout);
+            tc_mma_tf32(tmem, da_h, db_l, idesc, 1u);
+            tc_mma_tf32(tmem, da_l, db_h, idesc, 1u);
+          }
+        }
+        tc_commit(tc_smem_u32(&empty[st]));
+      }
+      __syncwarp();
     }
   }
-  cp_async_wait<0>();   // nothing of ours may still be landing in shared memory when the CTA winds down
 
   // all MMAs done: the last commit covers every earlier one
-  if (ok && nchunks > 0 && !(g.debug & 2)) {
+  if (ok && nchunks > 0) {
     const int last = nchunks - 1;
-    ok = tc_mbar_wait(tc_smem_u32(&bars[last % kStages]), (last / kStages) & 1);
+    ok = tc_mbar_wait(tc_smem_u32(&empty[last % S]), (last / S) & 1);
   }
   ok = __syncthreads_and(ok);
   if (!ok && tid == 0) atomicExch(&g_tc_gemm_error, 1u);
   tc_fence_after();
 
-  if (ok) {
+  if (ok && is_stager) {
     // Warp w reads TMEM lanes 32*(w%4)..+31 (the only ones it can reach); warps 0-3 take the left half
     // of the columns, warps 4-7 the right half.
     float *out = g.c + (int64_t)blockIdx.z * g.M * g.N;
@@ -452,15 +450,15 @@ __global__ void __launch_bounds__(T, T == 256 ? kCtasPerSM : 1) gemm_tc_kernel(c
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, int T>
-static int launch_tc_t(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)((kStages + 2) * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
+template <int BN, bool A_MN, bool B_MN, int S, int NS>
+static int launch_tc_s(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)(2 * S * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
   static bool configured = false;
   if (!configured) {
-    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN, S, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  gemm_tc_kernel<BN, A_MN, B_MN, T><<<grid, T, smem, stream>>>(g);
+  gemm_tc_kernel<BN, A_MN, B_MN, S, NS><<<grid, NS + 32, smem, stream>>>(g);
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -474,14 +472,20 @@ __global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float
   }
 }
 
-// 512 threads when every CTA has an SM to itself (more warps to hide the staging latency), 256 otherwise.
+// Six stages (the whole shared memory of an SM) when every CTA has an SM to itself, three when the grid can put
+// two CTAs on an SM.
 template <int BN, bool A_MN, bool B_MN>
 static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   const int64_t ctas = (int64_t)grid.x * grid.y * grid.z;
-  int threads = ctas <= kNumSMs ? 512 : 256;
-  if (getenv("NB_TC_THREADS")) threads = atoi(getenv("NB_TC_THREADS"));
-  if (threads == 512) return launch_tc_t<BN, A_MN, B_MN, 512>(g, grid, stream);
-  return launch_tc_t<BN, A_MN, B_MN, 256>(g, grid, stream);
+  int stages = ctas <= kNumSMs ? 6 : 3;
+  if (getenv("NB_TC_STAGES")) stages = atoi(getenv("NB_TC_STAGES"));
+  int stagers = stages >= 4 ? 512 : 256;
+  if (getenv("NB_TC_STAGERS")) stagers = atoi(getenv("NB_TC_STAGERS"));
+  if (stages >= 6) {
+    if (stagers == 512) return launch_tc_s<BN, A_MN, B_MN, 6, 512>(g, grid, stream);
+    return launch_tc_s<BN, A_MN, B_MN, 6, 256>(g, grid, stream);
+  }
+  return launch_tc_s<BN, A_MN, B_MN, 3, 256>(g, grid, stream);
 }
 
 // The three operand layouts of the GCN step: Y W (B transposed in memory relative to K-major), Y^T dZ
@@ -502,30 +506,40 @@ static int vec_of(const float *p, int64_t ld) {
 }
 
 // Tensor-core GEMM front end; same contract as the CUDA-core path in dense.cu.
-int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
-                     int trans_a, int trans_b, int mode, cudaStream_t stream) {
+int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
+                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream) {
   TcGemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K; g.mode = mode;
-  // op(A)(i,k): NN/NT -> A[i*K + k];  TN -> A[k*M + i]
-  g.a_row = trans_a ? 1 : K;  g.a_k = trans_a ? M : 1;
-  // op(B)^T(j,k) = op(B)(k,j): NN/TN -> B[k*N + j];  NT -> B[j*K + k]
-  g.b_row = trans_b ? K : 1;  g.b_k = trans_b ? 1 : N;
-  g.a_vec = vec_of(d_a, trans_a ? M : K);
-  g.b_vec = vec_of(d_b, trans_b ? K : N);
+  // op(A)(i,k): NN/NT -> A[i*lda + k];  TN -> A[k*lda + i]
+  g.a_row = trans_a ? 1 : lda;  g.a_k = trans_a ? lda : 1;
+  // op(B)^T(j,k) = op(B)(k,j): NN/TN -> B[k*ldb + j];  NT -> B[j*ldb + k]
+  g.b_row = trans_b ? ldb : 1;  g.b_k = trans_b ? 1 : ldb;
+  // widest piece that is aligned and divides the extent along the contiguous direction (a padded pitch must
+  // not let a piece reach into the padding)
+  auto piece = [](const float *p, int64_t ld, int64_t extent) {
+    int v = vec_of(p, ld);
+    while (v > 1 && extent % v != 0) v >>= 1;
+    return v;
+  };
+  g.a_vec = piece(d_a, lda, trans_a ? M : K);
+  g.b_vec = piece(d_b, ldb, trans_b ? K : N);
   const int bn = N > 64 ? 128 : (N > 32 ? 64 : 32);
   const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  // Split-K towards one CTA per SM; ranges are multiples of 32 so that both kernels cut K at the same places.
   int splits = 1;
-  const int64_t slots = (int64_t)kNumSMs * kCtasPerSM;   // CTAs resident at once
-  if (tiles < slots && K >= 256) {
-    splits = (int)(slots / tiles);
-    const int64_t max_splits = K / 128;
+  if (tiles < kNumSMs && K >= 512) {
+    splits = (int)(kNumSMs / tiles);
+    const int64_t max_splits = K / 256;
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
   }
   if (getenv("NB_TC_SPLITS")) splits = atoi(getenv("NB_TC_SPLITS"));
-  g.debug = getenv("NB_TC_DEBUG") ? atoi(getenv("NB_TC_DEBUG")) : 0;
-  g.k_per_split = ((K + splits - 1) / splits + kBK - 1) / kBK * kBK;
+  g.k_per_split = ((K + splits - 1) / splits + 31) / 32 * 32;
   splits = (int)((K + g.k_per_split - 1) / g.k_per_split);
+  // TMA tensor loads need 16-byte aligned bases and pitches, and boxes that fit inside the tensor
+  const bool a_mn = trans_a != 0, b_mn = trans_b == 0;
+  const bool use_tma = !getenv("NB_TC_NO_TMA") && tma_gemm_applicable(d_a, lda, d_b, ldb) && K >= 32 &&
+                       (a_mn ? M >= 32 : M >= kBM) && (b_mn ? N >= 32 : N >= bn);
   WsScope scope(ws);
   float *partial = nullptr;
   if (splits > 1) {
@@ -537,10 +551,14 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
   dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + bn - 1) / bn), (unsigned)splits);
   if (grid.y > 65535) return fail(NB_ERR_INVALID, "nb_gemm: N too large for one launch");
   int st;
-  switch (bn) {
-    case 128: st = launch_layout<128>(g, trans_a, trans_b, grid, stream); break;
-    case 64: st = launch_layout<64>(g, trans_a, trans_b, grid, stream); break;
-    default: st = launch_layout<32>(g, trans_a, trans_b, grid, stream); break;
+  if (use_tma) {
+    st = gemm_tma_launch(d_a, lda, d_b, ldb, g.c, M, N, K, trans_a, trans_b, bn, splits, g.k_per_split, mode, stream);
+  } else {
+    switch (bn) {
+      case 128: st = launch_layout<128>(g, trans_a, trans_b, grid, stream); break;
+      case 64: st = launch_layout<64>(g, trans_a, trans_b, grid, stream); break;
+      default: st = launch_layout<32>(g, trans_a, trans_b, grid, stream); break;
+    }
   }
   if (st != 0) return st;
   if (splits > 1) {
@@ -551,7 +569,10 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, 
 }
 
 int read_tc_error_flag(unsigned int *value) {
-  NB_CUDA(cudaMemcpyFromSymbol(value, g_tc_gemm_error, sizeof(unsigned int)));
+  unsigned int a = 0, b = 0;
+  NB_CUDA(cudaMemcpyFromSymbol(&a, g_tc_gemm_error, sizeof(unsigned int)));
+  NB_TRY(read_tma_gemm_error_flag(&b));
+  *value = a | b;
   return 0;
 }
 

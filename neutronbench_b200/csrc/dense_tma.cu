@@ -1,0 +1,311 @@
+// fp32 GEMM on tcgen05 (kind::tf32, three-term hi/lo split) with the operands brought into shared memory by
+// TMA tensor loads: one thread issues one cp.async.bulk.tensor per tile (four per transposed tile) and the tile
+// arrives already in the swizzled layout the tensor core reads, so no thread computes a source address or
+// issues a copy for an element, and the hi/lo split runs as a straight pass over whole tiles.
+//
+// Used when both operands qualify for a tensor map: base 16-byte aligned and pitch a multiple of 4 floats.  The
+// cp.async kernel of dense_tc.cu serves everything else.  Both issue the same MMAs in the same order (K steps of 8
+// ascending; hi*hi, hi*lo, lo*hi per step; split-K ranges in multiples of 32), so they give identical bits.
+//
+// Layouts (measured, see the notes on MN-major operands in dense_tc.cu):
+//   K-major operand   box {32 floats of K, ROWS rows}, CU_TENSOR_MAP_SWIZZLE_128B; descriptor layout type 2,
+//                     SBO = 1024 bytes (8 rows of 128 bytes), K step of 8 = +32 bytes inside the swizzle line.
+//   MN-major operand  boxes {32 rows, 32 k}, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, one per block of 32 rows (4 KB
+//                     each); descriptor layout type 1, LBO = 4096 (row blocks), SBO = 512 (groups of 4 k),
+//                     K step of 8 = +1024 bytes.
+// Rows beyond the matrix and the K tail are zero-filled by the TMA unit (out-of-bounds box elements).
+//
+// Warp roles: warps 0-7 split tiles (lo = x - hi) and run the epilogue, warp 8 issues the tensor loads, warp 9 the
+// MMAs.  Three barriers per stage: loaded (TMA transaction bytes), split (256 arrivals), free (tcgen05.commit).
+// Every wait is bounded; a wait that runs out sets the error word read by nb_device_error_flags.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace nb {
+
+__device__ unsigned int g_tma_gemm_error = 0;
+
+constexpr int kTmaBK = 32;            // K per chunk: one 128-byte swizzle line
+constexpr int kTmaStages = 3;
+constexpr int kSplitThreads = 256;    // warps 0-7
+constexpr int kTmaThreads = kSplitThreads + 64;
+
+struct TmaGemmArgs {
+  float *c;                 // output, or split-K partials [splits][M][N]
+  int64_t M, N, K;
+  int64_t k_per_split;      // multiple of kTmaBK
+  int mode;                 // 1: 3xTF32, 2: 1xTF32
+};
+
+template <bool MN> struct TmaDesc {};
+template <> struct TmaDesc<false> { static constexpr uint32_t lbo = 16, sbo = 1024, kstep = 32, layout = 2; };
+template <> struct TmaDesc<true> { static constexpr uint32_t lbo = 4096, sbo = 512, kstep = 1024, layout = 1; };
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// One operand tile of a chunk: ROWS rows starting at row0, K range [k0, k0 + 32).
+template <int ROWS, bool MN>
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap *map, int row0, int k0, uint32_t bar) {
+  if (MN) {
+#pragma unroll
+    for (int rb = 0; rb < ROWS / 32; rb++) tma_load_2d(dst + rb * 4096, map, row0 + rb * 32, k0, bar);
+  } else {
+    tma_load_2d(dst, map, k0, row0, bar);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_b,
+                                                                  const TmaGemmArgs g) {
+  extern __shared__ __align__(1024) unsigned char tc_smem[];
+  constexpr int S = kTmaStages;
+  constexpr uint32_t A_BYTES = kBM * kTmaBK * 4, B_BYTES = BN * kTmaBK * 4;   // 16 KB, and 4 / 8 / 16 KB
+  constexpr uint32_t STAGE = 2 * (A_BYTES + B_BYTES);                        // raw A | raw B | lo A | lo B
+  uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + (size_t)S * STAGE);
+  uint64_t *loaded = bars, *split_done = bars + S, *freed = bars + 2 * S;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool split = g.mode == 1;
+  const int row0 = (int)blockIdx.x * kBM, col0 = (int)blockIdx.y * BN;
+  const int64_t k_begin = (int64_t)blockIdx.z * g.k_per_split;
+  const int64_t k_end = min(g.K, k_begin + g.k_per_split);
+  const int nchunks = (int)((k_end - k_begin + kTmaBK - 1) / kTmaBK);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)),
+                 "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+      tc_mbar_init(tc_smem_u32(&loaded[s]), 1);
+      tc_mbar_init(tc_smem_u32(&split_done[s]), kSplitThreads);
+      tc_mbar_init(tc_smem_u32(&freed[s]), 1);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  bool ok = true;
+
+  if (warp == 8) {
+    // ---- producer: tensor loads, one stage ahead of nothing but the free barrier
+    if (lane == 0) {
+      for (int c = 0; c < nchunks; c++) {
+        const int st = c % S;
+        if (c >= S && !tc_mbar_wait(tc_smem_u32(&freed[st]), ((c / S) - 1) & 1)) { ok = false; break; }
+        const uint32_t bar = tc_smem_u32(&loaded[st]);
+        const uint32_t a_dst = tc_smem_u32(tc_smem + (size_t)st * STAGE), b_dst = a_dst + A_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(A_BYTES + B_BYTES) : "memory");
+        const int k0 = (int)(k_begin + (int64_t)c * kTmaBK);
+        tma_load_tile<kBM, A_MN>(a_dst, &map_a, row0, k0, bar);
+        tma_load_tile<BN, B_MN>(b_dst, &map_b, col0, k0, bar);
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  } else if (warp == 9) {
+    // ---- MMA issuer
+    for (int c = 0; c < nchunks; c++) {
+      const int st = c % S;
+      if (!tc_mbar_wait(tc_smem_u32(&split_done[st]), (c / S) & 1)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t a_h = tc_smem_u32(tc_smem + (size_t)st * STAGE), b_h = a_h + A_BYTES;
+        const uint32_t a_l = a_h + A_BYTES + B_BYTES, b_l = a_l + A_BYTES;
+        using DA = TmaDesc<A_MN>;
+        using DB = TmaDesc<B_MN>;
+#pragma unroll
+        for (int kk = 0; kk < kTmaBK / 8; kk++) {
+          const uint64_t da_h = tc_make_desc(a_h + kk * DA::kstep, DA::lbo, DA::sbo, DA::layout);
+          const uint64_t db_h = tc_make_desc(b_h + kk * DB::kstep, DB::lbo, DB::sbo, DB::layout);
+          tc_mma_tf32(tmem, da_h, db_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+          if (split) {
+            const uint64_t da_l = tc_make_desc(a_l + kk * DA::kstep, DA::lbo, DA::sbo, DA::layout);
+            const uint64_t db_l = tc_make_desc(b_l + kk * DB::kstep, DB::lbo, DB::sbo, DB::layout);
+            tc_mma_tf32(tmem, da_h, db_l, idesc, 1u);
+            tc_mma_tf32(tmem, da_l, db_h, idesc, 1u);
+          }
+        }
+        tc_commit(tc_smem_u32(&freed[st]));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---- splitters: hi in place (low 13 mantissa bits cleared), lo = x - hi into the second half of the stage.
+    // Element by element and position-preserving, so the swizzle pattern does not matter here.
+    constexpr int QUADS = (A_BYTES + B_BYTES) / 16;
+    for (int c = 0; c < nchunks && ok; c++) {
+      const int st = c % S;
+      if (!tc_mbar_wait(tc_smem_u32(&loaded[st]), (c / S) & 1)) { ok = false; break; }
+      float4 *raw = reinterpret_cast<float4 *>(tc_smem + (size_t)st * STAGE);
+      float4 *lo = raw + QUADS;
+#pragma unroll 4
+      for (int q = tid; q < QUADS; q += kSplitThreads) {
+        const float4 x = raw[q];
+        float h[4], l[4];
+        tc_split(x.x, h[0], l[0]); tc_split(x.y, h[1], l[1]); tc_split(x.z, h[2], l[2]); tc_split(x.w, h[3], l[3]);
+        raw[q] = make_float4(h[0], h[1], h[2], h[3]);
+        if (split) lo[q] = make_float4(l[0], l[1], l[2], l[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&split_done[st])) : "memory");
+    }
+  }
+
+  // all MMAs done: the last commit covers every earlier one
+  if (ok && nchunks > 0) {
+    const int last = nchunks - 1;
+    ok = tc_mbar_wait(tc_smem_u32(&freed[last % S]), (last / S) & 1);
+  }
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) atomicExch(&g_tma_gemm_error, 1u);
+  tc_fence_after();
+
+  if (ok && warp < 8) {
+    // Warp w reads TMEM lanes 32*(w%4)..+31; warps 0-3 and 4-7 alternate over the 32-column blocks.  The values go
+    // through shared memory (the stages are free by now) so that a warp writes whole 128-byte row segments of C.
+    float *out = g.c + (int64_t)blockIdx.z * g.M * g.N;
+    const int quarter = warp & 3, part = warp >> 2;
+    constexpr int CB = BN / 32;
+#pragma unroll
+    for (int cbi = 0; cbi < (CB + 1) / 2; cbi++) {
+      const int cb = cbi * 2 + part;
+      if (cb >= CB) continue;
+      uint32_t r[32];
+      const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + cb * 32;
+      if (nchunks > 0) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; q++) r[q] = 0u;
+      }
+      float *stage = reinterpret_cast<float *>(tc_smem) + warp * (32 * 33);
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 32; q++) stage[lane * 33 + q] = __uint_as_float(r[q]);
+      __syncwarp();
+      const int64_t gj = col0 + cb * 32 + lane;
+      for (int rr = 0; rr < 32; rr++) {
+        const int64_t grow = row0 + quarter * 32 + rr;
+        if (grow < g.M && gj < g.N) out[grow * g.N + gj] = stage[rr * 33 + lane];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+    tried = true;
+  }
+  return fn;
+}
+
+// Tensor map of one operand.  K-major: the matrix is [rows x K] with pitch ld; boxes of 32 k by box_rows rows.
+// MN-major: the matrix is [K x rows] with pitch ld; boxes of 32 rows by 32 k.
+static bool make_operand_map(CUtensorMap *map, const float *base, bool mn, int64_t rows, int64_t K, int64_t ld,
+                             int box_rows) {
+  PFN_cuTensorMapEncodeTiled encode = tensor_map_encoder();
+  if (!encode) return false;
+  cuuint64_t dims[2], strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2], estr[2] = {1, 1};
+  CUtensorMapSwizzle swz;
+  if (mn) {
+    dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K;
+    box[0] = 32; box[1] = kTmaBK;
+    swz = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  } else {
+    dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows;
+    box[0] = kTmaBK; box[1] = (cuuint32_t)box_rows;
+    swz = CU_TENSOR_MAP_SWIZZLE_128B;
+  }
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_tma(const CUtensorMap &ma, const CUtensorMap &mb, const TmaGemmArgs &g, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)kTmaStages * 2 * (kBM + BN) * kTmaBK * 4 + 256;
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(gemm_tma_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  gemm_tma_kernel<BN, A_MN, B_MN><<<grid, kTmaThreads, smem, stream>>>(ma, mb, g);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int BN>
+static int launch_tma_layout(const CUtensorMap &ma, const CUtensorMap &mb, const TmaGemmArgs &g, bool a_mn, bool b_mn,
+                             dim3 grid, cudaStream_t stream) {
+  if (!a_mn && b_mn) return launch_tma<BN, false, true>(ma, mb, g, grid, stream);
+  if (a_mn && b_mn) return launch_tma<BN, true, true>(ma, mb, g, grid, stream);
+  if (!a_mn && !b_mn) return launch_tma<BN, false, false>(ma, mb, g, grid, stream);
+  return launch_tma<BN, true, false>(ma, mb, g, grid, stream);
+}
+
+bool tma_gemm_applicable(const float *d_a, int64_t lda, const float *d_b, int64_t ldb) {
+  auto ok = [](const float *p, int64_t ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld & 3) == 0 && ld > 0; };
+  return ok(d_a, lda) && ok(d_b, ldb) && tensor_map_encoder() != nullptr;
+}
+
+// C (or the split-K partials) = op(A) op(B) for one launch; `c` is dense [splits][M][N].
+int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *c, int64_t M, int64_t N,
+                    int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
+                    cudaStream_t stream) {
+  const bool a_mn = trans_a != 0, b_mn = trans_b == 0;
+  CUtensorMap ma, mb;
+  if (!make_operand_map(&ma, d_a, a_mn, M, K, lda, kBM) || !make_operand_map(&mb, d_b, b_mn, N, K, ldb, bn))
+    return fail(NB_ERR_CUDA, "nb_gemm: cuTensorMapEncodeTiled failed");
+  TmaGemmArgs g{};
+  g.c = c; g.M = M; g.N = N; g.K = K; g.k_per_split = k_per_split; g.mode = mode;
+  dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + bn - 1) / bn), (unsigned)splits);
+  switch (bn) {
+    case 128: return launch_tma_layout<128>(ma, mb, g, a_mn, b_mn, grid, stream);
+    case 64: return launch_tma_layout<64>(ma, mb, g, a_mn, b_mn, grid, stream);
+    default: return launch_tma_layout<32>(ma, mb, g, a_mn, b_mn, grid, stream);
+  }
+}
+
+int read_tma_gemm_error_flag(unsigned int *value) {
+  NB_CUDA(cudaMemcpyFromSymbol(value, g_tma_gemm_error, sizeof(unsigned int)));
+  return 0;
+}
+
+}  // namespace nb

@@ -275,17 +275,22 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   const float p = train ? c.drop_rate : 0.0f;
   const float scale = p > 0.0f ? 1.0f / (1.0f - p) : 1.0f;
   float *Y[NB_MAX_LAYERS], *X[NB_MAX_LAYERS + 1];
+  size_t y_ld[NB_MAX_LAYERS];
   X[0] = nullptr;
   for (uint32_t l = 0; l < L; l++) {
     const Block &b = blk[l];
     const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
-    NB_TRY(arena(ws, (size_t)b.v * Fi, &Y[l]));
+    // Rows of the layer-0 aggregate are padded to 16 bytes when the dense layer runs on the tensor cores, so that
+    // its TMA tensor loads apply to any feature width (602 -> 604); the padding is never read.
+    y_ld[l] = Fi;
+    if (l == 0 && c.fuse_gather && nb::gemm_uses_tensor_cores(b.v, Fo, Fi)) y_ld[l] = (Fi + 3) / 4 * 4;
+    NB_TRY(arena(ws, (size_t)b.v * y_ld[l], &Y[l]));
     if (l == 0) {
       if (c.fuse_gather) {
         AggTimer t(g, stream, bytes_fwd(b, Fi, true, c.d_hashmap != nullptr), 0);
-        NB_TRY(nb_spmm_csc_fwd_gather_fused(ws, c.feat, c.feat_ld, c.d_cache, c.cache_ld, c.d_hashmap, b.source, Y[0],
-                                            b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, b.s, b.e, Fi,
-                                            stream));
+        NB_TRY(nb::spmm_csc_fwd_gather_fused_ld(ws, c.feat, c.feat_ld, c.d_cache, c.cache_ld, c.d_hashmap, b.source,
+                                                Y[0], y_ld[0], b.row_indices, b.column_offset, b.src_norm, b.dst_norm,
+                                                b.v, b.s, b.e, Fi, stream));
         agg_bytes += bytes_fwd(b, Fi, true, c.d_hashmap != nullptr);
       } else {
         NB_TRY(arena(ws, (size_t)b.s * Fi, &X[0]));
@@ -302,7 +307,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
       agg_bytes += bytes_fwd(b, Fi, false, false);
     }
     NB_TRY(arena(ws, (size_t)b.v * Fo, &X[l + 1]));
-    NB_TRY(nb_gemm(ws, Y[l], c.d_W + g->w_off[l], X[l + 1], b.v, Fo, Fi, 0, 0, stream));
+    NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], c.d_W + g->w_off[l], Fo, X[l + 1], b.v, Fo, Fi, 0, 0, nb::as_stream(stream)));
     if (l + 1 < L) NB_TRY(nb_relu_dropout(X[l + 1], (int64_t)b.v * Fo, p, c.seed, l, g->steps, stream));
   }
 
@@ -325,7 +330,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
     for (int l = (int)L - 1; l >= 0; l--) {
       const Block &b = blk[l];
       const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
-      NB_TRY(nb_gemm(ws, Y[l], dZ, c.d_grad + g->w_off[l], Fi, Fo, b.v, 1, 0, stream));
+      NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], dZ, Fo, c.d_grad + g->w_off[l], Fi, Fo, b.v, 1, 0, nb::as_stream(stream)));
       if (l == 0) break;   // the input-side block is never back-propagated (core/ntsContext.hpp:292)
       float *dY, *dX;
       NB_TRY(arena(ws, (size_t)b.v * Fi, &dY));

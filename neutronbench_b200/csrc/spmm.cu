@@ -58,6 +58,7 @@ struct SpmmArgs {
   const float *x;          // input rows (explicit / fused modes)
   size_t x_ld;             // pitch of x in floats
   float *y;                // n x F output
+  size_t y_ld;             // pitch of y in floats (0 = F)
   const uint32_t *offs;    // n+1 offsets (column_offset fwd, row_offset bwd)
   const uint32_t *idx;     // e indices into x rows
   const float *w;          // explicit per-edge weights
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmAr
 #pragma unroll
       for (int k = 0; k < VEC; k++) acc[t][k] = av[k] > 0.0f ? __fmul_rn(acc[t][k], a.act_scale) : 0.0f;
     }
-    store_vec<VEC>(a.y + (size_t)r * a.F + col, acc[t]);
+    store_vec<VEC>(a.y + (size_t)r * a.y_ld + col, acc[t]);
   }
 }
 
@@ -184,6 +185,7 @@ static int pick_vec(uint32_t F, std::initializer_list<size_t> pitches, std::init
 template <int VEC, int CT, int U, int MODE, bool MASK>
 static int launch_one(SpmmArgs a, cudaStream_t stream) {
   a.tiles = (a.F + CT * 32 * VEC - 1) / (CT * 32 * VEC);  // chunks per row
+  if (a.y_ld == 0) a.y_ld = a.F;
   const uint64_t warps = (uint64_t)a.n * a.tiles;
   const uint64_t blocks = (warps + kSpmmWarps - 1) / kSpmmWarps;
   if (blocks > 0x7fffffffull) return fail(NB_ERR_INVALID, "spmm: too many rows for one launch");
@@ -321,19 +323,21 @@ NB_API int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t 
   return launch_spmm<kFusedW, false>(a, vec, as_stream(stream));
 }
 
-NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache,
-                                        size_t cache_ld, const uint32_t *d_hashmap,
-                                        const uint32_t *d_source, float *d_y,
-                                        const uint32_t *d_row_indices, const uint32_t *d_column_offset,
-                                        const float *d_src_norm, const float *d_dst_norm, uint32_t v,
-                                        uint32_t s, uint32_t e, uint32_t F, void *stream) {
+namespace nb {
+// nb_spmm_csc_fwd_gather_fused with an output pitch (floats, >= F): the native step pads the rows of the
+// layer-0 aggregate to 16 bytes so that the dense layers can read them with TMA tensor loads.
+int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache, size_t cache_ld,
+                                 const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
+                                 const uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                                 const float *d_src_norm, const float *d_dst_norm, uint32_t v, uint32_t s, uint32_t e,
+                                 uint32_t F, void *stream) {
   if (v == 0) return 0;
   NB_REQUIRE(d_source && d_y && d_row_indices && d_column_offset && d_src_norm && d_dst_norm,
              "nb_spmm_csc_fwd_gather_fused: null pointer");
   NB_REQUIRE(feat != nullptr || (d_cache != nullptr && d_hashmap != nullptr),
              "nb_spmm_csc_fwd_gather_fused: no feature store");
   NB_REQUIRE(d_hashmap == nullptr || d_cache != nullptr, "nb_spmm_csc_fwd_gather_fused: hashmap without cache");
-  NB_REQUIRE(F > 0 && (feat == nullptr || feat_ld >= F) && (d_cache == nullptr || cache_ld >= F),
+  NB_REQUIRE(F > 0 && (feat == nullptr || feat_ld >= F) && (d_cache == nullptr || cache_ld >= F) && y_ld >= F,
              "nb_spmm_csc_fwd_gather_fused: bad width or pitch");
   // Staged path: hits (cache rows, or the table itself when there is no cache) go through the TMA
   // unit; misses are rows of `feat` that the lanes copy.  Needs scratch for per-edge references.
@@ -349,7 +353,7 @@ NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t fea
       NB_TRY(launch_gather_refs(d_column_offset, d_row_indices, v, e, d_source, d_hashmap, d_hashmap == nullptr,
                                 d_src_norm, d_dst_norm, ref, w, st));
       TmaSpmmArgs t{};
-      t.x = hit_base; t.x_ld = hit_ld; t.miss = feat; t.miss_ld = feat_ld; t.y = d_y; t.offs = d_column_offset;
+      t.x = hit_base; t.x_ld = hit_ld; t.miss = feat; t.miss_ld = feat_ld; t.y = d_y; t.y_ld = y_ld; t.offs = d_column_offset;
       t.ref = ref; t.w = w; t.n = v; t.F = F; t.act = nullptr; t.act_scale = 1.0f; t.src_rows_hint = s;
       t.out_vec = pick_vec(F, {}, {d_y});
       return launch_spmm_tma(t, st);
@@ -357,8 +361,19 @@ NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t fea
   }
   SpmmArgs a{};
   a.feat = feat; a.feat_ld = feat_ld; a.cache = d_cache; a.cache_ld = cache_ld; a.hashmap = d_hashmap;
-  a.source = d_source; a.y = d_y; a.offs = d_column_offset; a.idx = d_row_indices;
+  a.source = d_source; a.y = d_y; a.y_ld = y_ld; a.offs = d_column_offset; a.idx = d_row_indices;
   a.norm_row = d_dst_norm; a.norm_idx = d_src_norm; a.n = v; a.F = F;
   std::initializer_list<size_t> pitches = {feat ? feat_ld : (size_t)4, d_cache ? cache_ld : (size_t)4};
   return launch_spmm<kFusedGather, false>(a, pick_vec(F, pitches, {feat, d_cache, d_y}), as_stream(stream));
+}
+}  // namespace nb
+
+NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache,
+                                        size_t cache_ld, const uint32_t *d_hashmap,
+                                        const uint32_t *d_source, float *d_y,
+                                        const uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                                        const float *d_src_norm, const float *d_dst_norm, uint32_t v,
+                                        uint32_t s, uint32_t e, uint32_t F, void *stream) {
+  return nb::spmm_csc_fwd_gather_fused_ld(ws, feat, feat_ld, d_cache, cache_ld, d_hashmap, d_source, d_y, F,
+                                          d_row_indices, d_column_offset, d_src_norm, d_dst_norm, v, s, e, F, stream);
 }

@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
     }
     if (cur.last) {
       const uint32_t out_row = cur.row;
-      float *out = a.y + (size_t)out_row * a.F + pcol0;
+      float *out = a.y + (size_t)out_row * a.y_ld + pcol0;
       const float *act = MASK ? a.act + (size_t)out_row * a.F + pcol0 : nullptr;
 #pragma unroll
       for (int t = 0; t < TILES; t++) {
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   float nrow = a.w ? 0.0f : __ldg(a.norm_row + row);
 
   auto finish_row = [&]() {      // write the accumulated row, move to the next one
-    float *out = a.y + (size_t)row * a.F;
+    float *out = a.y + (size_t)row * a.y_ld;
     const float *act = MASK ? a.act + (size_t)row * a.F : nullptr;
 #pragma unroll
     for (int t = 0; t < TILES; t++) {
@@ -542,6 +542,7 @@ bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F) {
 int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (a.n == 0) return 0;
   a.fpad = ((a.F + 3) / 4) * 4;
+  if (a.y_ld == 0) a.y_ld = a.F;
   a.l2_prefetch = g_l2_prefetch;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
   // into panels whose working set fits, and panels are processed one after the other.

@@ -34,7 +34,8 @@ def _close(a, b, k, mode=1):
     assert np.abs(a - b).max() / scale < tol, (np.abs(a - b).max(), scale)
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (63, 17, 65), (1024, 128, 41), (3000, 602, 128), (200, 1433, 16)])
+@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (63, 17, 65), (1024, 128, 41), (3000, 602, 128), (200, 1433, 16),
+                                   (3000, 604, 128), (777, 100, 128), (19000, 128, 64), (130, 32, 32)])
 def test_gemm_nn(cuda_device, ws, gemm_mode, M, K, N):
     rng = np.random.RandomState(M + K + N)
     a, b = rng.randn(M, K).astype(np.float32), rng.randn(K, N).astype(np.float32)
@@ -45,7 +46,8 @@ def test_gemm_nn(cuda_device, ws, gemm_mode, M, K, N):
     _close(host_f32(c), oracle.gemm_nn(a, b), K, gemm_mode)
 
 
-@pytest.mark.parametrize("M,K,N", [(5000, 602, 128), (1024, 128, 41), (70, 3, 5), (25000, 100, 128)])
+@pytest.mark.parametrize("M,K,N", [(5000, 602, 128), (1024, 128, 41), (70, 3, 5), (25000, 100, 128), (5000, 604, 128),
+                                   (4001, 36, 64)])
 def test_gemm_tn_weight_gradient(cuda_device, ws, gemm_mode, M, K, N):
     """dW[K x N] = Y^T[K x M] dZ[M x N]; the long reduction over M runs split-K."""
     rng = np.random.RandomState(M + N)
@@ -57,7 +59,7 @@ def test_gemm_tn_weight_gradient(cuda_device, ws, gemm_mode, M, K, N):
     _close(host_f32(c), oracle.gemm_tn(y, dz), M, gemm_mode)
 
 
-@pytest.mark.parametrize("M,N,K", [(1024, 41, 128), (3000, 128, 128), (7, 5, 3)])
+@pytest.mark.parametrize("M,N,K", [(1024, 41, 128), (3000, 128, 128), (7, 5, 3), (1000, 64, 96), (20000, 128, 128)])
 def test_gemm_nt_input_gradient(cuda_device, ws, gemm_mode, M, N, K):
     """dY[M x K] = dZ[M x N] W^T with W[K x N]."""
     rng = np.random.RandomState(M + N + K)
@@ -141,3 +143,33 @@ def test_sigmoid_bce_matches_oracle(cuda_device, ws, B, C):
     _lib.call("nb_sigmoid_bce", ws.handle, ptr(dev_f32(z, cuda_device)), ptr(dev_i64(y, cuda_device)), B, C, None,
               ptr(stats), st)
     assert abs(float(stats[0]) - loss) <= 2e-5 * max(1.0, abs(loss))
+
+
+@pytest.mark.parametrize("kind,M,N,K", [("NN", 3000, 128, 604), ("TN", 604, 128, 9000), ("NT", 5000, 128, 128)])
+def test_tma_and_cp_async_kernels_give_identical_bits(cuda_device, ws, kind, M, N, K):
+    """The TMA-fed kernel and the cp.async kernel issue the same MMAs in the same order and cut K at the same
+    places, so a caller whose operands do not qualify for tensor maps gets the same bits as one whose do."""
+    import os
+    lib = _lib.load()
+    old = lib.nb_set_gemm_mode(17)
+    rng = np.random.RandomState(M + N + K)
+    if kind == "NN":
+        a, b, ta, tb = rng.randn(M, K), rng.randn(K, N), 0, 0
+    elif kind == "TN":
+        a, b, ta, tb = rng.randn(K, M), rng.randn(K, N), 1, 0
+    else:
+        a, b, ta, tb = rng.randn(M, K), rng.randn(N, K), 0, 1
+    da, db = dev_f32(a.astype(np.float32), cuda_device), dev_f32(b.astype(np.float32), cuda_device)
+    outs = []
+    try:
+        for no_tma in ("", "1"):
+            if no_tma:
+                os.environ["NB_TC_NO_TMA"] = "1"
+            c = torch.full((M, N), float("nan"), device=cuda_device)
+            _lib.call("nb_gemm", ws.handle, ptr(da), ptr(db), ptr(c), M, N, K, ta, tb, torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            outs.append(host_f32(c).copy())
+    finally:
+        os.environ.pop("NB_TC_NO_TMA", None)
+        lib.nb_set_gemm_mode(old)
+    np.testing.assert_array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
