@@ -131,6 +131,9 @@ int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
                     cudaStream_t stream);
 int read_tma_gemm_error_flag(unsigned int *value);
+bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K);
+int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
+                         int64_t K, int mode, cudaStream_t stream);
 int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache, size_t cache_ld,
                                  const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
                                  const uint32_t *d_row_indices, const uint32_t *d_column_offset,

@@ -551,7 +551,12 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b,
   dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + bn - 1) / bn), (unsigned)splits);
   if (grid.y > 65535) return fail(NB_ERR_INVALID, "nb_gemm: N too large for one launch");
   int st;
-  if (use_tma) {
+  // Y W with a short W: rows dealt evenly to the SMs (one wave whatever the row count, up to 160 rows per SM)
+  const bool rows_form = use_tma && !trans_a && !trans_b && splits == 1 && !getenv("NB_TC_NO_ROWS_FORM") &&
+                         tma_rows_form_applicable(M, N, K);
+  if (rows_form) {
+    st = gemm_tma_rows_launch(d_a, lda, d_b, ldb, d_c, M, N, K, mode, stream);
+  } else if (use_tma) {
     st = gemm_tma_launch(d_a, lda, d_b, ldb, g.c, M, N, K, trans_a, trans_b, bn, splits, g.k_per_split, mode, stream);
   } else {
     switch (bn) {

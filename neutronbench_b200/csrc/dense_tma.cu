@@ -220,6 +220,166 @@ __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_kernel(const __grid_c
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Row-balanced form of C = Y W for a wide, short W (N <= 128): the product is computed as C^T = W^T Y^T, so the
+// rows of Y become the N dimension of the MMA, which can be any multiple of 16 up to 256 instead of exactly 128.
+// Every CTA takes ceil(M / #SMs) rows (rounded up to 16, at most kRowsMax), which keeps a product of, say, 150
+// row tiles of 128 in ONE wave over 148 SMs instead of two.  W^T is the MN-major A operand (128 outputs, zero rows
+// beyond N), the rows of Y the K-major B operand.  The three MMAs per K step are issued in the order
+// hi*hi, lo(W)*hi(Y), hi(W)*lo(Y), i.e. the same three products in the same order as the plain form, so both
+// forms give identical bits.  The accumulator holds C^T (lane = output column, TMEM column = row), which the
+// epilogue writes straight out: a warp stores 32 consecutive output columns of one row per instruction.
+constexpr int kRowsMax = 160;
+
+struct TmaRowsArgs {
+  float *c;
+  int64_t M, N, K;
+  int rows_per_cta;         // multiple of 16, <= kRowsMax
+  int mode;
+};
+
+__global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_rows_kernel(const __grid_constant__ CUtensorMap map_y,
+                                                                       const __grid_constant__ CUtensorMap map_w,
+                                                                       const TmaRowsArgs g) {
+  extern __shared__ __align__(1024) unsigned char tc_smem[];
+  constexpr int S = kTmaStages;
+  constexpr uint32_t W_BYTES = kBM * kTmaBK * 4;                 // W^T tile: 128 outputs x 32 k
+  constexpr uint32_t Y_MAX = kRowsMax * kTmaBK * 4;              // Y tile: up to 160 rows x 32 k
+  constexpr uint32_t STAGE = 2 * (W_BYTES + Y_MAX);              // raw W | raw Y | lo W | lo Y
+  uint64_t *bars = reinterpret_cast<uint64_t *>(tc_smem + (size_t)S * STAGE);
+  uint64_t *loaded = bars, *split_done = bars + S, *freed = bars + 2 * S;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool split = g.mode == 1;
+  const int rows = g.rows_per_cta;
+  const int row0 = (int)blockIdx.x * rows;
+  const uint32_t y_bytes = (uint32_t)rows * kTmaBK * 4;
+  const int nchunks = (int)((g.K + kTmaBK - 1) / kTmaBK);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)),
+                 "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+      tc_mbar_init(tc_smem_u32(&loaded[s]), 1);
+      tc_mbar_init(tc_smem_u32(&split_done[s]), kSplitThreads);
+      tc_mbar_init(tc_smem_u32(&freed[s]), 1);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // A = W^T is MN-major (bit 15), B = Y rows K-major; N = rows of this CTA, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((uint32_t)(rows >> 3) << 17) |
+                         ((uint32_t)(kBM >> 4) << 24);
+  bool ok = true;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int c = 0; c < nchunks; c++) {
+        const int st = c % S;
+        if (c >= S && !tc_mbar_wait(tc_smem_u32(&freed[st]), ((c / S) - 1) & 1)) { ok = false; break; }
+        const uint32_t bar = tc_smem_u32(&loaded[st]);
+        const uint32_t w_dst = tc_smem_u32(tc_smem + (size_t)st * STAGE), y_dst = w_dst + W_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(W_BYTES + y_bytes) : "memory");
+        const int k0 = c * kTmaBK;
+        tma_load_tile<kBM, true>(w_dst, &map_w, 0, k0, bar);
+        tma_load_2d(y_dst, &map_y, k0, row0, bar);     // box {32 k, rows}
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  } else if (warp == 9) {
+    for (int c = 0; c < nchunks; c++) {
+      const int st = c % S;
+      if (!tc_mbar_wait(tc_smem_u32(&split_done[st]), (c / S) & 1)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t w_h = tc_smem_u32(tc_smem + (size_t)st * STAGE), y_h = w_h + W_BYTES;
+        const uint32_t w_l = w_h + W_BYTES + Y_MAX, y_l = w_l + W_BYTES;
+        using DW = TmaDesc<true>;
+        using DY = TmaDesc<false>;
+#pragma unroll
+        for (int kk = 0; kk < kTmaBK / 8; kk++) {
+          const uint64_t dw_h = tc_make_desc(w_h + kk * DW::kstep, DW::lbo, DW::sbo, DW::layout);
+          const uint64_t dy_h = tc_make_desc(y_h + kk * DY::kstep, DY::lbo, DY::sbo, DY::layout);
+          tc_mma_tf32(tmem, dw_h, dy_h, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+          if (split) {
+            const uint64_t dw_l = tc_make_desc(w_l + kk * DW::kstep, DW::lbo, DW::sbo, DW::layout);
+            const uint64_t dy_l = tc_make_desc(y_l + kk * DY::kstep, DY::lbo, DY::sbo, DY::layout);
+            tc_mma_tf32(tmem, dw_l, dy_h, idesc, 1u);   // hi(Y) * lo(W): second term of the plain form
+            tc_mma_tf32(tmem, dw_h, dy_l, idesc, 1u);   // lo(Y) * hi(W): third term
+          }
+        }
+        tc_commit(tc_smem_u32(&freed[st]));
+      }
+      __syncwarp();
+    }
+  } else {
+    const int w_quads = W_BYTES / 16, y_quads = (int)(y_bytes / 16);
+    for (int c = 0; c < nchunks && ok; c++) {
+      const int st = c % S;
+      if (!tc_mbar_wait(tc_smem_u32(&loaded[st]), (c / S) & 1)) { ok = false; break; }
+      float4 *raw = reinterpret_cast<float4 *>(tc_smem + (size_t)st * STAGE);
+      float4 *lo = raw + (W_BYTES + Y_MAX) / 16;
+      // the W tile and the used part of the Y tile; the two sit W_BYTES / 16 quads apart in both halves
+      for (int q = tid; q < w_quads + y_quads; q += kSplitThreads) {
+        const float4 x = raw[q];
+        float h[4], l[4];
+        tc_split(x.x, h[0], l[0]); tc_split(x.y, h[1], l[1]); tc_split(x.z, h[2], l[2]); tc_split(x.w, h[3], l[3]);
+        raw[q] = make_float4(h[0], h[1], h[2], h[3]);
+        if (split) lo[q] = make_float4(l[0], l[1], l[2], l[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&split_done[st])) : "memory");
+    }
+  }
+
+  if (ok && nchunks > 0) {
+    const int last = nchunks - 1;
+    ok = tc_mbar_wait(tc_smem_u32(&freed[last % S]), (last / S) & 1);
+  }
+  ok = __syncthreads_and(ok);
+  if (!ok && tid == 0) atomicExch(&g_tma_gemm_error, 1u);
+  tc_fence_after();
+
+  if (ok && warp < 8) {
+    // lane = output column 32*(w%4) + lane, TMEM column = row of this CTA; warps 0-3 / 4-7 alternate over the
+    // blocks of 32 rows
+    const int quarter = warp & 3, part = warp >> 2;
+    const int64_t col = quarter * 32 + lane;
+    for (int cb = part; cb * 32 < rows; cb += 2) {
+      uint32_t r[32];
+      const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + cb * 32;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+            "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+            "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+            "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          : "r"(taddr) : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        const int64_t grow = (int64_t)row0 + cb * 32 + j;
+        if (cb * 32 + j < rows && grow < g.M && col < g.N) g.c[grow * g.N + col] = __uint_as_float(r[j]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 static PFN_cuTensorMapEncodeTiled tensor_map_encoder() {
   static PFN_cuTensorMapEncodeTiled fn = nullptr;
@@ -301,6 +461,33 @@ int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb
     case 64: return launch_tma_layout<64>(ma, mb, g, a_mn, b_mn, grid, stream);
     default: return launch_tma_layout<32>(ma, mb, g, a_mn, b_mn, grid, stream);
   }
+}
+
+// C = Y W in the row-balanced form; applicable to NN products with N <= 128 and no split-K.
+bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K) {
+  if (N > kBM || N < 32 || K < kTmaBK || M < 8192) return false;   // small products: plain tiles and split-K
+  const int64_t rows = ((M + kNumSMs - 1) / kNumSMs + 15) / 16 * 16;
+  return rows <= kRowsMax && M >= rows;
+}
+
+int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
+                         int64_t K, int mode, cudaStream_t stream) {
+  const int rows = (int)(((M + kNumSMs - 1) / kNumSMs + 15) / 16 * 16);
+  CUtensorMap my, mw;
+  if (!make_operand_map(&my, d_y, false, M, K, ldy, rows) || !make_operand_map(&mw, d_w, true, N, K, ldw, 0))
+    return fail(NB_ERR_CUDA, "nb_gemm: cuTensorMapEncodeTiled failed");
+  TmaRowsArgs g{};
+  g.c = c; g.M = M; g.N = N; g.K = K; g.rows_per_cta = rows; g.mode = mode;
+  constexpr size_t smem = (size_t)kTmaStages * 2 * (kBM + kRowsMax) * kTmaBK * 4 + 256;
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(gemm_tma_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const unsigned grid = (unsigned)((M + rows - 1) / rows);
+  gemm_tma_rows_kernel<<<grid, kTmaThreads, smem, stream>>>(my, mw, g);
+  NB_LAUNCH_CHECK();
+  return 0;
 }
 
 int read_tma_gemm_error_flag(unsigned int *value) {

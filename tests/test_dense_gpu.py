@@ -35,7 +35,8 @@ def _close(a, b, k, mode=1):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 1, 1), (63, 17, 65), (1024, 128, 41), (3000, 602, 128), (200, 1433, 16),
-                                   (3000, 604, 128), (777, 100, 128), (19000, 128, 64), (130, 32, 32)])
+                                   (3000, 604, 128), (777, 100, 128), (19000, 128, 64), (130, 32, 32), (19777, 604, 128),
+                                   (8200, 36, 96), (23600, 100, 128)])
 def test_gemm_nn(cuda_device, ws, gemm_mode, M, K, N):
     rng = np.random.RandomState(M + K + N)
     a, b = rng.randn(M, K).astype(np.float32), rng.randn(K, N).astype(np.float32)
@@ -145,7 +146,8 @@ def test_sigmoid_bce_matches_oracle(cuda_device, ws, B, C):
     assert abs(float(stats[0]) - loss) <= 2e-5 * max(1.0, abs(loss))
 
 
-@pytest.mark.parametrize("kind,M,N,K", [("NN", 3000, 128, 604), ("TN", 604, 128, 9000), ("NT", 5000, 128, 128)])
+@pytest.mark.parametrize("kind,M,N,K", [("NN", 3000, 128, 604), ("TN", 604, 128, 9000), ("NT", 5000, 128, 128),
+                                        ("NN", 19777, 128, 604), ("NN", 9000, 64, 100)])
 def test_tma_and_cp_async_kernels_give_identical_bits(cuda_device, ws, kind, M, N, K):
     """The TMA-fed kernel and the cp.async kernel issue the same MMAs in the same order and cut K at the same
     places, so a caller whose operands do not qualify for tensor maps gets the same bits as one whose do."""
