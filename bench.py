@@ -57,8 +57,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-gather", action="store_true")
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
-    ap.add_argument("--pipelines", type=int, default=2,
-                    help="PIPELINES of the reference's cfg: 2 = sample batch i+1 while batch i trains, 1 = plain loop")
+    ap.add_argument("--pipelines", type=int, default=3,
+                    help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain loop")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
 

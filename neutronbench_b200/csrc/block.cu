@@ -120,6 +120,47 @@ __global__ void csr_weight_kernel(const uint32_t *__restrict__ row_offset, const
   }
 }
 
+// Lean path (no explicit weight arrays): source emission, reindex + row counting and cursor clearing in one
+// launch.  The three jobs are independent of one another; the row counters were cleared by an earlier launch.
+__global__ void emit_remap_kernel(const uint32_t *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                                  uint64_t words, uint32_t *__restrict__ source, uint32_t *row_indices, uint32_t e,
+                                  uint32_t num_vertices, uint32_t *row_count, uint32_t *__restrict__ cursor, uint32_t s) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, t0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (uint64_t i = t0; i < s; i += stride) cursor[i] = 0u;
+  for (uint64_t w = t0; w < words; w += stride) {
+    uint32_t word = bitmap[w];
+    uint32_t p = prefix[w];
+    while (word) {
+      const int b = __ffs(word) - 1;
+      source[p++] = (uint32_t)(w << 5) + b;
+      word &= word - 1;
+    }
+  }
+  for (uint64_t j = t0; j < e; j += stride) {
+    const uint32_t g = row_indices[j];
+    if (g >= num_vertices) continue;
+    const uint32_t below = (1u << (g & 31)) - 1u;
+    const uint32_t local = prefix[g >> 5] + __popc(bitmap[g >> 5] & below);
+    row_indices[j] = local;
+    atomicAdd(&row_count[local], 1u);
+  }
+}
+
+// Lean path: CSR fill (cursor counts from zero on top of the row offsets) and both degree factors in one launch.
+__global__ void fill_norms_kernel(const uint32_t *__restrict__ column_offset, const uint32_t *__restrict__ row_indices,
+                                  uint32_t v, uint32_t e, const uint32_t *__restrict__ row_offset, uint32_t *cursor,
+                                  uint32_t *__restrict__ column_indices, uint32_t s, float *__restrict__ src_norm,
+                                  float *__restrict__ dst_norm) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, t0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (uint64_t i = t0; i < s; i += stride) src_norm[i] = (float)sqrt((double)(row_offset[i + 1] - row_offset[i]));
+  for (uint64_t i = t0; i < v; i += stride) dst_norm[i] = (float)sqrt((double)(column_offset[i + 1] - column_offset[i]));
+  for (uint64_t j = t0; j < e; j += stride) {
+    const uint32_t d = find_segment(column_offset, v, (uint32_t)j);
+    const uint32_t ls = row_indices[j];
+    column_indices[row_offset[ls] + atomicAdd(&cursor[ls], 1u)] = d;
+  }
+}
+
 // ------------------------------------------------------------------------------------ per-row sort
 // Rows of length <= 32: one warp, rank by counting (stable for equal keys, which are identical anyway).
 // Longer rows go to a worklist handled by whole CTAs.
@@ -247,10 +288,14 @@ __global__ void __launch_bounds__(kThreads) sort_long_rows_kernel(const uint32_t
 
 using namespace nb;
 
-NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices,
-                          const uint32_t *d_column_offset, uint32_t v, uint32_t e, uint32_t *d_source,
-                          uint32_t *src_size, uint32_t *d_row_offset, uint32_t *d_column_indices,
-                          float *d_src_norm, float *d_dst_norm, float *d_w_fwd, float *d_w_bwd, void *stream_) {
+namespace nb {
+// nb_block_build; `marked` (nullable) is a bitmap of |V| bits plus 4 flag words that the sampler has already
+// cleared and marked (the native step fuses the marking into its sampling kernel), and zero_cap, when not 0,
+// tells how many row counters of d_row_offset this call may clear inside its first launch.
+int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                     uint32_t v, uint32_t e, uint32_t *d_source, uint32_t *src_size, uint32_t *d_row_offset,
+                     uint32_t *d_column_indices, float *d_src_norm, float *d_dst_norm, float *d_w_fwd, float *d_w_bwd,
+                     uint32_t *marked, void *stream_) {
   NB_REQUIRE(ws && src_size, "nb_block_build: null workspace or src_size");
   NB_REQUIRE(d_column_offset && d_source && d_row_offset && d_src_norm && d_dst_norm,
              "nb_block_build: null output pointer");
@@ -260,19 +305,27 @@ NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indi
   WsScope scope(ws);
 
   const uint64_t words = ((uint64_t)num_vertices + 31) / 32;
-  uint32_t *bitmap = ws->alloc_n<uint32_t>(words + 4);   // + flags, cleared by the same memset
+  uint32_t *bitmap = marked ? marked : ws->alloc_n<uint32_t>(words + 4);   // + flags, cleared by the same memset
   uint32_t *prefix = ws->alloc_n<uint32_t>(words + 1);
   if (!bitmap || !prefix) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
   uint32_t *flags = bitmap + words;  // [0] error, [1] long-row count
-  NB_CUDA(cudaMemsetAsync(bitmap, 0, (words + 4) * sizeof(uint32_t), stream));
-
-  if (e > 0) {
-    mark_bitmap_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_row_indices, e, num_vertices, bitmap, flags);
-    NB_LAUNCH_CHECK();
+  if (!marked) {
+    NB_CUDA(cudaMemsetAsync(bitmap, 0, (words + 4) * sizeof(uint32_t), stream));
+    if (e > 0) {
+      mark_bitmap_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_row_indices, e, num_vertices, bitmap, flags);
+      NB_LAUNCH_CHECK();
+    }
   }
+  // Without explicit weight arrays the rest runs in fewer, merged launches; their first one needs the row
+  // counters cleared, which the popcount launch does on the side (at most min(|V|, e) + 1 of them exist).
+  const bool lean = d_w_fwd == nullptr && d_w_bwd == nullptr && e > 0;
+  const uint64_t zero_cap = lean ? (uint64_t)(e < num_vertices ? e : num_vertices) + 1 : 0;
+  bool counters_cleared = false;
   if (words <= kSingleBlockScanMax) {   // popcount and scan in one launch
-    scan_single_block<uint32_t, ScanLoadPopc><<<1, 1024, 0, stream>>>(ScanLoadPopc{bitmap}, prefix, words, true);
+    scan_single_block<uint32_t, ScanLoadPopc><<<1, 1024, 0, stream>>>(ScanLoadPopc{bitmap}, prefix, words, true,
+                                                                      d_row_offset, zero_cap);
     NB_LAUNCH_CHECK();
+    counters_cleared = lean;
   } else {
     popc_words_kernel<<<grid_for(words, kThreads), kThreads, 0, stream>>>(bitmap, prefix, words);
     NB_LAUNCH_CHECK();
@@ -284,6 +337,28 @@ NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indi
   const uint32_t s = ws->mailbox[0];
   if (ws->mailbox[1] != 0) return fail(NB_ERR_INVALID, "nb_block_build: a source id is >= num_vertices");
   *src_size = s;
+
+  if (lean) {
+    uint32_t *cursor = ws->alloc_n<uint32_t>((size_t)s + 1);
+    uint32_t *long_rows = ws->alloc_n<uint32_t>((size_t)e / 32 + 1);
+    uint32_t *scratch = ws->alloc_n<uint32_t>(e);
+    if (!cursor || !long_rows || !scratch) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
+    if (!counters_cleared) NB_CUDA(cudaMemsetAsync(d_row_offset, 0, ((size_t)s + 1) * sizeof(uint32_t), stream));
+    emit_remap_kernel<<<grid_for(words > e ? words : e, kThreads), kThreads, 0, stream>>>(
+        bitmap, prefix, words, d_source, d_row_indices, e, num_vertices, d_row_offset, cursor, s);
+    NB_LAUNCH_CHECK();
+    NB_TRY(exclusive_scan_u32(ws, d_row_offset, d_row_offset, s, true, stream));
+    fill_norms_kernel<<<grid_for(e, kThreads), kThreads, 0, stream>>>(d_column_offset, d_row_indices, v, e, d_row_offset,
+                                                                      cursor, d_column_indices, s, d_src_norm, d_dst_norm);
+    NB_LAUNCH_CHECK();
+    sort_short_rows_kernel<<<grid_for((uint64_t)s * 32, kThreads), kThreads, 0, stream>>>(
+        d_row_offset, s, d_column_indices, long_rows, flags + 1);
+    NB_LAUNCH_CHECK();
+    sort_long_rows_kernel<<<kNumSMs * 4, kThreads, 0, stream>>>(d_row_offset, d_column_indices, v, long_rows,
+                                                                flags + 1, scratch);
+    NB_LAUNCH_CHECK();
+    return 0;
+  }
 
   // CSR: count -> scan -> fill -> sort rows
   emit_source_kernel<<<grid_for(words > s ? words : s + 1, kThreads), kThreads, 0, stream>>>(
@@ -325,4 +400,13 @@ NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indi
     }
   }
   return 0;
+}
+}  // namespace nb
+
+NB_API int nb_block_build(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices,
+                          const uint32_t *d_column_offset, uint32_t v, uint32_t e, uint32_t *d_source,
+                          uint32_t *src_size, uint32_t *d_row_offset, uint32_t *d_column_indices,
+                          float *d_src_norm, float *d_dst_norm, float *d_w_fwd, float *d_w_bwd, void *stream) {
+  return nb::block_build_impl(ws, num_vertices, d_row_indices, d_column_offset, v, e, d_source, src_size, d_row_offset,
+                              d_column_indices, d_src_norm, d_dst_norm, d_w_fwd, d_w_bwd, nullptr, stream);
 }

@@ -131,6 +131,13 @@ int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
                     cudaStream_t stream);
 int read_tma_gemm_error_flag(unsigned int *value);
+int sample_hop_impl(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices, const uint32_t *d_dst,
+                    uint32_t v, int fanout, const uint32_t *d_column_offset, uint64_t seed, uint32_t hop,
+                    uint32_t *d_row_indices, uint32_t *bitmap, void *stream);
+int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, const uint32_t *d_column_offset,
+                     uint32_t v, uint32_t e, uint32_t *d_source, uint32_t *src_size, uint32_t *d_row_offset,
+                     uint32_t *d_column_indices, float *d_src_norm, float *d_dst_norm, float *d_w_fwd, float *d_w_bwd,
+                     uint32_t *marked, void *stream);
 bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K);
 int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
                          int64_t K, int mode, cudaStream_t stream);

@@ -240,16 +240,22 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
     else
       NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
     NB_TRY(arena(ws, b.e, &b.row_indices));
-    NB_TRY(nb_sample_hop(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, by_rate ? -1 : c.fanout[h], b.column_offset, c.seed,
-                         (draw << 8) | h, b.row_indices, stream));
+    // the sampler marks the dedup bitmap of the hop while it writes the ids (cleared here, |V| bits + 4 flag words)
+    const size_t words = ((size_t)c.num_vertices + 31) / 32;
+    uint32_t *marked;
+    NB_TRY(arena(ws, words + 4, &marked));
+    NB_CUDA(cudaMemsetAsync(marked, 0, (words + 4) * sizeof(uint32_t), nb::as_stream(stream)));
+    NB_TRY(nb::sample_hop_impl(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, by_rate ? -1 : c.fanout[h],
+                               b.column_offset, c.seed, (draw << 8) | h, b.row_indices, marked, stream));
     const size_t cap = b.e < c.num_vertices ? (b.e ? b.e : 1) : c.num_vertices;
     NB_TRY(arena(ws, cap, &b.source));
     NB_TRY(arena(ws, cap + 1, &b.row_offset));
     NB_TRY(arena(ws, b.e, &b.column_indices));
     NB_TRY(arena(ws, cap, &b.src_norm));
     NB_TRY(arena(ws, v, &b.dst_norm));
-    NB_TRY(nb_block_build(ws, c.num_vertices, b.row_indices, b.column_offset, v, b.e, b.source, &b.s, b.row_offset,
-                          b.column_indices, b.src_norm, b.dst_norm, nullptr, nullptr, stream));
+    NB_TRY(nb::block_build_impl(ws, c.num_vertices, b.row_indices, b.column_offset, v, b.e, b.source, &b.s, b.row_offset,
+                                b.column_indices, b.src_norm, b.dst_norm, nullptr, nullptr, b.e > 0 ? marked : nullptr,
+                                stream));
     dst = b.source;
     v = b.s;
   }

@@ -29,6 +29,14 @@ struct ScanLoadHopCount {
   }
 };
 
+// Marks a sampled source in the dedup bitmap of the hop (the block builder's first step, done here while the id is
+// in a register).
+__device__ __forceinline__ void mark_source(uint32_t *bitmap, uint32_t g) {
+  if (bitmap == nullptr) return;
+  const uint32_t bit = 1u << (g & 31);
+  if ((bitmap[g >> 5] & bit) == 0) atomicOr(&bitmap[g >> 5], bit);
+}
+
 constexpr uint32_t kFloydMax = 128;   // Floyd's duplicate test is quadratic in the subset size
 
 // count[i] = max(int(deg * rate), min(lower, deg))  — SAMPLE_RATE mode, core/ntsSampler.hpp:901-912
@@ -54,7 +62,7 @@ __global__ void hop_counts_rate_kernel(const uint64_t *__restrict__ g_co, const 
 __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint32_t *__restrict__ g_ri,
                                   const uint32_t *__restrict__ dst, uint32_t v, int fanout,
                                   const uint32_t *__restrict__ column_offset, uint32_t seed_lo, uint32_t seed_hi,
-                                  uint32_t hop, uint32_t *row_indices) {
+                                  uint32_t hop, uint32_t *row_indices, uint32_t *bitmap) {
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v; i += (uint64_t)gridDim.x * blockDim.x) {
     const uint32_t d = dst[i];
     const uint64_t base = g_co[d];
@@ -62,7 +70,11 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
     const uint32_t pos = column_offset[i];
     const uint32_t k = column_offset[i + 1] - pos;
     if (k >= deg) {   // the counts already carry the fan-out rule: nothing to choose
-      for (uint32_t j = 0; j < deg; j++) row_indices[pos + j] = g_ri[base + j];
+      for (uint32_t j = 0; j < deg; j++) {
+        const uint32_t g = g_ri[base + j];
+        row_indices[pos + j] = g;
+        mark_source(bitmap, g);
+      }
       continue;
     }
     uint32_t r[4];
@@ -72,7 +84,11 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
       uint32_t m = 0;
       for (uint32_t j = 0; j < deg && m < k; j++) {
         if ((j & 3) == 0) philox4x32_10(j >> 2, (uint32_t)i, hop, 2u, seed_lo, seed_hi, r);
-        if (__umulhi(r[j & 3], deg - j) < k - m) row_indices[pos + m++] = g_ri[base + j];
+        if (__umulhi(r[j & 3], deg - j) < k - m) {
+          const uint32_t g = g_ri[base + j];
+          row_indices[pos + m++] = g;
+          mark_source(bitmap, g);
+        }
       }
       continue;
     }
@@ -84,7 +100,11 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
         if (row_indices[pos + q] == c) { c = j; break; }
       row_indices[pos + t] = c;
     }
-    for (uint32_t t = 0; t < k; t++) row_indices[pos + t] = g_ri[base + row_indices[pos + t]];
+    for (uint32_t t = 0; t < k; t++) {
+      const uint32_t g = g_ri[base + row_indices[pos + t]];
+      row_indices[pos + t] = g;
+      mark_source(bitmap, g);
+    }
   }
 }
 
@@ -94,7 +114,8 @@ __global__ void sample_hop_kernel(const uint64_t *__restrict__ g_co, const uint3
 __global__ void sample_hop_warp_kernel(const uint64_t *__restrict__ g_co, const uint32_t *__restrict__ g_ri,
                                        const uint32_t *__restrict__ dst, uint32_t v, int fanout,
                                        const uint32_t *__restrict__ column_offset, uint32_t seed_lo,
-                                       uint32_t seed_hi, uint32_t hop, uint32_t *__restrict__ row_indices) {
+                                       uint32_t seed_hi, uint32_t hop, uint32_t *__restrict__ row_indices,
+                                       uint32_t *bitmap) {
   const unsigned lane = threadIdx.x & 31;
   const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
   for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < v; i += warps) {
@@ -103,7 +124,11 @@ __global__ void sample_hop_warp_kernel(const uint64_t *__restrict__ g_co, const 
     const uint32_t deg = (uint32_t)(g_co[d + 1] - base);
     const uint32_t pos = column_offset[i];
     if (deg <= (uint32_t)fanout) {
-      for (uint32_t j = lane; j < deg; j += 32) row_indices[pos + j] = g_ri[base + j];
+      for (uint32_t j = lane; j < deg; j += 32) {
+        const uint32_t g = g_ri[base + j];
+        row_indices[pos + j] = g;
+        mark_source(bitmap, g);
+      }
       continue;
     }
     const uint32_t k = (uint32_t)fanout;      // <= 32
@@ -118,7 +143,11 @@ __global__ void sample_hop_warp_kernel(const uint64_t *__restrict__ g_co, const 
       const unsigned dup = __ballot_sync(0xffffffffu, lane < t && chosen == c);
       if (dup && lane == t) chosen = deg - k + t;           // Floyd: a repeated candidate yields j itself
     }
-    if (lane < k) row_indices[pos + lane] = g_ri[base + chosen];
+    if (lane < k) {
+      const uint32_t g = g_ri[base + chosen];
+      row_indices[pos + lane] = g;
+      mark_source(bitmap, g);
+    }
   }
 }
 
@@ -257,9 +286,11 @@ NB_API int nb_sample_hop_offsets_rate(nb_ws *ws, const uint64_t *d_graph_column_
   return 0;
 }
 
-NB_API int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices,
-                         const uint32_t *d_dst, uint32_t v, int fanout, const uint32_t *d_column_offset,
-                         uint64_t seed, uint32_t hop, uint32_t *d_row_indices, void *stream_) {
+namespace nb {
+// nb_sample_hop that also marks every sampled source in `bitmap` (nullable; |V| bits, cleared by the caller).
+int sample_hop_impl(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices, const uint32_t *d_dst,
+                    uint32_t v, int fanout, const uint32_t *d_column_offset, uint64_t seed, uint32_t hop,
+                    uint32_t *d_row_indices, uint32_t *bitmap, void *stream_) {
   if (v == 0) return 0;
   NB_REQUIRE(d_graph_column_offset && d_graph_row_indices && d_dst && d_column_offset && d_row_indices,
              "nb_sample_hop: null pointer");
@@ -267,14 +298,22 @@ NB_API int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *
   if (fanout > 0 && fanout <= 32) {
     sample_hop_warp_kernel<<<grid_for((uint64_t)v * 32, 256), 256, 0, as_stream(stream_)>>>(
         d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, (uint32_t)seed,
-        (uint32_t)(seed >> 32), hop, d_row_indices);
+        (uint32_t)(seed >> 32), hop, d_row_indices, bitmap);
   } else {
     sample_hop_kernel<<<grid_for(v, 128), 128, 0, as_stream(stream_)>>>(
         d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, (uint32_t)seed,
-        (uint32_t)(seed >> 32), hop, d_row_indices);
+        (uint32_t)(seed >> 32), hop, d_row_indices, bitmap);
   }
   NB_LAUNCH_CHECK();
   return 0;
+}
+}  // namespace nb
+
+NB_API int nb_sample_hop(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices,
+                         const uint32_t *d_dst, uint32_t v, int fanout, const uint32_t *d_column_offset,
+                         uint64_t seed, uint32_t hop, uint32_t *d_row_indices, void *stream) {
+  return nb::sample_hop_impl(d_graph_column_offset, d_graph_row_indices, d_dst, v, fanout, d_column_offset, seed, hop,
+                             d_row_indices, nullptr, stream);
 }
 
 NB_API int nb_graph_build_csc(nb_ws *ws, const uint32_t *d_edges, uint64_t num_edges, uint32_t num_vertices,
