@@ -258,6 +258,18 @@ int nb_softmax_nll(nb_ws *ws, const float *d_logits, const int64_t *d_label, int
  *     the previous call's rows; the kernels rewrite every row they read, so no clearing is required. */
 int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t B, int64_t C,
                           float *d_dlogits, float *d_stats, void *stream);
+/* The last GCN layer with one label per vertex in two launches instead of six: logits = Y W (B x H times H x C),
+ * Loss and get_correct (utils/torch_func.hpp:16-29, 67-82) on the labels label[dst[i]], and for train != 0 the
+ * gradients d_dw = Y^T dZ (H x C) and d_dy = dZ W^T (B x H, nullable).  d_stats as nb_softmax_nll.  Same values as
+ * nb_gemm + nb_label_gather + nb_softmax_nll + two nb_gemm up to summation order.  nb_output_layer_supported tells
+ * whether a layer fits the fused form (C <= 64 and W in about 90 KB of shared memory). */
+int nb_output_layer_supported(uint32_t H, uint32_t C);
+/* nb_gcn_step / nb_gcn_compute use nb_output_layer for the last layer where it applies; 0 switches that off
+ * (the layer then runs as separate calls).  Returns the previous setting. */
+int nb_set_fused_output_layer(int enabled);
+int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const int64_t *d_label, const uint32_t *d_dst,
+                    uint32_t B, uint32_t H, uint32_t C, int train, float *d_dw, float *d_dy, float *d_stats,
+                    void *stream);
 /* Multi-label loss and F1 counters (CLASSES > 1; Loss with onelabel = false and f1_score,
  * utils/torch_func.hpp:31-75): loss = mean over B*C of binary_cross_entropy(sigmoid(z), y) with libtorch's
  * clamp of each log at -100; d_dlogits (nullable) = its gradient; d_label: B x C, zero / non-zero.

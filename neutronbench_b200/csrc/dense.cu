@@ -222,6 +222,113 @@ __global__ void __launch_bounds__(1024) bce_reduce_kernel(const float4 *__restri
   }
 }
 
+// ------------------------------------------------------------------------------------ fused output layer
+// Last GCN layer with one label per vertex: logits = Y W, softmax / NLL, dZ, dY = dZ W^T and the per-CTA part of
+// dW = Y^T dZ in one launch; a second launch adds the parts up in CTA order and reduces loss and hits.  The layer is
+// small (1,024 x 128 x 41 on the Reddit-shaped model) and was six launch-latency-bound kernels before.
+// One warp per row.  Lane c (and c + 32) owns class c for the logits; lane h (+32q) owns hidden unit h for dY.
+constexpr int kOutRows = 8;          // rows per CTA = warps per CTA
+constexpr int kOutMaxC = 64;
+
+__global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
+    const float *__restrict__ y, const float *__restrict__ w, const int64_t *__restrict__ label_table,
+    const uint32_t *__restrict__ dst, uint32_t B, uint32_t H, uint32_t C, uint32_t CP, int train, float *dy,
+    float *dw_part, float *row_loss, float *row_hit) {
+  extern __shared__ float out_smem[];
+  float *ws = out_smem;                       // [H][CP]
+  float *ys = ws + (size_t)H * CP;            // [kOutRows][H]
+  float *dzs = ys + (size_t)kOutRows * H;     // [kOutRows][kOutMaxC]
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row = blockIdx.x * kOutRows + warp;
+  for (uint32_t i = threadIdx.x; i < H * C; i += blockDim.x) ws[(i / C) * CP + (i % C)] = w[i];
+  if (row < B)
+    for (uint32_t h = lane; h < H; h += 32) ys[warp * H + h] = y[(size_t)row * H + h];
+  else
+    for (uint32_t h = lane; h < H; h += 32) ys[warp * H + h] = 0.0f;
+  dzs[warp * kOutMaxC + lane] = 0.0f;
+  dzs[warp * kOutMaxC + lane + 32] = 0.0f;
+  __syncthreads();
+
+  if (row < B) {
+    const uint32_t c0 = lane, c1 = lane + 32;
+    float z0 = 0.0f, z1 = 0.0f;
+    for (uint32_t h = 0; h < H; h++) {
+      const float yh = ys[warp * H + h];
+      if (c0 < C) z0 = fmaf(yh, ws[h * CP + c0], z0);
+      if (c1 < C) z1 = fmaf(yh, ws[h * CP + c1], z1);
+    }
+    // max / argmax (first maximum wins), log-sum-exp
+    float m = c0 < C ? z0 : -INFINITY;
+    uint32_t arg = c0;
+    if (c1 < C && z1 > m) { m = z1; arg = c1; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const uint32_t oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (om > m || (om == m && oa < arg)) { m = om; arg = oa; }
+    }
+    float sum = (c0 < C ? expf(z0 - m) : 0.0f) + (c1 < C ? expf(z1 - m) : 0.0f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float lse = logf(sum);
+    const int64_t lab = label_table[dst[row]];
+    const float z_lab = __shfl_sync(0xffffffffu, (lab >= 32) ? z1 : z0, (unsigned)(lab & 31));
+    if (lane == 0) {
+      row_loss[row] = -((z_lab - m) - lse);
+      row_hit[row] = ((int64_t)arg == lab) ? 1.0f : 0.0f;
+    }
+    if (train) {
+      const float inv_b = 1.0f / (float)B;
+      if (c0 < C) dzs[warp * kOutMaxC + c0] = (expf(z0 - m - lse) - ((int64_t)c0 == lab ? 1.0f : 0.0f)) * inv_b;
+      if (c1 < C) dzs[warp * kOutMaxC + c1] = (expf(z1 - m - lse) - ((int64_t)c1 == lab ? 1.0f : 0.0f)) * inv_b;
+      __syncwarp();
+      if (dy) {
+        for (uint32_t h = lane; h < H; h += 32) {
+          float acc = 0.0f;
+          for (uint32_t c = 0; c < C; c++) acc = fmaf(dzs[warp * kOutMaxC + c], ws[h * CP + c], acc);
+          dy[(size_t)row * H + h] = acc;
+        }
+      }
+    }
+  }
+  if (!train) return;
+  __syncthreads();
+  // this CTA's part of dW = Y^T dZ: rows in order, one (h, c) pair per thread and step
+  float *part = dw_part + (size_t)blockIdx.x * H * C;
+  for (uint32_t i = threadIdx.x; i < H * C; i += blockDim.x) {
+    const uint32_t h = i / C, c = i % C;
+    float acc = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kOutRows; r++) acc = fmaf(ys[r * H + h], dzs[r * kOutMaxC + c], acc);
+    part[i] = acc;
+  }
+}
+
+// Blocks 0 .. n-2: dW[i] = sum of the CTA parts in CTA order.  Last block: loss and hits, fixed-shape tree.
+__global__ void __launch_bounds__(256) output_layer_reduce_kernel(const float *__restrict__ dw_part, uint32_t parts,
+                                                                  uint32_t hc, float *dw, const float *__restrict__ row_loss,
+                                                                  const float *__restrict__ row_hit, uint32_t B, float *stats) {
+  if (blockIdx.x + 1 < gridDim.x) {
+    if (dw == nullptr) return;
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= hc) return;
+    float acc = 0.0f;
+    for (uint32_t p = 0; p < parts; p++) acc += dw_part[(size_t)p * hc + i];
+    dw[i] = acc;
+    return;
+  }
+  __shared__ float sl[256], sh[256];
+  float l = 0.0f, h = 0.0f;
+  for (uint32_t i = threadIdx.x; i < B; i += 256) { l += row_loss[i]; h += row_hit[i]; }
+  sl[threadIdx.x] = l; sh[threadIdx.x] = h;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) { sl[threadIdx.x] += sl[threadIdx.x + o]; sh[threadIdx.x] += sh[threadIdx.x + o]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { stats[0] = sl[0] / (float)B; stats[1] = sh[0]; }
+}
+
 // ------------------------------------------------------------------------------------ Adam
 __global__ void adam_kernel(float *W, const float *__restrict__ grad, float *M, float *V, int64_t n, float alpha,
                             float b1, float b2, float eps, float wd, float c1, float c2) {
@@ -356,6 +463,44 @@ NB_API int nb_sigmoid_bce(nb_ws *ws, const float *d_logits, const int64_t *d_lab
                                                                                row_part);
   NB_LAUNCH_CHECK();
   bce_reduce_kernel<<<1, 1024, 0, stream>>>(row_part, B, C, d_stats);
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+static size_t output_layer_smem(uint32_t H, uint32_t C) {
+  const uint32_t CP = C | 1u;
+  return ((size_t)H * CP + (size_t)kOutRows * H + (size_t)kOutRows * kOutMaxC) * sizeof(float);
+}
+
+NB_API int nb_output_layer_supported(uint32_t H, uint32_t C) {
+  return (H > 0 && C > 0 && C <= (uint32_t)kOutMaxC && output_layer_smem(H, C) <= 96 * 1024) ? 1 : 0;
+}
+
+NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const int64_t *d_label, const uint32_t *d_dst,
+                           uint32_t B, uint32_t H, uint32_t C, int train, float *d_dw, float *d_dy, float *d_stats,
+                           void *stream_) {
+  NB_REQUIRE(ws && d_y && d_w && d_label && d_dst && d_stats, "nb_output_layer: null pointer");
+  NB_REQUIRE(B > 0, "nb_output_layer: empty batch");
+  NB_REQUIRE(nb_output_layer_supported(H, C), "nb_output_layer: layer too wide for the fused form (C <= 64, H*C*4 <= ~90 KB)");
+  NB_REQUIRE(!train || d_dw, "nb_output_layer: training needs the weight-gradient buffer");
+  cudaStream_t stream = as_stream(stream_);
+  WsScope scope(ws);
+  const uint32_t ctas = (B + kOutRows - 1) / kOutRows, hc = H * C;
+  float *row_loss = ws->alloc_n<float>(B), *row_hit = ws->alloc_n<float>(B);
+  float *part = train ? ws->alloc_n<float>((size_t)ctas * hc) : nullptr;
+  if (!row_loss || !row_hit || (train && !part)) return fail(NB_ERR_NOMEM, "nb_output_layer: workspace arena exhausted");
+  const size_t smem = output_layer_smem(H, C);
+  static bool configured = false;
+  if (!configured) {
+    NB_CUDA(cudaFuncSetAttribute(output_layer_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    configured = true;
+  }
+  output_layer_rows_kernel<<<ctas, kOutRows * 32, smem, stream>>>(d_y, d_w, d_label, d_dst, B, H, C, C | 1u, train ? 1 : 0,
+                                                                   train ? d_dy : nullptr, part, row_loss, row_hit);
+  NB_LAUNCH_CHECK();
+  const unsigned blocks = (train ? (hc + 255) / 256 : 0) + 1;
+  output_layer_reduce_kernel<<<blocks, 256, 0, stream>>>(part, ctas, hc, train ? d_dw : nullptr, row_loss, row_hit, B,
+                                                         d_stats);
   NB_LAUNCH_CHECK();
   return 0;
 }

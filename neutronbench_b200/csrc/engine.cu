@@ -66,6 +66,8 @@ struct nb_gcn {
   bool stop = false;
 };
 
+int g_fuse_output_layer = 1;   // nb_set_fused_output_layer
+
 namespace {
 
 using Block = BlockArrays;
@@ -283,6 +285,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   float *Y[NB_MAX_LAYERS], *X[NB_MAX_LAYERS + 1];
   size_t y_ld[NB_MAX_LAYERS];
   X[0] = nullptr;
+  bool fused_out = false;
   for (uint32_t l = 0; l < L; l++) {
     const Block &b = blk[l];
     const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
@@ -312,6 +315,9 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
       NB_TRY(nb_spmm_csc_fwd_fused(X[l], Y[l], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi, stream));
       agg_bytes += bytes_fwd(b, Fi, false, false);
     }
+    // The last layer with one label per vertex runs fused with the loss and its own gradients (nb_output_layer).
+    fused_out = l + 1 == L && c.classes <= 1 && y_ld[l] == Fi && g_fuse_output_layer && nb_output_layer_supported(Fi, Fo);
+    if (fused_out) break;
     NB_TRY(arena(ws, (size_t)b.v * Fo, &X[l + 1]));
     NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], c.d_W + g->w_off[l], Fo, X[l + 1], b.v, Fo, Fi, 0, 0, nb::as_stream(stream)));
     if (l + 1 < L) NB_TRY(nb_relu_dropout(X[l + 1], (int64_t)b.v * Fo, p, c.seed, l, g->steps, stream));
@@ -321,26 +327,37 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   const Block &last = blk[L - 1];
   const int64_t B = last.v, C = c.layer_size[L];
   const bool multi = c.classes > 1;   // CLASSES > 1: C labels per vertex, BCE loss (utils/torch_func.hpp:67-75)
-  int64_t *lab;
-  NB_TRY(arena(ws, (size_t)(multi ? B * C : B), &lab));
-  NB_TRY(nb_label_gather(lab, c.d_label, last.destination, last.v, multi ? (uint32_t)C : 1u, stream));
-  float *dZ = nullptr;
-  if (train) NB_TRY(arena(ws, (size_t)(B * C), &dZ));
-  if (multi)
-    NB_TRY(nb_sigmoid_bce(ws, X[L], lab, B, C, dZ, d_stats, stream));
-  else
-    NB_TRY(nb_softmax_nll(ws, X[L], lab, B, C, dZ, d_stats, stream));
+  float *dZ = nullptr, *dY_out = nullptr;
+  if (fused_out) {
+    const uint32_t H = c.layer_size[L - 1];
+    if (train && L > 1) NB_TRY(arena(ws, (size_t)B * H, &dY_out));
+    NB_TRY(nb_output_layer(ws, Y[L - 1], c.d_W + g->w_off[L - 1], c.d_label, last.destination, (uint32_t)B, H, (uint32_t)C,
+                           train, c.d_grad + g->w_off[L - 1], dY_out, d_stats, stream));
+  } else {
+    int64_t *lab;
+    NB_TRY(arena(ws, (size_t)(multi ? B * C : B), &lab));
+    NB_TRY(nb_label_gather(lab, c.d_label, last.destination, last.v, multi ? (uint32_t)C : 1u, stream));
+    if (train) NB_TRY(arena(ws, (size_t)(B * C), &dZ));
+    if (multi)
+      NB_TRY(nb_sigmoid_bce(ws, X[L], lab, B, C, dZ, d_stats, stream));
+    else
+      NB_TRY(nb_softmax_nll(ws, X[L], lab, B, C, dZ, d_stats, stream));
+  }
 
   // ---- backward: dW_l = Y_l^T dZ_l; dY_l = dZ_l W_l^T; dZ_{l-1} = (A_l^T dY_l) masked by X_l > 0
   if (train) {
     for (int l = (int)L - 1; l >= 0; l--) {
       const Block &b = blk[l];
       const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
-      NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], dZ, Fo, c.d_grad + g->w_off[l], Fi, Fo, b.v, 1, 0, nb::as_stream(stream)));
+      const bool from_fused = fused_out && l + 1 == (int)L;   // dW and dY of the last layer are already there
+      if (!from_fused)
+        NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], dZ, Fo, c.d_grad + g->w_off[l], Fi, Fo, b.v, 1, 0, nb::as_stream(stream)));
       if (l == 0) break;   // the input-side block is never back-propagated (core/ntsContext.hpp:292)
-      float *dY, *dX;
-      NB_TRY(arena(ws, (size_t)b.v * Fi, &dY));
-      NB_TRY(nb_gemm(ws, dZ, c.d_W + g->w_off[l], dY, b.v, Fi, Fo, 0, 1, stream));
+      float *dY = dY_out, *dX;
+      if (!from_fused) {
+        NB_TRY(arena(ws, (size_t)b.v * Fi, &dY));
+        NB_TRY(nb_gemm(ws, dZ, c.d_W + g->w_off[l], dY, b.v, Fi, Fo, 0, 1, stream));
+      }
       NB_TRY(arena(ws, (size_t)b.s * Fi, &dX));
       AggTimer t(g, stream, bytes_bwd(b, Fi));
       NB_TRY(nb_spmm_csr_bwd_fused(dY, dX, b.row_offset, b.column_indices, b.src_norm, b.dst_norm, X[l], scale, b.s, Fi,
@@ -454,6 +471,12 @@ NB_API int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_coun
   NB_CUDA(cudaEventRecord(batch->consumed, nb::as_stream(stream)));
   batch->in_use = true;
   return 0;
+}
+
+NB_API int nb_set_fused_output_layer(int enabled) {
+  const int old = g_fuse_output_layer;
+  g_fuse_output_layer = enabled != 0;
+  return old;
 }
 
 NB_API int nb_gcn_set_sampler_threads(nb_gcn *g, int threads) {

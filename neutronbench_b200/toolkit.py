@@ -162,6 +162,7 @@ class GCN_GPU_NEIGHBOR_impl:
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._stats_host = torch.zeros(4, dtype=torch.float32).pin_memory()
         self.multi_label = int(cfg.classes) > 1
+        self.fuse_output_layer = True   # last layer + loss + its gradients in two launches (nb_output_layer)
         if self.multi_label:
             assert int(cfg.classes) == int(cfg.layers[-1]), "CLASSES > 1 needs one output per class"
             assert datum.local_label.dim() == 2 and datum.local_label.size(1) == int(cfg.classes)
@@ -302,6 +303,9 @@ class GCN_GPU_NEIGHBOR_impl:
         scale = 1.0 / (1.0 - p) if p > 0 else 1.0
         Y: List[torch.Tensor] = []
         X: List[Optional[torch.Tensor]] = [None]
+        # the last layer with one label per vertex runs fused with its loss and gradients, as in the native step
+        fused_out = (self.fuse_output_layer and not self.multi_label
+                     and bool(_lib.load().nb_output_layer_supported(int(c.layers[L - 1]), int(c.layers[L]))))
         for l in range(L):
             blk = ssg.sampled_sgs[l]
             if l == 0:
@@ -312,6 +316,8 @@ class GCN_GPU_NEIGHBOR_impl:
                     "nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(blk.row_indices), ptr(blk.column_offset),
                     ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, c.layers[l], stream))
             Y.append(y)
+            if l == L - 1 and fused_out:
+                break
             z = torch.empty((blk.v_size, c.layers[l + 1]), dtype=torch.float32, device=self.device)
             _lib.call("nb_gemm", wsh, ptr(y), ptr(self.P.w(l)), ptr(z), blk.v_size, c.layers[l + 1], c.layers[l], 0,
                       0, stream)
@@ -320,8 +326,16 @@ class GCN_GPU_NEIGHBOR_impl:
             X.append(z)
         last = ssg.sampled_sgs[L - 1]
         B, C = last.v_size, c.layers[L]
-        dZ = torch.empty((B, C), dtype=torch.float32, device=self.device) if train else None
-        if self.multi_label:   # Loss(..., onelabel=false), utils/torch_func.hpp:67-75
+        dZ = torch.empty((B, C), dtype=torch.float32, device=self.device) if (train and not fused_out) else None
+        dY_out = None
+        if fused_out:
+            H = c.layers[L - 1]
+            if train and L > 1:
+                dY_out = torch.empty((B, H), dtype=torch.float32, device=self.device)
+            _lib.call("nb_output_layer", wsh, ptr(Y[L - 1]), ptr(self.P.w(L - 1)), ptr(self.datum.local_label),
+                      ptr(last.destination), B, H, C, 1 if train else 0, ptr(self.P.g(L - 1)), ptr(dY_out),
+                      ptr(self.stats), stream)
+        elif self.multi_label:   # Loss(..., onelabel=false), utils/torch_func.hpp:67-75
             lab = torch.empty((B, C), dtype=torch.int64, device=self.device)
             _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(last.destination), B, C, stream)
             _lib.call("nb_sigmoid_bce", wsh, ptr(X[L]), ptr(lab), B, C, ptr(dZ), ptr(self.stats), stream)
@@ -335,11 +349,16 @@ class GCN_GPU_NEIGHBOR_impl:
         for l in range(L - 1, -1, -1):
             blk = ssg.sampled_sgs[l]
             Fi, Fo = c.layers[l], c.layers[l + 1]
-            _lib.call("nb_gemm", wsh, ptr(Y[l]), ptr(dZ), ptr(self.P.g(l)), Fi, Fo, blk.v_size, 1, 0, stream)
+            from_fused = fused_out and l == L - 1     # dW and dY of the last layer are already there
+            if not from_fused:
+                _lib.call("nb_gemm", wsh, ptr(Y[l]), ptr(dZ), ptr(self.P.g(l)), Fi, Fo, blk.v_size, 1, 0, stream)
             if l == 0:
                 break  # the input-side block is never back-propagated (core/ntsContext.hpp:292)
-            dY = torch.empty((blk.v_size, Fi), dtype=torch.float32, device=self.device)
-            _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), blk.v_size, Fi, Fo, 0, 1, stream)
+            if from_fused:
+                dY = dY_out
+            else:
+                dY = torch.empty((blk.v_size, Fi), dtype=torch.float32, device=self.device)
+                _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), blk.v_size, Fi, Fo, 0, 1, stream)
             dX = torch.empty((blk.src_size, Fi), dtype=torch.float32, device=self.device)
             self._timed(f"bwd{l}", self.agg_bytes_bwd(blk, Fi), lambda: _lib.call(
                 "nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(blk.row_offset), ptr(blk.column_indices),
@@ -376,6 +395,7 @@ class GCN_GPU_NEIGHBOR_impl:
         ec.d_label = ptr(self.datum.local_label)
         ec.d_W, ec.d_grad, ec.d_M, ec.d_V = ptr(self.P.W), ptr(self.P.grad), ptr(self.P.M), ptr(self.P.V)
         handle = C.c_void_p()
+        _lib.load().nb_set_fused_output_layer(1 if self.fuse_output_layer else 0)
         _lib.call("nb_gcn_create", C.byref(handle), C.byref(ec), self.ws.handle)
         self._engine, self._engine_cfg = handle, ec
         return handle

@@ -175,3 +175,58 @@ def test_tma_and_cp_async_kernels_give_identical_bits(cuda_device, ws, kind, M, 
         os.environ.pop("NB_TC_NO_TMA", None)
         lib.nb_set_gemm_mode(old)
     np.testing.assert_array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+@pytest.mark.parametrize("B,H,C", [(1024, 128, 41), (37, 16, 7), (300, 32, 64), (9, 5, 1), (1000, 100, 47)])
+def test_fused_output_layer_matches_oracle(cuda_device, ws, B, H, C):
+    """nb_output_layer = Y W, softmax/NLL on gathered labels, dW = Y^T dZ, dY = dZ W^T in two launches."""
+    assert _lib.load().nb_output_layer_supported(H, C) == 1
+    rng = np.random.RandomState(B + H + C)
+    V = B * 3
+    y, w = rng.randn(B, H).astype(np.float32), (rng.randn(H, C) * 0.3).astype(np.float32)
+    table = rng.randint(0, C, size=V).astype(np.int64)
+    dst = rng.choice(V, B, replace=False).astype(np.uint32)
+    z = oracle.gemm_nn(y, w)
+    loss, dz, correct = oracle.softmax_nll(z, table[dst])
+    dw_ref, dy_ref = oracle.gemm_tn(y, dz), oracle.gemm_nt(dz, w)
+    st = torch.cuda.current_stream().cuda_stream
+    dy = torch.full((B, H), float("nan"), device=cuda_device)
+    dw = torch.full((H, C), float("nan"), device=cuda_device)
+    stats = torch.zeros(4, device=cuda_device)
+    from helpers import dev_i32
+    args = (ws.handle, ptr(dev_f32(y, cuda_device)), ptr(dev_f32(w, cuda_device)), ptr(dev_i64(table, cuda_device)),
+            ptr(dev_i32(dst, cuda_device)), B, H, C)
+    _lib.call("nb_output_layer", *args, 1, ptr(dw), ptr(dy), ptr(stats), st)
+    s = stats.cpu().numpy()
+    assert abs(s[0] - loss) < 1e-5 * max(1.0, abs(loss)) and int(s[1]) == correct
+    _close(host_f32(dw), dw_ref, B)
+    _close(host_f32(dy), dy_ref, C)
+    # evaluation: loss and hits only, gradients untouched
+    dw.fill_(7.0)
+    _lib.call("nb_output_layer", *args, 0, ptr(dw), 0, ptr(stats), st)
+    s2 = stats.cpu().numpy()
+    assert s2[0] == s[0] and s2[1] == s[1] and float(dw.min()) == 7.0
+    # wider layers are refused, not mis-computed
+    assert _lib.load().nb_output_layer_supported(128, 65) == 0 and _lib.load().nb_output_layer_supported(4096, 64) == 0
+
+
+def test_native_step_with_and_without_the_fused_output_layer(cuda_device):
+    """Switching nb_output_layer off changes the last layer's summation order only: same loss curve to 1e-5."""
+    from neutronbench_b200 import FullyRepGraph, GCN_GPU_NEIGHBOR_impl, GCNConfig, GNNDatum, Sampler, Workspace
+    from helpers import small_graph
+    V = 3000
+    edges, co, ri = small_graph(V, 40000, seed=4)
+    rng = np.random.RandomState(0)
+    feat, label = rng.randn(V, 24).astype(np.float32), rng.randint(0, 5, size=V).astype(np.int64)
+    curves = []
+    for fused in (True, False):
+        cfg = GCNConfig(layers=[24, 16, 5], fanout=(6, 4), batch_size=128, drop_rate=0.2, seed=11)
+        g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
+        datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device), np.zeros(V, np.int32))
+        tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg)
+        tk.fuse_output_layer = fused
+        smp = Sampler(g, np.arange(600, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                      with_edge_weights=False)
+        curves.append([tk.Forward(smp, train=True)[1] for _ in range(3)])
+    _lib.load().nb_set_fused_output_layer(1)
+    np.testing.assert_allclose(curves[0], curves[1], rtol=2e-5)
