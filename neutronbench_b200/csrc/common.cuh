@@ -102,7 +102,9 @@ struct TmaSpmmArgs {
   float *y;                // n x F output
   size_t y_ld;             // pitch of y in floats (0 = F)
   const uint32_t *offs;    // n + 1 offsets
-  const uint32_t *ref;     // per edge: row reference
+  const uint32_t *ref;     // per edge: row reference (null in the gather form below)
+  // gather form (ring kernel only): the reference of edge j is formed on the fly from idx[j] -> source -> hashmap
+  const uint32_t *gidx, *gsource, *ghashmap;   // ghashmap null = no cache: rows come from x by global id
   const float *w;          // per edge weight, or null to form it from the two factors below
   const float *norm_row;   // [n]
   const float *norm_idx;   // indexed by ref (only valid when references are plain local indices)

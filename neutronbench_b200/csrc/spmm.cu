@@ -344,6 +344,16 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
   {
     const float *hit_base = d_hashmap ? d_cache : feat;
     const size_t hit_ld = d_hashmap ? cache_ld : feat_ld;
+    if (g_staged_spmm && g_spmm_ring && g_l2_panel_bytes == 0 && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
+      // ring kernel: references and weights are formed inside the kernel, one window of 32 edges ahead
+      TmaSpmmArgs t{};
+      t.x = hit_base; t.x_ld = hit_ld; t.miss = feat; t.miss_ld = feat_ld; t.y = d_y; t.y_ld = y_ld; t.offs = d_column_offset;
+      t.gidx = d_row_indices; t.gsource = d_source; t.ghashmap = d_hashmap;
+      t.norm_row = d_dst_norm; t.norm_idx = d_src_norm;
+      t.n = v; t.F = F; t.act = nullptr; t.act_scale = 1.0f; t.src_rows_hint = s;
+      t.out_vec = pick_vec(F, {}, {d_y});
+      return launch_spmm_tma(t, as_stream(stream));
+    }
     if (g_staged_spmm && ws != nullptr && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
       cudaStream_t st = as_stream(stream);
       WsScope scope(ws);

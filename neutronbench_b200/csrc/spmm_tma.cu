@@ -325,15 +325,29 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   const uint32_t j0 = __ldg(a.offs + r_begin), j1 = __ldg(a.offs + r_end);
 
   // operand windows of 32 edges aligned to j0: `cur` holds the window being consumed, `nxt` the next
-  auto load_ref = [&](uint32_t wbase) -> uint32_t { const uint32_t j = wbase + lane; return j < j1 ? __ldg(a.ref + j) : 0u; };
-  auto load_w = [&](uint32_t wbase, uint32_t ref) -> float {
+  // Reference and weight (or, without explicit weights, the degree factor of the indexed side) of edge wbase + lane.
+  // In the gather form the reference is the cache slot of the edge's source (bit 31 set + global id when the source
+  // is not cached and rows come from `miss`; the plain global id when there is no cache at all).
+  auto load_edge = [&](uint32_t wbase, uint32_t &ref, float &w) {
     const uint32_t j = wbase + lane;
-    if (j >= j1) return 0.0f;
-    return a.w ? __ldg(a.w + j) : __ldg(a.norm_idx + ref);    // fused form: factor of the indexed side
+    ref = 0u; w = 0.0f;
+    if (j >= j1) return;
+    if (a.gidx) {
+      const uint32_t li = __ldg(a.gidx + j);
+      const uint32_t g = __ldg(a.gsource + li);
+      const uint32_t slot = a.ghashmap ? __ldg(a.ghashmap + g) : 0xFFFFFFFFu;
+      ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? (g | 0x80000000u) : g);
+      w = __ldg(a.norm_idx + li);
+    } else {
+      ref = __ldg(a.ref + j);
+      w = a.w ? __ldg(a.w + j) : __ldg(a.norm_idx + ref);     // fused form: factor of the indexed side
+    }
   };
   uint32_t win = j0;                                          // base of the consume window
-  uint32_t ref_cur = load_ref(win), ref_nxt = load_ref(win + 32);
-  float w_cur = load_w(win, ref_cur), w_nxt = load_w(win + 32, ref_nxt);
+  uint32_t ref_cur, ref_nxt;
+  float w_cur, w_nxt;
+  load_edge(win, ref_cur, w_cur);
+  load_edge(win + 32, ref_nxt, w_nxt);
 
   // issue the copy of edge j (j0 <= j < j1) into its slot; executed by the whole warp
   auto issue = [&](uint32_t j) {
@@ -410,8 +424,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     if (j - win >= 32) {                                      // consume window moves on; fetch the one after
       win += 32;
       ref_cur = ref_nxt; w_cur = w_nxt;
-      ref_nxt = load_ref(win + 32);
-      w_nxt = load_w(win + 32, ref_nxt);
+      load_edge(win + 32, ref_nxt, w_nxt);
     }
     const uint32_t slot = (j - j0) % R;
     {
@@ -565,6 +578,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
       return a.act ? launch_ring<true>(a, smem, stream) : launch_ring<false>(a, smem, stream);
     }
   }
+  if (a.ref == nullptr) return fail(NB_ERR_INVALID, "spmm (staged): the segment kernel needs per-edge references");
   a.panel_floats = ((a.fpad / 4 + panels - 1) / panels) * 4;   // multiple of 4 floats = 16 bytes
   a.panels = (a.fpad + a.panel_floats - 1) / a.panel_floats;
   a.copy_bytes = a.panel_floats * 4;
