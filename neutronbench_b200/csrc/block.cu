@@ -317,15 +317,15 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
     }
   }
   // Without explicit weight arrays the rest runs in fewer, merged launches; their first one needs the row
-  // counters cleared, which the popcount launch does on the side (at most min(|V|, e) + 1 of them exist).
+  // counters cleared.
   const bool lean = d_w_fwd == nullptr && d_w_bwd == nullptr && e > 0;
-  const uint64_t zero_cap = lean ? (uint64_t)(e < num_vertices ? e : num_vertices) + 1 : 0;
-  bool counters_cleared = false;
+  if (lean) {   // at most min(|V|, e) + 1 row counters exist; cleared before the size is known, off the critical path
+    const uint64_t zero_cap = (uint64_t)(e < num_vertices ? e : num_vertices) + 1;
+    NB_CUDA(cudaMemsetAsync(d_row_offset, 0, zero_cap * sizeof(uint32_t), stream));
+  }
   if (words <= kSingleBlockScanMax) {   // popcount and scan in one launch
-    scan_single_block<uint32_t, ScanLoadPopc><<<1, 1024, 0, stream>>>(ScanLoadPopc{bitmap}, prefix, words, true,
-                                                                      d_row_offset, zero_cap);
+    scan_single_block<uint32_t, ScanLoadPopc><<<1, 1024, 0, stream>>>(ScanLoadPopc{bitmap}, prefix, words, true);
     NB_LAUNCH_CHECK();
-    counters_cleared = lean;
   } else {
     popc_words_kernel<<<grid_for(words, kThreads), kThreads, 0, stream>>>(bitmap, prefix, words);
     NB_LAUNCH_CHECK();
@@ -343,7 +343,6 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
     uint32_t *long_rows = ws->alloc_n<uint32_t>((size_t)e / 32 + 1);
     uint32_t *scratch = ws->alloc_n<uint32_t>(e);
     if (!cursor || !long_rows || !scratch) return fail(NB_ERR_NOMEM, "nb_block_build: workspace arena exhausted");
-    if (!counters_cleared) NB_CUDA(cudaMemsetAsync(d_row_offset, 0, ((size_t)s + 1) * sizeof(uint32_t), stream));
     emit_remap_kernel<<<grid_for(words > e ? words : e, kThreads), kThreads, 0, stream>>>(
         bitmap, prefix, words, d_source, d_row_indices, e, num_vertices, d_row_offset, cursor, s);
     NB_LAUNCH_CHECK();

@@ -17,7 +17,7 @@ void set_error(const char *fmt, ...) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Three-pass exclusive scan: tile sums -> scan of the tile sums by one block -> per-tile scan.
+// Exclusive scan in passes: tile sums -> (scan of the tile sums by one block, for very long inputs) -> per-tile scan.
 // No inter-block waiting, so there is nothing that can spin.  Traffic: reads the input twice and
 // writes the output once (12 bytes per element for u32 -> u32).
 // ---------------------------------------------------------------------------------------------
@@ -50,6 +50,38 @@ __global__ void __launch_bounds__(1024) scan_tile_offsets(TOut *tile_sums, uint6
     carry += total;
   }
   if (threadIdx.x == 0 && grand_total) *grand_total = carry;
+}
+
+// Two-pass form for up to kScanThreads * 4 tiles (2 M elements): every block adds up the sums of the tiles
+// before its own (at most a thousand values) instead of waiting for a middle launch to scan them.
+template <typename TOut>
+__global__ void __launch_bounds__(kScanThreads) scan_tiles_self_offset(const uint32_t *in, TOut *out,
+                                                                       const TOut *__restrict__ tile_sums, uint64_t n,
+                                                                       bool write_total) {
+  __shared__ TOut smem[33];
+  __shared__ TOut s_offset;
+  TOut before = 0;
+  for (uint32_t t = threadIdx.x; t < blockIdx.x; t += kScanThreads) before += tile_sums[t];
+  TOut off_total;
+  block_exclusive_scan<TOut>(before, &off_total, smem);
+  if (threadIdx.x == 0) s_offset = off_total;
+  __syncthreads();
+  uint64_t base = (uint64_t)blockIdx.x * kScanTile + (uint64_t)threadIdx.x * kScanItems;
+  uint32_t v[kScanItems];
+  TOut sum = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    v[k] = (base + k < n) ? in[base + k] : 0u;
+    sum += v[k];
+  }
+  TOut total;
+  TOut ex = block_exclusive_scan<TOut>(sum, &total, smem) + s_offset;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    if (base + k < n) out[base + k] = ex;
+    ex += v[k];
+  }
+  if (write_total && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) out[n] = s_offset + total;
 }
 
 template <typename TOut>
@@ -92,6 +124,11 @@ static int scan_impl(nb_ws *ws, const uint32_t *d_in, TOut *d_out, uint64_t n, b
   if (!tile_sums) return fail(NB_ERR_NOMEM, "scan: workspace arena exhausted");
   scan_tile_sums<TOut><<<(unsigned)tiles, kScanThreads, 0, stream>>>(d_in, tile_sums, n);
   NB_LAUNCH_CHECK();
+  if (tiles <= (uint64_t)kScanThreads * 4) {
+    scan_tiles_self_offset<TOut><<<(unsigned)tiles, kScanThreads, 0, stream>>>(d_in, d_out, tile_sums, n, write_total);
+    NB_LAUNCH_CHECK();
+    return 0;
+  }
   scan_tile_offsets<TOut><<<1, 1024, 0, stream>>>(tile_sums, tiles, write_total ? d_out + n : nullptr);
   NB_LAUNCH_CHECK();
   scan_tiles<TOut><<<(unsigned)tiles, kScanThreads, 0, stream>>>(d_in, d_out, tile_sums, n);

@@ -48,11 +48,8 @@ struct ScanLoadArray {
 // Small inputs (the per-hop arrays of a sampled block): one block walks the sequence in chunks of
 // 1024 x 8 with a running carry.  One launch instead of three; every element is produced once.
 template <typename TOut, typename Load>
-__global__ void __launch_bounds__(1024) scan_single_block(Load load, TOut *out, uint64_t n, bool write_total,
-                                                          uint32_t *zero = nullptr, uint64_t zero_n = 0) {
+__global__ void __launch_bounds__(1024) scan_single_block(Load load, TOut *out, uint64_t n, bool write_total) {
   __shared__ TOut smem[33];
-  // side job for callers that need an array cleared before their next kernel and have this launch to spare
-  for (uint64_t i = threadIdx.x; i < zero_n; i += 1024) zero[i] = 0u;
   TOut carry = 0;
   for (uint64_t start = 0; start < n; start += 1024 * kScanItems) {
     const uint64_t base = start + (uint64_t)threadIdx.x * kScanItems;
