@@ -327,6 +327,11 @@ int nb_gcn_destroy(nb_gcn *g);
 int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int train, float *d_stats,
                 nb_gcn_step_info *info, void *stream);
 int nb_gcn_update(nb_gcn *g, void *stream);
+/* The update may run on a stream of its own, so that the gradient sum over ranks and Adam overlap the layer-0
+ * aggregation of the next batch (which does not read the weights): nb_gcn_wait_gradients makes `stream` wait for
+ * the gradients of the last step / compute call (enqueue the all-reduce on it afterwards), nb_gcn_update on that
+ * stream then orders itself after them, and the next step waits for the update before its first weight read. */
+int nb_gcn_wait_gradients(nb_gcn *g, void *stream);
 /* The same step in two halves, so that sampling batch i+1 overlaps the training of batch i — the
  * reference's pipelined batch loop (pipeline_version, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, where each
  * pipeline thread owns its SampledSubgraph and three streams).  A nb_gcn_batch is one SampledSubgraph

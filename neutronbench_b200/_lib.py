@@ -81,6 +81,7 @@ SIGNATURES = {
     "nb_gcn_destroy": (C.c_int, [ptr]),
     "nb_gcn_step": (C.c_int, [ptr, u32p, C.c_uint32, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),
     "nb_gcn_update": (C.c_int, [ptr] * 2),
+    "nb_gcn_wait_gradients": (C.c_int, [ptr] * 2),
     "nb_gcn_batch_create": (C.c_int, [C.POINTER(C.c_void_p), ptr]),
     "nb_gcn_batch_destroy": (C.c_int, [ptr]),
     "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.c_int, ptr]),

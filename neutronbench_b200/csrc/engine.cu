@@ -55,6 +55,10 @@ struct nb_gcn {
   uint64_t timed_bytes = 0;
   std::vector<int> ev_class;         // per pair: 0 = layer-0 forward aggregation, 1 = any other aggregation
   std::vector<uint64_t> ev_bytes;
+  // cross-stream ordering of gradients and weights when the caller runs the update on a stream of its own
+  cudaEvent_t ev_grad = nullptr;      // recorded after the last kernel of a compute call
+  cudaEvent_t ev_updated = nullptr;   // recorded after Adam
+  bool updated_recorded = false;
   // sampler thread (one of the reference's pipeline threads, toolkits/GCN_GPU_NEIGHBOR.hpp:399-505, reduced to
   // the part that blocks on the device): started by the first nb_gcn_sample_async
   int device = 0;
@@ -134,6 +138,8 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   g->ws = ws;
   g->own.ws = ws;
   NB_CUDA(cudaGetDevice(&g->device));
+  NB_CUDA(cudaEventCreateWithFlags(&g->ev_grad, cudaEventDisableTiming));
+  NB_CUDA(cudaEventCreateWithFlags(&g->ev_updated, cudaEventDisableTiming));
   g->draws = 0;
   g->steps = 0;
   g->beta1_t = cfg->beta1;
@@ -156,6 +162,8 @@ NB_API int nb_gcn_destroy(nb_gcn *g) {
       for (std::thread &t : g->samplers) t.join();
     }
     for (cudaEvent_t e : g->ev_pool) cudaEventDestroy(e);
+    if (g->ev_grad) cudaEventDestroy(g->ev_grad);
+    if (g->ev_updated) cudaEventDestroy(g->ev_updated);
     if (g->own.sampled) cudaEventDestroy(g->own.sampled);
     if (g->own.consumed) cudaEventDestroy(g->own.consumed);
   }
@@ -315,6 +323,9 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
       NB_TRY(nb_spmm_csc_fwd_fused(X[l], Y[l], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi, stream));
       agg_bytes += bytes_fwd(b, Fi, false, false);
     }
+    // First reader of the weights in this step: if the previous update ran on another stream, wait for it here,
+    // after the layer-0 aggregation (which does not touch the weights) has been enqueued.
+    if (l == 0 && g->updated_recorded) NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), g->ev_updated, 0));
     // The last layer with one label per vertex runs fused with the loss and its own gradients (nb_output_layer).
     fused_out = l + 1 == L && c.classes <= 1 && y_ld[l] == Fi && g_fuse_output_layer && nb_output_layer_supported(Fi, Fo);
     if (fused_out) break;
@@ -371,6 +382,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
     info->agg_bytes = agg_bytes;
   }
   NB_CUDA(cudaEventRecord(bt->consumed, nb::as_stream(stream)));
+  NB_CUDA(cudaEventRecord(g->ev_grad, nb::as_stream(stream)));
   bt->in_use = true;
   return 0;
 }
@@ -509,11 +521,20 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
   return compute_from(g, &g->own, train, d_stats, info, stream);
 }
 
+NB_API int nb_gcn_wait_gradients(nb_gcn *g, void *stream) {
+  NB_REQUIRE(g != nullptr, "nb_gcn_wait_gradients: null pointer");
+  NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), g->ev_grad, 0));
+  return 0;
+}
+
 NB_API int nb_gcn_update(nb_gcn *g, void *stream) {
   NB_REQUIRE(g != nullptr, "nb_gcn_update: null pointer");
   const nb_gcn_config &c = g->cfg;
+  NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), g->ev_grad, 0));   // no-op on the stream that computed them
   NB_TRY(nb_adam(c.d_W, c.d_grad, c.d_M, c.d_V, (int64_t)g->w_off[c.num_layers], c.learn_rate, c.beta1, c.beta2,
                  c.epsilon, c.weight_decay, g->beta1_t, g->beta2_t, stream));
+  NB_CUDA(cudaEventRecord(g->ev_updated, nb::as_stream(stream)));
+  g->updated_recorded = true;
   g->beta1_t *= c.beta1;   // Parameter::next (core/NtsScheduler.hpp:700-711)
   g->beta2_t *= c.beta2;
   g->steps++;

@@ -162,6 +162,9 @@ class GCN_GPU_NEIGHBOR_impl:
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._stats_host = torch.zeros(4, dtype=torch.float32).pin_memory()
         self.multi_label = int(cfg.classes) > 1
+        # gradient sum + Adam on a stream of their own (pays off when there is an all-reduce to hide)
+        self.overlap_update = world_size > 1
+        self._update_stream = None
         self.fuse_output_layer = True   # last layer + loss + its gradients in two launches (nb_output_layer)
         if self.multi_label:
             assert int(cfg.classes) == int(cfg.layers[-1]), "CLASSES > 1 needs one output per class"
@@ -511,15 +514,31 @@ class GCN_GPU_NEIGHBOR_impl:
             loss, score = self._loss_and_score(pending_read[0])
             loss_sum += loss
             correct += score
+        self._join_update_stream()
         return correct, nodes, loss_sum, batches
 
     def Update(self):
         """Gradient SUM over ranks (MPI_SUM in the reference, comm/network.h:189-193) then Adam."""
+        if self.use_engine and self.overlap_update:
+            # on a stream of their own, the gradient sum and Adam overlap the next batch's layer-0 aggregation
+            if self._update_stream is None:
+                self._update_stream = torch.cuda.Stream(device=self.device)
+            us = self._update_stream
+            with torch.cuda.stream(us):
+                _lib.call("nb_gcn_wait_gradients", self._ensure_engine(), us.cuda_stream)
+                sum_gradients(self.P.grad, self.world_size)
+                _lib.call("nb_gcn_update", self._ensure_engine(), us.cuda_stream)
+            return
         sum_gradients(self.P.grad, self.world_size)
         if self.use_engine:
             _lib.call("nb_gcn_update", self._ensure_engine(), torch.cuda.current_stream().cuda_stream)
         else:
             self.P.learn_with_decay_Adam(torch.cuda.current_stream().cuda_stream)
+
+    def _join_update_stream(self):
+        """Later work on the current stream (reading the weights, evaluation) sees the last update."""
+        if self._update_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._update_stream)
 
     def UpdateZero(self):
         """A rank that ran out of batches still joins the collective with zeros
@@ -534,6 +553,7 @@ class GCN_GPU_NEIGHBOR_impl:
             self.forward_backward(sampler.sample_one(), train=True)
         self.Update()
         self.step_count += 1
+        self._join_update_stream()
 
     def _loss_and_score(self, host: torch.Tensor):
         """(loss, hits) of a batch, or with CLASSES > 1 (loss, F1 of the batch) as f1_score computes it
@@ -588,6 +608,7 @@ class GCN_GPU_NEIGHBOR_impl:
             correct += hits
             nodes += batch_nodes
             batches += 1
+        self._join_update_stream()
         sampler.restart()
         return self._epoch_accuracy(correct, nodes, batches), loss_epoch / max(batches, 1), batches
 

@@ -211,3 +211,22 @@ def test_multi_label_training_matches_oracle(cuda_device, pipelines):
         s2 = Sampler(g, ids, fanout, cfg.batch_size, t.ws, seed=cfg.seed, with_edge_weights=False)
         t.Forward(s2, train=True)
     np.testing.assert_array_equal(tk2.P.W.cpu().numpy().view(np.uint32), tk3.P.W.cpu().numpy().view(np.uint32))
+
+
+@pytest.mark.parametrize("pipelines", [1, 3], ids=["plain", "pipelined"])
+def test_update_on_its_own_stream_changes_nothing(cuda_device, pipelines):
+    """overlap_update runs the gradient sum and Adam on a second stream, ordered by events against the step that
+    produced the gradients and the step that next reads the weights: weights and loss curve stay bit-identical."""
+    outs = []
+    for overlap in (False, True):
+        edges, co, ri, feat, label, cfg, g, tk, ref = _setup(cuda_device, fanout=(10, 5), drop=0.5, cache_rate=0.3,
+                                                             pipelines=pipelines)
+        tk.overlap_update = overlap
+        smp = Sampler(g, np.arange(1100, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                      with_edge_weights=False)
+        rng = np.random.RandomState(5)
+        curve = [tk.Forward(smp, rng=rng, train=True) for _ in range(3)]
+        val = tk.Forward(Sampler(g, np.arange(2000, 2200, dtype=np.uint32), cfg.fanout, 200, tk.ws, seed=1), train=False)
+        outs.append((tk.P.W.cpu().numpy().copy(), curve, val))
+    np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
+    assert outs[0][1] == outs[1][1] and outs[0][2] == outs[1][2]
