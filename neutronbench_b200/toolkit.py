@@ -162,8 +162,10 @@ class GCN_GPU_NEIGHBOR_impl:
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
         self._stats_host = torch.zeros(4, dtype=torch.float32).pin_memory()
         self.multi_label = int(cfg.classes) > 1
-        # gradient sum + Adam on a stream of their own (pays off when there is an all-reduce to hide)
-        self.overlap_update = world_size > 1
+        # Gradient sum + Adam on a stream of their own.  Off by default: measured on 2 GPUs the NCCL kernel cannot
+        # get an SM while the layer-0 aggregation (one long-running CTA per SM) is resident, so the step got slower
+        # (0.42 against 0.34 ms); kept for callers whose aggregation leaves SMs free.
+        self.overlap_update = False
         self._update_stream = None
         self.fuse_output_layer = True   # last layer + loss + its gradients in two launches (nb_output_layer)
         if self.multi_label:
