@@ -189,6 +189,7 @@ class GCN_GPU_NEIGHBOR_impl:
         self._batches = None
         self._batch_ws = None
         self._sample_streams = None
+        self._compute_stream = None
 
     def _timed(self, name: str, nbytes: int, fn):
         """Runs fn(); with self.events set, brackets it with CUDA events on the current stream."""
@@ -475,6 +476,20 @@ class GCN_GPU_NEIGHBOR_impl:
             return correct, nodes, loss_sum, batches
         self._ensure_pipeline()
         slots = len(self._batches)
+        # The training half runs on a high-priority stream: when an SM frees up, its kernels are placed before the
+        # short sampling kernels of the batches drawn ahead, which have slack.
+        if self._compute_stream is None:
+            self._compute_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        outer = torch.cuda.current_stream()
+        self._compute_stream.wait_stream(outer)
+        with torch.cuda.stream(self._compute_stream):
+            result = self._run_pipelined_on_current_stream(sampler, max_batches, train, on_batch, read_back, slots)
+        outer.wait_stream(self._compute_stream)
+        return result
+
+    def _run_pipelined_on_current_stream(self, sampler, max_batches, train, on_batch, read_back, slots):
+        correct = nodes = batches = 0
+        loss_sum = 0.0
 
         def more_to_issue():
             return sampler.sample_not_finished() and (max_batches is None or issued < max_batches)
