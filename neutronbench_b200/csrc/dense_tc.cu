@@ -7,14 +7,14 @@
 // hi*hi + hi*lo + lo*hi into the same fp32 TMEM accumulator; the dropped lo*lo term is below 2^-22 of
 // the product.  mode 2 issues only hi*hi (plain TF32).
 //
-// Data path: raw fp32 tiles are copied global -> shared with cp.async straight into the canonical
-// no-swizzle K-major core-matrix layout (8 rows x 16 bytes per core matrix), four stages deep and two
-// chunks ahead of the math; a short pass rewrites each arrived tile as hi in place and lo next to it
-// (the split needs arithmetic, so the TMA unit cannot do it); one elected thread issues tcgen05.mma
-// from shared-memory descriptors; the accumulator lives in tensor memory and is read back with
-// tcgen05.ld (a warp reaches its own 32 TMEM lanes).  A tcgen05.commit mbarrier per stage tells when
-// the MMAs that read it have finished.
-#include <cstdlib>
+// This file: the kernel for operands that cannot have a TMA tensor map (pitch not a multiple of 16 bytes).  Raw
+// fp32 tiles are copied global -> shared with cp.async in 4/8/16-byte pieces straight into the layouts the tensor
+// core reads (see "Tile layouts" below), three to six stages deep; every staging thread then writes lo for exactly
+// the pieces it copied (the raw words stay in place and serve as hi), fences them towards the tensor core's proxy
+// and arrives on the stage's mbarrier; a separate warp issues tcgen05.mma from shared-memory descriptors; the
+// accumulator lives in tensor memory and is read back with tcgen05.ld (a warp reaches its own 32 TMEM lanes).  A
+// tcgen05.commit mbarrier per stage tells when the MMAs that read it have finished.  dense_tma.cu holds the TMA-fed
+// kernels, which issue the same MMAs in the same order.
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -158,8 +158,8 @@ struct CopyPlan {
     else if (vec == 2) issue_vec<2>(tile_s, p);
     else issue_vec<1>(tile_s, p);
   }
-  // hi/lo split of exactly the pieces this thread copied (after its own cp.async.wait_group): raw -> hi in
-  // place, lo = raw - hi into the same offsets of `lo`.  No other thread's data is touched, so the staging
+  // lo = raw - hi of exactly the pieces this thread copied (after its own cp.async.wait_group) into the same
+  // offsets of `lo`; the raw words stay in place as hi.  No other thread's data is touched, so the staging
   // threads need no barrier among themselves.  Zero-filled pieces are processed too (lo must be zero there).
   template <int VEC>
   __device__ __forceinline__ void split_vec(unsigned char *raw, unsigned char *lo, bool split) const {
@@ -173,16 +173,10 @@ struct CopyPlan {
         else x[0] = *reinterpret_cast<const float *>(raw + dst[i]);
 #pragma unroll
         for (int e = 0; e < VEC; e++) tc_split(x[e], h[e], l[e]);
-        if (VEC == 4) {
-          *reinterpret_cast<float4 *>(raw + dst[i]) = *reinterpret_cast<float4 *>(h);
-          if (split) *reinterpret_cast<float4 *>(lo + dst[i]) = *reinterpret_cast<float4 *>(l);
-        } else if (VEC == 2) {
-          *reinterpret_cast<float2 *>(raw + dst[i]) = *reinterpret_cast<float2 *>(h);
-          if (split) *reinterpret_cast<float2 *>(lo + dst[i]) = *reinterpret_cast<float2 *>(l);
-        } else {
-          *reinterpret_cast<float *>(raw + dst[i]) = h[0];
-          if (split) *reinterpret_cast<float *>(lo + dst[i]) = l[0];
-        }
+        if (!split) continue;   // the raw words serve as hi: the tensor core ignores their low 13 mantissa bits
+        if (VEC == 4) *reinterpret_cast<float4 *>(lo + dst[i]) = *reinterpret_cast<float4 *>(l);
+        else if (VEC == 2) *reinterpret_cast<float2 *>(lo + dst[i]) = *reinterpret_cast<float2 *>(l);
+        else *reinterpret_cast<float *>(lo + dst[i]) = l[0];
       }
     }
   }
@@ -199,7 +193,6 @@ struct CopyPlan {
       const uint32_t off = tile_off<MN>(r, k);
       float h, l;
       tc_split(raw[off], h, l);
-      raw[off] = h;
       if (split) lo[off] = l;
     }
   }
