@@ -59,6 +59,7 @@ def parse_args():
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
     ap.add_argument("--pipelines", type=int, default=3,
                     help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain loop")
+    ap.add_argument("--pdl", type=int, default=None, help="1 / 0: programmatic dependent launch for the training half's kernels")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
 
@@ -270,6 +271,8 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, Sampler, _lib
+    if args.pdl is not None:
+        _lib.load().nb_set_pdl(int(args.pdl))
     sh, cfg, graph, datum, train_ids, feat_dev = build_workload(args.workload, args, device)
     batches_per_epoch = (len(train_ids) + cfg.batch_size - 1) // cfg.batch_size
 

@@ -264,6 +264,10 @@ int nb_softmax_nll_static(const float *d_logits, const int64_t *d_label, int64_t
  * nb_gemm + nb_label_gather + nb_softmax_nll + two nb_gemm up to summation order.  nb_output_layer_supported tells
  * whether a layer fits the fused form (C <= 64 and W in about 90 KB of shared memory). */
 int nb_output_layer_supported(uint32_t H, uint32_t C);
+/* Programmatic dependent launch for the kernels of the training half of a step (aggregation, dense layers, output
+ * layer, Adam): a kernel may be scheduled while its predecessor on the stream drains and waits for it at its first
+ * instruction.  On by default; same results either way.  Returns the previous setting. */
+int nb_set_pdl(int enabled);
 /* nb_gcn_step / nb_gcn_compute use nb_output_layer for the last layer where it applies; 0 switches that off
  * (the layer then runs as separate calls).  Returns the previous setting. */
 int nb_set_fused_output_layer(int enabled);

@@ -93,6 +93,7 @@ SIGNATURES = {
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_gcn_read_timing_by_class": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_set_fused_output_layer": (C.c_int, [C.c_int]),
+    "nb_set_pdl": (C.c_int, [C.c_int]),
     "nb_output_layer_supported": (C.c_int, [C.c_uint32, C.c_uint32]),
     "nb_output_layer": (C.c_int, [ptr, f32p, f32p, i64p, u32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, f32p, f32p,
                                   f32p, ptr]),

@@ -172,3 +172,37 @@ int exclusive_scan_u32(nb_ws *ws, const uint32_t *d_in, uint32_t *d_out, uint64_
 int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, uint64_t n,
                               bool write_total, cudaStream_t stream);
 }  // namespace nb
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch (PDL) for the kernels of the training half of a step, which follow one another
+// on one stream: a dependent kernel may be scheduled while its predecessor drains, and waits at
+// griddepcontrol.wait — its first statement here, so nothing of the predecessor's output is read and none of its
+// inputs overwritten before the predecessor has completed and flushed.  Every such kernel lets its own dependents
+// go right afterwards.  Kernels launched without the attribute execute the two instructions as no-ops.
+// ---------------------------------------------------------------------------------------------
+namespace nb {
+extern int g_use_pdl;   // nb_set_pdl
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+}  // namespace nb

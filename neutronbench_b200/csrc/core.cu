@@ -8,6 +8,7 @@ namespace nb {
 
 static thread_local char g_err[512] = "";
 unsigned long long g_launches = 0;
+int g_use_pdl = 1;
 
 void set_error(const char *fmt, ...) {
   va_list ap;

@@ -89,6 +89,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *_
 // ------------------------------------------------------------------------------------ ReLU + dropout
 __global__ void relu_dropout_kernel(float *z, int64_t n, float p, float scale, uint32_t seed_lo, uint32_t seed_hi,
                                     uint32_t layer, uint32_t step) {
+  pdl_enter();
   const int64_t quads = (n + 3) >> 2;
   for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (int64_t)gridDim.x * blockDim.x) {
     uint32_t r[4] = {0, 0, 0, 0};
@@ -234,6 +235,7 @@ __global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
     const float *__restrict__ y, const float *__restrict__ w, const int64_t *__restrict__ label_table,
     const uint32_t *__restrict__ dst, uint32_t B, uint32_t H, uint32_t C, uint32_t CP, int train, float *dy,
     float *dw_part, float *row_loss, float *row_hit) {
+  pdl_enter();
   extern __shared__ float out_smem[];
   float *ws = out_smem;                       // [H][CP]
   float *ys = ws + (size_t)H * CP;            // [kOutRows][H]
@@ -308,6 +310,7 @@ __global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
 __global__ void __launch_bounds__(256) output_layer_reduce_kernel(const float *__restrict__ dw_part, uint32_t parts,
                                                                   uint32_t hc, float *dw, const float *__restrict__ row_loss,
                                                                   const float *__restrict__ row_hit, uint32_t B, float *stats) {
+  pdl_enter();
   if (blockIdx.x + 1 < gridDim.x) {
     if (dw == nullptr) return;
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
@@ -332,6 +335,7 @@ __global__ void __launch_bounds__(256) output_layer_reduce_kernel(const float *_
 // ------------------------------------------------------------------------------------ Adam
 __global__ void adam_kernel(float *W, const float *__restrict__ grad, float *M, float *V, int64_t n, float alpha,
                             float b1, float b2, float eps, float wd, float c1, float c2) {
+  pdl_enter();
   const float one_m_b1 = 1.0f - b1, one_m_b2 = 1.0f - b2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float w = W[i];
@@ -427,8 +431,8 @@ NB_API int nb_relu_dropout(float *d_z, int64_t n, float p, uint64_t seed, uint32
   NB_REQUIRE(d_z != nullptr && n > 0, "nb_relu_dropout: null pointer");
   NB_REQUIRE(p >= 0.0f && p < 1.0f, "nb_relu_dropout: drop rate must be in [0,1)");
   const float scale = p > 0.0f ? 1.0f / (1.0f - p) : 1.0f;
-  relu_dropout_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, as_stream(stream)>>>(d_z, n, p, scale, (uint32_t)seed,
-                                                                                (uint32_t)(seed >> 32), layer, step);
+  NB_CUDA(launch_chained(relu_dropout_kernel, dim3(grid_for((n + 3) / 4, 256)), dim3(256), 0, as_stream(stream), d_z, n, p, scale, (uint32_t)seed,
+                         (uint32_t)(seed >> 32), layer, step));
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -495,22 +499,28 @@ NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const 
     NB_CUDA(cudaFuncSetAttribute(output_layer_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     configured = true;
   }
-  output_layer_rows_kernel<<<ctas, kOutRows * 32, smem, stream>>>(d_y, d_w, d_label, d_dst, B, H, C, C | 1u, train ? 1 : 0,
-                                                                   train ? d_dy : nullptr, part, row_loss, row_hit);
+  NB_CUDA(launch_chained(output_layer_rows_kernel, dim3(ctas), dim3(kOutRows * 32), smem, stream, d_y, d_w, d_label, d_dst, B,
+                         H, C, C | 1u, train ? 1 : 0, train ? d_dy : (float *)nullptr, part, row_loss, row_hit));
   NB_LAUNCH_CHECK();
   const unsigned blocks = (train ? (hc + 255) / 256 : 0) + 1;
-  output_layer_reduce_kernel<<<blocks, 256, 0, stream>>>(part, ctas, hc, train ? d_dw : nullptr, row_loss, row_hit, B,
-                                                         d_stats);
+  NB_CUDA(launch_chained(output_layer_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float *)part, ctas, hc,
+                         train ? d_dw : (float *)nullptr, (const float *)row_loss, (const float *)row_hit, B, d_stats));
   NB_LAUNCH_CHECK();
   return 0;
+}
+
+NB_API int nb_set_pdl(int enabled) {
+  const int old = nb::g_use_pdl;
+  nb::g_use_pdl = enabled != 0;
+  return old;
 }
 
 NB_API int nb_adam(float *d_W, const float *d_grad, float *d_M, float *d_V, int64_t n, float alpha, float b1,
                    float b2, float eps, float wd, float b1_t, float b2_t, void *stream) {
   if (n == 0) return 0;
   NB_REQUIRE(d_W && d_grad && d_M && d_V && n > 0, "nb_adam: null pointer");
-  adam_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(d_W, d_grad, d_M, d_V, n, alpha, b1, b2, eps, wd,
-                                                               1.0f - b1_t, 1.0f - b2_t);
+  NB_CUDA(launch_chained(adam_kernel, dim3(grid_for(n, 256)), dim3(256), 0, as_stream(stream), d_W, d_grad, d_M, d_V, n, alpha,
+                         b1, b2, eps, wd, 1.0f - b1_t, 1.0f - b2_t));
   NB_LAUNCH_CHECK();
   return 0;
 }

@@ -458,6 +458,7 @@ static int launch_tc_s(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
 
 __global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ c, int64_t mn,
                                         int splits) {
+  pdl_enter();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (int64_t)gridDim.x * blockDim.x) {
     float s = partial[i];
     for (int z = 1; z < splits; z++) s += partial[(int64_t)z * mn + i];
@@ -560,7 +561,8 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b,
   }
   if (st != 0) return st;
   if (splits > 1) {
-    tc_splitk_reduce_kernel<<<grid_for(M * N, 256), 256, 0, stream>>>(partial, d_c, M * N, splits);
+    NB_CUDA(launch_chained(tc_splitk_reduce_kernel, dim3(grid_for(M * N, 256)), dim3(256), 0, stream, partial, d_c, M * N,
+                           splits));
     NB_LAUNCH_CHECK();
   }
   return 0;

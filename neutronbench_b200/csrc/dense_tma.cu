@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_b,
                                                                   const TmaGemmArgs g) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
+  pdl_enter();
   constexpr int S = kTmaStages;
   constexpr uint32_t A_BYTES = kBM * kTmaBK * 4, B_BYTES = BN * kTmaBK * 4;   // 16 KB, and 4 / 8 / 16 KB
   constexpr uint32_t STAGE = 2 * (A_BYTES + B_BYTES);                        // raw A | raw B | lo A | lo B
@@ -245,6 +246,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_rows_kernel(const __g
                                                                        const __grid_constant__ CUtensorMap map_w,
                                                                        const TmaRowsArgs g) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
+  pdl_enter();
   constexpr int S = kTmaStages;
   constexpr uint32_t W_BYTES = kBM * kTmaBK * 4;                 // W^T tile: 128 outputs x 32 k
   constexpr uint32_t Y_MAX = kRowsMax * kTmaBK * 4;              // Y tile: up to 160 rows x 32 k
@@ -428,7 +430,7 @@ static int launch_tma(const CUtensorMap &ma, const CUtensorMap &mb, const TmaGem
     NB_CUDA(cudaFuncSetAttribute(gemm_tma_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  gemm_tma_kernel<BN, A_MN, B_MN><<<grid, kTmaThreads, smem, stream>>>(ma, mb, g);
+  NB_CUDA(launch_chained(gemm_tma_kernel<BN, A_MN, B_MN>, grid, dim3(kTmaThreads), smem, stream, ma, mb, g));
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -487,7 +489,7 @@ int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_
     configured = true;
   }
   const unsigned grid = (unsigned)((M + rows - 1) / rows);
-  gemm_tma_rows_kernel<<<grid, kTmaThreads, smem, stream>>>(my, mw, g);
+  NB_CUDA(launch_chained(gemm_tma_rows_kernel, dim3(grid), dim3(kTmaThreads), smem, stream, my, mw, g));
   NB_LAUNCH_CHECK();
   return 0;
 }

@@ -84,6 +84,7 @@ struct SpmmArgs {
 // paid once per chunk.  Wide rows (F = 602: VEC 2, CT 5 -> 2 chunks) need it most.
 template <int VEC, int CT, int U, int MODE, bool MASK>
 __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmArgs a) {
+  pdl_enter();
   const unsigned lane = threadIdx.x & 31;
   const uint64_t warp_global = (uint64_t)blockIdx.x * kSpmmWarps + (threadIdx.x >> 5);
   const uint32_t r = (uint32_t)(warp_global / a.tiles);   // a.tiles = chunks per row
@@ -189,7 +190,7 @@ static int launch_one(SpmmArgs a, cudaStream_t stream) {
   const uint64_t warps = (uint64_t)a.n * a.tiles;
   const uint64_t blocks = (warps + kSpmmWarps - 1) / kSpmmWarps;
   if (blocks > 0x7fffffffull) return fail(NB_ERR_INVALID, "spmm: too many rows for one launch");
-  spmm_rows_kernel<VEC, CT, U, MODE, MASK><<<(unsigned)blocks, kSpmmWarps * 32, 0, stream>>>(a);
+  NB_CUDA(launch_chained(spmm_rows_kernel<VEC, CT, U, MODE, MASK>, dim3((unsigned)blocks), dim3(kSpmmWarps * 32), 0, stream, a));
   NB_LAUNCH_CHECK();
   return 0;
 }
@@ -352,6 +353,9 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
       t.norm_row = d_dst_norm; t.norm_idx = d_src_norm;
       t.n = v; t.F = F; t.act = nullptr; t.act_scale = 1.0f; t.src_rows_hint = s;
       t.out_vec = pick_vec(F, {}, {d_y});
+      // rows padded to 16 bytes take whole float4 stores even when F is not a multiple of 4 (the tail lands in the
+      // padding)
+      if (y_ld % 4 == 0 && y_ld >= (size_t)(F + 3) / 4 * 4 && aligned_to(d_y, 16)) t.out_vec = 4;
       return launch_spmm_tma(t, as_stream(stream));
     }
     if (g_staged_spmm && ws != nullptr && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {

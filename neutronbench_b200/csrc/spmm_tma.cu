@@ -307,6 +307,7 @@ constexpr int kRingWarps = 16;
 template <int TILES, bool MASK>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const TmaSpmmArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  pdl_enter();
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t R = a.seg;                                   // slots per warp
   unsigned char *my_smem = smem_raw + (size_t)warp * R * a.slot_bytes;
@@ -395,15 +396,17 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
             if constexpr (MASK) r[c] = __ldg(act + col + c) > 0.0f ? __fmul_rn(r[c], a.act_scale) : 0.0f;
           }
         }
+        // streaming stores: the output is consumed by a later kernel that streams it once; keeping it out of the
+        // way leaves L2 to the source rows, which are re-read by other destinations
         if (a.out_vec == 4) {
-          *reinterpret_cast<float4 *>(out + col) = make_float4(r[0], r[1], r[2], r[3]);
+          __stcs(reinterpret_cast<float4 *>(out + col), make_float4(r[0], r[1], r[2], r[3]));
         } else if (a.out_vec == 2) {
-          if (col + 1 < a.F) *reinterpret_cast<float2 *>(out + col) = make_float2(r[0], r[1]);
-          if (col + 3 < a.F) *reinterpret_cast<float2 *>(out + col + 2) = make_float2(r[2], r[3]);
+          if (col + 1 < a.F) __stcs(reinterpret_cast<float2 *>(out + col), make_float2(r[0], r[1]));
+          if (col + 3 < a.F) __stcs(reinterpret_cast<float2 *>(out + col + 2), make_float2(r[2], r[3]));
         } else {
 #pragma unroll
           for (int c = 0; c < 4; c++)
-            if (col + c < a.F) out[col + c] = r[c];
+            if (col + c < a.F) __stcs(out + col + c, r[c]);
         }
       }
       acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
@@ -509,7 +512,7 @@ static int launch_ring_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t str
   // enough CTAs that every warp gets at least a few rows, at most one CTA per SM
   const unsigned want = (a.n + kRingWarps * 4 - 1) / (kRingWarps * 4);
   const unsigned grid = want < (unsigned)kNumSMs ? (want ? want : 1) : (unsigned)kNumSMs;
-  spmm_ring_kernel<TILES, MASK><<<grid, kRingWarps * 32, smem, stream>>>(a);
+  NB_CUDA(launch_chained(spmm_ring_kernel<TILES, MASK>, dim3(grid), dim3(kRingWarps * 32), smem, stream, a));
   NB_LAUNCH_CHECK();
   return 0;
 }

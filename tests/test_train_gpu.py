@@ -230,3 +230,23 @@ def test_update_on_its_own_stream_changes_nothing(cuda_device, pipelines):
         outs.append((tk.P.W.cpu().numpy().copy(), curve, val))
     np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
     assert outs[0][1] == outs[1][1] and outs[0][2] == outs[1][2]
+
+
+def test_programmatic_dependent_launch_changes_nothing(cuda_device):
+    """nb_set_pdl(1) lets each kernel of the training half be scheduled while its predecessor drains; every kernel
+    waits for the predecessor before touching memory, so weights and losses stay bit-identical."""
+    from neutronbench_b200 import _lib
+    outs = []
+    try:
+        for pdl in (0, 1):
+            _lib.load().nb_set_pdl(pdl)
+            edges, co, ri, feat, label, cfg, g, tk, ref = _setup(cuda_device, V=6000, E=90000, F=300, hidden=128, classes=41,
+                                                                 fanout=(10, 5), batch=512, drop=0.5, cache_rate=1.0, pipelines=2)
+            smp = Sampler(g, np.arange(2000, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                          with_edge_weights=False)
+            curve = [tk.Forward(smp, train=True) for _ in range(2)]
+            outs.append((tk.P.W.cpu().numpy().copy(), curve))
+    finally:
+        _lib.load().nb_set_pdl(1)   # the default
+    np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
+    assert outs[0][1] == outs[1][1]
