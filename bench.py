@@ -48,7 +48,7 @@ NCU_TRAFFIC_BYTES = {("reddit", True, True): 324123392}
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=0, help="timed steps per rank (0 = one epoch of the workload)")
+    ap.add_argument("--steps", type=int, default=0, help="timed steps per rank (0 = eight epochs of the workload)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -313,7 +313,9 @@ def main():
     ids = train_ids.copy()
     rng.shuffle(ids)
     shard = ids[rank::world] if world > 1 else ids
-    K = args.steps if args.steps > 0 else (len(shard) + cfg.batch_size - 1) // cfg.batch_size
+    # default: eight epochs of this rank's shard, so that the timed region lasts long enough (a few tenths of a second)
+    # for the clock sampler to see it
+    K = args.steps if args.steps > 0 else 8 * ((len(shard) + cfg.batch_size - 1) // cfg.batch_size)
     W = max(args.warmup, 3)
     need = (W + K) * cfg.batch_size
     reps = (need + len(shard) - 1) // len(shard)
