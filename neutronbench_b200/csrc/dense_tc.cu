@@ -472,9 +472,7 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   const int64_t ctas = (int64_t)grid.x * grid.y * grid.z;
   int stages = ctas <= kNumSMs ? 6 : 3;
-  if (getenv("NB_TC_STAGES")) stages = atoi(getenv("NB_TC_STAGES"));
   int stagers = stages >= 4 ? 512 : 256;
-  if (getenv("NB_TC_STAGERS")) stagers = atoi(getenv("NB_TC_STAGERS"));
   if (stages >= 6) {
     if (stagers == 512) return launch_tc_s<BN, A_MN, B_MN, 6, 512>(g, grid, stream);
     return launch_tc_s<BN, A_MN, B_MN, 6, 256>(g, grid, stream);
@@ -499,7 +497,9 @@ static int vec_of(const float *p, int64_t ld) {
   return 1;
 }
 
-// Tensor-core GEMM front end; same contract as the CUDA-core path in dense.cu.
+// Tensor-core GEMM front end; same contract as the CUDA-core path in dense.cu.  Two environment switches exist for
+// tests and comparisons: NB_TC_NO_TMA (set: always the cp.async kernel) and NB_TC_NO_ROWS_FORM (set: Y W in plain
+// 128-row tiles); results are bit-identical either way.
 int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
                      int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream) {
   TcGemmArgs g{};
@@ -527,7 +527,6 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b,
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
   }
-  if (getenv("NB_TC_SPLITS")) splits = atoi(getenv("NB_TC_SPLITS"));
   g.k_per_split = ((K + splits - 1) / splits + 31) / 32 * 32;
   splits = (int)((K + g.k_per_split - 1) / g.k_per_split);
   // TMA tensor loads need 16-byte aligned bases and pitches, and boxes that fit inside the tensor

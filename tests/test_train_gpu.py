@@ -250,3 +250,4 @@ def test_programmatic_dependent_launch_changes_nothing(cuda_device):
         _lib.load().nb_set_pdl(1)   # the default
     np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
     assert outs[0][1] == outs[1][1]
+
