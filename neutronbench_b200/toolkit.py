@@ -281,11 +281,18 @@ class GCN_GPU_NEIGHBOR_impl:
             raise ValueError(f"cache_type {c.cache_type!r} is not one of none | rate | random | gpu_memory")
 
     # ------------------------------------------------------------------ one step
+    def _rows(self, shape) -> torch.Tensor:
+        """Uninitialised fp32 buffer of at least [rows x cols] on the device, handed to the library by address only.
+        A block without edges or vertices gives zero rows; one row is allocated then, so that the address is a valid
+        (never dereferenced) non-null pointer — torch reports a null address for an empty tensor."""
+        rows, cols = shape
+        return torch.empty((max(int(rows), 1), int(cols)), dtype=torch.float32, device=self.device)
+
     def _aggregate0(self, ssg: SampledSubgraph, stream: int) -> torch.Tensor:
         blk = ssg.sampled_sgs[0]
         F = self.cfg.layers[0]
         feat = self.datum.local_feature
-        Y = torch.empty((blk.v_size, F), dtype=torch.float32, device=self.device)
+        Y = self._rows((blk.v_size, F))
         cache, hm = self.dev_cache_feature, self.dev_cache_node_hashmap
         if self.cfg.fuse_gather:
             self._timed("fwd0_gather_fused", self.agg_bytes_fwd(blk, F, True, hm is not None), lambda: _lib.call(
@@ -293,7 +300,7 @@ class GCN_GPU_NEIGHBOR_impl:
                 cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), ptr(Y), ptr(blk.row_indices),
                 ptr(blk.column_offset), ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, blk.src_size, blk.e_size, F, stream))
         else:
-            X0 = torch.empty((blk.src_size, F), dtype=torch.float32, device=self.device)
+            X0 = self._rows((blk.src_size, F))
             _lib.call("nb_feature_gather", ptr(X0), ptr(feat), feat.stride(0), None, 0, 0, ptr(cache),
                       cache.stride(0) if cache is not None else 0, ptr(hm), ptr(blk.source), blk.src_size, F, stream)
             self._timed("fwd0", self.agg_bytes_fwd(blk, F), lambda: _lib.call(
@@ -318,18 +325,18 @@ class GCN_GPU_NEIGHBOR_impl:
             if l == 0:
                 y = self._aggregate0(ssg, stream)
             else:
-                y = torch.empty((blk.v_size, c.layers[l]), dtype=torch.float32, device=self.device)
+                y = self._rows((blk.v_size, c.layers[l]))
                 self._timed(f"fwd{l}", self.agg_bytes_fwd(blk, c.layers[l]), lambda: _lib.call(
                     "nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(blk.row_indices), ptr(blk.column_offset),
                     ptr(blk.src_norm), ptr(blk.dst_norm), blk.v_size, c.layers[l], stream))
             Y.append(y)
             if l == L - 1 and fused_out:
                 break
-            z = torch.empty((blk.v_size, c.layers[l + 1]), dtype=torch.float32, device=self.device)
+            z = self._rows((blk.v_size, c.layers[l + 1]))
             _lib.call("nb_gemm", wsh, ptr(y), ptr(self.P.w(l)), ptr(z), blk.v_size, c.layers[l + 1], c.layers[l], 0,
                       0, stream)
             if l < L - 1:
-                _lib.call("nb_relu_dropout", ptr(z), z.numel(), p, c.seed, l, self.step_count, stream)
+                _lib.call("nb_relu_dropout", ptr(z), blk.v_size * c.layers[l + 1], p, c.seed, l, self.step_count, stream)
             X.append(z)
         last = ssg.sampled_sgs[L - 1]
         B, C = last.v_size, c.layers[L]
@@ -364,9 +371,9 @@ class GCN_GPU_NEIGHBOR_impl:
             if from_fused:
                 dY = dY_out
             else:
-                dY = torch.empty((blk.v_size, Fi), dtype=torch.float32, device=self.device)
+                dY = self._rows((blk.v_size, Fi))
                 _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), blk.v_size, Fi, Fo, 0, 1, stream)
-            dX = torch.empty((blk.src_size, Fi), dtype=torch.float32, device=self.device)
+            dX = self._rows((blk.src_size, Fi))
             self._timed(f"bwd{l}", self.agg_bytes_bwd(blk, Fi), lambda: _lib.call(
                 "nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(blk.row_offset), ptr(blk.column_indices),
                 ptr(blk.src_norm), ptr(blk.dst_norm), ptr(X[l]), scale, blk.src_size, Fi, stream))

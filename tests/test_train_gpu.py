@@ -251,3 +251,31 @@ def test_programmatic_dependent_launch_changes_nothing(cuda_device):
     np.testing.assert_array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
     assert outs[0][1] == outs[1][1]
 
+
+
+def test_native_step_on_seeds_without_neighbours(cuda_device):
+    """Seeds with no in-edges give blocks without edges (and an input-side block without vertices): the step
+    still runs, the loss is log(C) under zero aggregates, and nothing is read out of bounds."""
+    V, F, C = 500, 12, 4
+    rng = np.random.RandomState(0)
+    src = rng.randint(0, 250, 3000)
+    dst = rng.randint(0, 250, 3000)                       # vertices 250.. have no edges at all
+    edges = np.stack([src, dst], axis=1).astype(np.int32)
+    feat = rng.randn(V, F).astype(np.float32)
+    label = rng.randint(0, C, size=V).astype(np.int64)
+    cfg = GCNConfig(layers=[F, 8, C], fanout=(4, 3), batch_size=64, drop_rate=0.0, seed=3)
+    g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(32 << 20))
+    datum = GNNDatum(torch.from_numpy(feat).to(cuda_device), torch.from_numpy(label).to(cuda_device), np.zeros(V, np.int32))
+    for use_engine in (True, False):
+        tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg, use_engine=use_engine)
+        w0 = tk.P.W.clone()
+        smp = Sampler(g, np.arange(300, 428, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                      with_edge_weights=False)
+        acc, loss, batches = tk.Forward(smp, train=True)
+        assert batches == 2 and abs(loss - np.log(C)) < 1e-5 and 0.0 <= acc <= 1.0
+        assert torch.isfinite(tk.P.W).all()
+        # mixed batch: some seeds with neighbours, some without
+        smp2 = Sampler(g, np.arange(200, 328, dtype=np.uint32), cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed,
+                       with_edge_weights=False)
+        acc2, loss2, _ = tk.Forward(smp2, train=True)
+        assert np.isfinite(loss2) and torch.isfinite(tk.P.W).all() and not torch.equal(w0, tk.P.W)
