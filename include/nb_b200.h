@@ -120,7 +120,7 @@ int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, c
 int nb_set_staged_spmm(int enabled);
 /* The staged gather-fused aggregation cuts wide rows into column panels whose distinct source data
  * (s rows x panel width) stays below this many bytes, so that reuse of a source row hits L2
- * (0 = never cut).  Returns the previous value; default 48 MiB. */
+ * (0 = never cut, the default).  Returns the previous value. */
 uint64_t nb_set_l2_panel_bytes(uint64_t bytes);
 int nb_device_error_flags(uint32_t *flags);
 

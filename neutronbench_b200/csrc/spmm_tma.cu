@@ -317,11 +317,12 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   fence_proxy_async();
   __syncwarp();
 
-  // rows of this warp: an equal share of the rows, contiguous
+  // rows of this warp: a contiguous share; shares differ by at most one row and the longer ones are spread over all
+  // CTAs, so that every SM has the same amount of work
   const uint32_t total_warps = gridDim.x * kRingWarps;
   const uint32_t gw = blockIdx.x * kRingWarps + warp;
-  const uint32_t per = (a.n + total_warps - 1) / total_warps;
-  const uint32_t r_begin = min(a.n, gw * per), r_end = min(a.n, r_begin + per);
+  const uint32_t r_begin = (uint32_t)((uint64_t)gw * a.n / total_warps);
+  const uint32_t r_end = (uint32_t)((uint64_t)(gw + 1) * a.n / total_warps);
   if (r_begin >= r_end) return;
   const uint32_t j0 = __ldg(a.offs + r_begin), j1 = __ldg(a.offs + r_end);
 
@@ -375,12 +376,13 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   // row bookkeeping: lane holds the end offset of row rw_base + lane
   uint32_t rw_base = r_begin;
   uint32_t rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
+  float rnorm = (!a.w && rw_base + lane < r_end) ? __ldg(a.norm_row + rw_base + lane) : 0.0f;   // same for the row's factor
   uint32_t row = r_begin;
   uint32_t row_end = __shfl_sync(0xffffffffu, rend, 0);
   float acc[TILES][4];
 #pragma unroll
   for (int t = 0; t < TILES; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
-  float nrow = a.w ? 0.0f : __ldg(a.norm_row + row);
+  float nrow = __shfl_sync(0xffffffffu, rnorm, 0);
 
   auto finish_row = [&]() {      // write the accumulated row, move to the next one
     float *out = a.y + (size_t)row * a.y_ld;
@@ -416,9 +418,10 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       if (row - rw_base >= 32) {
         rw_base = row;
         rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
+        rnorm = (!a.w && rw_base + lane < r_end) ? __ldg(a.norm_row + rw_base + lane) : 0.0f;
       }
       row_end = __shfl_sync(0xffffffffu, rend, row - rw_base);
-      if (!a.w) nrow = __ldg(a.norm_row + row);
+      nrow = __shfl_sync(0xffffffffu, rnorm, row - rw_base);
     }
   };
 

@@ -254,7 +254,9 @@ class GCN_GPU_NEIGHBOR_impl:
             raise ValueError(f"cache_policy {policy!r} is not one of degree | sample | random")
         self.dev_cache_node_hashmap = torch.from_numpy(hashmap.view(np.int32)).to(self.device)
         F = self.cfg.layers[0]
-        ld = (F + 3) // 4 * 4  # private layout: rows padded to 16 bytes so that 128-bit loads apply
+        # private layout: rows padded to 16 bytes so that 128-bit loads and bulk copies apply; wide rows (the ones the
+        # aggregation stages through shared memory) start on a 128-byte line, which saves a partly used line per row read
+        ld = (F + 31) // 32 * 32 if F >= 256 else (F + 3) // 4 * 4
         self.dev_cache_feature = torch.zeros((node_nums, ld), dtype=torch.float32, device=self.device)
         feat = self.datum.local_feature
         _lib.call("nb_cache_fill", ptr(self.dev_cache_feature), ld, ptr(feat), feat.stride(0),
