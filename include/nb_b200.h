@@ -111,9 +111,10 @@ int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, c
  * and F <= 1024, the aggregation entry points above stage source rows through shared memory with
  * non-multicast TMA bulk copies; otherwise they use direct vector loads.  Both give identical bits.
  * By default only rows of 256 floats or more are staged (narrow rows are faster with direct loads).
- * nb_set_staged_spmm(0) forces the direct-load path, 1 is the default (per-edge ring of row slots),
- * 2 stages every width the alignment rules allow, 3 / 4 are 1 / 2 with the two-stage segment kernel
- * instead of the ring; returns the previous on/off setting.
+ * nb_set_staged_spmm(0) forces the direct-load path, 1 is the default (per-warp ring of row slots,
+ * one copy barrier per pair of rows), 2 stages every width the alignment rules allow, 3 / 4 are 1 / 2
+ * with the two-stage segment kernel instead of the ring, 5 is 1 with a barrier per row; returns the
+ * previous on/off setting.
  * nb_device_error_flags reads (and so synchronises with) the device-side error word: bit 0 is set
  * when a bounded wait on a copy barrier gave up, bit 1 when a wait on a tensor-core completion
  * barrier gave up. */

@@ -112,7 +112,7 @@ struct TmaSpmmArgs {
   float act_scale;
   uint32_t n, F;
   uint32_t src_rows_hint;  // number of distinct rows the references can name (0 = unknown): sizes the panels
-  uint32_t slot_bytes, copy_bytes, seg, fpad, panels, panel_floats;   // filled by launch_spmm_tma
+  uint32_t slot_bytes, copy_bytes, seg, grp_shift, fpad, panels, panel_floats;   // filled by launch_spmm_tma
   int l2_prefetch;
   int out_vec;             // widest vector (floats) usable for y and act rows: 4, 2 or 1
 };
@@ -150,6 +150,7 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
                                  uint32_t F, void *stream);
 extern int g_gemm_mode;    // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
 extern uint64_t g_l2_panel_bytes;
+extern uint32_t g_ring_group_shift;
 extern int g_staged_min_width;
 extern int g_spmm_ring;
 extern int g_staged_spmm;  // 1: use the TMA-staged aggregation where its alignment rules hold

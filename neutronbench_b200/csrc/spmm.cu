@@ -238,6 +238,7 @@ NB_API int nb_set_staged_spmm(int enabled) {
   g_staged_spmm = enabled ? 1 : 0;
   g_staged_min_width = (enabled == 2 || enabled == 4) ? 1 : 256;   // 2, 4: stage every allowed width
   g_spmm_ring = (enabled == 3 || enabled == 4) ? 0 : 1;            // 3, 4: two-stage segment kernel, no ring
+  g_ring_group_shift = enabled == 5 ? 0 : 1;                       // 5: ring with one barrier per row, not per pair
   return old;
 }
 

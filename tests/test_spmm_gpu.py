@@ -209,3 +209,52 @@ def test_staged_and_direct_paths_give_identical_bits(cuda_device, F):
     flags = ctypes.c_uint32(7)
     _lib.call("nb_device_error_flags", ctypes.byref(flags))
     assert flags.value == 0
+
+
+@pytest.mark.parametrize("mode", [1, 5])
+@pytest.mark.parametrize("F", [256, 602, 1024])
+def test_ring_groupings_give_identical_bits(cuda_device, ws, F, mode):
+    """The ring kernel waits once per pair of rows (mode 1, the default, where four row slots fit: F = 1024 has three
+    and keeps a barrier per row) or once per row (mode 5).  Same arithmetic, same order: plain, masked backward and
+    gather-fused forms (cache hits and misses) keep their bits."""
+    V = 3000
+    blk = _block(V=V, fanouts=(25, 10))[0]
+    rng = np.random.RandomState(F + mode)
+    d = cuda_device
+    st = torch.cuda.current_stream().cuda_stream
+    lib = _lib.load()
+    feat = rng.randn(V, F).astype(np.float32)
+    hm, ids = oracle.cache_by_degree(rng.randint(1, 50, size=V).astype(np.uint32), V // 3)
+    ld = (F + 31) // 32 * 32
+    cache = np.zeros((len(ids), ld), dtype=np.float32)
+    cache[:, :F] = feat[ids]
+    x0 = oracle.feature_gather(feat, blk.source)
+    ref_g = oracle.spmm_fwd(x0, blk.edge_weight_forward, blk.row_indices, blk.column_offset)
+    gy = rng.randn(blk.v_size, F).astype(np.float32)
+    act = np.maximum(rng.randn(blk.src_size, F), 0).astype(np.float32)
+    ref_b = oracle.spmm_bwd(gy, blk.edge_weight_backward, blk.row_offset, blk.column_indices, act=act, scale=2.0)
+    ri, co = dev_i32(blk.row_indices, d), dev_i32(blk.column_offset, d)
+    ro, ci = dev_i32(blk.row_offset, d), dev_i32(blk.column_indices, d)
+    sn, dn = dev_f32(blk.src_norm, d), dev_f32(blk.dst_norm, d)
+    dfeat, dcache, dhm, dsrc = dev_f32(feat, d), dev_f32(cache, d), dev_i32(hm, d), dev_i32(blk.source, d)
+    old = lib.nb_set_staged_spmm(mode)
+    try:
+        dy = torch.full((blk.v_size, F), float("nan"), device=d)
+        _lib.call("nb_spmm_csc_fwd_gather_fused", ws.handle, ptr(dfeat), F, ptr(dcache), ld, ptr(dhm), ptr(dsrc), ptr(dy),
+                  ptr(ri), ptr(co), ptr(sn), ptr(dn), blk.v_size, blk.src_size, blk.e_size, F, st)
+        dy2 = torch.full((blk.v_size, F), float("nan"), device=d)
+        _lib.call("nb_spmm_csc_fwd_fused", ptr(dev_f32(x0, d)), ptr(dy2), ptr(ri), ptr(co), ptr(sn), ptr(dn),
+                  blk.v_size, F, st)
+        dgx = torch.full((blk.src_size, F), float("nan"), device=d)
+        _lib.call("nb_spmm_csr_bwd_fused", ptr(dev_f32(gy, d)), ptr(dgx), ptr(ro), ptr(ci), ptr(sn), ptr(dn),
+                  ptr(dev_f32(act, d)), 2.0, blk.src_size, F, st)
+        torch.cuda.synchronize()
+    finally:
+        lib.nb_set_staged_spmm(1 if old else 0)
+    np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref_g.view(np.uint32))
+    np.testing.assert_array_equal(host_f32(dy2).view(np.uint32), ref_g.view(np.uint32))
+    np.testing.assert_array_equal(host_f32(dgx).view(np.uint32), ref_b.view(np.uint32))
+    import ctypes
+    flags = ctypes.c_uint32(7)
+    _lib.call("nb_device_error_flags", ctypes.byref(flags))
+    assert flags.value == 0
