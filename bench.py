@@ -42,7 +42,7 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool; used only when M
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the layer-0 forward aggregation, from the ncu
 # capture summarised in profiles/ncu_aggregation_and_gemm_reddit.md; key = (workload, gather fused, all rows cached)
-NCU_TRAFFIC_BYTES = {("reddit", True, True): 324123392}
+NCU_TRAFFIC_BYTES = {("reddit", True, True): 316310528}
 
 
 def parse_args():

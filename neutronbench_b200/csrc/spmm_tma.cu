@@ -298,12 +298,15 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
 
 // ---------------------------------------------------------------------------------------------
 // Ring variant: a warp owns a CONTIGUOUS range of output rows, hence a contiguous range of edges,
-// and streams those edges through a ring of R row slots in shared memory, one mbarrier per slot.
-// A slot is refilled (edge j + R) as soon as edge j has been accumulated, so R - 1 of the R slots are
-// in flight at any time instead of one stage out of two.  16 warps per CTA share the SM's shared
-// memory (about 12 KB each).  Arithmetic and order are those of every other path.
+// and streams those edges through a ring of row slots in shared memory.  The slots form R groups of G
+// (1 or 2) rows with one mbarrier per group: the warp waits once per group, accumulates its rows in edge
+// order and refills the group with the edges R groups ahead (lane u issues the u-th copy), so R - 1
+// groups are in flight at any time.  Measured on the 2.4 KB rows of the Reddit-shaped layer-0 block:
+// the time per row and warp is set by this wait-accumulate-refill chain, not by the depth of the ring,
+// so pairs of rows per wait and 20 warps per CTA (about 10.8 KB of slots each) beat deeper rings.
+// Arithmetic and order are those of every other path.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRingWarps = 16;
+constexpr int kRingWarps = 20;
 
 template <int TILES, bool MASK>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const TmaSpmmArgs a) {
@@ -592,7 +595,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (panels == 1 && g_spmm_ring) {
     // ring variant: whole rows, per-warp ring of R slots out of about 13.5 KB
     a.panels = 1; a.panel_floats = a.fpad; a.copy_bytes = a.fpad * 4; a.slot_bytes = a.copy_bytes;
-    uint32_t slots = (13 * 1024 + 512) / a.slot_bytes;
+    uint32_t slots = (216 * 1024 / kRingWarps) / a.slot_bytes;   // the CTA's warps share 216 KB of row slots
     if (slots > 16) slots = 16;
     // two rows per barrier (one wait and one refill per pair of edges) where at least two pairs fit; measured on the
     // layer-0 block of the Reddit-shaped model: 78 us against 81 us with a barrier per row (65 against 75 from L2)
