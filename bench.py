@@ -13,8 +13,10 @@ ranks -> Adam.  Rank 0 prints ONE JSON line.
              the input-side block is never back-propagated, core/ntsContext.hpp:292).
   e2e        the same metric through the public API (train_step + read_stats) with the batch's seeds
              copied from pinned host memory and the loss read back to the host every step.
-  roofline   aggregation kernels (spmm_rows_kernel, all launches of the timed region): algorithmic
-             bytes / CUDA-event time against the measured HBM copy bandwidth.
+  roofline   the dominant kernel, the layer-0 forward aggregation (spmm_ring_kernel with the feature gather
+             fused; every launch of the timed region, timed by the library's own CUDA event pairs on the
+             launching stream): algorithmic bytes / that time against the measured HBM copy bandwidth;
+             all_aggregation carries the same ratio over all aggregation launches.
   cpu_baseline  the reference's own CPU training path (oracle/_ref/ref_harness, kind "reference") timed on
              this box's host cores on a few batches of the same workload; when that binary is absent,
              the C oracle port of it (kind "port").
