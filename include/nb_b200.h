@@ -355,6 +355,17 @@ int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint3
                   void *stream);
 int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_stats, nb_gcn_step_info *info,
                    void *stream);
+/* nb_gcn_sample with the drawing replaced by the caller's sampled edge lists: for a host that keeps the
+ * reference's CPU sampler (Sampler::sample_one, core/ntsSampler.hpp:843-1106, whose draws come from a thread-local
+ * mt19937 and cannot be reproduced on the device), and for parity runs, which are defined on identical sampled
+ * edge lists.  d_hop_edges: host array with one device (or pinned host) pointer per hop, seeds first; entry h
+ * holds the global source ids of hop h in CSC order, min(degree, fanout[h]) (the whole neighbourhood when the
+ * fan-out is negative) per destination, where hop 0's destinations are the seeds and hop h's the distinct sources
+ * of hop h-1 in ascending id order; hop_edge_counts (host) their lengths, checked against the column offsets.
+ * The sampler's own stream of draws does not advance.  Blocks, and so nb_gcn_compute's results, are what the
+ * reference builds from the same lists (sampCSC::postprocessing .. compute_weight, core/coocsc.hpp:136-425). */
+int nb_gcn_sample_from_edges(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds,
+                             const uint32_t *const *d_hop_edges, const uint32_t *hop_edge_counts, void *stream);
 /* nb_gcn_sample on a thread of the library (started at the first call, joined by nb_gcn_destroy), so that the
  * caller's thread is free to enqueue the training of the previous batch meanwhile; requests run in the order
  * they were made.  d_seeds must stay valid until the batch has been sampled.  nb_gcn_compute on the batch blocks

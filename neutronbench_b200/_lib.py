@@ -86,6 +86,8 @@ SIGNATURES = {
     "nb_gcn_batch_destroy": (C.c_int, [ptr]),
     "nb_gcn_sample": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.c_int, ptr]),
     "nb_gcn_sample_async": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.c_int, ptr]),
+    "nb_gcn_sample_from_edges": (C.c_int, [ptr, ptr, u32p, C.c_uint32, C.POINTER(C.c_void_p), C.POINTER(C.c_uint32),
+                                           ptr]),
     "nb_gcn_count_sources": (C.c_int, [ptr, ptr, u32p, ptr]),
     "nb_gcn_set_sampler_threads": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_compute": (C.c_int, [ptr, ptr, C.c_int, f32p, C.POINTER(GcnStepInfo), ptr]),

@@ -220,8 +220,11 @@ int ensure_events(nb_gcn_batch *bt) {
 }
 
 // sample_one: hop 0 starts at the seeds, hop h at the sources of hop h-1 (core/ntsSampler.hpp:843-1106).
+// With `ext_edges` (host array of one device pointer per hop, seeds first) the hop's global source ids are copied
+// from the caller instead of being drawn: the hop's column offsets still follow the fan-out rule and the supplied
+// list must have exactly that many entries.
 int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_seeds, uint32_t n_seeds, int train,
-                void *stream) {
+                void *stream, const uint32_t *const *ext_edges = nullptr, const uint32_t *ext_counts = nullptr) {
   const nb_gcn_config &c = g->cfg;
   const uint32_t L = c.num_layers;
   nb_ws *ws = bt->ws;
@@ -250,13 +253,19 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
     else
       NB_TRY(nb_sample_hop_offsets(ws, c.d_graph_column_offset, dst, v, c.fanout[h], b.column_offset, &b.e, stream));
     NB_TRY(arena(ws, b.e, &b.row_indices));
-    // the sampler marks the dedup bitmap of the hop while it writes the ids (cleared here, |V| bits + 4 flag words)
-    const size_t words = ((size_t)c.num_vertices + 31) / 32;
-    uint32_t *marked;
-    NB_TRY(arena(ws, words + 4, &marked));
-    NB_CUDA(cudaMemsetAsync(marked, 0, (words + 4) * sizeof(uint32_t), nb::as_stream(stream)));
-    NB_TRY(nb::sample_hop_impl(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, by_rate ? -1 : c.fanout[h],
-                               b.column_offset, c.seed, (draw << 8) | h, b.row_indices, marked, stream));
+    uint32_t *marked = nullptr;
+    if (ext_edges) {
+      NB_REQUIRE(ext_counts[h] == b.e, "nb_gcn_sample_from_edges: a hop's edge list does not have the length its "
+                                       "column offsets (min(degree, fan-out) per destination) give");
+      if (b.e) NB_CUDA(cudaMemcpyAsync(b.row_indices, ext_edges[h], 4ull * b.e, cudaMemcpyDefault, nb::as_stream(stream)));
+    } else {
+      // the sampler marks the dedup bitmap of the hop while it writes the ids (cleared here, |V| bits + 4 flag words)
+      const size_t words = ((size_t)c.num_vertices + 31) / 32;
+      NB_TRY(arena(ws, words + 4, &marked));
+      NB_CUDA(cudaMemsetAsync(marked, 0, (words + 4) * sizeof(uint32_t), nb::as_stream(stream)));
+      NB_TRY(nb::sample_hop_impl(c.d_graph_column_offset, c.d_graph_row_indices, dst, v, by_rate ? -1 : c.fanout[h],
+                                 b.column_offset, c.seed, (draw << 8) | h, b.row_indices, marked, stream));
+    }
     const size_t cap = b.e < c.num_vertices ? (b.e ? b.e : 1) : c.num_vertices;
     NB_TRY(arena(ws, cap, &b.source));
     NB_TRY(arena(ws, cap + 1, &b.row_offset));
@@ -449,6 +458,20 @@ NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds
     draw = g->draws++;
   }
   return sample_into(g, batch, draw, d_seeds, n_seeds, train, stream);
+}
+
+NB_API int nb_gcn_sample_from_edges(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds,
+                                    const uint32_t *const *d_hop_edges, const uint32_t *hop_edge_counts, void *stream) {
+  NB_REQUIRE(g && batch && d_seeds && d_hop_edges && hop_edge_counts, "nb_gcn_sample_from_edges: null pointer");
+  NB_REQUIRE(n_seeds > 0, "nb_gcn_sample_from_edges: empty batch");
+  NB_REQUIRE(batch->ws != g->ws, "nb_gcn_sample_from_edges: a batch needs a workspace of its own, not the model's");
+  for (uint32_t h = 0; h < g->cfg.num_layers; h++)
+    NB_REQUIRE(d_hop_edges[h] || hop_edge_counts[h] == 0, "nb_gcn_sample_from_edges: null edge list");
+  {
+    std::unique_lock<std::mutex> lk(g->mu);
+    g->cv_done.wait(lk, [&] { return !batch->pending; });
+  }
+  return sample_into(g, batch, 0, d_seeds, n_seeds, 0, stream, d_hop_edges, hop_edge_counts);
 }
 
 NB_API int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds, uint32_t n_seeds, int train,

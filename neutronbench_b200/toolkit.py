@@ -461,6 +461,20 @@ class GCN_GPU_NEIGHBOR_impl:
                   self._sample_streams[slot].cuda_stream)
         return n
 
+    def sample_from_edges(self, seeds: torch.Tensor, raw_edges: Sequence[torch.Tensor], slot: int = 0):
+        """nb_gcn_sample_from_edges: builds subgraph `slot` from externally sampled edge lists (one int32 device
+        tensor of global source ids per hop, seeds first) instead of drawing it; compute_batch(slot) trains on it.
+        This is how a run of the reference's trainer is replayed through the native step."""
+        import ctypes as C
+        self._ensure_pipeline()
+        L = self.layers
+        assert len(raw_edges) == L
+        ptrs = (C.c_void_p * L)(*[r.data_ptr() if r.numel() else None for r in raw_edges])
+        counts = (C.c_uint32 * L)(*[int(r.numel()) for r in raw_edges])
+        self._slot_refs[slot] = (seeds, list(raw_edges))
+        _lib.call("nb_gcn_sample_from_edges", self._ensure_engine(), self._batches[slot], ptr(seeds), int(seeds.numel()),
+                  ptrs, counts, self._sample_streams[slot].cuda_stream)
+
     def compute_batch(self, slot: int, train: bool = True):
         """nb_gcn_compute on subgraph `slot`, on the current stream; never blocks the host."""
         import ctypes as C
