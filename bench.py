@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the sampled mini-batch GCN training path (ALGORITHM:GCNNEIGHBORGPU) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload reddit|arxiv|products] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload reddit|arxiv|products|papers] [--impl reference]
 
 A "step" is one mini-batch through the whole hot path: fan-out sampling -> block construction ->
 feature/label gather -> per-layer aggregation + dense layer -> loss -> backward -> gradient sum over
@@ -11,15 +11,22 @@ ranks -> Adam.  Rank 0 prints ONE JSON line.
              Aggregated edges of a step = sum of e_size over the blocks (forward, the reference's
              Sampler::get_compute_cnt, core/ntsSampler.hpp:629-635) + sum over blocks l >= 1 (backward;
              the input-side block is never back-propagated, core/ntsContext.hpp:292).
-  e2e        the same metric through the public API (train_step + read_stats) with the batch's seeds
+  e2e        the same metric through the public API (the trainer's batch loop) with the batch's seeds
              copied from pinned host memory and the loss read back to the host every step.
+  timing     a region is EXACTLY --steps K steps between a barrier + device synchronize on both sides, timed
+             with CUDA events, max over ranks.  K steps of this workload last a few milliseconds, so the
+             region is repeated until about --min-region-s of device time has been measured and the MEDIAN
+             region is reported (`regions` says how many); the clock sampler runs across all of them.
   roofline   the dominant kernel, the layer-0 forward aggregation (spmm_ring_kernel with the feature gather
-             fused; every launch of the timed region, timed by the library's own CUDA event pairs on the
-             launching stream): algorithmic bytes / that time against the measured HBM copy bandwidth;
-             all_aggregation carries the same ratio over all aggregation launches.
+             fused; every launch of the timed regions, timed by the library's own CUDA event pairs on the
+             launching stream): algorithmic bytes / that time against the measured HBM copy bandwidth.
+  all_aggregation  the same ratio over all aggregation launches (forward and backward) of the timed regions.
   cpu_baseline  the reference's own CPU training path (oracle/_ref/ref_harness, kind "reference") timed on
-             this box's host cores on a few batches of the same workload; when that binary is absent,
-             the C oracle port of it (kind "port").
+             this box's host cores on a few batches of the same workload, at the reference's default thread
+             count and with all cores; when that binary is absent, the C oracle port of it (kind "port").
+  secondary  the Products-shaped workload (3 layers, 20 % of the rows cached, the others read from pinned host
+             memory) measured the same way at this N, so that its scaling can be read from the lines of a
+             1/2/4/8 run; --no-secondary switches it off.
 
 The datasets the reference uses are not available; graphs, features and labels are seeded synthetic
 data with the published shapes (see neutronbench_b200/synth.py).
@@ -28,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -40,47 +48,73 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool; used only when MEASURED_PEAKS.json is absent
+NVLINK_PEER_GBS = 770.0     # measured peer copy bandwidth per direction per GPU on this pool (900 nominal)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the layer-0 forward aggregation, from the ncu
-# capture summarised in profiles/ncu_aggregation_and_gemm_reddit.md; key = (workload, gather fused, all rows cached)
-NCU_TRAFFIC_BYTES = {("reddit", True, True): 316310528}
+def ncu_traffic_bytes(workload, fuse_gather, all_cached):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the layer-0 forward aggregation, from the
+    committed ncu capture of this workload (profiles/ncu_traffic.json holds the figure and names the capture)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if not os.path.exists(path):
+        return None
+    try:
+        table = json.load(open(path))
+    except Exception:
+        return None
+    key = f"{workload}|fuse_gather={int(bool(fuse_gather))}|all_cached={int(bool(all_cached))}"
+    entry = table.get(key)
+    return None if entry is None else entry.get("dram_bytes_per_launch")
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=0, help="timed steps per rank (0 = eight epochs of the workload)")
+    ap.add_argument("--steps", type=int, default=0, help="timed steps per region and rank (0 = one epoch of this rank's shard)")
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products"])
+    ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products", "papers"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cache-rate", type=float, default=None, help="override the workload's GPU cache rate")
     ap.add_argument("--cpu-batches", type=int, default=3, help="batches timed for the CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fuse-gather", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the Products-shaped secondary measurement")
+    ap.add_argument("--secondary-steps", type=int, default=100)
+    ap.add_argument("--min-region-s", type=float, default=0.3, help="repeat the K-step region until this much time is measured")
+    ap.add_argument("--max-regions", type=int, default=100)
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
     ap.add_argument("--pipelines", type=int, default=3,
                     help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain loop")
     ap.add_argument("--pdl", type=int, default=None, help="1 / 0: programmatic dependent launch for the training half's kernels")
+    ap.add_argument("--stage-misses", type=int, default=None,
+                    help="1 / 0: uncached rows staged once per distinct source by the sampling half (default: whenever the "
+                         "table is not in this GPU's memory)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="nb_gcn_set_option on the trainer's handle (tuning switches; results never depend on them)")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload's node and edge counts (functional checks)")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
 
 
 def workload_config(name, args):
     from neutronbench_b200 import GCNConfig, synth
+    import dataclasses
     sh = synth.SHAPES[name]
+    if args.scale != 1.0:
+        sh = dataclasses.replace(sh, vertices=max(1000, int(sh.vertices * args.scale)),
+                                 edges=max(10000, int(sh.edges * args.scale)))
     hidden = [sh.hidden] * (len(sh.fanout) - 1)
-    cache_rate = {"arxiv": 1.0, "reddit": 1.0, "products": 0.2}[name]
+    cache_rate = {"arxiv": 1.0, "reddit": 1.0, "products": 0.2, "papers": 0.0}[name]
     if args.cache_rate is not None:
         cache_rate = args.cache_rate
     cfg = GCNConfig(layers=[sh.feature] + hidden + [sh.classes], fanout=sh.fanout, batch_size=sh.batch,
                     learn_rate=0.01, weight_decay=0.0001, drop_rate=0.5,
                     cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate, seed=args.seed,
-                    fuse_gather=not args.no_fuse_gather)
+                    fuse_gather=not args.no_fuse_gather,
+                    stage_misses=None if args.stage_misses is None else bool(args.stage_misses))
     return sh, cfg
 
 
-def build_workload(name, args, device):
+def build_workload(name, args, device, rank=0, world=1):
     """Graph topology, features, labels and the train split, all seeded.  Data preparation is not timed."""
     import torch
     from neutronbench_b200 import FullyRepGraph, GNNDatum, Workspace, synth
@@ -94,20 +128,35 @@ def build_workload(name, args, device):
     del big
     torch.cuda.empty_cache()
     gen = torch.Generator(device=device).manual_seed(args.seed + 1)
+    mask = synth.split_mask(sh.vertices, args.seed)
+    train_ids = np.nonzero(mask == 0)[0].astype(np.uint32)
+    if name == "papers":
+        # the table does not fit one GPU at the full shape: every rank generates and keeps the rows of its own id range
+        from neutronbench_b200.peer import ShardedFeatureTable, shard_rows_for
+        rows_per = shard_rows_for(sh.vertices, world)
+        lo, hi = rank * rows_per, min(sh.vertices, (rank + 1) * rows_per)
+        g2 = torch.Generator(device=device).manual_seed(args.seed + 7 + rank)
+        local = torch.randn((max(hi - lo, 0), sh.feature), generator=g2, device=device, dtype=torch.float32)
+        label = torch.randint(0, sh.classes, (sh.vertices,), generator=gen, device=device, dtype=torch.int64)
+        if world > 1:
+            shards = ShardedFeatureTable.from_rank_shard(local, sh.vertices, rank, world, device)
+            del local
+        else:
+            shards = ShardedFeatureTable.from_local_parts([local], rows_per)
+        datum = GNNDatum(None, label, mask, shards=shards)
+        return sh, cfg, graph, datum, train_ids, None
     feat_dev = torch.randn((sh.vertices, sh.feature), generator=gen, device=device, dtype=torch.float32)
     label = torch.randint(0, sh.classes, (sh.vertices,), generator=gen, device=device, dtype=torch.int64)
-    mask = synth.split_mask(sh.vertices, args.seed)
     if cfg.cache_type == "rate" and cfg.cache_rate >= 1.0:
         feature = feat_dev                       # every row is a cache hit; the table only seeds the cache
     else:
-        feature = feat_dev.cpu().pin_memory()    # misses are zero-copy reads of mapped pinned host memory
+        feature = feat_dev.cpu().pin_memory()    # misses are reads of mapped pinned host memory
     datum = GNNDatum(feature, label, mask)
-    train_ids = np.nonzero(mask == 0)[0].astype(np.uint32)
     return sh, cfg, graph, datum, train_ids, feat_dev
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons while the timed regions run."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -198,8 +247,10 @@ def cpu_arm(sh, cfg, graph, feat_dev, label, train_ids, batches, warmup, seed):
 def cpu_arm_reference(sh, cfg, graph, feat_dev, label, train_ids, batches, warmup):
     """The reference's OWN CPU training path (oracle/_ref/ref_harness bench: its Sampler::sample_one,
     get_feature, MiniBatchFuseOp, libtorch mm/loss/autograd and CPU Adam, compiled from the reference
-    tree with single-rank shims) on the same graph, features and seed list.  Returns None when the
-    harness binary is not there (it is built only where the reference tree exists)."""
+    tree with single-rank shims) on the same graph, features and seed list, once with the reference's default
+    thread count (ncpus/2 - 1, core/ntsSampler.hpp:221-228) and once with THREADS = all cores.  Returns a list of
+    (edges/s, ms per batch, threads), or None when the harness binary is not there (it is built only where the
+    reference tree exists)."""
     import re
     import shutil
     import tempfile
@@ -221,17 +272,20 @@ def cpu_arm_reference(sh, cfg, graph, feat_dev, label, train_ids, batches, warmu
         label.cpu().numpy().astype("<i8").tofile(os.path.join(tmp, "label.i64"))
         need = (warmup + batches) * cfg.batch_size
         train_ids[:need].astype("<u4").tofile(os.path.join(tmp, "seeds.u32"))
-        cmd = [harness, "bench", os.path.join(tmp, "g.edge"), str(V), os.path.join(tmp, "feat.f32"),
-               os.path.join(tmp, "label.i64"), os.path.join(tmp, "seeds.u32"), ",".join(map(str, cfg.fanout)),
-               "-".join(map(str, cfg.layers)), str(cfg.batch_size), str(warmup), str(batches), str(cfg.drop_rate),
-               str(cfg.learn_rate), str(cfg.weight_decay)]
-        out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
-        m = re.search(r"REFBENCH ms_per_batch=([0-9.]+) agg_edges_per_batch=([0-9.]+) omp_threads=(\d+) batches=(\d+)",
-                      out.stdout)
-        if not m or int(m.group(4)) == 0:
-            return None
-        ms, edges, threads = float(m.group(1)), float(m.group(2)), int(m.group(3))
-        return edges / (ms * 1e-3), ms, threads
+        runs = []
+        for threads_arg in (0, os.cpu_count() or 0):
+            cmd = [harness, "bench", os.path.join(tmp, "g.edge"), str(V), os.path.join(tmp, "feat.f32"),
+                   os.path.join(tmp, "label.i64"), os.path.join(tmp, "seeds.u32"), ",".join(map(str, cfg.fanout)),
+                   "-".join(map(str, cfg.layers)), str(cfg.batch_size), str(warmup), str(batches), str(cfg.drop_rate),
+                   str(cfg.learn_rate), str(cfg.weight_decay), str(threads_arg)]
+            out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+            m = re.search(r"REFBENCH ms_per_batch=([0-9.]+) agg_edges_per_batch=([0-9.]+) omp_threads=(\d+) batches=(\d+)",
+                          out.stdout)
+            if not m or int(m.group(4)) == 0:
+                continue
+            ms, edges, threads = float(m.group(1)), float(m.group(2)), int(m.group(3))
+            runs.append((edges / (ms * 1e-3), ms, threads))
+        return runs or None
     except Exception:
         return None
     finally:
@@ -240,18 +294,155 @@ def cpu_arm_reference(sh, cfg, graph, feat_dev, label, train_ids, batches, warmu
 
 def host_baseline(sh, cfg, graph, feat, label, train_ids, batches, warmup, seed):
     """Reference binary when available (kind "reference"), otherwise the oracle port (kind "port")."""
-    ref = cpu_arm_reference(sh, cfg, graph, feat, label, train_ids, batches, warmup)
-    if ref is not None:
-        eps, ms, threads = ref
-        return {"value": eps, "unit": "edges/s", "cores": os.cpu_count(), "kind": "reference", "ms_per_step": ms,
+    runs = cpu_arm_reference(sh, cfg, graph, feat, label, train_ids, batches, warmup)
+    if runs:
+        eps, ms, threads = max(runs, key=lambda r: r[0])     # the faster of the two thread counts is the baseline
+        return {"value": eps, "unit": "edges/s", "cores": threads, "kind": "reference", "ms_per_step": ms,
+                "host_cpus": os.cpu_count(),
+                "by_threads": [{"threads": t, "value": e, "ms_per_step": m} for (e, m, t) in runs],
                 "sample": f"{batches} mini-batches of the same workload after {warmup} warm-up: the reference's own "
-                          f"CPU path (Sampler::sample_one + MiniBatchFuseOp + libtorch) with its default "
-                          f"{threads} OpenMP threads for sampling/aggregation and libtorch's default intra-op "
-                          f"threads for the dense layers"}
+                          f"CPU path (Sampler::sample_one + MiniBatchFuseOp + libtorch, built -O3 -march=native) with "
+                          f"THREADS at its default ({runs[0][2]}) and at all {os.cpu_count()} cores; the faster run "
+                          f"({threads} threads) is reported; libtorch uses its default intra-op threads for the dense "
+                          f"layers"}
     eps, ms, threads, _ = cpu_arm(sh, cfg, graph, feat, label, train_ids, batches, warmup, seed)
     return {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port", "ms_per_step": ms,
             "sample": f"{batches} mini-batches of the same workload after {warmup} warm-up, C oracle port of the "
                       f"reference's CPU path, OpenMP + BLAS on all host threads"}
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, device, want_events=True):
+    """Times the trainer's own batch loop on this rank's share of the shuffled train list.  Returns a dict with
+    the device-timed and end-to-end figures (max over ranks per region, median over regions)."""
+    import torch
+    import torch.distributed as dist
+    from neutronbench_b200 import Sampler, _lib
+    from neutronbench_b200.toolkit import shard_for_rank
+
+    rng = np.random.RandomState(args.seed)
+    ids = train_ids.copy()
+    rng.shuffle(ids)
+    shard = shard_for_rank(ids, rank, world)
+    if K <= 0:
+        K = (len(shard) + cfg.batch_size - 1) // cfg.batch_size      # one epoch of this rank's shard
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_vec(values, op):
+        if world == 1:
+            return list(values)
+        t = torch.tensor(list(values), dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=op)
+        return t.tolist()
+
+    def steps(smp, n, staged):
+        if cfg.pipelines > 1:
+            done = tk.run_pipelined(smp, max_batches=n, train=True, read_back=not staged, pad_to_steps=n)[3]
+            assert done == n
+            return
+        for _ in range(n):
+            tk.train_step(smp)
+            if not staged:
+                tk.read_stats()
+
+    def run(staged, record_events):
+        regions_cap = max(1, args.max_regions)
+        need = (W + K * regions_cap) * cfg.batch_size
+        reps = (need + len(shard) - 1) // len(shard)
+        seeds_all = np.tile(shard, reps)[:need]
+        smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
+        if staged:
+            smp.stage_seeds_on_device()
+        clocks = ClockSampler(local_rank)
+        if rank == 0 and record_events:
+            clocks.start()           # nvidia-smi needs ~0.1 s to produce its first sample: start before warm-up
+        steps(smp, W, staged)
+        barrier()
+        tk.events = [] if (record_events and not tk.use_engine) else None
+        if record_events and tk.use_engine:
+            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
+        launches0 = _lib.load().nb_launch_count()
+        region_ms, region_edges = [], []
+        regions = 1
+        r = 0
+        while r < regions:
+            tk.agg_edges_fwd = tk.agg_edges_bwd = 0
+            t0 = torch.cuda.Event(enable_timing=True)
+            t1 = torch.cuda.Event(enable_timing=True)
+            t0.record()
+            steps(smp, K, staged)
+            t1.record()
+            barrier()
+            region_ms.append(t0.elapsed_time(t1))
+            region_edges.append(tk.agg_edges_fwd + tk.agg_edges_bwd)
+            if r == 0:   # how many regions make up the minimum measured time: decided once, the same on every rank
+                first = reduce_vec([region_ms[0]], dist.ReduceOp.MAX if world > 1 else None)[0]
+                regions = min(regions_cap, max(1, math.ceil(args.min_region_s * 1e3 / max(first, 1e-3))))
+            r += 1
+        clk = clocks.stop() if (rank == 0 and record_events) else None
+        launches = _lib.load().nb_launch_count() - launches0
+        ev = tk.events
+        tk.events = None
+        if record_events and tk.use_engine:
+            import ctypes
+            a_ms, a_b, a_n = (ctypes.c_double * 2)(), (ctypes.c_uint64 * 2)(), (ctypes.c_uint64 * 2)()
+            _lib.call("nb_gcn_read_timing_by_class", tk._ensure_engine(), a_ms, a_b, a_n)
+            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 0)
+            ev = ("engine", list(a_ms), [int(x) for x in a_b], [int(x) for x in a_n])
+        tk.check_device_errors()     # a bounded wait that gave up, or an id outside its table, voids the numbers
+        ms_max = reduce_vec(region_ms, dist.ReduceOp.MAX if world > 1 else None)
+        edges_sum = reduce_vec(region_edges, dist.ReduceOp.SUM if world > 1 else None)
+        order = sorted(range(len(ms_max)), key=lambda i: ms_max[i])
+        mid = order[len(order) // 2] if len(order) % 2 else order[len(order) // 2 - 1]   # a measured region, not a mean
+        return {"ms": ms_max[mid], "edges": edges_sum[mid], "regions": len(ms_max), "ms_min": min(ms_max),
+                "ms_max": max(ms_max), "launches_per_region": launches / len(ms_max), "clocks": clk, "events": ev,
+                "total_steps": K * len(ms_max)}
+
+    a = run(staged=True, record_events=want_events)
+    b = run(staged=False, record_events=False)
+    return K, a, b
+
+
+def roofline_of(events, peak, peak_src, traffic, cfg):
+    def gbps(nbytes, ms):
+        return nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+
+    if isinstance(events, tuple):      # native step: totals measured by the library's own CUDA events
+        _, cls_ms, cls_bytes, cls_n = events
+        dom_ms, dom_bytes, dom_n = cls_ms[0], cls_bytes[0], cls_n[0]
+        all_ms, all_bytes, all_n = sum(cls_ms), sum(cls_bytes), sum(cls_n)
+        per_call = {"layer0_forward": {"GBps": gbps(cls_bytes[0], cls_ms[0]), "ms_avg": cls_ms[0] / max(cls_n[0], 1),
+                                       "bytes_avg": cls_bytes[0] / max(cls_n[0], 1)},
+                    "other_aggregation": {"GBps": gbps(cls_bytes[1], cls_ms[1]), "ms_avg": cls_ms[1] / max(cls_n[1], 1),
+                                          "bytes_avg": cls_bytes[1] / max(cls_n[1], 1)}}
+    else:                              # Python step: one event pair per aggregation call
+        per_kernel = {}
+        for (name, b, s_, e_) in events or []:
+            d = per_kernel.setdefault(name, [0, 0.0, 0])
+            d[0] += b
+            d[1] += s_.elapsed_time(e_)
+            d[2] += 1
+        first = next((k for k in ("fwd0_gather_fused", "fwd0") if k in per_kernel), None)
+        dom_bytes, dom_ms, dom_n = per_kernel[first] if first else (0, 0.0, 0)
+        all_ms = sum(v[1] for v in per_kernel.values())
+        all_bytes = sum(v[0] for v in per_kernel.values())
+        all_n = sum(v[2] for v in per_kernel.values())
+        per_call = {k: {"GBps": gbps(v[0], v[1]), "ms_avg": v[1] / v[2], "bytes_avg": v[0] / v[2]}
+                    for k, v in per_kernel.items()}
+    achieved = gbps(dom_bytes, dom_ms)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_source": peak_src,
+                "kernel": "layer-0 forward aggregation (gather fused)" if cfg.fuse_gather else "layer-0 forward aggregation",
+                "launches": dom_n, "avg_launch_ms": dom_ms / max(dom_n, 1),
+                "algorithmic_bytes_per_launch": dom_bytes / max(dom_n, 1), "per_call": per_call}
+    all_agg = {"bound": "hbm", "achieved": gbps(all_bytes, all_ms), "peak": peak, "unit": "GB/s",
+               "frac": gbps(all_bytes, all_ms) / peak, "launches": all_n,
+               "what": "every aggregation launch (forward and backward) of the timed regions"}
+    return roofline, all_agg
 
 
 def main():
@@ -270,32 +461,42 @@ def main():
     if world > 1 and args.impl != "reference":
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
             os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
+        # The only collective is a 329 KB gradient sum per step: a few channels carry it, and every channel is a CTA
+        # that holds an SM beside the one-CTA-per-SM aggregation kernel (which leaves that many SMs free).
+        os.environ.setdefault("NCCL_MAX_CTAS", "4")
         dist.init_process_group("nccl", device_id=device)
 
-    from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, Sampler, _lib
+    from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, _lib
     if args.pdl is not None:
         _lib.load().nb_set_pdl(int(args.pdl))
-    sh, cfg, graph, datum, train_ids, feat_dev = build_workload(args.workload, args, device)
+    if args.workload == "papers" and args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the Papers-shaped feature table (57 GB) is a multi-GPU "
+                          "scale test; the reference's CPU path is timed on the other workloads"}))
+        return 0
+    sh, cfg, graph, datum, train_ids, feat_dev = build_workload(args.workload, args, device, rank, world)
     batches_per_epoch = (len(train_ids) + cfg.batch_size - 1) // cfg.batch_size
 
-    workload_desc = {
-        "workload": f"{sh.name}-shaped synthetic R-MAT: {sh.vertices} nodes, {graph.global_edges} edges (incl. self "
-                    f"loops), feature {sh.feature}, layers {'-'.join(map(str, cfg.layers))}, fanout "
-                    f"{list(cfg.fanout)} (hop order), batch {cfg.batch_size}, cache_rate {cfg.cache_rate}",
-        "batches_per_epoch": batches_per_epoch,
-        "l2_policy": "inputs larger than L2 (feature store >> 126 MB, each step touches a new random subset)",
-        "parallelism": f"dp{world}",
-        "fuse_gather": cfg.fuse_gather,
-        "step": "python (one call per kernel family)" if args.python_step else
-                ("native (nb_gcn_sample on a second stream overlapping nb_gcn_compute)" if args.pipelines > 1
-                 else "native (nb_gcn_step)"),
-        "pipelines": 1 if args.python_step else max(1, args.pipelines),
-    }
+    def describe(sh, cfg, graph, pipelines, train_ids):
+        return {
+            "workload": f"{sh.name}-shaped synthetic R-MAT: {sh.vertices} nodes, {graph.global_edges} edges (incl. self "
+                        f"loops), feature {sh.feature}, layers {'-'.join(map(str, cfg.layers))}, fanout "
+                        f"{list(cfg.fanout)} (hop order), batch {cfg.batch_size}, cache_rate {cfg.cache_rate}",
+            "batches_per_epoch": (len(train_ids) + cfg.batch_size - 1) // cfg.batch_size,
+            "l2_policy": "inputs larger than L2 (feature store >> 126 MB, each step touches a new random subset)",
+            "parallelism": f"dp{world}",
+            "fuse_gather": cfg.fuse_gather,
+            "step": "python (one call per kernel family)" if args.python_step else
+                    ("native (nb_gcn_sample on library threads overlapping nb_gcn_compute)" if pipelines > 1
+                     else "native (nb_gcn_step)"),
+            "pipelines": pipelines,
+        }
+
+    pipelines = 1 if args.python_step else max(1, args.pipelines)
+    workload_desc = describe(sh, cfg, graph, pipelines, train_ids)
 
     if args.impl == "reference":
         K = args.steps if args.steps > 0 else 3
         W = max(args.warmup, 0)
-        W = min(W, 2)
         base = host_baseline(sh, cfg, graph, feat_dev, datum.local_label, train_ids, K, W, args.seed)
         eps, ms = base["value"], base["ms_per_step"]
         line = {"impl": "reference", "metric": "aggregated_edges_per_s", "value": eps, "unit": "edges/s",
@@ -306,162 +507,92 @@ def main():
         print(json.dumps(line))
         return 0
 
-    cfg.pipelines = 1 if args.python_step else max(1, args.pipelines)
-    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world, use_engine=not args.python_step)
-    tk.init_cache()
+    def make_trainer(graph, datum, cfg):
+        cfg.pipelines = pipelines
+        tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world, use_engine=not args.python_step)
+        tk.init_cache()
+        for opt in args.option:
+            name, value = opt.split("=", 1)
+            _lib.call("nb_gcn_set_option", tk._ensure_engine(), name.encode(), int(value))
+        return tk
+
+    tk = make_trainer(graph, datum, cfg)
     del feat_dev
-    # this rank's share of the shuffled train list: contiguous shard (data parallel over mini-batches)
-    rng = np.random.RandomState(args.seed)
-    ids = train_ids.copy()
-    rng.shuffle(ids)
-    shard = ids[rank::world] if world > 1 else ids
-    # default: eight epochs of this rank's shard, so that the timed region lasts long enough (a few tenths of a second)
-    # for the clock sampler to see it
-    K = args.steps if args.steps > 0 else 8 * ((len(shard) + cfg.batch_size - 1) // cfg.batch_size)
     W = max(args.warmup, 3)
-    need = (W + K) * cfg.batch_size
-    reps = (need + len(shard) - 1) // len(shard)
-    seeds_all = np.tile(shard, reps)[:need]
+    K, a, b = measure(tk, graph, cfg, train_ids, args, args.steps, W, rank, world, local_rank, device)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def run(staged: bool, record_events: bool):
-        smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
-        if staged:
-            smp.stage_seeds_on_device()
-        clocks = ClockSampler(local_rank)
-        if rank == 0 and record_events:
-            clocks.start()           # nvidia-smi needs ~0.1 s to produce its first sample: start before warm-up
-        def steps(n):
-            if cfg.pipelines > 1:
-                done = tk.run_pipelined(smp, max_batches=n, train=True, read_back=not staged)[3]
-                assert done == n
-                return
-            for _ in range(n):
-                tk.train_step(smp)
-                if not staged:
-                    tk.read_stats()
-
-        steps(W)
-        barrier()
-        tk.agg_edges_fwd = tk.agg_edges_bwd = 0
-        tk.events = [] if (record_events and not tk.use_engine) else None
-        if record_events and tk.use_engine:
-            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
-        launches0 = _lib.load().nb_launch_count()
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
-        t0.record()
-        steps(K)
-        t1.record()
-        barrier()
-        ms = t0.elapsed_time(t1)
-        clk = clocks.stop() if (rank == 0 and record_events) else None
-        launches = _lib.load().nb_launch_count() - launches0
-        edges = tk.agg_edges_fwd + tk.agg_edges_bwd
-        ev = tk.events
-        tk.events = None
-        if record_events and tk.use_engine:
-            import ctypes
-            a_ms, a_b, a_n = (ctypes.c_double * 2)(), (ctypes.c_uint64 * 2)(), (ctypes.c_uint64 * 2)()
-            _lib.call("nb_gcn_read_timing_by_class", tk._ensure_engine(), a_ms, a_b, a_n)
-            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 0)
-            ev = ("engine", list(a_ms), [int(x) for x in a_b], [int(x) for x in a_n])
-        return ms, edges, launches, clk, ev
-
-    ms_a, edges_a, launches, clk, events = run(staged=True, record_events=True)
-    ms_b, edges_b, _, _, _ = run(staged=False, record_events=False)
-
-    def reduce_max(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def reduce_sum(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    ms_a, ms_b = reduce_max(ms_a), reduce_max(ms_b)
-    edges_a, edges_b = reduce_sum(edges_a), reduce_sum(edges_b)
-
-    # roofline of the dominant kernel (the layer-0 forward aggregation, which reads the feature rows) from CUDA
-    # events recorded inside the timed region; the other aggregation launches are reported beside it
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         peak = float(json.load(open(peaks_path))["hbm_gbs"])
         peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
     else:
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    traffic = ncu_traffic_bytes(args.workload, cfg.fuse_gather, cfg.cache_rate >= 1.0)
+    roofline, all_agg = roofline_of(a["events"], peak, peak_src, traffic, cfg)
 
-    def gbps(nbytes, ms):
-        return nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+    def summary(K, a, b, cfg, bpe):
+        hops = len(cfg.fanout)
+        steps_per_epoch = (bpe + world - 1) // world
+        return {
+            "value": a["edges"] / (a["ms"] * 1e-3), "ms_per_step": a["ms"] / K,
+            "epoch_time_s": (a["ms"] / K) * steps_per_epoch / 1e3,
+            "regions": a["regions"], "region_ms": {"median": a["ms"], "min": a["ms_min"], "max": a["ms_max"]},
+            "e2e": {"value": b["edges"] / (b["ms"] * 1e-3), "unit": "edges/s", "ms_per_step": b["ms"] / K,
+                    "epoch_time_s": (b["ms"] / K) * steps_per_epoch / 1e3, "regions": b["regions"],
+                    "h2d_bytes_per_step": cfg.batch_size * 4, "d2h_bytes_per_step": 8 + hops * 12},
+            "gpu_launches": int(round(a["launches_per_region"])),
+            "aggregated_edges_per_step": a["edges"] / (K * world),
+        }
 
-    if isinstance(events, tuple):      # native step: totals measured by the library's own CUDA events
-        _, cls_ms, cls_bytes, cls_n = events
-        dom_ms, dom_bytes, dom_n = cls_ms[0], cls_bytes[0], cls_n[0]
-        all_ms, all_bytes, all_n = sum(cls_ms), sum(cls_bytes), sum(cls_n)
-        per_call = {"layer0_forward": {"GBps": gbps(cls_bytes[0], cls_ms[0]), "ms_avg": cls_ms[0] / max(cls_n[0], 1),
-                                       "bytes_avg": cls_bytes[0] / max(cls_n[0], 1)},
-                    "other_aggregation": {"GBps": gbps(cls_bytes[1], cls_ms[1]), "ms_avg": cls_ms[1] / max(cls_n[1], 1),
-                                          "bytes_avg": cls_bytes[1] / max(cls_n[1], 1)}}
-    else:                              # Python step: one event pair per aggregation call
-        per_kernel = {}
-        for (name, b, s_, e_) in events:
-            d = per_kernel.setdefault(name, [0, 0.0, 0])
-            d[0] += b
-            d[1] += s_.elapsed_time(e_)
-            d[2] += 1
-        first = next((k for k in ("fwd0_gather_fused", "fwd0") if k in per_kernel), None)
-        dom_bytes, dom_ms, dom_n = per_kernel[first] if first else (0, 0.0, 0)
-        all_ms = sum(v[1] for v in per_kernel.values())
-        all_bytes = sum(v[0] for v in per_kernel.values())
-        all_n = sum(v[2] for v in per_kernel.values())
-        per_call = {k: {"GBps": gbps(v[0], v[1]), "ms_avg": v[1] / v[2], "bytes_avg": v[0] / v[2]}
-                    for k, v in per_kernel.items()}
-    achieved = gbps(dom_bytes, dom_ms)
-    # DRAM bytes of one launch of that kernel from the committed ncu capture of this workload (read + write)
-    traffic = NCU_TRAFFIC_BYTES.get((args.workload, cfg.fuse_gather, cfg.cache_rate >= 1.0))
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_source": peak_src,
-                "kernel": "layer-0 forward aggregation (spmm_ring_kernel, gather fused)" if cfg.fuse_gather
-                          else "layer-0 forward aggregation",
-                "launches": dom_n, "avg_launch_ms": dom_ms / max(dom_n, 1),
-                "algorithmic_bytes_per_launch": dom_bytes / max(dom_n, 1),
-                "all_aggregation": {"achieved": gbps(all_bytes, all_ms), "frac": gbps(all_bytes, all_ms) / peak,
-                                    "launches": all_n},
-                "per_call": per_call}
+    primary = summary(K, a, b, cfg, batches_per_epoch)
+    stage_primary = bool(tk.stage_misses)
+
+    # ---- the reference's CPU path on the same workload, on this box's host cores (rank 0 of a 1-GPU run only)
+    base = None
+    if rank == 0 and not args.no_cpu_baseline and world == 1 and args.workload != "papers":
+        base = host_baseline(sh, cfg, graph, datum.local_feature, datum.local_label, train_ids, args.cpu_batches, 1,
+                             args.seed)
+        base["epoch_time_s"] = base["ms_per_step"] * batches_per_epoch / 1e3
+
+    # ---- secondary: the Products-shaped workload at this N (its scaling is a target of its own)
+    secondary = None
+    if not args.no_secondary and args.workload == "reddit" and args.scale == 1.0:
+        del tk, datum, graph
+        torch.cuda.empty_cache()
+        sh2, cfg2, graph2, datum2, train2, feat2 = build_workload("products", args, device, rank, world)
+        del feat2
+        tk2 = make_trainer(graph2, datum2, cfg2)
+        K2, a2, b2 = measure(tk2, graph2, cfg2, train2, args, args.secondary_steps, W, rank, world, local_rank, device)
+        bpe2 = (len(train2) + cfg2.batch_size - 1) // cfg2.batch_size
+        secondary = summary(K2, a2, b2, cfg2, bpe2)
+        r2, all2 = roofline_of(a2["events"], peak, peak_src, None, cfg2)
+        secondary.update({"metric": "aggregated_edges_per_s", "unit": "edges/s", "n_gpus": world, "steps": K2, "warmup": W,
+                          "config": describe(sh2, cfg2, graph2, pipelines, train2), "stage_misses": bool(tk2.stage_misses),
+                          "layer0_aggregation": {k: r2[k] for k in ("achieved", "frac", "avg_launch_ms",
+                                                                    "algorithmic_bytes_per_launch")},
+                          "all_aggregation": {k: all2[k] for k in ("achieved", "frac", "launches")}})
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return 0
 
-    value = edges_a / (ms_a * 1e-3)
-    e2e_value = edges_b / (ms_b * 1e-3)
-    hops = len(cfg.fanout)
     line = {
-        "metric": "aggregated_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": K,
-        "warmup": W, "ms_per_step": ms_a / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": workload_desc,
-        "epoch_time_s": (ms_a / K) * ((batches_per_epoch + world - 1) // world) / 1e3,
-        "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": ms_b / K,
-                "epoch_time_s": (ms_b / K) * ((batches_per_epoch + world - 1) // world) / 1e3,
-                "h2d_bytes_per_step": cfg.batch_size * 4, "d2h_bytes_per_step": 8 + hops * 12},
-        "gpu_launches": int(launches), "roofline": roofline, "clocks": clk,
-        "aggregated_edges_per_step": edges_a / (K * world),
+        "metric": "aggregated_edges_per_s", "value": primary["value"], "unit": "edges/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": primary["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_desc,
+        "epoch_time_s": primary["epoch_time_s"], "regions": primary["regions"], "region_ms": primary["region_ms"],
+        "e2e": primary["e2e"], "gpu_launches": primary["gpu_launches"], "roofline": roofline,
+        "all_aggregation": all_agg, "clocks": a["clocks"],
+        "aggregated_edges_per_step": primary["aggregated_edges_per_step"], "device_error": 0,
+        "stage_misses": stage_primary,
     }
-    if not args.no_cpu_baseline and world == 1:
-        base = host_baseline(sh, cfg, graph, datum.local_feature, datum.local_label, train_ids, args.cpu_batches, 1,
-                             args.seed)
-        base["epoch_time_s"] = base["ms_per_step"] * batches_per_epoch / 1e3
+    if args.workload == "papers":
+        # remote rows of the staging gathers against the NVLink ingress of one GPU
+        line["config"]["feature_table"] = f"sharded by node-id range over {world} GPUs, peers read with plain loads"
+    if secondary is not None:
+        line["secondary"] = secondary
+    if base is not None:
         line["cpu_baseline"] = base
     print(json.dumps(line))
     if world > 1:

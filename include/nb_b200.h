@@ -117,13 +117,18 @@ int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t feat_ld, c
  * previous on/off setting.
  * nb_device_error_flags reads (and so synchronises with) the device-side error word: bit 0 is set
  * when a bounded wait on a copy barrier gave up, bit 1 when a wait on a tensor-core completion
- * barrier gave up. */
+ * barrier gave up, bit 2 when a gather or gather-fused aggregation met a vertex id that no table holds (beyond
+ * the last shard, or not cached and no table given; the row is skipped or counts as zeros), bit 3 when a loss
+ * kernel met a label outside [0, C) (the row counts with loss 0, no hit, zero gradient).  The word belongs to the
+ * process and the device, not to a workspace or handle. */
 int nb_set_staged_spmm(int enabled);
 /* The staged gather-fused aggregation cuts wide rows into column panels whose distinct source data
  * (s rows x panel width) stays below this many bytes, so that reuse of a source row hits L2
  * (0 = never cut, the default).  Returns the previous value. */
 uint64_t nb_set_l2_panel_bytes(uint64_t bytes);
 int nb_device_error_flags(uint32_t *flags);
+/* Clears the error word (it is sticky otherwise); synchronises like nb_device_error_flags. */
+int nb_device_error_reset(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Block construction.
@@ -210,6 +215,22 @@ int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, const floa
                       uint32_t num_shards, uint32_t shard_rows, const float *d_cache, size_t cache_ld,
                       const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
                       void *stream);
+/* Shards of a feature table that other processes of the job read (one process per GPU): a shard is an allocation of
+ * its own (cudaMalloc), so that its inter-process handle names exactly that buffer.
+ *   nb_shard_alloc / nb_shard_free   device memory of the current device
+ *   nb_shard_upload                  copies `bytes` from `src` (host or device memory) into a shard; synchronous
+ *   nb_shard_export                  64-byte handle of a shard of THIS process (cudaIpcGetMemHandle)
+ *   nb_shard_open / nb_shard_close   maps a shard of ANOTHER process on the same machine into this process; the
+ *                                    returned pointer is valid on the current device, which reads the owner's memory
+ *                                    with plain loads over NVLink; nothing is copied.  Open each handle once.
+ * The pointers, own and opened, go into the d_feat_shards table of nb_gcn_config / nb_feature_gather.  The owner
+ * must keep a shard allocated until every peer has closed it. */
+int nb_shard_alloc(void **d_ptr, size_t bytes);
+int nb_shard_free(void *d_ptr);
+int nb_shard_upload(void *d_dst, const void *src, size_t bytes);
+int nb_shard_export(void *d_ptr, unsigned char handle[64]);
+int nb_shard_open(const unsigned char handle[64], void **d_ptr);
+int nb_shard_close(void *d_ptr);
 int nb_label_gather(int64_t *d_lab, const int64_t *d_label, const uint32_t *d_dst, uint32_t n,
                     uint32_t label_size, void *stream);
 int nb_cache_fill(float *d_cache, size_t cache_ld, const float *feat, size_t feat_ld,
@@ -316,6 +337,17 @@ typedef struct nb_gcn_config {
   int32_t lower_fanout;                     /* LOWER_FANOUT of that mode                             */
   uint32_t classes;                         /* CLASSES: 0 or 1 = one label per vertex (NLL loss); > 1 = that many
                                                zero/non-zero labels per vertex in d_label (BCE loss, 4 stats)  */
+  /* Feature table sharded by contiguous node-id range (replaces `feat`; the reference keeps remote rows behind an
+   * MPI RPC, core/ntsPeerRPC.hpp:44-46): d_feat_shards is a DEVICE array of num_shards row pointers, shard k holds
+   * the rows of vertices [k*shard_rows, (k+1)*shard_rows) with pitch feat_ld; a pointer may name this GPU's memory
+   * or a peer GPU's (mapped by the caller; read with plain loads only).  Needs stage_misses.                     */
+  const float *const *d_feat_shards;
+  uint32_t num_shards, shard_rows;
+  /* stage_misses != 0: the rows of the input block's distinct sources that have no cache slot are copied, once each,
+   * into a staging table in the batch's workspace by the sampling half (nb_gcn_sample*), and the layer-0 aggregation
+   * reads cache and staging table only.  For tables in mapped host memory or on peer GPUs: a row used by k edges
+   * crosses the link once instead of k times, and does so while the previous batch trains.  Same results.        */
+  int stage_misses;
 } nb_gcn_config;
 
 typedef struct nb_gcn_step_info {
@@ -377,6 +409,15 @@ int nb_gcn_sample_async(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds,
  * batch); every request takes its place in the sampler's sequence of draws when it is made, so results do
  * not depend on the number of threads. */
 int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
+/* Tuning switches of one handle.  A handle starts with the process defaults (the nb_set_* calls above change those
+ * and act on the stand-alone entry points and on handles created afterwards) and keeps its own copy, which is in
+ * force on the calling thread while one of its nb_gcn_* entry points runs; handles and threads do not share
+ * settings.  Names: "gemm_mode" (as nb_set_gemm_mode), "pdl", "fused_output_layer", "staged_spmm", "spmm_ring",
+ * "staged_min_width", "ring_group_shift", "l2_panel_bytes", "l2_prefetch", "l2_hint" (0 off; 1 rows that a single
+ * edge of the launch uses are copied with the L2 evict-first policy; 2 the others evict-last as well),
+ * "y_stream_stores" (streaming stores for the wide layer-0 aggregate), "reserve_sms" (SMs that the
+ * one-CTA-per-SM aggregation kernel leaves free for a collective running beside it).  Results never depend on them. */
+int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);
 /* nb_count_ids over the source list of every block of a sampled batch (one step of the dry-run epoch of
  * CACHE_POLICY:sample); waits for the batch's sampling like nb_gcn_compute. */
 int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_counts, void *stream);
@@ -388,6 +429,12 @@ int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t 
 /* The same, split in two classes: [0] the layer-0 forward aggregation (the launch that reads the feature rows,
  * the dominant kernel of a step), [1] all other aggregation launches. */
 int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]);
+/* The four per-phase times of the reference's epoch log line (toolkits/GCN_GPU_NEIGHBOR.hpp:60-72, 750-761,
+ * 1499-1505) since timing was switched on or last read, in milliseconds: [0] sample = wall time the sampling halves
+ * took on their threads (they overlap the training half when batches are drawn ahead), [1] trans = device time
+ * of staging rows that are not cached, [2] graph = device time of the aggregation launches, [3] nn = device time
+ * of the training half minus graph.  Consumes the same event pairs as the two calls above. */
+int nb_gcn_read_phase_times(nb_gcn *g, double ms[4]);
 
 #ifdef __cplusplus
 }

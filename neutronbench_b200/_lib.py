@@ -31,7 +31,8 @@ class GcnConfig(C.Structure):
                 ("feat", C.c_void_p), ("feat_ld", C.c_size_t), ("d_cache", C.c_void_p), ("cache_ld", C.c_size_t),
                 ("d_hashmap", C.c_void_p), ("d_label", C.c_void_p), ("d_W", C.c_void_p), ("d_grad", C.c_void_p),
                 ("d_M", C.c_void_p), ("d_V", C.c_void_p), ("sample_rate", C.c_float), ("lower_fanout", C.c_int32),
-                ("classes", C.c_uint32)]
+                ("classes", C.c_uint32), ("d_feat_shards", C.c_void_p), ("num_shards", C.c_uint32),
+                ("shard_rows", C.c_uint32), ("stage_misses", C.c_int)]
 
 
 class GcnStepInfo(C.Structure):
@@ -60,6 +61,8 @@ SIGNATURES = {
     "nb_set_l2_panel_bytes": (C.c_uint64, [C.c_uint64]),
     "nb_set_staged_spmm": (C.c_int, [C.c_int]),
     "nb_device_error_flags": (C.c_int, [C.POINTER(C.c_uint32)]),
+    "nb_device_error_reset": (C.c_int, []),
+    "nb_gcn_set_option": (C.c_int, [ptr, C.c_char_p, C.c_int64]),
     "nb_block_build": (C.c_int, [ptr, C.c_uint32, u32p, u32p, C.c_uint32, C.c_uint32, u32p,
                                  C.POINTER(C.c_uint32), u32p, u32p, f32p, f32p, f32p, f32p, ptr]),
     "nb_sample_hop_offsets": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_int, u32p, C.POINTER(C.c_uint32), ptr]),
@@ -69,6 +72,12 @@ SIGNATURES = {
     "nb_graph_build_csc": (C.c_int, [ptr, u32p, C.c_uint64, C.c_uint32, u64p, u32p, u32p, u32p, ptr]),
     "nb_feature_gather": (C.c_int, [f32p, f32p, C.c_size_t, ptr, C.c_uint32, C.c_uint32, f32p, C.c_size_t, u32p,
                                     u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_shard_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
+    "nb_shard_free": (C.c_int, [ptr]),
+    "nb_shard_upload": (C.c_int, [ptr, ptr, C.c_size_t]),
+    "nb_shard_export": (C.c_int, [ptr, C.c_char_p]),
+    "nb_shard_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "nb_shard_close": (C.c_int, [ptr]),
     "nb_label_gather": (C.c_int, [i64p, i64p, u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_cache_fill": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, C.c_uint32, C.c_uint32, ptr]),
     "nb_count_ids": (C.c_int, [u32p, C.c_uint64, C.c_uint32, u32p, ptr]),
@@ -94,6 +103,7 @@ SIGNATURES = {
     "nb_gcn_set_timing": (C.c_int, [ptr, C.c_int]),
     "nb_gcn_read_timing": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "nb_gcn_read_timing_by_class": (C.c_int, [ptr, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "nb_gcn_read_phase_times": (C.c_int, [ptr, C.POINTER(C.c_double)]),
     "nb_set_fused_output_layer": (C.c_int, [C.c_int]),
     "nb_set_pdl": (C.c_int, [C.c_int]),
     "nb_output_layer_supported": (C.c_int, [C.c_uint32, C.c_uint32]),

@@ -353,7 +353,7 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
     sort_short_rows_kernel<<<grid_for((uint64_t)s * 32, kThreads), kThreads, 0, stream>>>(
         d_row_offset, s, d_column_indices, long_rows, flags + 1);
     NB_LAUNCH_CHECK();
-    sort_long_rows_kernel<<<kNumSMs * 4, kThreads, 0, stream>>>(d_row_offset, d_column_indices, v, long_rows,
+    sort_long_rows_kernel<<<num_sms() * 4, kThreads, 0, stream>>>(d_row_offset, d_column_indices, v, long_rows,
                                                                 flags + 1, scratch);
     NB_LAUNCH_CHECK();
     return 0;
@@ -389,7 +389,7 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
     sort_short_rows_kernel<<<grid_for((uint64_t)s * 32, kThreads), kThreads, 0, stream>>>(
         d_row_offset, s, d_column_indices, long_rows, flags + 1);
     NB_LAUNCH_CHECK();
-    sort_long_rows_kernel<<<kNumSMs * 4, kThreads, 0, stream>>>(d_row_offset, d_column_indices, v, long_rows,
+    sort_long_rows_kernel<<<num_sms() * 4, kThreads, 0, stream>>>(d_row_offset, d_column_indices, v, long_rows,
                                                                 flags + 1, scratch);
     NB_LAUNCH_CHECK();
     if (d_w_bwd) {

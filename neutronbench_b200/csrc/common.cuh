@@ -11,7 +11,50 @@
 
 namespace nb {
 
-constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+// Number of SMs of the current device (148 on B200: 2 dies x 74), asked from the driver once per device.
+int num_sms();
+
+// Flag per device for set-up that CUDA keeps per device (function attributes such as the dynamic shared-memory
+// limit): need() is true until done() has been called with that device current.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  bool flag[kMaxDevices] = {};
+  static int dev() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return -1;
+    return d;
+  }
+  bool need() const { const int d = dev(); return d < 0 || !flag[d]; }
+  void done() { const int d = dev(); if (d >= 0) flag[d] = true; }
+};
+
+// Tuning switches.  Stand-alone entry points read the process defaults (changed by the nb_set_* calls);
+// an nb_gcn handle copies the defaults when it is created, keeps its own copy (nb_gcn_set_option) and makes it
+// current for the calling thread while one of its entry points runs, so that two handles, or two threads,
+// never see each other's settings.
+struct Tuning {
+  int gemm_mode = 1;             // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
+  int gemm_force_tc = 0;         // tensor cores for every product size
+  int use_pdl = 1;               // programmatic dependent launch for the training half's kernels
+  int fuse_output_layer = 1;     // last layer + loss + its gradients in two launches
+  int staged_spmm = 1;           // TMA-staged aggregation where its alignment rules hold
+  int spmm_ring = 1;             // per-edge ring variant when rows are not cut into panels
+  int staged_min_width = 256;    // narrowest row (floats) that takes the staged path
+  int l2_prefetch = 0;           // segment kernel: prefetch rows into L2 two segments ahead
+  int l2_hint = 1;               // ring kernel, fused weights: rows used by one edge only are copied with the
+                                 // L2 evict-first policy (1); 2: rows with more uses evict-last as well; 0: off
+  int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
+  int reserve_sms = 0;           // SMs the one-CTA-per-SM aggregation kernel leaves to kernels that run beside it
+  uint32_t ring_group_shift = 1; // ring kernel: 1 << shift row slots share one barrier
+  uint64_t l2_panel_bytes = 0;   // working-set target of one column panel (0: no panels)
+};
+Tuning &default_tuning();
+Tuning &tuning();                // the calling thread's current settings
+struct TuningScope {
+  Tuning *prev;
+  explicit TuningScope(Tuning *t);
+  ~TuningScope();
+};
 
 void set_error(const char *fmt, ...);
 
@@ -59,10 +102,10 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 inline unsigned div_up(uint64_t a, uint64_t b) { return (unsigned)((a + b - 1) / b); }
 
 // Grid for a grid-stride kernel: enough blocks to cover `items`, capped at `waves` full waves of the
-// 148 SMs at `blocks_per_sm` resident blocks each.
+// device's SMs at `blocks_per_sm` resident blocks each.
 inline unsigned grid_for(uint64_t items, unsigned block, unsigned blocks_per_sm = 8, unsigned waves = 4) {
   uint64_t need = (items + block - 1) / block;
-  uint64_t cap = (uint64_t)kNumSMs * blocks_per_sm * waves;
+  uint64_t cap = (uint64_t)num_sms() * blocks_per_sm * waves;
   if (need < 1) need = 1;
   return (unsigned)(need < cap ? need : cap);
 }
@@ -97,8 +140,10 @@ namespace nb {
 struct TmaSpmmArgs {
   const float *x;          // base of the rows that the TMA unit copies: row(ref) = x + ref * x_ld
   size_t x_ld;             // pitch in floats, a multiple of 4; x is 16-byte aligned
-  const float *miss;       // base of rows whose reference has bit 31 set (copied by the lanes), or null
+  const float *miss;       // base of rows whose reference has bit 31 set, or null
   size_t miss_ld;
+  int miss_local;          // 1: `miss` holds one row per source of the block (row li), not one per vertex (row g)
+  int miss_bulk;           // 1: rows of `miss` are 16-byte aligned device memory: the TMA unit copies them too
   float *y;                // n x F output
   size_t y_ld;             // pitch of y in floats (0 = F)
   const uint32_t *offs;    // n + 1 offsets
@@ -114,6 +159,8 @@ struct TmaSpmmArgs {
   uint32_t src_rows_hint;  // number of distinct rows the references can name (0 = unknown): sizes the panels
   uint32_t slot_bytes, copy_bytes, seg, grp_shift, fpad, panels, panel_floats;   // filled by launch_spmm_tma
   int l2_prefetch;
+  int l2_hint;             // ring kernel: L2 eviction policy per copied row (Tuning::l2_hint)
+  int y_stream;            // ring kernel: streaming stores for y
   int out_vec;             // widest vector (floats) usable for y and act rows: 4, 2 or 1
 };
 bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F);
@@ -122,6 +169,19 @@ int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, ui
                        const uint32_t *hashmap, bool feat_is_hit, const float *norm_idx, const float *norm_row,
                        uint32_t *ref, float *w, cudaStream_t stream);
 int read_tma_error_flag(unsigned int *value);
+int read_gather_error_flag(unsigned int *value);
+int read_spmm_error_flag(unsigned int *value);
+int read_loss_error_flag(unsigned int *value);
+int reset_tma_error_flag();
+int reset_tc_error_flag();
+int reset_gather_error_flag();
+int reset_loss_error_flag();
+// nb_feature_gather with an output pitch; misses_only = 1 copies only the rows that have no cache slot (row i of the
+// output belongs to source[i] either way).
+int feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const float *feat, size_t feat_ld,
+                        const float *const *feat_shards, uint32_t num_shards, uint32_t shard_rows, const float *d_cache,
+                        size_t cache_ld, const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
+                        void *stream);
 int read_tc_error_flag(unsigned int *value);
 int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
                      int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream);
@@ -133,6 +193,7 @@ int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
                     cudaStream_t stream);
 int read_tma_gemm_error_flag(unsigned int *value);
+int reset_tma_gemm_error_flag();
 int sample_hop_impl(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices, const uint32_t *d_dst,
                     uint32_t v, int fanout, const uint32_t *d_column_offset, uint64_t seed, uint32_t hop,
                     uint32_t *d_row_indices, uint32_t *bitmap, void *stream);
@@ -147,13 +208,7 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
                                  const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
                                  const uint32_t *d_row_indices, const uint32_t *d_column_offset,
                                  const float *d_src_norm, const float *d_dst_norm, uint32_t v, uint32_t s, uint32_t e,
-                                 uint32_t F, void *stream);
-extern int g_gemm_mode;    // 0: CUDA cores (fp32 FMA), 1: tcgen05 3xTF32 (fp32-level accuracy), 2: tcgen05 TF32
-extern uint64_t g_l2_panel_bytes;
-extern uint32_t g_ring_group_shift;
-extern int g_staged_min_width;
-extern int g_spmm_ring;
-extern int g_staged_spmm;  // 1: use the TMA-staged aggregation where its alignment rules hold
+                                 uint32_t F, void *stream, const float *d_stage, size_t stage_ld);
 
 // Scoped mark/release so that a call's scratch is returned to the arena when it ends.
 struct WsScope {
@@ -182,7 +237,6 @@ int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, 
 // go right afterwards.  Kernels launched without the attribute execute the two instructions as no-ops.
 // ---------------------------------------------------------------------------------------------
 namespace nb {
-extern int g_use_pdl;   // nb_set_pdl
 
 #if defined(__CUDACC__)
 __device__ __forceinline__ void pdl_enter() {
@@ -202,7 +256,7 @@ inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  cfg.numAttrs = tuning().use_pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif

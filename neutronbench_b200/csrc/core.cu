@@ -8,7 +8,63 @@ namespace nb {
 
 static thread_local char g_err[512] = "";
 unsigned long long g_launches = 0;
-int g_use_pdl = 1;
+
+static Tuning g_default_tuning;
+static thread_local Tuning *t_tuning = nullptr;
+Tuning &default_tuning() { return g_default_tuning; }
+Tuning &tuning() { return t_tuning ? *t_tuning : g_default_tuning; }
+TuningScope::TuningScope(Tuning *t) : prev(t_tuning) { t_tuning = t; }
+TuningScope::~TuningScope() { t_tuning = prev; }
+
+}  // namespace nb
+
+static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes inter-process handles as 64 bytes");
+
+NB_API int nb_shard_alloc(void **d_ptr, size_t bytes) {
+  NB_REQUIRE(d_ptr && bytes > 0, "nb_shard_alloc: null pointer or empty shard");
+  NB_CUDA(cudaMalloc(d_ptr, bytes));
+  return 0;
+}
+NB_API int nb_shard_free(void *d_ptr) {
+  if (d_ptr) NB_CUDA(cudaFree(d_ptr));
+  return 0;
+}
+NB_API int nb_shard_upload(void *d_dst, const void *src, size_t bytes) {
+  NB_REQUIRE(d_dst && src, "nb_shard_upload: null pointer");
+  NB_CUDA(cudaMemcpy(d_dst, src, bytes, cudaMemcpyDefault));
+  return 0;
+}
+NB_API int nb_shard_export(void *d_ptr, unsigned char handle[64]) {
+  NB_REQUIRE(d_ptr && handle, "nb_shard_export: null pointer");
+  cudaIpcMemHandle_t h;
+  NB_CUDA(cudaIpcGetMemHandle(&h, d_ptr));
+  memcpy(handle, &h, sizeof(h));
+  return 0;
+}
+NB_API int nb_shard_open(const unsigned char handle[64], void **d_ptr) {
+  NB_REQUIRE(handle && d_ptr, "nb_shard_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  NB_CUDA(cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+NB_API int nb_shard_close(void *d_ptr) {
+  if (d_ptr) NB_CUDA(cudaIpcCloseMemHandle(d_ptr));
+  return 0;
+}
+
+namespace nb {
+int num_sms() {
+  static int cached[kMaxDevices] = {};
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return 148;
+  if (cached[d] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) return 148;
+    cached[d] = n;
+  }
+  return cached[d];
+}
 
 void set_error(const char *fmt, ...) {
   va_list ap;

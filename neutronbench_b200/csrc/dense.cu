@@ -6,8 +6,6 @@
 
 namespace nb {
 
-int g_gemm_mode = 1;   // tcgen05 with the three-term TF32 split
-int g_gemm_force_tc = 0;   // 1: send even tiny products to the tensor-core kernel (tests)
 
 // ------------------------------------------------------------------------------------ GEMM (SIMT)
 // C[M x N] = op(A) op(B), element access through strides so that NN / TN / NT share one kernel.
@@ -109,6 +107,10 @@ __global__ void relu_dropout_kernel(float *z, int64_t n, float p, float scale, u
 }
 
 // ------------------------------------------------------------------------------------ loss
+// Set (never cleared by the kernels) when a label was outside [0, C): that row then counts with loss 0, no hit and a
+// zero gradient instead of indexing the logits with it.
+__device__ unsigned int g_loss_error = 0;
+
 // One warp per row: max, log-sum-exp, NLL at the label, gradient (softmax - onehot)/B, argmax hit.
 __global__ void softmax_nll_rows_kernel(const float *__restrict__ logits, const int64_t *__restrict__ label, int64_t B,
                                         int64_t C, float *dlogits, float *row_loss, float *row_hit) {
@@ -132,15 +134,17 @@ __global__ void softmax_nll_rows_kernel(const float *__restrict__ logits, const 
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float lse = logf(sum);
     const int64_t y = label[i];
+    const bool labelled = y >= 0 && y < C;
     if (lane == 0) {
-      row_loss[i] = -((z[y] - m) - lse);
-      row_hit[i] = (arg == y) ? 1.0f : 0.0f;
+      if (!labelled) atomicOr(&g_loss_error, 1u);
+      row_loss[i] = labelled ? -((z[y] - m) - lse) : 0.0f;
+      row_hit[i] = (labelled && arg == y) ? 1.0f : 0.0f;
     }
     if (dlogits) {
       const float inv_b = 1.0f / (float)B;
       for (int64_t c = lane; c < C; c += 32) {
         const float pr = expf(z[c] - m - lse);
-        dlogits[i * C + c] = (pr - (c == y ? 1.0f : 0.0f)) * inv_b;
+        dlogits[i * C + c] = labelled ? (pr - (c == y ? 1.0f : 0.0f)) * inv_b : 0.0f;
       }
     }
   }
@@ -274,13 +278,15 @@ __global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float lse = logf(sum);
     const int64_t lab = label_table[dst[row]];
+    const bool labelled = lab >= 0 && lab < (int64_t)C;
     const float z_lab = __shfl_sync(0xffffffffu, (lab >= 32) ? z1 : z0, (unsigned)(lab & 31));
     if (lane == 0) {
-      row_loss[row] = -((z_lab - m) - lse);
-      row_hit[row] = ((int64_t)arg == lab) ? 1.0f : 0.0f;
+      if (!labelled) atomicOr(&g_loss_error, 1u);
+      row_loss[row] = labelled ? -((z_lab - m) - lse) : 0.0f;
+      row_hit[row] = (labelled && (int64_t)arg == lab) ? 1.0f : 0.0f;
     }
     if (train) {
-      const float inv_b = 1.0f / (float)B;
+      const float inv_b = labelled ? 1.0f / (float)B : 0.0f;   // a row without a valid label has no gradient
       if (c0 < C) dzs[warp * kOutMaxC + c0] = (expf(z0 - m - lse) - ((int64_t)c0 == lab ? 1.0f : 0.0f)) * inv_b;
       if (c1 < C) dzs[warp * kOutMaxC + c1] = (expf(z1 - m - lse) - ((int64_t)c1 == lab ? 1.0f : 0.0f)) * inv_b;
       __syncwarp();
@@ -361,8 +367,8 @@ NB_API int nb_gemm(nb_ws *ws, const float *d_a, const float *d_b, float *d_c, in
 namespace nb {
 
 bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K) {
-  const bool tiny = 2.0 * (double)M * (double)N * (double)K < 4.0e7 && g_gemm_force_tc == 0;
-  return g_gemm_mode != 0 && !tiny;
+  const bool tiny = 2.0 * (double)M * (double)N * (double)K < 4.0e7 && tuning().gemm_force_tc == 0;
+  return tuning().gemm_mode != 0 && !tiny;
 }
 
 // nb_gemm with operand pitches (floats): A is stored with pitch lda >= its row length, B with ldb; C is dense.
@@ -380,15 +386,15 @@ int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t 
   // Small products (the output layer and its gradients) finish sooner on the CUDA cores than the
   // tensor-core kernel takes to set up its pipeline (TMEM allocation, 200 KB of staging buffers).
   if (gemm_uses_tensor_cores(M, N, K))
-    return gemm_tensor_core(ws, d_a, lda, d_b, ldb, d_c, M, N, K, trans_a, trans_b, g_gemm_mode, stream);
+    return gemm_tensor_core(ws, d_a, lda, d_b, ldb, d_c, M, N, K, trans_a, trans_b, tuning().gemm_mode, stream);
   GemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
   g.sa_i = trans_a ? 1 : lda;  g.sa_k = trans_a ? lda : 1;
   g.sb_k = trans_b ? 1 : ldb;  g.sb_j = trans_b ? ldb : 1;
   const int64_t tiles = ((M + kTM - 1) / kTM) * ((N + kTN - 1) / kTN);
   int splits = 1;
-  if (tiles < 2 * kNumSMs && K >= 4 * kTK * 8) {
-    splits = (int)((2 * kNumSMs + tiles - 1) / tiles);
+  if (tiles < 2 * num_sms() && K >= 4 * kTK * 8) {
+    splits = (int)((2 * num_sms() + tiles - 1) / tiles);
     const int64_t max_splits = K / (kTK * 8);
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
@@ -418,10 +424,23 @@ int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t 
 
 }  // namespace nb
 
+namespace nb {
+int read_loss_error_flag(unsigned int *value) {
+  NB_CUDA(cudaMemcpyFromSymbol(value, g_loss_error, sizeof(unsigned int)));
+  return 0;
+}
+int reset_loss_error_flag() {
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_loss_error, &zero, sizeof(unsigned int)));
+  return 0;
+}
+}  // namespace nb
+
 NB_API int nb_set_gemm_mode(int mode) {
-  const int old = g_gemm_mode;
-  if (mode >= 0 && mode <= 2) { g_gemm_mode = mode; g_gemm_force_tc = 0; }
-  if (mode >= 16 && mode <= 18) { g_gemm_mode = mode - 16; g_gemm_force_tc = 1; }   // 17 / 18: tensor cores for every size
+  nb::Tuning &t = nb::default_tuning();
+  const int old = t.gemm_mode;
+  if (mode >= 0 && mode <= 2) { t.gemm_mode = mode; t.gemm_force_tc = 0; }
+  if (mode >= 16 && mode <= 18) { t.gemm_mode = mode - 16; t.gemm_force_tc = 1; }   // 17 / 18: tensor cores for every size
   return old;
 }
 
@@ -494,10 +513,10 @@ NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const 
   float *part = train ? ws->alloc_n<float>((size_t)ctas * hc) : nullptr;
   if (!row_loss || !row_hit || (train && !part)) return fail(NB_ERR_NOMEM, "nb_output_layer: workspace arena exhausted");
   const size_t smem = output_layer_smem(H, C);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(output_layer_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    configured = true;
+    configured.done();
   }
   NB_CUDA(launch_chained(output_layer_rows_kernel, dim3(ctas), dim3(kOutRows * 32), smem, stream, d_y, d_w, d_label, d_dst, B,
                          H, C, C | 1u, train ? 1 : 0, train ? d_dy : (float *)nullptr, part, row_loss, row_hit));
@@ -510,8 +529,8 @@ NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const 
 }
 
 NB_API int nb_set_pdl(int enabled) {
-  const int old = nb::g_use_pdl;
-  nb::g_use_pdl = enabled != 0;
+  const int old = nb::default_tuning().use_pdl;
+  nb::default_tuning().use_pdl = enabled != 0;
   return old;
 }
 
@@ -535,8 +554,7 @@ constexpr int64_t kNoAllocMaxRows = 65536;
 static __device__ __align__(256) float g_loss_scratch[2 * kNoAllocMaxRows];   // [row_loss | row_hit]
 
 namespace {
-constexpr int kMaxDevices = 64;
-float *g_loss_scratch_addr[kMaxDevices] = {};   // device address of g_loss_scratch, per device
+float *g_loss_scratch_addr[nb::kMaxDevices] = {};   // device address of g_loss_scratch, per device
 }  // namespace
 
 // In host code `g_loss_scratch` names a host-side shadow of the symbol, not device memory, so the
@@ -544,7 +562,7 @@ float *g_loss_scratch_addr[kMaxDevices] = {};   // device address of g_loss_scra
 static int loss_scratch_address(float **out) {
   int dev = -1;
   NB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return nb::fail(NB_ERR_INVALID, "nb_softmax_nll_static: device index out of range");
+  if (dev < 0 || dev >= nb::kMaxDevices) return nb::fail(NB_ERR_INVALID, "nb_softmax_nll_static: device index out of range");
   float *p = __atomic_load_n(&g_loss_scratch_addr[dev], __ATOMIC_ACQUIRE);
   if (p == nullptr) {
     void *addr = nullptr;

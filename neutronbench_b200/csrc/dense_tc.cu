@@ -446,10 +446,10 @@ __global__ void __launch_bounds__(NS + 32, S <= 3 ? kCtasPerSM : 1) gemm_tc_kern
 template <int BN, bool A_MN, bool B_MN, int S, int NS>
 static int launch_tc_s(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   constexpr size_t smem = (size_t)(2 * S * (TileFloats<kBM>::value + TileFloats<BN>::value)) * sizeof(float) + 128;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN, S, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.done();
   }
   gemm_tc_kernel<BN, A_MN, B_MN, S, NS><<<grid, NS + 32, smem, stream>>>(g);
   NB_LAUNCH_CHECK();
@@ -471,7 +471,7 @@ __global__ void tc_splitk_reduce_kernel(const float *__restrict__ partial, float
 template <int BN, bool A_MN, bool B_MN>
 static int launch_tc(const TcGemmArgs &g, dim3 grid, cudaStream_t stream) {
   const int64_t ctas = (int64_t)grid.x * grid.y * grid.z;
-  int stages = ctas <= kNumSMs ? 6 : 3;
+  int stages = ctas <= num_sms() ? 6 : 3;
   int stagers = stages >= 4 ? 512 : 256;
   if (stages >= 6) {
     if (stagers == 512) return launch_tc_s<BN, A_MN, B_MN, 6, 512>(g, grid, stream);
@@ -521,8 +521,8 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b,
   const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   // Split-K towards one CTA per SM; ranges are multiples of 32 so that both kernels cut K at the same places.
   int splits = 1;
-  if (tiles < kNumSMs && K >= 512) {
-    splits = (int)(kNumSMs / tiles);
+  if (tiles < num_sms() && K >= 512) {
+    splits = (int)(num_sms() / tiles);
     const int64_t max_splits = K / 256;
     if (splits > max_splits) splits = (int)max_splits;
     if (splits < 1) splits = 1;
@@ -573,6 +573,11 @@ int read_tc_error_flag(unsigned int *value) {
   NB_TRY(read_tma_gemm_error_flag(&b));
   *value = a | b;
   return 0;
+}
+int reset_tc_error_flag() {
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_tc_gemm_error, &zero, sizeof(unsigned int)));
+  return reset_tma_gemm_error_flag();
 }
 
 }  // namespace nb

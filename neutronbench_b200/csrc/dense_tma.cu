@@ -425,10 +425,10 @@ static bool make_operand_map(CUtensorMap *map, const float *base, bool mn, int64
 template <int BN, bool A_MN, bool B_MN>
 static int launch_tma(const CUtensorMap &ma, const CUtensorMap &mb, const TmaGemmArgs &g, dim3 grid, cudaStream_t stream) {
   constexpr size_t smem = (size_t)kTmaStages * 2 * (kBM + BN) * kTmaBK * 4 + 256;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(gemm_tma_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.done();
   }
   NB_CUDA(launch_chained(gemm_tma_kernel<BN, A_MN, B_MN>, grid, dim3(kTmaThreads), smem, stream, ma, mb, g));
   NB_LAUNCH_CHECK();
@@ -470,23 +470,23 @@ int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb
 // C = Y W in the row-balanced form; applicable to NN products with N <= 128 and no split-K.
 bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K) {
   if (N > kBM || N < 32 || K < kTmaBK || M < 8192) return false;   // small products: plain tiles and split-K
-  const int64_t rows = ((M + kNumSMs - 1) / kNumSMs + 15) / 16 * 16;
+  const int64_t rows = ((M + num_sms() - 1) / num_sms() + 15) / 16 * 16;
   return rows <= kRowsMax && M >= rows;
 }
 
 int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
                          int64_t K, int mode, cudaStream_t stream) {
-  const int rows = (int)(((M + kNumSMs - 1) / kNumSMs + 15) / 16 * 16);
+  const int rows = (int)(((M + num_sms() - 1) / num_sms() + 15) / 16 * 16);
   CUtensorMap my, mw;
   if (!make_operand_map(&my, d_y, false, M, K, ldy, rows) || !make_operand_map(&mw, d_w, true, N, K, ldw, 0))
     return fail(NB_ERR_CUDA, "nb_gemm: cuTensorMapEncodeTiled failed");
   TmaRowsArgs g{};
   g.c = c; g.M = M; g.N = N; g.K = K; g.rows_per_cta = rows; g.mode = mode;
   constexpr size_t smem = (size_t)kTmaStages * 2 * (kBM + kRowsMax) * kTmaBK * 4 + 256;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(gemm_tma_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    configured.done();
   }
   const unsigned grid = (unsigned)((M + rows - 1) / rows);
   NB_CUDA(launch_chained(gemm_tma_rows_kernel, dim3(grid), dim3(kTmaThreads), smem, stream, my, mw, g));
@@ -496,6 +496,11 @@ int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_
 
 int read_tma_gemm_error_flag(unsigned int *value) {
   NB_CUDA(cudaMemcpyFromSymbol(value, g_tma_gemm_error, sizeof(unsigned int)));
+  return 0;
+}
+int reset_tma_gemm_error_flag() {
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_tma_gemm_error, &zero, sizeof(unsigned int)));
   return 0;
 }
 

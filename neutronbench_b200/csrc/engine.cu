@@ -1,6 +1,7 @@
 // Whole training step issued from native code: the batch-loop body of the reference toolkit
 // (toolkits/GCN_GPU_NEIGHBOR.hpp:604-713) as a sequence of this library's kernels on one stream.
 // No kernels of its own: it exists so that a step costs one host call and no per-step allocations.
+#include <chrono>
 #include <condition_variable>
 #include <deque>
 #include <mutex>
@@ -22,6 +23,8 @@ struct nb_gcn_batch {
   nb_ws *ws = nullptr;
   uint32_t layers = 0;
   BlockArrays blk[NB_MAX_LAYERS];   // index 0 = input side (core/ntsSampler.hpp:1088)
+  float *stage = nullptr;           // rows of the input block's sources that have no cache slot (row li), or null
+  size_t stage_ld = 0;
   cudaEvent_t sampled = nullptr;    // recorded when the last sampling kernel is enqueued
   cudaEvent_t consumed = nullptr;   // recorded after the last kernel that reads the arrays
   bool in_use = false;              // a compute call has been enqueued since the last sample call
@@ -42,6 +45,7 @@ struct SampleJob {
 
 struct nb_gcn {
   nb_gcn_config cfg;
+  nb::Tuning tuning;   // this handle's switches: the process defaults at creation, then nb_gcn_set_option
   nb_ws *ws;
   nb_gcn_batch own;    // the batch nb_gcn_step samples into: shares `ws` with the activations
   uint32_t draws;      // sample_one calls so far: part of the Philox counter of the sampler
@@ -53,7 +57,9 @@ struct nb_gcn {
   std::vector<cudaEvent_t> ev_pool;   // pairs: start, stop
   size_t ev_used = 0;
   uint64_t timed_bytes = 0;
-  std::vector<int> ev_class;         // per pair: 0 = layer-0 forward aggregation, 1 = any other aggregation
+  std::vector<int> ev_class;         // per pair: 0 = layer-0 forward aggregation, 1 = any other aggregation,
+                                     // 2 = a whole compute call (forward, loss, backward), 3 = staging of uncached rows
+  double sample_host_ms = 0.0;       // wall time the sampling halves took on their threads while timing was on
   std::vector<uint64_t> ev_bytes;
   // cross-stream ordering of gradients and weights when the caller runs the update on a stream of its own
   cudaEvent_t ev_grad = nullptr;      // recorded after the last kernel of a compute call
@@ -70,7 +76,6 @@ struct nb_gcn {
   bool stop = false;
 };
 
-int g_fuse_output_layer = 1;   // nb_set_fused_output_layer
 
 namespace {
 
@@ -97,23 +102,31 @@ struct AggTimer {
   nb_gcn *g;
   cudaStream_t st;
   bool on;
+  cudaEvent_t stop = nullptr;
+  // The pool is shared by the thread that enqueues the training half and the sampler threads (class 3): a pair is
+  // reserved under the handle's mutex and its two events are recorded outside it.
   AggTimer(nb_gcn *g_, void *stream, uint64_t bytes, int cls = 1) : g(g_), st(nb::as_stream(stream)), on(g_->timing) {
     if (!on) return;
-    if (g->ev_used + 2 > g->ev_pool.size()) {
-      cudaEvent_t a, b;
-      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { on = false; return; }
-      g->ev_pool.push_back(a);
-      g->ev_pool.push_back(b);
+    cudaEvent_t start;
+    {
+      std::lock_guard<std::mutex> lk(g->mu);
+      if (g->ev_used + 2 > g->ev_pool.size()) {
+        cudaEvent_t a, b;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { on = false; return; }
+        g->ev_pool.push_back(a);
+        g->ev_pool.push_back(b);
+      }
+      start = g->ev_pool[g->ev_used];
+      stop = g->ev_pool[g->ev_used + 1];
+      g->ev_used += 2;
+      g->timed_bytes += bytes;
+      g->ev_class.push_back(cls);
+      g->ev_bytes.push_back(bytes);
     }
-    cudaEventRecord(g->ev_pool[g->ev_used], st);
-    g->timed_bytes += bytes;
-    g->ev_class.push_back(cls);
-    g->ev_bytes.push_back(bytes);
+    cudaEventRecord(start, st);
   }
   ~AggTimer() {
-    if (!on) return;
-    cudaEventRecord(g->ev_pool[g->ev_used + 1], st);
-    g->ev_used += 2;
+    if (on) cudaEventRecord(stop, st);
   }
 };
 
@@ -124,7 +137,12 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   NB_REQUIRE(cfg->num_layers >= 1 && cfg->num_layers <= NB_MAX_LAYERS, "nb_gcn_create: 1..8 layers");
   NB_REQUIRE(cfg->d_graph_column_offset && cfg->d_graph_row_indices && cfg->d_label, "nb_gcn_create: null graph or labels");
   NB_REQUIRE(cfg->d_W && cfg->d_grad && cfg->d_M && cfg->d_V, "nb_gcn_create: null parameter buffers");
-  NB_REQUIRE(cfg->feat || (cfg->d_cache && cfg->d_hashmap), "nb_gcn_create: no feature store");
+  NB_REQUIRE(cfg->feat || cfg->d_feat_shards || (cfg->d_cache && cfg->d_hashmap), "nb_gcn_create: no feature store");
+  NB_REQUIRE(cfg->d_feat_shards == nullptr || (cfg->num_shards > 0 && cfg->shard_rows > 0 &&
+                                               (uint64_t)cfg->num_shards * cfg->shard_rows >= cfg->num_vertices),
+             "nb_gcn_create: the shards of the feature table do not cover every vertex");
+  NB_REQUIRE(cfg->d_feat_shards == nullptr || cfg->stage_misses,
+             "nb_gcn_create: a sharded feature table is read through the staging table (set stage_misses)");
   NB_REQUIRE(cfg->drop_rate >= 0.0f && cfg->drop_rate < 1.0f, "nb_gcn_create: drop rate must be in [0,1)");
   NB_REQUIRE(cfg->classes <= 1 || cfg->classes == cfg->layer_size[cfg->num_layers],
              "nb_gcn_create: with classes > 1 the last layer must have one output per class");
@@ -135,6 +153,7 @@ NB_API int nb_gcn_create(nb_gcn **out, const nb_gcn_config *cfg, nb_ws *ws) {
   nb_gcn *g = new (std::nothrow) nb_gcn();
   if (!g) return nb::fail(NB_ERR_NOMEM, "nb_gcn_create: out of host memory");
   g->cfg = *cfg;
+  g->tuning = nb::default_tuning();
   g->ws = ws;
   g->own.ws = ws;
   NB_CUDA(cudaGetDevice(&g->device));
@@ -173,7 +192,9 @@ NB_API int nb_gcn_destroy(nb_gcn *g) {
 
 NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
   NB_REQUIRE(g != nullptr, "nb_gcn_set_timing: null pointer");
+  std::lock_guard<std::mutex> lk(g->mu);
   g->timing = enabled != 0;
+  g->sample_host_ms = 0.0;
   g->ev_used = 0;
   g->timed_bytes = 0;
   g->ev_class.clear();
@@ -181,14 +202,16 @@ NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
   return 0;
 }
 
-NB_API int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]) {
-  NB_REQUIRE(g && ms && bytes && launches, "nb_gcn_read_timing_by_class: null pointer");
-  for (int k = 0; k < 2; k++) { ms[k] = 0.0; bytes[k] = 0; launches[k] = 0; }
+namespace {
+// Sums the recorded event pairs per class (4 classes) and forgets them.
+int drain_events(nb_gcn *g, double ms[4], uint64_t bytes[4], uint64_t launches[4]) {
+  std::lock_guard<std::mutex> lk(g->mu);
+  for (int k = 0; k < 4; k++) { ms[k] = 0.0; bytes[k] = 0; launches[k] = 0; }
   for (size_t i = 0; i + 1 < g->ev_used; i += 2) {
     NB_CUDA(cudaEventSynchronize(g->ev_pool[i + 1]));
     float t = 0.0f;
     NB_CUDA(cudaEventElapsedTime(&t, g->ev_pool[i], g->ev_pool[i + 1]));
-    const int k = g->ev_class[i / 2] == 0 ? 0 : 1;
+    const int k = g->ev_class[i / 2] & 3;
     ms[k] += t;
     bytes[k] += g->ev_bytes[i / 2];
     launches[k]++;
@@ -197,6 +220,30 @@ NB_API int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2
   g->timed_bytes = 0;
   g->ev_class.clear();
   g->ev_bytes.clear();
+  return 0;
+}
+}  // namespace
+
+NB_API int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]) {
+  NB_REQUIRE(g && ms && bytes && launches, "nb_gcn_read_timing_by_class: null pointer");
+  double m[4];
+  uint64_t b[4], n[4];
+  NB_TRY(drain_events(g, m, b, n));
+  for (int k = 0; k < 2; k++) { ms[k] = m[k]; bytes[k] = b[k]; launches[k] = n[k]; }
+  return 0;
+}
+
+NB_API int nb_gcn_read_phase_times(nb_gcn *g, double ms[4]) {
+  NB_REQUIRE(g && ms, "nb_gcn_read_phase_times: null pointer");
+  double m[4];
+  uint64_t b[4], n[4];
+  NB_TRY(drain_events(g, m, b, n));
+  std::lock_guard<std::mutex> lk(g->mu);
+  ms[0] = g->sample_host_ms;
+  ms[1] = m[3];
+  ms[2] = m[0] + m[1];
+  ms[3] = m[2] > ms[2] ? m[2] - ms[2] : 0.0;
+  g->sample_host_ms = 0.0;
   return 0;
 }
 
@@ -228,6 +275,16 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
   const nb_gcn_config &c = g->cfg;
   const uint32_t L = c.num_layers;
   nb_ws *ws = bt->ws;
+  struct HostTimer {   // wall time of this call, added to the handle's sampling total while timing is on
+    nb_gcn *g;
+    std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+    ~HostTimer() {
+      if (!g->timing) return;
+      const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+      std::lock_guard<std::mutex> lk(g->mu);
+      g->sample_host_ms += ms;
+    }
+  } host_timer{g};
   NB_TRY(ensure_events(bt));
   if (bt->in_use) {   // the arrays of the batch sampled here before may still be read by a compute call
     NB_CUDA(cudaEventSynchronize(bt->consumed));
@@ -280,6 +337,21 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
   }
   bt->layers = L;
   for (uint32_t l = 0; l < L; l++) bt->blk[l] = hops[L - 1 - l];
+  // Rows of the input block's sources that are not cached, fetched here, in the sampling half, once per distinct
+  // source: from mapped host memory or from the GPU that owns the row's shard (plain loads).  The aggregation then
+  // reads device memory only.
+  bt->stage = nullptr;
+  bt->stage_ld = 0;
+  if (c.stage_misses && c.fuse_gather && (c.feat || c.d_feat_shards) && bt->blk[0].s > 0) {
+    const Block &b0 = bt->blk[0];
+    const uint32_t F0 = c.layer_size[0];
+    bt->stage_ld = (F0 + 3) / 4 * 4;
+    NB_TRY(arena(ws, (size_t)b0.s * bt->stage_ld, &bt->stage));
+    AggTimer t(g, stream, 0, 3);
+    NB_TRY(nb::feature_gather_impl(bt->stage, bt->stage_ld, c.d_hashmap != nullptr, c.feat, c.feat_ld, c.d_feat_shards,
+                                   c.num_shards, c.shard_rows, c.d_cache, c.cache_ld, c.d_hashmap, b0.source, b0.s, F0,
+                                   stream));
+  }
   NB_CUDA(cudaEventRecord(bt->sampled, nb::as_stream(stream)));
   return 0;
 }
@@ -295,6 +367,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   }
   const Block *blk = bt->blk;
   uint64_t agg_bytes = 0;
+  AggTimer whole(g, stream, 0, 2);   // the whole training half of the step, for the per-phase epoch times
 
   // ---- forward
   const float p = train ? c.drop_rate : 0.0f;
@@ -316,12 +389,12 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
         AggTimer t(g, stream, bytes_fwd(b, Fi, true, c.d_hashmap != nullptr), 0);
         NB_TRY(nb::spmm_csc_fwd_gather_fused_ld(ws, c.feat, c.feat_ld, c.d_cache, c.cache_ld, c.d_hashmap, b.source,
                                                 Y[0], y_ld[0], b.row_indices, b.column_offset, b.src_norm, b.dst_norm,
-                                                b.v, b.s, b.e, Fi, stream));
+                                                b.v, b.s, b.e, Fi, stream, bt->stage, bt->stage_ld));
         agg_bytes += bytes_fwd(b, Fi, true, c.d_hashmap != nullptr);
       } else {
         NB_TRY(arena(ws, (size_t)b.s * Fi, &X[0]));
-        NB_TRY(nb_feature_gather(X[0], c.feat, c.feat_ld, nullptr, 0, 0, c.d_cache, c.cache_ld, c.d_hashmap, b.source,
-                                 b.s, Fi, stream));
+        NB_TRY(nb_feature_gather(X[0], c.feat, c.feat_ld, c.d_feat_shards, c.num_shards, c.shard_rows, c.d_cache,
+                                 c.cache_ld, c.d_hashmap, b.source, b.s, Fi, stream));
         AggTimer t(g, stream, bytes_fwd(b, Fi, false, false), 0);
         NB_TRY(nb_spmm_csc_fwd_fused(X[0], Y[0], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi,
                                      stream));
@@ -336,7 +409,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
     // after the layer-0 aggregation (which does not touch the weights) has been enqueued.
     if (l == 0 && g->updated_recorded) NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), g->ev_updated, 0));
     // The last layer with one label per vertex runs fused with the loss and its own gradients (nb_output_layer).
-    fused_out = l + 1 == L && c.classes <= 1 && y_ld[l] == Fi && g_fuse_output_layer && nb_output_layer_supported(Fi, Fo);
+    fused_out = l + 1 == L && c.classes <= 1 && y_ld[l] == Fi && nb::tuning().fuse_output_layer && nb_output_layer_supported(Fi, Fo);
     if (fused_out) break;
     NB_TRY(arena(ws, (size_t)b.v * Fo, &X[l + 1]));
     NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], c.d_W + g->w_off[l], Fo, X[l + 1], b.v, Fo, Fi, 0, 0, nb::as_stream(stream)));
@@ -415,6 +488,7 @@ void sampler_main(nb_gcn *g) {
       job = g->jobs.front();
       g->jobs.pop_front();
     }
+    nb::TuningScope scope(&g->tuning);
     const int st = sample_into(g, job.batch, job.draw, job.seeds, job.n, job.train, job.stream);
     {
       std::lock_guard<std::mutex> lk(g->mu);
@@ -457,6 +531,7 @@ NB_API int nb_gcn_sample(nb_gcn *g, nb_gcn_batch *batch, const uint32_t *d_seeds
     g->cv_done.wait(lk, [&] { return !batch->pending; });
     draw = g->draws++;
   }
+  nb::TuningScope scope(&g->tuning);
   return sample_into(g, batch, draw, d_seeds, n_seeds, train, stream);
 }
 
@@ -471,6 +546,7 @@ NB_API int nb_gcn_sample_from_edges(nb_gcn *g, nb_gcn_batch *batch, const uint32
     std::unique_lock<std::mutex> lk(g->mu);
     g->cv_done.wait(lk, [&] { return !batch->pending; });
   }
+  nb::TuningScope scope(&g->tuning);
   return sample_into(g, batch, 0, d_seeds, n_seeds, 0, stream, d_hop_edges, hop_edge_counts);
 }
 
@@ -509,9 +585,36 @@ NB_API int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_coun
 }
 
 NB_API int nb_set_fused_output_layer(int enabled) {
-  const int old = g_fuse_output_layer;
-  g_fuse_output_layer = enabled != 0;
+  const int old = nb::default_tuning().fuse_output_layer;
+  nb::default_tuning().fuse_output_layer = enabled != 0;
   return old;
+}
+
+NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
+  NB_REQUIRE(g && name, "nb_gcn_set_option: null pointer");
+  nb::Tuning &t = g->tuning;
+  const std::string n(name);
+  if (n == "gemm_mode") {
+    NB_REQUIRE((value >= 0 && value <= 2) || (value >= 16 && value <= 18), "nb_gcn_set_option: gemm_mode is 0..2 or 16..18");
+    t.gemm_mode = (int)(value & 15);
+    t.gemm_force_tc = value >= 16;
+  } else if (n == "pdl") t.use_pdl = value != 0;
+  else if (n == "fused_output_layer") t.fuse_output_layer = value != 0;
+  else if (n == "staged_spmm") t.staged_spmm = value != 0;
+  else if (n == "spmm_ring") t.spmm_ring = value != 0;
+  else if (n == "staged_min_width") t.staged_min_width = (int)(value > 0 ? value : 1);
+  else if (n == "ring_group_shift") t.ring_group_shift = value != 0 ? 1u : 0u;
+  else if (n == "l2_panel_bytes") t.l2_panel_bytes = (uint64_t)(value > 0 ? value : 0);
+  else if (n == "l2_prefetch") t.l2_prefetch = value != 0;
+  else if (n == "l2_hint") {
+    NB_REQUIRE(value >= 0 && value <= 2, "nb_gcn_set_option: l2_hint is 0, 1 or 2");
+    t.l2_hint = (int)value;
+  } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
+  else if (n == "reserve_sms") {
+    NB_REQUIRE(value >= 0 && value < 64, "nb_gcn_set_option: reserve_sms is 0..63");
+    t.reserve_sms = (int)value;
+  } else return nb::fail(NB_ERR_INVALID, "nb_gcn_set_option: unknown option");
+  return 0;
 }
 
 NB_API int nb_gcn_set_sampler_threads(nb_gcn *g, int threads) {
@@ -527,6 +630,7 @@ NB_API int nb_gcn_compute(nb_gcn *g, nb_gcn_batch *batch, int train, float *d_st
                           void *stream) {
   NB_REQUIRE(g && batch && d_stats, "nb_gcn_compute: null pointer");
   NB_TRY(wait_sampled(g, batch));
+  nb::TuningScope scope(&g->tuning);
   return compute_from(g, batch, train, d_stats, info, stream);
 }
 
@@ -540,6 +644,7 @@ NB_API int nb_gcn_step(nb_gcn *g, const uint32_t *d_seeds, uint32_t n_seeds, int
     std::lock_guard<std::mutex> lk(g->mu);
     draw = g->draws++;
   }
+  nb::TuningScope scope(&g->tuning);
   NB_TRY(sample_into(g, &g->own, draw, d_seeds, n_seeds, train, stream));
   return compute_from(g, &g->own, train, d_stats, info, stream);
 }
@@ -552,6 +657,7 @@ NB_API int nb_gcn_wait_gradients(nb_gcn *g, void *stream) {
 
 NB_API int nb_gcn_update(nb_gcn *g, void *stream) {
   NB_REQUIRE(g != nullptr, "nb_gcn_update: null pointer");
+  nb::TuningScope scope(&g->tuning);
   const nb_gcn_config &c = g->cfg;
   NB_CUDA(cudaStreamWaitEvent(nb::as_stream(stream), g->ev_grad, 0));   // no-op on the stream that computed them
   NB_TRY(nb_adam(c.d_W, c.d_grad, c.d_M, c.d_V, (int64_t)g->w_off[c.num_layers], c.learn_rate, c.beta1, c.beta2,

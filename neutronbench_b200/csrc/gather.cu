@@ -9,8 +9,14 @@ namespace nb {
 
 constexpr int kWarps = 8;
 
+// Set (never cleared by the kernels) when an id named a row outside every table it could come from: beyond the last
+// shard of a sharded table, or not cached while there is no table to read it from.  The row is skipped, not read.
+__device__ unsigned int g_gather_error = 0;
+
 struct GatherArgs {
   float *x0;
+  size_t x0_ld;            // pitch of x0 in floats
+  int misses_only;         // 1: rows with a cache slot are left untouched (the caller reads them from the cache)
   const float *feat;
   size_t feat_ld;
   const float *const *shards;
@@ -56,19 +62,22 @@ __global__ void __launch_bounds__(kWarps * 32) feature_gather_kernel(const Gathe
       const uint32_t g = a.source[i];
       const uint32_t slot = a.hashmap ? a.hashmap[g] : 0xFFFFFFFFu;
       if (slot != 0xFFFFFFFFu) {
-        src[k] = a.cache + (size_t)slot * a.cache_ld;
+        if (!a.misses_only) src[k] = a.cache + (size_t)slot * a.cache_ld;
       } else if (a.shards) {
         const uint32_t owner = g / a.shard_rows;
-        src[k] = a.shards[owner] + (size_t)(g - owner * a.shard_rows) * a.feat_ld;
-      } else {
+        if (owner < a.num_shards) src[k] = a.shards[owner] + (size_t)(g - owner * a.shard_rows) * a.feat_ld;
+        else if (lane == 0) atomicOr(&g_gather_error, 1u);
+      } else if (a.feat) {
         src[k] = a.feat + (size_t)g * a.feat_ld;
+      } else if (lane == 0) {
+        atomicOr(&g_gather_error, 1u);
       }
     }
   }
   if (col >= a.F) return;
 #pragma unroll
   for (int k = 0; k < kRows; k++) {
-    if (src[k]) copy_vec<VEC>(a.x0 + (grp * kRows + k) * a.F + col, src[k] + col);
+    if (src[k]) copy_vec<VEC>(a.x0 + (grp * kRows + k) * a.x0_ld + col, src[k] + col);
   }
 }
 
@@ -117,6 +126,16 @@ static int pick_vec(uint32_t F, std::initializer_list<size_t> pitches, std::init
   return 1;
 }
 
+int read_gather_error_flag(unsigned int *value) {
+  NB_CUDA(cudaMemcpyFromSymbol(value, g_gather_error, sizeof(unsigned int)));
+  return 0;
+}
+
+int reset_gather_error_flag() {
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_gather_error, &zero, sizeof(unsigned int)));
+  return 0;
+}
 }  // namespace nb
 
 using namespace nb;
@@ -125,7 +144,16 @@ NB_API int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, con
                              uint32_t num_shards, uint32_t shard_rows, const float *d_cache, size_t cache_ld,
                              const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
                              void *stream) {
+  return feature_gather_impl(d_x0, F, 0, feat, feat_ld, feat_shards, num_shards, shard_rows, d_cache, cache_ld, d_hashmap,
+                             d_source, n, F, stream);
+}
+
+int nb::feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const float *feat, size_t feat_ld,
+                            const float *const *feat_shards, uint32_t num_shards, uint32_t shard_rows,
+                            const float *d_cache, size_t cache_ld, const uint32_t *d_hashmap, const uint32_t *d_source,
+                            uint32_t n, uint32_t F, void *stream) {
   if (n == 0) return 0;
+  NB_REQUIRE(x0_ld >= F, "nb_feature_gather: output pitch smaller than width");
   NB_REQUIRE(d_x0 && d_source, "nb_feature_gather: null pointer");
   NB_REQUIRE(F > 0, "nb_feature_gather: feature width is zero");
   NB_REQUIRE(feat || feat_shards || (d_cache && d_hashmap), "nb_feature_gather: no feature store");
@@ -134,11 +162,11 @@ NB_API int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, con
   NB_REQUIRE((!feat && !feat_shards) || feat_ld >= F, "nb_feature_gather: feature pitch smaller than width");
   NB_REQUIRE(d_cache == nullptr || cache_ld >= F, "nb_feature_gather: cache pitch smaller than width");
   GatherArgs a{};
-  a.x0 = d_x0; a.feat = feat; a.feat_ld = feat_ld; a.shards = feat_shards; a.num_shards = num_shards;
+  a.x0 = d_x0; a.x0_ld = x0_ld; a.misses_only = misses_only; a.feat = feat; a.feat_ld = feat_ld; a.shards = feat_shards; a.num_shards = num_shards;
   a.shard_rows = shard_rows; a.cache = d_cache; a.cache_ld = cache_ld; a.hashmap = d_hashmap;
   a.source = d_source; a.n = n; a.F = F;
   // Shard base pointers live in device memory; they are cudaMalloc'ed, hence at least 256-byte aligned.
-  const int vec = pick_vec(F, {(feat || feat_shards) ? feat_ld : (size_t)4, d_cache ? cache_ld : (size_t)4},
+  const int vec = pick_vec(F, {(feat || feat_shards) ? feat_ld : (size_t)4, d_cache ? cache_ld : (size_t)4, x0_ld},
                            {d_x0, feat, d_cache});
   a.tiles = (F + 32 * vec - 1) / (32 * vec);
   const uint64_t warps = (((uint64_t)n + 3) / 4) * a.tiles;

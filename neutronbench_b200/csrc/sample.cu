@@ -352,7 +352,7 @@ NB_API int nb_graph_build_csc(nb_ws *ws, const uint32_t *d_edges, uint64_t num_e
     csc_order_short_columns_kernel<<<grid_for((uint64_t)num_vertices * 32, kThreads), kThreads, 0, stream>>>(
         d_column_offset, num_vertices, tags, d_row_indices, long_cols, long_count);
     NB_LAUNCH_CHECK();
-    csc_order_long_columns_kernel<<<kNumSMs * 4, kThreads, 0, stream>>>(d_column_offset, tags, d_row_indices,
+    csc_order_long_columns_kernel<<<num_sms() * 4, kThreads, 0, stream>>>(d_column_offset, tags, d_row_indices,
                                                                        long_cols, long_count);
     NB_LAUNCH_CHECK();
   }

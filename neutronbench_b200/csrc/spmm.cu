@@ -54,6 +54,10 @@ __device__ __forceinline__ void store_vec(float *p, const float (&v)[VEC]) {
 
 enum SpmmMode { kExplicitW = 0, kFusedW = 1, kFusedGather = 2 };
 
+// Set (never cleared by the kernels) when the gather-fused aggregation met a source that is not cached while there is
+// no table to read it from; the edge is skipped.
+__device__ unsigned int g_spmm_error = 0;
+
 struct SpmmArgs {
   const float *x;          // input rows (explicit / fused modes)
   size_t x_ld;             // pitch of x in floats
@@ -69,6 +73,7 @@ struct SpmmArgs {
   // gather-fused mode: x row of local index i is row(source[i]) of the feature store
   const float *feat;
   size_t feat_ld;
+  int feat_by_local;       // 1: `feat` holds one row per source of the block (row li), not one per vertex (row g)
   const float *cache;
   size_t cache_ld;
   const uint32_t *hashmap;
@@ -117,7 +122,9 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmAr
       if constexpr (MODE == kFusedGather) {
         const uint32_t g = a.source[li];
         const uint32_t slot = a.hashmap ? a.hashmap[g] : 0xFFFFFFFFu;
-        my_ptr = (slot != 0xFFFFFFFFu) ? a.cache + (size_t)slot * a.cache_ld : a.feat + (size_t)g * a.feat_ld;
+        if (slot != 0xFFFFFFFFu) my_ptr = a.cache + (size_t)slot * a.cache_ld;
+        else if (a.feat) my_ptr = a.feat + (size_t)(a.feat_by_local ? li : g) * a.feat_ld;
+        else atomicOr(&g_spmm_error, 1u);   // my_ptr stays null: the edge contributes nothing
       } else {
         my_ptr = a.x + (size_t)li * a.x_ld;
       }
@@ -131,7 +138,7 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmAr
         const unsigned src_lane = (jj + u) & 31;  // lanes >= cnt hold nullptr / 0 weights
         const uintptr_t p = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_ptr, src_lane);
         ws[u] = __shfl_sync(0xffffffffu, my_w, src_lane);
-        const bool valid = (jj + u) < cnt;
+        const bool valid = (jj + u) < cnt && p != 0;
 #pragma unroll
         for (int t = 0; t < CT; t++) {
           const uint32_t col = col0 + t * (32 * VEC);
@@ -213,14 +220,13 @@ static int launch_spmm(const SpmmArgs &a, int vec, cudaStream_t stream) {
   }
 }
 
-int g_staged_spmm = 1;
 
 // Staged (TMA) path for the plain forms: references are the block-local indices themselves.
 static int try_staged(const float *x, float *y, const uint32_t *offs, const uint32_t *idx, const float *w,
                       const float *norm_row, const float *norm_idx, const float *act, float act_scale, uint32_t n,
                       uint32_t F, cudaStream_t stream, bool *done) {
   *done = false;
-  if (!g_staged_spmm || !tma_spmm_applicable(x, F, F)) return 0;
+  if (!tuning().staged_spmm || !tma_spmm_applicable(x, F, F)) return 0;
   TmaSpmmArgs t{};
   t.x = x; t.x_ld = F; t.y = y; t.offs = offs; t.ref = idx; t.w = w; t.norm_row = norm_row; t.norm_idx = norm_idx;
   t.act = act; t.act_scale = act_scale; t.n = n; t.F = F;
@@ -234,26 +240,40 @@ static int try_staged(const float *x, float *y, const uint32_t *offs, const uint
 using namespace nb;
 
 NB_API int nb_set_staged_spmm(int enabled) {
-  const int old = g_staged_spmm;
-  g_staged_spmm = enabled ? 1 : 0;
-  g_staged_min_width = (enabled == 2 || enabled == 4) ? 1 : 256;   // 2, 4: stage every allowed width
-  g_spmm_ring = (enabled == 3 || enabled == 4) ? 0 : 1;            // 3, 4: two-stage segment kernel, no ring
-  g_ring_group_shift = enabled == 5 ? 0 : 1;                       // 5: ring with one barrier per row, not per pair
+  Tuning &t = default_tuning();
+  const int old = t.staged_spmm;
+  t.staged_spmm = enabled ? 1 : 0;
+  t.staged_min_width = (enabled == 2 || enabled == 4) ? 1 : 256;   // 2, 4: stage every allowed width
+  t.spmm_ring = (enabled == 3 || enabled == 4) ? 0 : 1;            // 3, 4: two-stage segment kernel, no ring
+  t.ring_group_shift = enabled == 5 ? 0 : 1;                       // 5: ring with one barrier per row, not per pair
   return old;
 }
 
 NB_API uint64_t nb_set_l2_panel_bytes(uint64_t bytes) {
-  const uint64_t old = g_l2_panel_bytes;
-  g_l2_panel_bytes = bytes;
+  const uint64_t old = default_tuning().l2_panel_bytes;
+  default_tuning().l2_panel_bytes = bytes;
   return old;
 }
 
 NB_API int nb_device_error_flags(uint32_t *flags) {
   NB_REQUIRE(flags != nullptr, "nb_device_error_flags: null pointer");
-  unsigned int v = 0, t = 0;
+  unsigned int v = 0, t = 0, g = 0, s = 0, l = 0;
   NB_TRY(read_tma_error_flag(&v));
   NB_TRY(read_tc_error_flag(&t));
-  *flags = (v ? 1u : 0u) | (t ? 2u : 0u);
+  NB_TRY(read_gather_error_flag(&g));
+  NB_CUDA(cudaMemcpyFromSymbol(&s, g_spmm_error, sizeof(unsigned int)));
+  NB_TRY(read_loss_error_flag(&l));
+  *flags = ((v & 1u) ? 1u : 0u) | (t ? 2u : 0u) | ((g || s || (v & 2u)) ? 4u : 0u) | (l ? 8u : 0u);
+  return 0;
+}
+
+NB_API int nb_device_error_reset(void) {
+  NB_TRY(reset_tma_error_flag());
+  NB_TRY(reset_tc_error_flag());
+  NB_TRY(reset_gather_error_flag());
+  NB_TRY(reset_loss_error_flag());
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_spmm_error, &zero, sizeof(unsigned int)));
   return 0;
 }
 
@@ -328,12 +348,39 @@ NB_API int nb_spmm_csr_bwd_fused(const float *d_gy, float *d_gx, const uint32_t 
 namespace nb {
 // nb_spmm_csc_fwd_gather_fused with an output pitch (floats, >= F): the native step pads the rows of the
 // layer-0 aggregate to 16 bytes so that the dense layers can read them with TMA tensor loads.
+//
+// d_stage (nullable): a staging table with one row per source of the block (row li, pitch stage_ld floats) that holds
+// the rows of the sources without a cache slot (every source's row when there is no cache).  Rows that are not cached
+// are then read from it instead of from `feat`: the table a batch's sampling half fills from host or peer memory, so
+// that each distinct row crosses that link once and the aggregation reads device memory only.
 int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache, size_t cache_ld,
                                  const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
                                  const uint32_t *d_row_indices, const uint32_t *d_column_offset,
                                  const float *d_src_norm, const float *d_dst_norm, uint32_t v, uint32_t s, uint32_t e,
-                                 uint32_t F, void *stream) {
+                                 uint32_t F, void *stream, const float *d_stage, size_t stage_ld) {
   if (v == 0) return 0;
+  if (d_stage != nullptr) {
+    NB_REQUIRE(stage_ld >= F, "nb_spmm_csc_fwd_gather_fused: staging pitch smaller than width");
+    if (d_hashmap == nullptr) {   // no cache: the staging table is the gathered input itself
+      NB_REQUIRE(d_y && d_row_indices && d_column_offset && d_src_norm && d_dst_norm && y_ld >= F,
+                 "nb_spmm_csc_fwd_gather_fused: null pointer or bad pitch");
+      if (tuning().staged_spmm && tuning().spmm_ring && tuning().l2_panel_bytes == 0 && e > 0 &&
+          tma_spmm_applicable(d_stage, stage_ld, F)) {
+        TmaSpmmArgs t{};
+        t.x = d_stage; t.x_ld = stage_ld; t.y = d_y; t.y_ld = y_ld; t.offs = d_column_offset; t.ref = d_row_indices;
+        t.norm_row = d_dst_norm; t.norm_idx = d_src_norm; t.n = v; t.F = F; t.act_scale = 1.0f; t.src_rows_hint = s;
+        t.out_vec = pick_vec(F, {y_ld}, {d_y});
+        return launch_spmm_tma(t, as_stream(stream));
+      }
+      SpmmArgs a{};
+      a.x = d_stage; a.x_ld = stage_ld; a.y = d_y; a.y_ld = y_ld; a.offs = d_column_offset; a.idx = d_row_indices;
+      a.norm_row = d_dst_norm; a.norm_idx = d_src_norm; a.n = v; a.F = F;
+      return launch_spmm<kFusedW, false>(a, pick_vec(F, {stage_ld, y_ld}, {d_stage, d_y}), as_stream(stream));
+    }
+    feat = d_stage;               // rows without a slot: row li of the staging table
+    feat_ld = stage_ld;
+  }
+  const int by_local = d_stage != nullptr ? 1 : 0;
   NB_REQUIRE(d_source && d_y && d_row_indices && d_column_offset && d_src_norm && d_dst_norm,
              "nb_spmm_csc_fwd_gather_fused: null pointer");
   NB_REQUIRE(feat != nullptr || (d_cache != nullptr && d_hashmap != nullptr),
@@ -346,10 +393,12 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
   {
     const float *hit_base = d_hashmap ? d_cache : feat;
     const size_t hit_ld = d_hashmap ? cache_ld : feat_ld;
-    if (g_staged_spmm && g_spmm_ring && g_l2_panel_bytes == 0 && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
+    if (tuning().staged_spmm && tuning().spmm_ring && tuning().l2_panel_bytes == 0 && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
       // ring kernel: references and weights are formed inside the kernel, one window of 32 edges ahead
       TmaSpmmArgs t{};
       t.x = hit_base; t.x_ld = hit_ld; t.miss = feat; t.miss_ld = feat_ld; t.y = d_y; t.y_ld = y_ld; t.offs = d_column_offset;
+      t.miss_local = by_local;
+      t.miss_bulk = by_local && aligned_to(feat, 16) && feat_ld % 4 == 0 && feat_ld >= (size_t)(F + 3) / 4 * 4;
       t.gidx = d_row_indices; t.gsource = d_source; t.ghashmap = d_hashmap;
       t.norm_row = d_dst_norm; t.norm_idx = d_src_norm;
       t.n = v; t.F = F; t.act = nullptr; t.act_scale = 1.0f; t.src_rows_hint = s;
@@ -359,7 +408,7 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
       if (y_ld % 4 == 0 && y_ld >= (size_t)(F + 3) / 4 * 4 && aligned_to(d_y, 16)) t.out_vec = 4;
       return launch_spmm_tma(t, as_stream(stream));
     }
-    if (g_staged_spmm && ws != nullptr && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
+    if (!by_local && tuning().staged_spmm && ws != nullptr && e > 0 && tma_spmm_applicable(hit_base, hit_ld, F)) {
       cudaStream_t st = as_stream(stream);
       WsScope scope(ws);
       uint32_t *ref = ws->alloc_n<uint32_t>(e);
@@ -375,7 +424,7 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
     }
   }
   SpmmArgs a{};
-  a.feat = feat; a.feat_ld = feat_ld; a.cache = d_cache; a.cache_ld = cache_ld; a.hashmap = d_hashmap;
+  a.feat = feat; a.feat_ld = feat_ld; a.feat_by_local = by_local; a.cache = d_cache; a.cache_ld = cache_ld; a.hashmap = d_hashmap;
   a.source = d_source; a.y = d_y; a.y_ld = y_ld; a.offs = d_column_offset; a.idx = d_row_indices;
   a.norm_row = d_dst_norm; a.norm_idx = d_src_norm; a.n = v; a.F = F;
   std::initializer_list<size_t> pitches = {feat ? feat_ld : (size_t)4, d_cache ? cache_ld : (size_t)4};
@@ -390,5 +439,6 @@ NB_API int nb_spmm_csc_fwd_gather_fused(nb_ws *ws, const float *feat, size_t fea
                                         const float *d_src_norm, const float *d_dst_norm, uint32_t v,
                                         uint32_t s, uint32_t e, uint32_t F, void *stream) {
   return nb::spmm_csc_fwd_gather_fused_ld(ws, feat, feat_ld, d_cache, cache_ld, d_hashmap, d_source, d_y, F,
-                                          d_row_indices, d_column_offset, d_src_norm, d_dst_norm, v, s, e, F, stream);
+                                          d_row_indices, d_column_offset, d_src_norm, d_dst_norm, v, s, e, F, stream,
+                                          nullptr, 0);
 }

@@ -22,11 +22,6 @@ constexpr int kTmaStages = 2;
 constexpr uint32_t kWaitLimit = 1u << 18;   // bounded spin on the mbarrier; then the error flag is set
 
 __device__ unsigned int g_tma_spmm_error = 0;   // 1: an mbarrier wait gave up
-uint32_t g_ring_group_shift = 1;                 // ring kernel: 1 << shift row slots share one barrier
-uint64_t g_l2_panel_bytes = 0;                  // working-set target of one column panel (0: no panels)
-int g_l2_prefetch = 0;
-int g_spmm_ring = 1;                             // 1: per-edge ring variant when rows are not cut into panels
-int g_staged_min_width = 256;                   // narrowest row (floats) that takes the staged path                          // 1: prefetch rows into L2 two segments ahead
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -52,6 +47,23 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+// The same copy with an L2 eviction policy for the lines it brings in.
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 // Ask L2 to fetch a row ahead of the copy that will stage it (no shared memory is held meanwhile).
 __device__ __forceinline__ void prefetch_l2(const void *src, uint32_t bytes) {
@@ -179,10 +191,15 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
       const int u = __ffs(mm) - 1;
       mm &= mm - 1;
       const uint32_t id = __shfl_sync(0xffffffffu, o.ref, u) & 0x7FFFFFFFu;
-      const float *src = a.miss + (size_t)id * a.miss_ld + col0;
       float *dst = reinterpret_cast<float *>(stage_base + (size_t)u * a.slot_bytes);
       const uint32_t width = min(a.panel_floats, a.F - col0);
-      for (uint32_t c = lane; c < width; c += 32) dst[c] = __ldg(src + c);
+      if (a.miss) {
+        const float *src = a.miss + (size_t)id * a.miss_ld + col0;
+        for (uint32_t c = lane; c < width; c += 32) dst[c] = __ldg(src + c);
+      } else {                      // no table to read the row from: zeros, reported through the error word
+        for (uint32_t c = lane; c < width; c += 32) dst[c] = 0.0f;
+        if (lane == 0) atomicOr(&g_tma_spmm_error, 2u);
+      }
     }
   };
 
@@ -218,7 +235,7 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
       uint32_t spins = 0;
       while (!mbar_try_wait(bar, parity)) {
         if (++spins > kWaitLimit) {
-          if (lane == 0) atomicExch(&g_tma_spmm_error, 1u);
+          if (lane == 0) atomicOr(&g_tma_spmm_error, 1u);
           // give copies that may still be in flight a second, equally bounded, chance to land
           for (uint32_t t = 0; t < kWaitLimit && !mbar_try_wait(bar, parity); t++) {}
           return;
@@ -343,7 +360,8 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       const uint32_t li = __ldg(a.gidx + j);
       const uint32_t g = __ldg(a.gsource + li);
       const uint32_t slot = a.ghashmap ? __ldg(a.ghashmap + g) : 0xFFFFFFFFu;
-      ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? (g | 0x80000000u) : g);
+      // not cached: row g of the table `miss`, or row li of a staging table that holds one row per source
+      ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? ((a.miss_local ? li : g) | 0x80000000u) : g);
       w = __ldg(a.norm_idx + li);
     } else {
       ref = __ldg(a.ref + j);
@@ -355,6 +373,13 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   float w_cur, w_nxt;
   load_edge(win, ref_cur, w_cur);
   load_edge(win + 32, ref_nxt, w_nxt);
+  // L2 policy per copied row.  With fused weights the lane's factor is (float)sqrt(number of edges that use the
+  // row in this block), so a factor of exactly 1 marks a row that no other edge of the launch will read: it is
+  // copied with the evict-first policy and leaves L2 to the rows that are read again.
+  const bool hints = a.l2_hint != 0 && a.w == nullptr;
+  const uint64_t pol_first = policy_evict_first(), pol_last = policy_evict_last();
+  unsigned once_cur = hints ? __ballot_sync(0xffffffffu, w_cur == 1.0f) : 0u;
+  unsigned once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
 
   // Issue the copies of group `gi` (edges j0 + gi*G .. of this warp) into the group's slots `gs`; executed by the
   // whole warp.  Lane u takes the group's u-th edge.  The references come from the two operand windows, which cover
@@ -364,25 +389,39 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     const uint32_t t = (gi << Gs) + lane;                     // this lane's edge, relative to j0
     const uint32_t cnt = min(G, n_edges - (gi << Gs));
     const uint32_t rc = __shfl_sync(0xffffffffu, ref_cur, t & 31), rn = __shfl_sync(0xffffffffu, ref_nxt, t & 31);
-    const uint32_t ref = (j0 + t < win + 32) ? rc : rn;
+    const bool in_cur = j0 + t < win + 32;
+    const uint32_t ref = in_cur ? rc : rn;
+    const bool once = (((in_cur ? once_cur : once_nxt) >> (t & 31)) & 1u) != 0;
     const bool mine = lane < cnt;
     const uint32_t bar = bar0 + 8 * gs;
     unsigned char *dst0 = my_smem + (size_t)(gs << Gs) * a.slot_bytes;
-    const unsigned miss_mask = __ballot_sync(0xffffffffu, mine && (ref & 0x80000000u));
+    const bool is_miss = (ref & 0x80000000u) != 0;
+    // Rows that are not cached: copied by the TMA unit like the hits when they sit in an aligned staging table
+    // (miss_bulk), else by the lanes (any pitch, any alignment: a table in mapped host memory).
+    const unsigned miss_mask = a.miss_bulk ? 0u : __ballot_sync(0xffffffffu, mine && is_miss);
     unsigned mm = miss_mask;
-    while (mm) {                    // rows that are not cached: the lanes copy them
+    while (mm) {
       const int u = __ffs(mm) - 1;
       mm &= mm - 1;
       const uint32_t id = __shfl_sync(0xffffffffu, ref, u) & 0x7FFFFFFFu;
-      const float *src = a.miss + (size_t)id * a.miss_ld;
       float *dst = reinterpret_cast<float *>(dst0 + (size_t)u * a.slot_bytes);
-      for (uint32_t c = lane; c < a.F; c += 32) dst[c] = __ldg(src + c);
+      if (a.miss) {
+        const float *src = a.miss + (size_t)id * a.miss_ld;
+        for (uint32_t c = lane; c < a.F; c += 32) dst[c] = __ldg(src + c);
+      } else {                      // no table to read the row from: contributes zeros, reported through the error word
+        for (uint32_t c = lane; c < a.F; c += 32) dst[c] = 0.0f;
+        if (lane == 0) atomicOr(&g_tma_spmm_error, 2u);
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive_expect_tx(bar, a.copy_bytes * (cnt - __popc(miss_mask)));   // the group's one arrival
     __syncwarp();
-    if (mine && !(ref & 0x80000000u))
-      bulk_g2s(smem_u32(dst0 + (size_t)lane * a.slot_bytes), a.x + (size_t)ref * a.x_ld, a.copy_bytes, bar);
+    if (mine && (a.miss_bulk || !is_miss)) {
+      const uint32_t dst = smem_u32(dst0 + (size_t)lane * a.slot_bytes);
+      const float *src = is_miss ? a.miss + (size_t)(ref & 0x7FFFFFFFu) * a.miss_ld : a.x + (size_t)ref * a.x_ld;
+      if (!hints || (!once && a.l2_hint == 1)) bulk_g2s(dst, src, a.copy_bytes, bar);
+      else bulk_g2s_hint(dst, src, a.copy_bytes, bar, once ? pol_first : pol_last);
+    }
   };
 
   // prologue: fill the ring
@@ -416,7 +455,8 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
         // streaming stores: the output is consumed by a later kernel that streams it once; keeping it out of the
         // way leaves L2 to the source rows, which are re-read by other destinations
         if (a.out_vec == 4) {
-          __stcs(reinterpret_cast<float4 *>(out + col), make_float4(r[0], r[1], r[2], r[3]));
+          if (a.y_stream) __stcs(reinterpret_cast<float4 *>(out + col), make_float4(r[0], r[1], r[2], r[3]));
+          else *reinterpret_cast<float4 *>(out + col) = make_float4(r[0], r[1], r[2], r[3]);
         } else if (a.out_vec == 2) {
           if (col + 1 < a.F) __stcs(reinterpret_cast<float2 *>(out + col), make_float2(r[0], r[1]));
           if (col + 3 < a.F) __stcs(reinterpret_cast<float2 *>(out + col + 2), make_float2(r[2], r[3]));
@@ -445,8 +485,9 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     while (j == row_end && row < r_end) finish_row();        // rows without (more) edges
     if (j - win >= 32) {                                      // consume window moves on; fetch the one after
       win += 32;
-      ref_cur = ref_nxt; w_cur = w_nxt;
+      ref_cur = ref_nxt; w_cur = w_nxt; once_cur = once_nxt;
       load_edge(win + 32, ref_nxt, w_nxt);
+      once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
     }
     const uint32_t t = j - j0, in_group = t & (G - 1);
     if (in_group == 0) {                                      // first edge of a group: wait for the group's copies
@@ -455,7 +496,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       uint32_t spins = 0;
       while (!mbar_try_wait(bar, cur_parity)) {
         if (++spins > kWaitLimit) {
-          if (lane == 0) atomicExch(&g_tma_spmm_error, 1u);
+          if (lane == 0) atomicOr(&g_tma_spmm_error, 1u);
           for (uint32_t k = 0; k < kWaitLimit && !mbar_try_wait(bar, cur_parity); k++) {}
           return;
         }
@@ -510,14 +551,14 @@ __global__ void gather_refs_kernel(const uint32_t *__restrict__ offs, const uint
 
 template <int TILES, bool MASK>
 static int launch_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
-  static bool configured = false;   // per instantiation; the attribute is sticky for the process
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(spmm_tma_kernel<TILES, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
-    configured = true;
+    configured.done();
   }
   const unsigned need = (unsigned)(((uint64_t)a.n * a.panels + kTmaWarps - 1) / kTmaWarps);
-  const unsigned grid = need < (unsigned)kNumSMs ? need : (unsigned)kNumSMs;
+  const unsigned grid = need < (unsigned)num_sms() ? need : (unsigned)num_sms();
   spmm_tma_kernel<TILES, MASK><<<grid, kTmaWarps * 32, smem, stream>>>(a);
   NB_LAUNCH_CHECK();
   return 0;
@@ -525,15 +566,19 @@ static int launch_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) 
 
 template <int TILES, bool MASK>
 static int launch_ring_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;   // the attribute is kept per device
+  if (configured.need()) {
     NB_CUDA(cudaFuncSetAttribute(spmm_ring_kernel<TILES, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  220 * 1024));
-    configured = true;
+    configured.done();
   }
   // enough CTAs that every warp gets at least a few rows, at most one CTA per SM
   const unsigned want = (a.n + kRingWarps * 4 - 1) / (kRingWarps * 4);
-  const unsigned grid = want < (unsigned)kNumSMs ? (want ? want : 1) : (unsigned)kNumSMs;
+  // one CTA per SM; SMs held by a kernel that runs beside this one (a gradient all-reduce on another stream) would
+  // make their CTAs wait for a second wave, so the caller can keep a few SMs out of the grid
+  const int reserve = tuning().reserve_sms > 0 ? tuning().reserve_sms : 0;
+  const unsigned sms = (unsigned)(num_sms() > reserve + 1 ? num_sms() - reserve : 1);
+  const unsigned grid = want < sms ? (want ? want : 1) : sms;
   NB_CUDA(launch_chained(spmm_ring_kernel<TILES, MASK>, dim3(grid), dim3(kRingWarps * 32), smem, stream, a));
   NB_LAUNCH_CHECK();
   return 0;
@@ -572,7 +617,7 @@ static int launch_mask(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
 // Staging pays off for wide rows (one bulk copy moves a kilobyte or more); narrow rows are faster with
 // direct vector loads at high occupancy (measured on B200: F = 100..128 direct, F = 602 staged).
 bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F) {
-  if (x == nullptr || F < (uint32_t)g_staged_min_width || F > 1024) return false;
+  if (x == nullptr || F < (uint32_t)tuning().staged_min_width || F > 1024) return false;
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (x_ld & 3) != 0) return false;
   return (size_t)((F + 3) / 4) * 4 <= x_ld;   // the 16-byte-granular copy stays inside the row pitch
 }
@@ -581,25 +626,27 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (a.n == 0) return 0;
   a.fpad = ((a.F + 3) / 4) * 4;
   if (a.y_ld == 0) a.y_ld = a.F;
-  a.l2_prefetch = g_l2_prefetch;
+  a.l2_prefetch = tuning().l2_prefetch;
+  a.l2_hint = tuning().l2_hint;
+  a.y_stream = tuning().y_stream_stores;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
   // into panels whose working set fits, and panels are processed one after the other.
   uint32_t panels = 1;
-  if (a.src_rows_hint > 0 && g_l2_panel_bytes > 0) {
+  if (a.src_rows_hint > 0 && tuning().l2_panel_bytes > 0) {
     const uint64_t working_set = (uint64_t)a.src_rows_hint * a.fpad * 4;
-    panels = (uint32_t)((working_set + g_l2_panel_bytes - 1) / g_l2_panel_bytes);
+    panels = (uint32_t)((working_set + tuning().l2_panel_bytes - 1) / tuning().l2_panel_bytes);
     const uint32_t max_panels = (a.fpad + 63) / 64;            // keep copies at 256 bytes or more
     if (panels > max_panels) panels = max_panels;
     if (panels < 1) panels = 1;
   }
-  if (panels == 1 && g_spmm_ring) {
+  if (panels == 1 && tuning().spmm_ring) {
     // ring variant: whole rows, per-warp ring of R slots out of about 13.5 KB
     a.panels = 1; a.panel_floats = a.fpad; a.copy_bytes = a.fpad * 4; a.slot_bytes = a.copy_bytes;
     uint32_t slots = (216 * 1024 / kRingWarps) / a.slot_bytes;   // the CTA's warps share 216 KB of row slots
     if (slots > 16) slots = 16;
     // two rows per barrier (one wait and one refill per pair of edges) where at least two pairs fit; measured on the
     // layer-0 block of the Reddit-shaped model: 78 us against 81 us with a barrier per row (65 against 75 from L2)
-    const uint32_t shift = slots >= 4 ? g_ring_group_shift : 0;
+    const uint32_t shift = slots >= 4 ? tuning().ring_group_shift : 0;
     const uint32_t R = slots >> shift;                         // groups of 1 << shift slots
     if (R >= 2) {
       a.seg = R;
@@ -636,6 +683,11 @@ int launch_gather_refs(const uint32_t *offs, const uint32_t *idx, uint32_t v, ui
 
 int read_tma_error_flag(unsigned int *value) {
   NB_CUDA(cudaMemcpyFromSymbol(value, g_tma_spmm_error, sizeof(unsigned int)));
+  return 0;
+}
+int reset_tma_error_flag() {
+  const unsigned int zero = 0;
+  NB_CUDA(cudaMemcpyToSymbol(g_tma_spmm_error, &zero, sizeof(unsigned int)));
   return 0;
 }
 

@@ -212,8 +212,8 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     """init_graph + init_nn + run() of GCN_GPU_NEIGHBOR_impl (toolkits/GCN_GPU_NEIGHBOR.hpp:171-288, 1330-1555).
     Returns the best validation accuracy."""
     import torch
-    from . import FullyRepGraph, GCN_GPU_NEIGHBOR_impl, GCNConfig, GNNDatum, Sampler, Workspace
-    from .toolkit import drop_train_ids_by_degree
+    from . import FullyRepGraph, GCN_GPU_NEIGHBOR_impl, GCNConfig, GNNDatum, Sampler, Workspace, _lib
+    from .toolkit import drop_train_ids_by_degree, shard_for_rank
 
     info = InputInfo().readFromCfgFile(cfg_path)
     if info.algorithm != "GCNNEIGHBORGPU":
@@ -225,6 +225,15 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     if classes > 1 and classes != info.layers()[-1]:
         raise SystemExit("CLASSES > 1 needs a last layer with one output per class")
     assert torch.cuda.is_available(), "nts needs a CUDA device; there is no CPU fallback"
+    # One process per GPU, started by torchrun (the reference: one MPI rank per GPU, toolkits/main.cpp): every rank
+    # holds the whole topology and trains on its own share of the train list.
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        if not torch.distributed.is_initialized():
+            torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        if rank != 0:
+            out = open(os.devnull, "w")
     dev = torch.device("cuda", torch.cuda.current_device())
     layers = info.layers()
     V = info.vertices
@@ -252,7 +261,7 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     # the table stays in pinned host memory (zero-copy misses) unless every row is cached on the GPU anyway
     feature = feature.to(dev) if cache_rate >= 1.0 else feature.pin_memory()
     datum = GNNDatum(feature, torch.from_numpy(label).to(dev), mask)
-    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg)
+    tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world)
     ids = [np.nonzero(mask == k)[0].astype(np.uint32) for k in (0, 1, 2)]
     print("label rate: %.3f, train/val/test: (%d/%d/%d)" % (sum(map(len, ids)) / V, *map(len, ids)), file=out)
     if info.batch_type == "metis":
@@ -261,6 +270,10 @@ def run(cfg_path: str, out=sys.stdout) -> float:
         raise ValueError(f"BATCH_TYPE {info.batch_type!r} is not one of shuffle | sequence | random | dellow | delhigh")
     in_deg = np.diff(graph.column_offset.cpu().numpy().astype(np.int64))
     train_ids = drop_train_ids_by_degree(ids[0], in_deg, info.batch_type, info.del_frac)
+    # this rank's share of every split (the reference: the nodes of the rank's own vertex range,
+    # toolkits/GCN_GPU_NEIGHBOR.hpp:1339-1348); statistics are summed over the ranks at every epoch end
+    global_sizes = [len(train_ids), len(ids[1]), len(ids[2])]
+    train_ids, ids[1], ids[2] = (shard_for_rank(x, rank, world) for x in (train_ids, ids[1], ids[2]))
     train = Sampler(graph, train_ids, cfg.fanout, cfg.batch_size, tk.ws, with_edge_weights=False,
                     sample_rate=cfg.sample_rate, lower_fanout=cfg.lower_fanout)
     train.random_batches = info.batch_type == "random"
@@ -269,7 +282,10 @@ def run(cfg_path: str, out=sys.stdout) -> float:
         print("cache_node_num %d (%.3f)" % (tk.cache_node_num, tk.cache_node_num / V), file=out)
     # validation / test: one full batch each with the validation fanout (toolkits/...:1381-1392)
     evals = [Sampler(graph, ids[k], cfg.val_fanout, max(len(ids[k]), 1), tk.ws, full_batch=True,
-                     with_edge_weights=False) if len(ids[k]) else None for k in (1, 2)]
+                     with_edge_weights=False) if global_sizes[k] else None for k in (1, 2)]
+    import ctypes
+    if tk.use_engine:   # per-phase times of the epoch line come from the library's own clocks
+        _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
     rng = np.random.RandomState(2000)
     best_val, run_time = 0.0, 0.0
     for epoch in range(info.epochs):
@@ -281,12 +297,17 @@ def run(cfg_path: str, out=sys.stdout) -> float:
         torch.cuda.synchronize()
         train_time = time.time() - t0
         run_time += train_time
+        phase = (ctypes.c_double * 4)()
+        if tk.use_engine:
+            _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), phase)
         t1 = time.time()
         val_acc, val_loss = (tk.Forward(evals[0], train=False)[:2] if evals[0] else (0.0, 0.0))
         val_time = time.time() - t1
         test_acc = tk.Forward(evals[1], train=False)[0] if evals[1] else 0.0
-        print(epoch_log_line(epoch, train_loss, train_acc, val_loss, val_acc, test_acc, train_time, 0.0, 0.0, 0.0, 0.0,
-                             val_time, run_time, train.batch_size, evals[0].batch_size if evals[0] else 0), file=out)
+        if tk.use_engine:   # evaluation launches are not part of the next epoch's training times
+            _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), (ctypes.c_double * 4)())
+        print(epoch_log_line(epoch, train_loss, train_acc, val_loss, val_acc, test_acc, train_time, phase[0] / 1e3,
+                             phase[1] / 1e3, phase[2] / 1e3, phase[3] / 1e3, val_time, run_time, train.batch_size, evals[0].batch_size if evals[0] else 0), file=out)
         best_val = max(best_val, val_acc)
     return best_val
 

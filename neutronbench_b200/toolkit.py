@@ -45,6 +45,10 @@ class GCNConfig:
     pipelines: int = 1                            # PIPELINES > 1: sampling of batch i+1 overlaps training of batch i
     sample_rate: float = 0.0                      # SAMPLE_RATE > 0: degree-proportional fan-out for training batches
     lower_fanout: int = 0                         # LOWER_FANOUT of that mode
+    # rows that are not cached are copied once per distinct source into a staging table by the sampling half
+    # (None: whenever the feature table is not in this GPU's memory)
+    stage_misses: Optional[bool] = None
+    reserve_sms: Optional[int] = None             # SMs left to the gradient all-reduce (None: 4 when world_size > 1)
 
 
 class Parameter:
@@ -90,13 +94,15 @@ class Parameter:
 
 class GNNDatum:
     """Feature table, labels and split mask (core/ntsDataloador.hpp:32-476).  Features stay where the
-    caller put them: a CUDA tensor, or a pinned host tensor that the gather kernel reads zero-copy."""
+    caller put them: a CUDA tensor, a pinned host tensor that the gather kernel reads zero-copy, or
+    (`shards`) a table sharded by node-id range over the GPUs of the job."""
 
-    def __init__(self, feature: torch.Tensor, label: torch.Tensor, mask: np.ndarray):
-        assert feature.dtype == torch.float32 and feature.dim() == 2
+    def __init__(self, feature: Optional[torch.Tensor], label: torch.Tensor, mask: np.ndarray, shards=None):
+        assert shards is not None or (feature.dtype == torch.float32 and feature.dim() == 2)
         self.local_feature = feature
         self.local_label = label      # int64 on the GPU
         self.local_mask = mask        # 0 train, 1 val, 2 test (core/ntsDataloador.hpp:318-330)
+        self.shards = shards          # a peer.ShardedFeatureTable, or None
 
 
 def cache_slots_by_key(key: np.ndarray, cache_num: int) -> np.ndarray:
@@ -158,6 +164,9 @@ class GCN_GPU_NEIGHBOR_impl:
         self.cuda_stream = Cuda_Stream()
         gen = torch.Generator().manual_seed(cfg.seed)
         self.P = Parameter(cfg.layers, cfg, self.device, gen)
+        if world_size > 1:
+            # every rank starts from rank 0's weights (Parameter::init_parameter, core/NtsScheduler.hpp:691)
+            torch.distributed.broadcast(self.P.W, src=0)
         self.step_count = 0
         # (loss, hits) for one label per node; (loss, predicted-and-true, predicted, true) with CLASSES > 1
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
@@ -175,7 +184,10 @@ class GCN_GPU_NEIGHBOR_impl:
         self.dev_cache_feature = None
         self.dev_cache_node_hashmap = None
         self.cache_node_num = 0
-        self.feature_on_device = datum.local_feature.is_cuda
+        self.feature_on_device = datum.shards is None and datum.local_feature.is_cuda
+        self.stage_misses = (not self.feature_on_device) if cfg.stage_misses is None else bool(cfg.stage_misses)
+        self.reserve_sms = (4 if world_size > 1 else 0) if cfg.reserve_sms is None else int(cfg.reserve_sms)
+        self.device_errors_checked = 0
         self.agg_edges_fwd = 0
         self.agg_edges_bwd = 0
         self.events = None  # when a list: (name, algorithmic bytes, start event, end event) per aggregation
@@ -403,8 +415,14 @@ class GCN_GPU_NEIGHBOR_impl:
         ec.classes = int(c.classes)
         ec.d_graph_column_offset = ptr(self.graph.column_offset)
         ec.d_graph_row_indices = ptr(self.graph.row_indices)
-        feat = self.datum.local_feature
-        ec.feat, ec.feat_ld = ptr(feat), feat.stride(0)
+        if self.datum.shards is not None:
+            sh = self.datum.shards
+            ec.d_feat_shards, ec.num_shards, ec.shard_rows = ptr(sh.table), sh.num_shards, sh.shard_rows
+            ec.feat, ec.feat_ld = None, sh.ld
+        else:
+            feat = self.datum.local_feature
+            ec.feat, ec.feat_ld = ptr(feat), feat.stride(0)
+        ec.stage_misses = 1 if self.stage_misses else 0
         if self.dev_cache_feature is not None:
             ec.d_cache, ec.cache_ld = ptr(self.dev_cache_feature), self.dev_cache_feature.stride(0)
             ec.d_hashmap = ptr(self.dev_cache_node_hashmap)
@@ -414,6 +432,8 @@ class GCN_GPU_NEIGHBOR_impl:
         _lib.load().nb_set_fused_output_layer(1 if self.fuse_output_layer else 0)
         _lib.call("nb_gcn_create", C.byref(handle), C.byref(ec), self.ws.handle)
         self._engine, self._engine_cfg = handle, ec
+        if self.reserve_sms:
+            _lib.call("nb_gcn_set_option", handle, b"reserve_sms", self.reserve_sms)
         return handle
 
     def engine_step(self, sampler: Sampler, train: bool = True):
@@ -489,14 +509,18 @@ class GCN_GPU_NEIGHBOR_impl:
         return info
 
     def run_pipelined(self, sampler: Sampler, max_batches: Optional[int] = None, train: bool = True,
-                      on_batch=None, read_back: bool = True):
+                      on_batch=None, read_back: bool = True, pad_to_steps: int = 0):
         """Batch loop with the next batch's sampling issued while the current batch trains.  The order of
         batches, sampler draws and optimizer steps is that of the plain loop, so results are identical.
-        Returns (correct, nodes, loss sum, batches); with read_back False no statistics are read."""
+        Returns (correct, nodes, loss sum, batches); with read_back False no statistics are read.
+        pad_to_steps: when this rank has fewer batches than that, it joins the remaining gradient sums with
+        zeros (UpdateZero), so that every rank of a data-parallel job issues the same number of collectives."""
         assert self.use_engine, "the pipelined loop runs on the native step"
         correct = nodes = batches = 0
         loss_sum = 0.0
         if not sampler.sample_not_finished() or (max_batches is not None and max_batches <= 0):
+            if train:
+                self._pad_steps(pad_to_steps - batches)
             return correct, nodes, loss_sum, batches
         self._ensure_pipeline()
         slots = len(self._batches)
@@ -508,8 +532,17 @@ class GCN_GPU_NEIGHBOR_impl:
         self._compute_stream.wait_stream(outer)
         with torch.cuda.stream(self._compute_stream):
             result = self._run_pipelined_on_current_stream(sampler, max_batches, train, on_batch, read_back, slots)
+            if train:
+                self._pad_steps(pad_to_steps - result[3])
         outer.wait_stream(self._compute_stream)
         return result
+
+    def _pad_steps(self, n: int):
+        for _ in range(max(0, n)):
+            self.UpdateZero()
+            self.step_count += 1
+        if n > 0:
+            self._join_update_stream()
 
     def _run_pipelined_on_current_stream(self, sampler, max_batches, train, on_batch, read_back, slots):
         correct = nodes = batches = 0
@@ -571,6 +604,9 @@ class GCN_GPU_NEIGHBOR_impl:
                 _lib.call("nb_gcn_update", self._ensure_engine(), us.cuda_stream)
             return
         sum_gradients(self.P.grad, self.world_size)
+        self._apply_adam()
+
+    def _apply_adam(self):
         if self.use_engine:
             _lib.call("nb_gcn_update", self._ensure_engine(), torch.cuda.current_stream().cuda_stream)
         else:
@@ -583,9 +619,54 @@ class GCN_GPU_NEIGHBOR_impl:
 
     def UpdateZero(self):
         """A rank that ran out of batches still joins the collective with zeros
-        (toolkits/GCN_GPU_NEIGHBOR.hpp:309-313)."""
-        self.P.grad.zero_()
+        (toolkits/GCN_GPU_NEIGHBOR.hpp:309-313).  The zeroing is ordered after every earlier reader of the
+        gradient bucket (the previous step's sum and Adam) and before this step's sum: with the update on a
+        stream of its own it runs on that stream, behind the previous update."""
+        if self.use_engine and self.overlap_update:
+            if self._update_stream is None:
+                self._update_stream = torch.cuda.Stream(device=self.device, priority=-1)
+            us = self._update_stream
+            with torch.cuda.stream(us):
+                _lib.call("nb_gcn_wait_gradients", self._ensure_engine(), us.cuda_stream)
+                self.P.grad.zero_()
+                sum_gradients(self.P.grad, self.world_size)
+                _lib.call("nb_gcn_update", self._ensure_engine(), us.cuda_stream)
+            return
+        self.P.grad.zero_()      # same stream as the previous update: stream order is enough
         self.Update()
+
+    def check_device_errors(self):
+        """Reads the library's device-side error word (bounded waits that gave up, ids or labels outside their
+        tables) and raises if it is set: a step that met one has left rows unwritten or skipped.  Synchronises;
+        called at epoch ends, outside timed regions."""
+        import ctypes as C
+        flags = C.c_uint32(0)
+        _lib.call("nb_device_error_flags", C.byref(flags))
+        self.device_errors_checked += 1
+        if flags.value:
+            raise RuntimeError(f"libnb_b200 device error word is {flags.value:#x} (1: copy wait gave up, 2: tensor-core "
+                               "wait gave up, 4: vertex id outside every feature table, 8: label outside [0, C))")
+
+    def epoch_steps(self, sampler: Sampler) -> int:
+        """Optimizer steps of one epoch of a data-parallel job: the largest batch count over the ranks (one
+        scalar MAX-reduce per epoch).  Ranks with fewer batches pad with UpdateZero."""
+        n = int(sampler.batch_nums)
+        if self.world_size > 1:
+            t = torch.tensor([n], dtype=torch.int64, device=self.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            n = int(t.item())
+        return n
+
+    def _sum_epoch_stats(self, correct, nodes, loss_sum, batches):
+        """correct / nodes / loss / batch count summed over the ranks, as the reference all-reduces its epoch
+        statistics (toolkits/GCN_GPU_NEIGHBOR.hpp:785-790)."""
+        if self.world_size == 1:
+            return correct, nodes, loss_sum, batches
+        t = torch.tensor([float(correct), float(nodes), float(loss_sum), float(batches)], dtype=torch.float64,
+                         device=self.device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.SUM)
+        c, n, l, b = t.tolist()
+        return (c if self.multi_label else int(round(c))), int(round(n)), l, int(round(b))
 
     def train_step(self, sampler: Sampler):
         if self.use_engine:
@@ -625,9 +706,15 @@ class GCN_GPU_NEIGHBOR_impl:
         native = (self.use_engine and list(sampler.fanout) == list(self.cfg.fanout)
                   and sampler.batch_size <= self.cfg.batch_size
                   and (not train or (sampler.sample_rate, sampler.lower_fanout) == (self.cfg.sample_rate, self.cfg.lower_fanout)))
+        # data parallel: every rank takes the same number of optimizer steps (the largest shard's batch count)
+        steps = self.epoch_steps(sampler) if (train and self.world_size > 1) else 0
+        if max_batches is not None:
+            steps = min(steps, max_batches)
         if native and self.cfg.pipelines > 1:
-            correct, nodes, loss_epoch, batches = self.run_pipelined(sampler, max_batches, train=train)
+            correct, nodes, loss_epoch, batches = self.run_pipelined(sampler, max_batches, train=train, pad_to_steps=steps)
             sampler.restart()
+            self.check_device_errors()
+            correct, nodes, loss_epoch, batches = self._sum_epoch_stats(correct, nodes, loss_epoch, batches)
             return self._epoch_accuracy(correct, nodes, batches), loss_epoch / max(batches, 1), batches
         correct = nodes = batches = 0
         loss_epoch = 0.0
@@ -649,8 +736,12 @@ class GCN_GPU_NEIGHBOR_impl:
             correct += hits
             nodes += batch_nodes
             batches += 1
+        if train:
+            self._pad_steps(steps - batches)
         self._join_update_stream()
         sampler.restart()
+        self.check_device_errors()
+        correct, nodes, loss_epoch, batches = self._sum_epoch_stats(correct, nodes, loss_epoch, batches)
         return self._epoch_accuracy(correct, nodes, batches), loss_epoch / max(batches, 1), batches
 
     def _epoch_accuracy(self, score_sum, nodes: int, batches: int) -> float:
@@ -723,5 +814,5 @@ def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
         width = max(cfg.layers[layer], cfg.layers[layer + 1])
         acts += 6 * 4 * v * width
         v = min(num_vertices, v * (f if f > 0 else 64))
-    acts += 4 * v * cfg.layers[0]                            # gathered input rows when the gather is not fused
+    acts += 4 * v * ((cfg.layers[0] + 3) // 4 * 4)           # gathered input rows (gather not fused) / staged misses
     return int(block + splitk + acts + (64 << 20))

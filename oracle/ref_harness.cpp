@@ -42,7 +42,8 @@ static void dump(const std::string &name, const char *dtype, const T *data, size
 // sample_one -> get_feature / get_label -> runGraphOp<MiniBatchFuseOp> + vertexForward per layer ->
 // Loss -> appendNNOp -> self_backward -> all_reduce_to_gradient + learnC2C_with_decay_Adam + next.
 // usage: ref_harness bench <edge_file> <vertices> <feat.f32> <label.i64> <seeds.u32> <fanouts>
-//                          <layers a-b-c> <batch> <warmup batches> <timed batches> <drop> <lr> <wd>
+//                          <layers a-b-c> <batch> <warmup batches> <timed batches> <drop> <lr> <wd> [threads]
+// threads: the cfg key THREADS (0 or absent = the reference's default, ncpus/2 - 1, core/ntsSampler.hpp:221-228).
 // prints one line: REFBENCH ms_per_batch=<..> agg_edges_per_batch=<..> omp_threads=<..> batches=<..>
 // ---------------------------------------------------------------------------------------------
 static int bench_main(int argc, char **argv) {
@@ -64,6 +65,7 @@ static int bench_main(int argc, char **argv) {
   const VertexId batch = (VertexId)std::stoul(argv[9]);
   const int warm = std::stoi(argv[10]), timed = std::stoi(argv[11]);
   const float drop = std::stof(argv[12]), lr = std::stof(argv[13]), wd = std::stof(argv[14]);
+  const int cfg_threads = argc > 15 ? std::stoi(argv[15]) : 0;
   const int L = (int)fanout.size();
 
   std::vector<VertexId> seeds;
@@ -90,6 +92,7 @@ static int bench_main(int argc, char **argv) {
   graph->config->sample_rate = -1;
   graph->config->mini_pull = 1;
   graph->config->classes = 1;
+  if (cfg_threads > 0) graph->config->threads = cfg_threads;
 
   FullyRepGraph *frg = new FullyRepGraph(graph);
   frg->ReadRepGraphFromRawFile();
@@ -154,7 +157,9 @@ static int bench_main(int argc, char **argv) {
   }
   printf("REFBENCH ms_per_batch=%.4f agg_edges_per_batch=%.1f omp_threads=%d batches=%d\n",
          done ? 1e3 * total / done : 0.0, done ? (double)edges / done : 0.0,
-         std::max(1, numa_num_configured_cpus() / 2 - 1), done);
+         (cfg_threads > 0 && cfg_threads <= numa_num_configured_cpus()) ? cfg_threads
+                                                                        : std::max(1, numa_num_configured_cpus() / 2 - 1),
+         done);
   fflush(stdout);
   _exit(0);   // the reference's destructors free members they never initialised
 }

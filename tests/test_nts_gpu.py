@@ -53,3 +53,12 @@ def test_cfg_driven_training_learns(tmp_path, cuda_device, cache, pipelines):
     last = float(lines[-1].split("train_loss ")[1].split()[0])
     assert last < first
     assert best > 0.6          # 4 balanced classes: chance is 0.25
+    # the per-phase times of the epoch line (the text exp/utils.py of the reference parses) come from the library's
+    # clocks: sampling and the two device-side shares are never zero, and graph + nn fit inside the epoch
+    import re
+    m = re.search(r"train_time ([0-9.]+)\(sample ([0-9.]+) trans ([0-9.]+) graph ([0-9.]+) nn ([0-9.]+)\)", lines[-1])
+    train_t, sample_t, trans_t, graph_t, nn_t = map(float, m.groups())
+    phase_sum = sum(float(x) for l in lines
+                    for x in re.search(r"sample ([0-9.]+) trans ([0-9.]+) graph ([0-9.]+) nn ([0-9.]+)", l).groups())
+    assert phase_sum > 0.0
+    assert graph_t + nn_t <= train_t + 1e-3
