@@ -90,6 +90,7 @@ def parse_args():
                          "table is not in this GPU's memory)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="nb_gcn_set_option on the trainer's handle (tuning switches; results never depend on them)")
+    ap.add_argument("--cache-row-pitch", type=int, default=0, help="floats between rows of the GPU feature cache (0: default)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload's node and edge counts (functional checks)")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
@@ -110,7 +111,8 @@ def workload_config(name, args):
                     learn_rate=0.01, weight_decay=0.0001, drop_rate=0.5,
                     cache_type="rate" if cache_rate > 0 else "none", cache_rate=cache_rate, seed=args.seed,
                     fuse_gather=not args.no_fuse_gather,
-                    stage_misses=None if args.stage_misses is None else bool(args.stage_misses))
+                    stage_misses=None if args.stage_misses is None else bool(args.stage_misses),
+                    cache_row_pitch=getattr(args, "cache_row_pitch", 0))
     return sh, cfg
 
 
@@ -366,6 +368,7 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
         if record_events and tk.use_engine:
             _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
         launches0 = _lib.load().nb_launch_count()
+        phase = None
         region_ms, region_edges = [], []
         regions = 1
         r = 0
@@ -391,8 +394,12 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
             import ctypes
             a_ms, a_b, a_n = (ctypes.c_double * 2)(), (ctypes.c_uint64 * 2)(), (ctypes.c_uint64 * 2)()
             _lib.call("nb_gcn_read_timing_by_class", tk._ensure_engine(), a_ms, a_b, a_n)
+            ph = (ctypes.c_double * 4)()
+            _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), ph)
             _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 0)
             ev = ("engine", list(a_ms), [int(x) for x in a_b], [int(x) for x in a_n])
+            n_steps = K * len(region_ms)
+            phase = {"sample_host": ph[0] / n_steps, "trans": ph[1] / n_steps, "graph": ph[2] / n_steps, "nn": ph[3] / n_steps}
         tk.check_device_errors()     # a bounded wait that gave up, or an id outside its table, voids the numbers
         ms_max = reduce_vec(region_ms, dist.ReduceOp.MAX if world > 1 else None)
         edges_sum = reduce_vec(region_edges, dist.ReduceOp.SUM if world > 1 else None)
@@ -400,7 +407,7 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
         mid = order[len(order) // 2] if len(order) % 2 else order[len(order) // 2 - 1]   # a measured region, not a mean
         return {"ms": ms_max[mid], "edges": edges_sum[mid], "regions": len(ms_max), "ms_min": min(ms_max),
                 "ms_max": max(ms_max), "launches_per_region": launches / len(ms_max), "clocks": clk, "events": ev,
-                "total_steps": K * len(ms_max)}
+                "total_steps": K * len(ms_max), "phase_ms_per_step": phase}
 
     a = run(staged=True, record_events=want_events)
     b = run(staged=False, record_events=False)
@@ -541,6 +548,7 @@ def main():
                     "epoch_time_s": (b["ms"] / K) * steps_per_epoch / 1e3, "regions": b["regions"],
                     "h2d_bytes_per_step": cfg.batch_size * 4, "d2h_bytes_per_step": 8 + hops * 12},
             "gpu_launches": int(round(a["launches_per_region"])),
+            "phase_ms_per_step": a["phase_ms_per_step"],
             "aggregated_edges_per_step": a["edges"] / (K * world),
         }
 
@@ -585,6 +593,7 @@ def main():
         "e2e": primary["e2e"], "gpu_launches": primary["gpu_launches"], "roofline": roofline,
         "all_aggregation": all_agg, "clocks": a["clocks"],
         "aggregated_edges_per_step": primary["aggregated_edges_per_step"], "device_error": 0,
+        "phase_ms_per_step": primary["phase_ms_per_step"],
         "stage_misses": stage_primary,
     }
     if args.workload == "papers":

@@ -215,6 +215,16 @@ int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, const floa
                       uint32_t num_shards, uint32_t shard_rows, const float *d_cache, size_t cache_ld,
                       const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
                       void *stream);
+/* The index-list form of the reference's cache path, for callers that keep its host-side hit/miss split
+ * (Sampler::load_feature_gpu_cache, core/ntsSampler.hpp:424-469): for i < n, with lid = local_idx[i],
+ *     x0[lid,:] = table[source[lid],:]              when d_slot_map == NULL
+ *                 (Cuda_Stream::zero_copy_feature_move_gpu_cache, cuda/ntsCUDAGraphOP.cu:398-409), or
+ *     x0[lid,:] = table[slot_map[source[lid]],:]    otherwise
+ *                 (Cuda_Stream::gather_feature_from_gpu_cache, cuda/ntsCUDAGraphOP.cu:411-423).
+ * Rows whose slot is 0xFFFFFFFF are skipped and reported through nb_device_error_flags (bit 2). */
+int nb_feature_gather_indexed(float *d_x0, size_t x0_ld, const float *table, size_t table_ld,
+                              const uint32_t *d_source, const uint32_t *d_local_idx, const uint32_t *d_slot_map,
+                              uint32_t n, uint32_t F, void *stream);
 /* Shards of a feature table that other processes of the job read (one process per GPU): a shard is an allocation of
  * its own (cudaMalloc), so that its inter-process handle names exactly that buffer.
  *   nb_shard_alloc / nb_shard_free   device memory of the current device

@@ -72,6 +72,8 @@ SIGNATURES = {
     "nb_graph_build_csc": (C.c_int, [ptr, u32p, C.c_uint64, C.c_uint32, u64p, u32p, u32p, u32p, ptr]),
     "nb_feature_gather": (C.c_int, [f32p, f32p, C.c_size_t, ptr, C.c_uint32, C.c_uint32, f32p, C.c_size_t, u32p,
                                     u32p, C.c_uint32, C.c_uint32, ptr]),
+    "nb_feature_gather_indexed": (C.c_int, [f32p, C.c_size_t, f32p, C.c_size_t, u32p, u32p, u32p, C.c_uint32,
+                                            C.c_uint32, ptr]),
     "nb_shard_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "nb_shard_free": (C.c_int, [ptr]),
     "nb_shard_upload": (C.c_int, [ptr, ptr, C.c_size_t]),

@@ -41,9 +41,14 @@ struct Tuning {
   int spmm_ring = 1;             // per-edge ring variant when rows are not cut into panels
   int staged_min_width = 256;    // narrowest row (floats) that takes the staged path
   int l2_prefetch = 0;           // segment kernel: prefetch rows into L2 two segments ahead
-  int l2_hint = 1;               // ring kernel, fused weights: rows used by one edge only are copied with the
-                                 // L2 evict-first policy (1); 2: rows with more uses evict-last as well; 0: off
+  int l2_hint = 3;               // ring kernel, fused weights: rows used by one edge only are copied with the
+                                 // L2 evict-first policy (1); 2: rows with more uses evict-last as well; 3: only
+                                 // rows with at least l2_keep_min_uses uses evict-last; 0: off
+  int l2_keep_min_uses = 4;
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
+  int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
+  int wide_rows_in_flight = 2;   // source rows in flight per warp of that kernel: 1, 2 or 4
+  int wide_col_split = 1;        // warps that share one output row of that kernel, each taking a range of columns
   int reserve_sms = 0;           // SMs the one-CTA-per-SM aggregation kernel leaves to kernels that run beside it
   uint32_t ring_group_shift = 1; // ring kernel: 1 << shift row slots share one barrier
   uint64_t l2_panel_bytes = 0;   // working-set target of one column panel (0: no panels)
@@ -160,6 +165,7 @@ struct TmaSpmmArgs {
   uint32_t slot_bytes, copy_bytes, seg, grp_shift, fpad, panels, panel_floats;   // filled by launch_spmm_tma
   int l2_prefetch;
   int l2_hint;             // ring kernel: L2 eviction policy per copied row (Tuning::l2_hint)
+  float keep_uses;         // rows read by at least this many edges of the launch are copied with evict-last
   int y_stream;            // ring kernel: streaming stores for y
   int out_vec;             // widest vector (floats) usable for y and act rows: 4, 2 or 1
 };

@@ -60,6 +60,9 @@ struct nb_gcn {
   std::vector<int> ev_class;         // per pair: 0 = layer-0 forward aggregation, 1 = any other aggregation,
                                      // 2 = a whole compute call (forward, loss, backward), 3 = staging of uncached rows
   double sample_host_ms = 0.0;       // wall time the sampling halves took on their threads while timing was on
+  // event pairs already read out, per class: one set for each of the two readers, cleared by its reader
+  double cls_ms[4] = {}, phase_ms[4] = {};
+  uint64_t cls_bytes[4] = {}, cls_launches[4] = {};
   std::vector<uint64_t> ev_bytes;
   // cross-stream ordering of gradients and weights when the caller runs the update on a stream of its own
   cudaEvent_t ev_grad = nullptr;      // recorded after the last kernel of a compute call
@@ -195,6 +198,7 @@ NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
   std::lock_guard<std::mutex> lk(g->mu);
   g->timing = enabled != 0;
   g->sample_host_ms = 0.0;
+  for (int k = 0; k < 4; k++) { g->cls_ms[k] = g->phase_ms[k] = 0.0; g->cls_bytes[k] = g->cls_launches[k] = 0; }
   g->ev_used = 0;
   g->timed_bytes = 0;
   g->ev_class.clear();
@@ -203,18 +207,17 @@ NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
 }
 
 namespace {
-// Sums the recorded event pairs per class (4 classes) and forgets them.
-int drain_events(nb_gcn *g, double ms[4], uint64_t bytes[4], uint64_t launches[4]) {
-  std::lock_guard<std::mutex> lk(g->mu);
-  for (int k = 0; k < 4; k++) { ms[k] = 0.0; bytes[k] = 0; launches[k] = 0; }
+// Adds the recorded event pairs to the per-class totals of both readers and forgets the pairs.  Caller holds g->mu.
+int drain_events(nb_gcn *g) {
   for (size_t i = 0; i + 1 < g->ev_used; i += 2) {
     NB_CUDA(cudaEventSynchronize(g->ev_pool[i + 1]));
     float t = 0.0f;
     NB_CUDA(cudaEventElapsedTime(&t, g->ev_pool[i], g->ev_pool[i + 1]));
     const int k = g->ev_class[i / 2] & 3;
-    ms[k] += t;
-    bytes[k] += g->ev_bytes[i / 2];
-    launches[k]++;
+    g->cls_ms[k] += t;
+    g->phase_ms[k] += t;
+    g->cls_bytes[k] += g->ev_bytes[i / 2];
+    g->cls_launches[k]++;
   }
   g->ev_used = 0;
   g->timed_bytes = 0;
@@ -226,24 +229,27 @@ int drain_events(nb_gcn *g, double ms[4], uint64_t bytes[4], uint64_t launches[4
 
 NB_API int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint64_t launches[2]) {
   NB_REQUIRE(g && ms && bytes && launches, "nb_gcn_read_timing_by_class: null pointer");
-  double m[4];
-  uint64_t b[4], n[4];
-  NB_TRY(drain_events(g, m, b, n));
-  for (int k = 0; k < 2; k++) { ms[k] = m[k]; bytes[k] = b[k]; launches[k] = n[k]; }
+  std::lock_guard<std::mutex> lk(g->mu);
+  NB_TRY(drain_events(g));
+  for (int k = 0; k < 4; k++) {
+    if (k < 2) { ms[k] = g->cls_ms[k]; bytes[k] = g->cls_bytes[k]; launches[k] = g->cls_launches[k]; }
+    g->cls_ms[k] = 0.0;
+    g->cls_bytes[k] = g->cls_launches[k] = 0;
+  }
   return 0;
 }
 
 NB_API int nb_gcn_read_phase_times(nb_gcn *g, double ms[4]) {
   NB_REQUIRE(g && ms, "nb_gcn_read_phase_times: null pointer");
-  double m[4];
-  uint64_t b[4], n[4];
-  NB_TRY(drain_events(g, m, b, n));
   std::lock_guard<std::mutex> lk(g->mu);
+  NB_TRY(drain_events(g));
+  const double *m = g->phase_ms;
   ms[0] = g->sample_host_ms;
   ms[1] = m[3];
   ms[2] = m[0] + m[1];
   ms[3] = m[2] > ms[2] ? m[2] - ms[2] : 0.0;
   g->sample_host_ms = 0.0;
+  for (int k = 0; k < 4; k++) g->phase_ms[k] = 0.0;
   return 0;
 }
 
@@ -607,9 +613,20 @@ NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
   else if (n == "l2_panel_bytes") t.l2_panel_bytes = (uint64_t)(value > 0 ? value : 0);
   else if (n == "l2_prefetch") t.l2_prefetch = value != 0;
   else if (n == "l2_hint") {
-    NB_REQUIRE(value >= 0 && value <= 2, "nb_gcn_set_option: l2_hint is 0, 1 or 2");
+    NB_REQUIRE(value >= 0 && value <= 3, "nb_gcn_set_option: l2_hint is 0..3");
     t.l2_hint = (int)value;
+  } else if (n == "l2_keep_min_uses") {
+    NB_REQUIRE(value >= 2 && value <= 1000000, "nb_gcn_set_option: l2_keep_min_uses is at least 2");
+    t.l2_keep_min_uses = (int)value;
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
+  else if (n == "wide_direct") t.wide_direct = value != 0;
+  else if (n == "wide_col_split") {
+    NB_REQUIRE(value >= 1 && value <= 4, "nb_gcn_set_option: wide_col_split is 1..4");
+    t.wide_col_split = (int)value;
+  } else if (n == "wide_rows_in_flight") {
+    NB_REQUIRE(value == 1 || value == 2 || value == 4, "nb_gcn_set_option: wide_rows_in_flight is 1, 2 or 4");
+    t.wide_rows_in_flight = (int)value;
+  }
   else if (n == "reserve_sms") {
     NB_REQUIRE(value >= 0 && value < 64, "nb_gcn_set_option: reserve_sms is 0..63");
     t.reserve_sms = (int)value;

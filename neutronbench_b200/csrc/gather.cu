@@ -81,6 +81,33 @@ __global__ void __launch_bounds__(kWarps * 32) feature_gather_kernel(const Gathe
   }
 }
 
+// x0[lid,:] = table[map(src[lid]),:] for lid = local_idx[i], i < n: the index-list form of the reference's two cache
+// kernels (misses: map = identity over the host table; hits: map = the slot map over the cache).
+template <int VEC>
+__global__ void __launch_bounds__(kWarps * 32) gather_indexed_kernel(float *x0, size_t x0_ld, const float *table,
+                                                                     size_t table_ld, const uint32_t *__restrict__ src,
+                                                                     const uint32_t *__restrict__ local_idx,
+                                                                     const uint32_t *__restrict__ slot_map, uint32_t n,
+                                                                     uint32_t F, uint32_t tiles) {
+  const unsigned lane = threadIdx.x & 31;
+  const uint64_t warps = (uint64_t)gridDim.x * kWarps;
+  for (uint64_t w = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); w < (uint64_t)n * tiles; w += warps) {
+    const uint32_t i = (uint32_t)(w / tiles);
+    const uint32_t col = (uint32_t)(w - (uint64_t)i * tiles) * (32 * VEC) + lane * VEC;
+    if (col >= F) continue;
+    const uint32_t lid = local_idx[i];
+    uint32_t row = src[lid];
+    if (slot_map) {
+      row = slot_map[row];
+      if (row == 0xFFFFFFFFu) {   // listed as cached but has no slot: skipped, reported
+        if (lane == 0) atomicOr(&g_gather_error, 1u);
+        continue;
+      }
+    }
+    copy_vec<VEC>(x0 + (size_t)lid * x0_ld + col, table + (size_t)row * table_ld + col);
+  }
+}
+
 __global__ void label_gather_kernel(int64_t *__restrict__ lab, const int64_t *__restrict__ label,
                                     const uint32_t *__restrict__ dst, uint32_t n, uint32_t label_size) {
   const uint64_t total = (uint64_t)n * label_size;
@@ -177,6 +204,25 @@ int nb::feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const fl
     case 4: feature_gather_kernel<4><<<(unsigned)blocks, kWarps * 32, 0, st>>>(a); break;
     case 2: feature_gather_kernel<2><<<(unsigned)blocks, kWarps * 32, 0, st>>>(a); break;
     default: feature_gather_kernel<1><<<(unsigned)blocks, kWarps * 32, 0, st>>>(a); break;
+  }
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+NB_API int nb_feature_gather_indexed(float *d_x0, size_t x0_ld, const float *table, size_t table_ld,
+                                     const uint32_t *d_source, const uint32_t *d_local_idx, const uint32_t *d_slot_map,
+                                     uint32_t n, uint32_t F, void *stream) {
+  if (n == 0) return 0;
+  NB_REQUIRE(d_x0 && table && d_source && d_local_idx, "nb_feature_gather_indexed: null pointer");
+  NB_REQUIRE(F > 0 && x0_ld >= F && table_ld >= F, "nb_feature_gather_indexed: bad width or pitch");
+  const int vec = pick_vec(F, {x0_ld, table_ld}, {d_x0, table});
+  const uint32_t tiles = (F + 32 * vec - 1) / (32 * vec);
+  const unsigned grid = grid_for((uint64_t)n * tiles * 32, kWarps * 32, 8, 8);
+  cudaStream_t st = as_stream(stream);
+  switch (vec) {
+    case 4: gather_indexed_kernel<4><<<grid, kWarps * 32, 0, st>>>(d_x0, x0_ld, table, table_ld, d_source, d_local_idx, d_slot_map, n, F, tiles); break;
+    case 2: gather_indexed_kernel<2><<<grid, kWarps * 32, 0, st>>>(d_x0, x0_ld, table, table_ld, d_source, d_local_idx, d_slot_map, n, F, tiles); break;
+    default: gather_indexed_kernel<1><<<grid, kWarps * 32, 0, st>>>(d_x0, x0_ld, table, table_ld, d_source, d_local_idx, d_slot_map, n, F, tiles); break;
   }
   NB_LAUNCH_CHECK();
   return 0;

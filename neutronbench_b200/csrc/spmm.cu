@@ -221,6 +221,212 @@ static int launch_spmm(const SpmmArgs &a, int vec, cudaStream_t stream) {
 }
 
 
+// ---------------------------------------------------------------------------------------------
+// Wide rows (hundreds of floats) with plain 16-byte loads: one warp per output row, every lane owns TILES float4
+// columns of the row, U source rows are in flight per warp, and the per-edge references of the NEXT row of the warp
+// (index -> source id -> cache slot -> row address, weight) are requested before the current row is accumulated, so
+// that the index chain is off the critical path.  Many resident warps (the kernel holds no shared memory) keep far
+// more row reads in flight than the shared-memory ring can, which is what random 2.4 KB row reads from DRAM need:
+// measured on B200, 140 K such rows stream at 5.9 TB/s with plain loads.
+// Needs the cache (or, without one, the plain input) 16-byte aligned with a pitch that is a multiple of 4 floats and
+// at least ceil(F/4)*4 (the cache and the staging table are laid out like that; columns from F up to the pitch are
+// never stored).  Rows without a cache slot may come from a table of any pitch and alignment (mapped host memory):
+// those are read element by element.
+// Same arithmetic and order as every other aggregation path.
+// ---------------------------------------------------------------------------------------------
+struct WideArgs {
+  const float *x;          // rows named by a plain index (no cache): row(li) = x + li * x_ld   (gather == 0)
+  size_t x_ld;
+  // gather form: row of edge j = cache[hashmap[source[idx[j]]]] if it has a slot, else miss row
+  const float *cache; size_t cache_ld;
+  const uint32_t *hashmap, *source;
+  const float *miss; size_t miss_ld;   // table for rows without a slot: by vertex id, or (miss_local) by source index
+  int miss_local;
+  int miss_aligned;        // rows of `miss` can be read with float4 loads like cache rows
+  int gather;
+  float *y; size_t y_ld;
+  const uint32_t *offs, *idx;
+  const float *norm_row, *norm_idx;
+  uint32_t n, F;
+  int out_vec;             // 4: whole float4 stores (the row's padding takes the tail), else 2 or 1
+  int stream_stores;
+  uint32_t split;          // warps per output row: each takes part_f4 consecutive float4 columns
+  uint32_t part_f4;
+};
+
+constexpr int kWideThreads = 128;
+
+template <int TILES, int U>
+__global__ void __launch_bounds__(kWideThreads) spmm_wide_kernel(const WideArgs a) {
+  pdl_enter();
+  const unsigned lane = threadIdx.x & 31;
+  // work items are (row, part) pairs, a.split parts per row; a warp walks items item, item + stride, ...
+  const uint32_t items = a.n * a.split;
+  const uint32_t total_warps = ((gridDim.x * blockDim.x) >> 5) / a.split * a.split;   // keeps a warp on one part
+  uint32_t item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (item >= total_warps || item >= items) return;
+  const uint32_t part = item % a.split;
+  uint32_t r = item / a.split;
+  const uint32_t row_stride = total_warps / a.split;
+  const uint32_t q0 = part * a.part_f4;                                       // first float4 column of this part
+  const uint32_t fpad4 = min((a.F + 3) >> 2, q0 + a.part_f4);                 // one past its last float4 column
+
+  // Reference and weight of edge `j` of a row whose degree factor is nr (lanes past the row's end get a null row).
+  auto resolve = [&](uint32_t j, uint32_t end, float nr, const float4 *&ptr, float &w) {
+    ptr = nullptr; w = 0.0f;
+    if (j >= end) return;
+    const uint32_t li = __ldg(a.idx + j);
+    w = __fdiv_rn(1.0f, __fmul_rn(__ldg(a.norm_idx + li), nr));
+    if (a.gather) {
+      const uint32_t g = __ldg(a.source + li);
+      const uint32_t slot = a.hashmap ? __ldg(a.hashmap + g) : 0xFFFFFFFFu;
+      if (slot != 0xFFFFFFFFu) ptr = reinterpret_cast<const float4 *>(a.cache + (size_t)slot * a.cache_ld);
+      else if (a.miss) {
+        // bit 0 of the address marks a row that has to be read element by element
+        const uintptr_t p = reinterpret_cast<uintptr_t>(a.miss + (size_t)(a.miss_local ? li : g) * a.miss_ld);
+        ptr = reinterpret_cast<const float4 *>(a.miss_aligned ? p : (p | 1u));
+      } else atomicOr(&g_spmm_error, 1u);
+    } else {
+      ptr = reinterpret_cast<const float4 *>(a.x + (size_t)li * a.x_ld);
+    }
+  };
+
+  uint32_t start = __ldg(a.offs + r), end = __ldg(a.offs + r + 1);
+  float nr = __ldg(a.norm_row + r);
+  const float4 *my_ptr; float my_w;
+  resolve(start + lane, end, nr, my_ptr, my_w);
+  while (true) {
+    // request the first window of this warp's next row now; it is consumed after the current row
+    const uint32_t r_next = r + row_stride;
+    uint32_t n_start = 0, n_end = 0; float n_nr = 0.0f;
+    const float4 *n_ptr = nullptr; float n_w = 0.0f;
+    if (r_next < a.n) {
+      n_start = __ldg(a.offs + r_next); n_end = __ldg(a.offs + r_next + 1); n_nr = __ldg(a.norm_row + r_next);
+      resolve(n_start + lane, n_end, n_nr, n_ptr, n_w);
+    }
+    float acc[TILES][4];
+#pragma unroll
+    for (int t = 0; t < TILES; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    for (uint32_t base = start; base < end; base += 32) {
+      if (base != start) resolve(base + lane, end, nr, my_ptr, my_w);   // rows of more than 32 edges: further windows
+      const uint32_t cnt = min(32u, end - base);
+      for (uint32_t jj = 0; jj < cnt; jj += U) {
+        float4 v[U][TILES];
+        float ws[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          const unsigned src_lane = (jj + u) & 31;
+          const unsigned long long praw = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_ptr, src_lane);
+          ws[u] = __shfl_sync(0xffffffffu, my_w, src_lane);
+          const bool valid = (jj + u) < cnt && praw != 0;
+          if (praw & 1ull) {      // a row of a table without 16-byte alignment
+            const float *fp = reinterpret_cast<const float *>(praw & ~1ull);
+#pragma unroll
+            for (int t = 0; t < TILES; t++) {
+              const uint32_t c = (q0 + lane + 32 * t) * 4;
+              float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              if (valid && q0 + lane + 32 * t < fpad4) {
+                if (c < a.F) x.x = __ldg(fp + c);
+                if (c + 1 < a.F) x.y = __ldg(fp + c + 1);
+                if (c + 2 < a.F) x.z = __ldg(fp + c + 2);
+                if (c + 3 < a.F) x.w = __ldg(fp + c + 3);
+              }
+              v[u][t] = x;
+            }
+          } else {
+            const float4 *p = reinterpret_cast<const float4 *>(praw);
+#pragma unroll
+            for (int t = 0; t < TILES; t++) {
+              const uint32_t q = q0 + lane + 32 * t;
+              v[u][t] = (valid && q < fpad4) ? __ldg(p + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+          if ((jj + u) < cnt) {
+#pragma unroll
+            for (int t = 0; t < TILES; t++) {
+              acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(v[u][t].x, ws[u]));
+              acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(v[u][t].y, ws[u]));
+              acc[t][2] = __fadd_rn(acc[t][2], __fmul_rn(v[u][t].z, ws[u]));
+              acc[t][3] = __fadd_rn(acc[t][3], __fmul_rn(v[u][t].w, ws[u]));
+            }
+          }
+        }
+      }
+    }
+    float *out = a.y + (size_t)r * a.y_ld;
+#pragma unroll
+    for (int t = 0; t < TILES; t++) {
+      const uint32_t col = (q0 + lane + 32 * t) * 4;
+      if (q0 + lane + 32 * t >= fpad4) continue;
+      if (a.out_vec == 4) {
+        const float4 o = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+        if (a.stream_stores) __stcs(reinterpret_cast<float4 *>(out + col), o);
+        else *reinterpret_cast<float4 *>(out + col) = o;
+      } else if (a.out_vec == 2) {
+        if (col + 1 < a.F) __stcs(reinterpret_cast<float2 *>(out + col), make_float2(acc[t][0], acc[t][1]));
+        if (col + 3 < a.F) __stcs(reinterpret_cast<float2 *>(out + col + 2), make_float2(acc[t][2], acc[t][3]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+          if (col + c < a.F) __stcs(out + col + c, acc[t][c]);
+      }
+    }
+    if (r_next >= a.n) break;
+    r = r_next; start = n_start; end = n_end; nr = n_nr; my_ptr = n_ptr; my_w = n_w;
+  }
+}
+
+template <int TILES, int U>
+static int launch_wide_tiles(const WideArgs &a, cudaStream_t stream) {
+  int per_sm = 0;   // resident CTAs per SM of this instantiation: the grid is exactly one wave of them
+  NB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, spmm_wide_kernel<TILES, U>, kWideThreads, 0));
+  if (per_sm < 1) per_sm = 1;
+  const int reserve = tuning().reserve_sms > 0 ? tuning().reserve_sms : 0;
+  const unsigned sms = (unsigned)(num_sms() > reserve + 1 ? num_sms() - reserve : 1);
+  const unsigned warps_per_cta = kWideThreads / 32;
+  const unsigned need = (unsigned)(((uint64_t)a.n * a.split + warps_per_cta - 1) / warps_per_cta);
+  const unsigned grid = need < sms * per_sm ? need : sms * per_sm;
+  if ((uint64_t)grid * warps_per_cta < a.split) return fail(NB_ERR_INVALID, "spmm (wide rows): grid smaller than a row's parts");
+  NB_CUDA(launch_chained(spmm_wide_kernel<TILES, U>, dim3(grid), dim3(kWideThreads), 0, stream, a));
+  NB_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int U>
+static int launch_wide_u(const WideArgs &a, cudaStream_t stream) {
+  switch ((a.part_f4 + 31) / 32) {
+    case 1: return launch_wide_tiles<1, U>(a, stream);
+    case 2: return launch_wide_tiles<2, U>(a, stream);
+    case 3: return launch_wide_tiles<3, U>(a, stream);
+    case 4: return launch_wide_tiles<4, U>(a, stream);
+    case 5: return launch_wide_tiles<5, U>(a, stream);
+    case 6: return launch_wide_tiles<6, U>(a, stream);
+    case 7: return launch_wide_tiles<7, U>(a, stream);
+    case 8: return launch_wide_tiles<8, U>(a, stream);
+    default: return fail(NB_ERR_INVALID, "spmm (wide rows): feature width above 1024");
+  }
+}
+
+static int launch_wide(WideArgs a, cudaStream_t stream) {
+  if (a.n == 0) return 0;
+  const uint32_t f4 = (a.F + 3) / 4;
+  a.split = tuning().wide_col_split > 1 && f4 >= 64 ? (uint32_t)tuning().wide_col_split : 1u;
+  a.part_f4 = (f4 + a.split - 1) / a.split;
+  switch (tuning().wide_rows_in_flight) {
+    case 1: return launch_wide_u<1>(a, stream);
+    case 4: return launch_wide_u<4>(a, stream);
+    default: return launch_wide_u<2>(a, stream);
+  }
+}
+
+// A row source can be read with aligned float4 loads over ceil(F/4) columns.
+static bool wide_rows_ok(const float *p, size_t ld, uint32_t F) {
+  return p == nullptr || (aligned_to(p, 16) && ld % 4 == 0 && ld >= (size_t)(F + 3) / 4 * 4);
+}
+
 // Staged (TMA) path for the plain forms: references are the block-local indices themselves.
 static int try_staged(const float *x, float *y, const uint32_t *offs, const uint32_t *idx, const float *w,
                       const float *norm_row, const float *norm_idx, const float *act, float act_scale, uint32_t n,
@@ -390,6 +596,19 @@ int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, c
              "nb_spmm_csc_fwd_gather_fused: bad width or pitch");
   // Staged path: hits (cache rows, or the table itself when there is no cache) go through the TMA
   // unit; misses are rows of `feat` that the lanes copy.  Needs scratch for per-edge references.
+  // Wide rows with plain loads (tuning().wide_direct), when every row source is aligned for float4 loads.
+  if (tuning().wide_direct && F >= (uint32_t)tuning().staged_min_width && F <= 1024 && e > 0 &&
+      wide_rows_ok(d_cache, cache_ld, F) && (d_hashmap != nullptr || wide_rows_ok(feat, feat_ld, F))) {
+    WideArgs w{};
+    w.gather = 1; w.cache = d_cache; w.cache_ld = cache_ld; w.hashmap = d_hashmap; w.source = d_source;
+    w.miss = feat; w.miss_ld = feat_ld; w.miss_local = by_local;
+    w.miss_aligned = feat != nullptr && wide_rows_ok(feat, feat_ld, F);
+    w.y = d_y; w.y_ld = y_ld; w.offs = d_column_offset; w.idx = d_row_indices; w.norm_row = d_dst_norm;
+    w.norm_idx = d_src_norm; w.n = v; w.F = F; w.stream_stores = tuning().y_stream_stores;
+    w.out_vec = pick_vec(F, {y_ld}, {d_y});
+    if (y_ld % 4 == 0 && y_ld >= (size_t)(F + 3) / 4 * 4 && aligned_to(d_y, 16)) w.out_vec = 4;
+    return launch_wide(w, as_stream(stream));
+  }
   {
     const float *hit_base = d_hashmap ? d_cache : feat;
     const size_t hit_ld = d_hashmap ? cache_ld : feat_ld;

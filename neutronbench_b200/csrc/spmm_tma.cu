@@ -380,6 +380,9 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   const uint64_t pol_first = policy_evict_first(), pol_last = policy_evict_last();
   unsigned once_cur = hints ? __ballot_sync(0xffffffffu, w_cur == 1.0f) : 0u;
   unsigned once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
+  // rows that at least keep_uses edges read (factor^2 = number of uses) are kept with the evict-last policy
+  unsigned keep_cur = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_cur, w_cur) >= a.keep_uses) : 0u;
+  unsigned keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_nxt, w_nxt) >= a.keep_uses) : 0u;
 
   // Issue the copies of group `gi` (edges j0 + gi*G .. of this warp) into the group's slots `gs`; executed by the
   // whole warp.  Lane u takes the group's u-th edge.  The references come from the two operand windows, which cover
@@ -392,6 +395,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     const bool in_cur = j0 + t < win + 32;
     const uint32_t ref = in_cur ? rc : rn;
     const bool once = (((in_cur ? once_cur : once_nxt) >> (t & 31)) & 1u) != 0;
+    const bool keep = (((in_cur ? keep_cur : keep_nxt) >> (t & 31)) & 1u) != 0;
     const bool mine = lane < cnt;
     const uint32_t bar = bar0 + 8 * gs;
     unsigned char *dst0 = my_smem + (size_t)(gs << Gs) * a.slot_bytes;
@@ -419,8 +423,9 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     if (mine && (a.miss_bulk || !is_miss)) {
       const uint32_t dst = smem_u32(dst0 + (size_t)lane * a.slot_bytes);
       const float *src = is_miss ? a.miss + (size_t)(ref & 0x7FFFFFFFu) * a.miss_ld : a.x + (size_t)ref * a.x_ld;
-      if (!hints || (!once && a.l2_hint == 1)) bulk_g2s(dst, src, a.copy_bytes, bar);
-      else bulk_g2s_hint(dst, src, a.copy_bytes, bar, once ? pol_first : pol_last);
+      if (once) bulk_g2s_hint(dst, src, a.copy_bytes, bar, pol_first);
+      else if (keep) bulk_g2s_hint(dst, src, a.copy_bytes, bar, pol_last);
+      else bulk_g2s(dst, src, a.copy_bytes, bar);
     }
   };
 
@@ -485,9 +490,10 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     while (j == row_end && row < r_end) finish_row();        // rows without (more) edges
     if (j - win >= 32) {                                      // consume window moves on; fetch the one after
       win += 32;
-      ref_cur = ref_nxt; w_cur = w_nxt; once_cur = once_nxt;
+      ref_cur = ref_nxt; w_cur = w_nxt; once_cur = once_nxt; keep_cur = keep_nxt;
       load_edge(win + 32, ref_nxt, w_nxt);
       once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
+      keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_nxt, w_nxt) >= a.keep_uses) : 0u;
     }
     const uint32_t t = j - j0, in_group = t & (G - 1);
     if (in_group == 0) {                                      // first edge of a group: wait for the group's copies
@@ -628,6 +634,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (a.y_ld == 0) a.y_ld = a.F;
   a.l2_prefetch = tuning().l2_prefetch;
   a.l2_hint = tuning().l2_hint;
+  a.keep_uses = a.l2_hint == 2 ? 1.5f : (a.l2_hint == 3 ? (float)tuning().l2_keep_min_uses - 0.5f : 3.0e38f);
   a.y_stream = tuning().y_stream_stores;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
   // into panels whose working set fits, and panels are processed one after the other.

@@ -49,6 +49,7 @@ class GCNConfig:
     # (None: whenever the feature table is not in this GPU's memory)
     stage_misses: Optional[bool] = None
     reserve_sms: Optional[int] = None             # SMs left to the gradient all-reduce (None: 4 when world_size > 1)
+    cache_row_pitch: int = 0                      # floats between rows of the GPU feature cache (0: chosen from the width)
 
 
 class Parameter:
@@ -269,6 +270,9 @@ class GCN_GPU_NEIGHBOR_impl:
         # private layout: rows padded to 16 bytes so that 128-bit loads and bulk copies apply; wide rows (the ones the
         # aggregation stages through shared memory) start on a 128-byte line, which saves a partly used line per row read
         ld = (F + 31) // 32 * 32 if F >= 256 else (F + 3) // 4 * 4
+        if self.cfg.cache_row_pitch:
+            assert self.cfg.cache_row_pitch >= F and self.cfg.cache_row_pitch % 4 == 0
+            ld = int(self.cfg.cache_row_pitch)
         self.dev_cache_feature = torch.zeros((node_nums, ld), dtype=torch.float32, device=self.device)
         feat = self.datum.local_feature
         _lib.call("nb_cache_fill", ptr(self.dev_cache_feature), ld, ptr(feat), feat.stride(0),

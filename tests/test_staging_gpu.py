@@ -87,7 +87,10 @@ def test_sharded_table_needs_staging(cuda_device):
 
 
 @pytest.mark.parametrize("options", [(("l2_hint", 0),), (("l2_hint", 2),), (("y_stream_stores", 0),),
-                                     (("reserve_sms", 8),), (("ring_group_shift", 0),), (("gemm_mode", 1), ("pdl", 0))])
+                                     (("reserve_sms", 8),), (("ring_group_shift", 0),), (("gemm_mode", 1), ("pdl", 0)),
+                                     (("l2_hint", 3), ("l2_keep_min_uses", 3)), (("wide_direct", 1),),
+                                     (("wide_direct", 1), ("wide_rows_in_flight", 1)),
+                                     (("wide_direct", 1), ("wide_rows_in_flight", 4), ("y_stream_stores", 0))])
 def test_handle_options_change_no_result(cuda_device, options):
     """nb_gcn_set_option acts on one handle only and never on results (wide rows: the ring kernel runs)."""
     w0, l0 = _train(cuda_device, 602, 128, 41, (10, 5), 1.0, "device", stage=None)
@@ -163,3 +166,41 @@ def test_label_outside_the_class_range_is_reported(cuda_device, ws):
     assert abs(float(stats[0]) - ref) < 1e-5
     _lib.call("nb_device_error_reset")
     assert _flags() == 0
+
+
+def test_phase_times_of_the_epoch_line(cuda_device):
+    """nb_gcn_read_phase_times: sample (host wall time of the sampling halves), trans (staging), graph (aggregation
+    launches) and nn (rest of the training half) are all measured, and reading them resets them."""
+    edges, co, ri = small_graph(5000, 70000, seed=8)
+    rng = np.random.RandomState(1)
+    V, F = 5000, 100
+    cfg = GCNConfig(layers=[F, 64, 7], fanout=(6, 4), batch_size=300, drop_rate=0.3, cache_type="rate", cache_rate=0.3,
+                    seed=2000, pipelines=3, stage_misses=True)
+    g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(cuda_device), V, Workspace(64 << 20))
+    datum = GNNDatum(torch.from_numpy(rng.randn(V, F).astype(np.float32)).pin_memory(),
+                     torch.from_numpy(rng.randint(0, 7, size=V).astype(np.int64)).to(cuda_device), np.zeros(V, np.int32))
+    tk = GCN_GPU_NEIGHBOR_impl(g, datum, cfg)
+    tk.init_cache()
+    _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
+    smp = Sampler(g, np.arange(1500, dtype=np.uint32), cfg.fanout, 300, tk.ws, seed=cfg.seed, with_edge_weights=False)
+    tk.Forward(smp, train=True)
+    torch.cuda.synchronize()
+    ms = (C.c_double * 4)()
+    _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), ms)
+    sample, trans, graph, nn = list(ms)
+    assert sample > 0 and trans > 0 and graph > 0 and nn > 0, list(ms)
+    _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), ms)
+    assert list(ms) == [0.0, 0.0, 0.0, 0.0]
+
+
+@pytest.mark.parametrize("cache_rate,stage,where", [(0.3, True, "pinned_host"), (0.3, False, "device"), (0.0, True, "device"),
+                                                    (1.0, None, "device")])
+@pytest.mark.parametrize("in_flight", [1, 2, 4])
+def test_plain_load_wide_row_kernel_equals_the_ring(cuda_device, cache_rate, stage, where, in_flight):
+    """The one-warp-per-row plain-load aggregation for wide rows (option wide_direct) against the shared-memory ring:
+    cache hits, rows of the staging table and rows of a device table, 1 / 2 / 4 source rows in flight per warp."""
+    w0, l0 = _train(cuda_device, 602, 128, 41, (10, 5), cache_rate, where, stage=stage)
+    w1, l1 = _train(cuda_device, 602, 128, 41, (10, 5), cache_rate, where, stage=stage,
+                    options=(("wide_direct", 1), ("wide_rows_in_flight", in_flight)))
+    np.testing.assert_array_equal(w0.view(np.uint32), w1.view(np.uint32))
+    assert l0 == l1
