@@ -71,7 +71,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="timed steps per region and rank (0 = one epoch of this rank's shard)")
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products", "papers"])
+    ap.add_argument("--workload", default="reddit", choices=["arxiv", "reddit", "products", "papers", "cora"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cache-rate", type=float, default=None, help="override the workload's GPU cache rate")
     ap.add_argument("--cpu-batches", type=int, default=3, help="batches timed for the CPU baseline")
@@ -82,12 +82,12 @@ def parse_args():
     ap.add_argument("--min-region-s", type=float, default=0.3, help="repeat the K-step region until this much time is measured")
     ap.add_argument("--max-regions", type=int, default=100)
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
-    ap.add_argument("--pipelines", type=int, default=3,
+    ap.add_argument("--pipelines", type=int, default=4,
                     help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain loop")
     ap.add_argument("--pdl", type=int, default=None, help="1 / 0: programmatic dependent launch for the training half's kernels")
     ap.add_argument("--stage-misses", type=int, default=None,
-                    help="1 / 0: uncached rows staged once per distinct source by the sampling half (default: whenever the "
-                         "table is not in this GPU's memory)")
+                    help="1 / 0: uncached rows staged once per distinct source by the sampling half (default: only for a "
+                         "feature table sharded over GPUs)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="nb_gcn_set_option on the trainer's handle (tuning switches; results never depend on them)")
     ap.add_argument("--cache-row-pitch", type=int, default=0, help="floats between rows of the GPU feature cache (0: default)")
@@ -452,6 +452,132 @@ def roofline_of(events, peak, peak_src, traffic, cfg):
     return roofline, all_agg
 
 
+# ------------------------------------------------------------------------------------------ full-graph workload
+def bench_cora(args, device):
+    """--workload cora: the full-graph GCN (configuration of the reference's CPU-runnable case: 2,708 vertices, 13,264
+    edges with self loops, 1433-16-7, 200 epochs) through GCN_GPU_impl / ForwardSingleGPUfuseOp.  A step is one epoch
+    (forward, masked loss, backward, Adam over the whole graph); aggregated edges per step = 2 forward + 1 backward
+    aggregation over all edges.  The CPU baseline is the C oracle port of the same epoch (kind "port": the reference's
+    GCN_CPU toolkit loads its graph through the distributed engine and is not built here)."""
+    import torch
+    from neutronbench_b200 import (FullyRepGraph, GCN_GPU_impl, GCNConfig, GNNDatum, PartitionedGraph, Workspace, _lib,
+                                   synth)
+    V, F, C, hidden = 2708, 1433, 7, 16
+    edges = synth.uniform_undirected_numpy(V, 5278, args.seed)
+    rng = np.random.RandomState(args.seed + 1)
+    feat = (rng.random_sample((V, F)) < 0.013).astype(np.float32)
+    label = rng.randint(0, C, size=V).astype(np.int64)
+    mask = synth.split_mask(V, args.seed)
+    cfg = GCNConfig(layers=[F, hidden, C], fanout=(-1, -1), batch_size=V, drop_rate=0.5, learn_rate=0.01,
+                    weight_decay=0.0005, seed=args.seed)
+    g = FullyRepGraph.from_edges(torch.from_numpy(edges).to(device), V, Workspace(64 << 20))
+    pg = PartitionedGraph(g, Workspace(64 << 20))
+    tk = GCN_GPU_impl(pg, GNNDatum(torch.from_numpy(feat).to(device), torch.from_numpy(label).to(device), mask), cfg)
+    K = args.steps if args.steps > 0 else 200
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        tk.epoch(train=True)
+    torch.cuda.synchronize()
+    clocks = ClockSampler(0)
+    clocks.start()
+
+    def region(read_back):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(K):
+            tk.epoch(train=True)
+            if read_back:
+                tk.read_stats()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1)
+
+    def median_region(read_back):
+        first = region(read_back)
+        n = min(args.max_regions, max(1, math.ceil(args.min_region_s * 1e3 / max(first, 1e-3))))
+        ms = sorted([first] + [region(read_back) for _ in range(n - 1)])
+        return ms[(len(ms) - 1) // 2], len(ms)
+
+    launches0 = _lib.load().nb_launch_count()
+    ms_a, regions = median_region(False)
+    launches = (_lib.load().nb_launch_count() - launches0) / regions
+    ms_b, regions_b = median_region(True)
+    clk = clocks.stop()
+    edges_per_step = 3 * pg.edges
+    # the layer-0 aggregation alone, for the roofline figure
+    y = torch.empty((V, F), device=device)
+    x = tk.datum.local_feature
+    stream = torch.cuda.current_stream().cuda_stream
+    from neutronbench_b200.cuda_stream import ptr
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 200
+    e0.record()
+    for _ in range(reps):
+        _lib.call("nb_spmm_csc_fwd_fused", ptr(x), ptr(y), ptr(pg.row_indices), ptr(pg.column_offset), ptr(pg.src_norm),
+                  ptr(pg.dst_norm), V, F, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    agg_ms = e0.elapsed_time(e1) / reps
+    agg_bytes = 4 * F * (V + V) + 4 * pg.edges + 4 * (V + 1) + 4 * (V + V)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else FALLBACK_HBM_GBS
+    achieved = agg_bytes / (agg_ms * 1e-3) / 1e9
+    line = {"metric": "aggregated_edges_per_s", "value": edges_per_step * K / (ms_a * 1e-3), "unit": "edges/s", "n_gpus": 1,
+            "steps": K, "warmup": W, "ms_per_step": ms_a / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cora-shaped full graph: {V} nodes, {pg.edges} edges (incl. self loops), layers "
+                                   f"{F}-{hidden}-{C}, one step = one full-graph epoch",
+                       "l2_policy": "none: the whole working set of this workload (about 31 MB) is smaller than L2, on every "
+                                    "implementation", "parallelism": "dp1"},
+            "epoch_time_s": ms_a / K / 1e3, "regions": regions,
+            "e2e": {"value": edges_per_step * K / (ms_b * 1e-3), "unit": "edges/s", "ms_per_step": ms_b / K,
+                    "regions": regions_b, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 16},
+            "gpu_launches": int(round(launches)),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "layer-0 aggregation of the full graph (F = 1433), L2-resident",
+                         "avg_launch_ms": agg_ms, "algorithmic_bytes_per_launch": agg_bytes},
+            "clocks": clk}
+    if not args.no_cpu_baseline:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle
+        co64, ri = oracle.build_csc(edges, V)
+        co = co64.astype(np.uint32)
+        ro, ci = oracle.csr_from_csc(co, ri, V)
+        out_d, in_d = oracle.degrees(edges, V, clamp=True)
+        s_out, s_in = np.sqrt(out_d.astype(np.float64)).astype(np.float32), np.sqrt(in_d.astype(np.float64)).astype(np.float32)
+        wf = np.float32(1) / (s_out[ri] * s_in[np.repeat(np.arange(V), np.diff(co.astype(np.int64)))])
+        wb = np.float32(1) / (s_out[np.repeat(np.arange(V), np.diff(ro.astype(np.int64)))] * s_in[ci])
+        Wt = tk.P.W.cpu().numpy().copy()
+        M, Vv, grad = np.zeros_like(Wt), np.zeros_like(Wt), np.zeros_like(Wt)
+        o = tk.P.offsets
+        train = np.nonzero(mask == 0)[0]
+        times = []
+        for ep in range(1 + max(1, args.cpu_batches)):
+            t0 = time.perf_counter()
+            w0, w1 = Wt[o[0]:o[1]].reshape(F, hidden), Wt[o[1]:o[2]].reshape(hidden, C)
+            y0 = oracle.spmm_fwd(feat, wf, ri, co)
+            x1 = oracle.relu_dropout(y0 @ w0, 0.5, args.seed, 0, ep)
+            y1 = oracle.spmm_fwd(x1, wf, ri, co)
+            z = y1 @ w1
+            _, dzt, _ = oracle.softmax_nll(z[train], label[train])
+            dz = np.zeros_like(z)
+            dz[train] = dzt
+            grad[o[1]:o[2]] = (y1.T @ dz).reshape(-1)
+            dx1 = oracle.spmm_bwd(dz @ w1.T, wb, ro, ci, act=x1, scale=2.0)
+            grad[o[0]:o[1]] = (y0.T @ dx1).reshape(-1)
+            oracle.adam(Wt, grad, M, Vv, 0.01, 0.9, 0.999, 1e-9, 0.0005, 0.9, 0.999)
+            if ep > 0:
+                times.append(time.perf_counter() - t0)
+        ms = 1e3 * sum(times) / len(times)
+        line["cpu_baseline"] = {"value": edges_per_step / (ms * 1e-3), "unit": "edges/s", "cores": oracle.lib().orc_num_threads(),
+                                "kind": "port", "ms_per_step": ms,
+                                "sample": f"{len(times)} full-graph epochs after 1 warm-up: C oracle port (OpenMP aggregation, "
+                                          f"numpy BLAS dense layers) on the host cores"}
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     args = parse_args()
     import torch
@@ -476,6 +602,15 @@ def main():
     from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, _lib
     if args.pdl is not None:
         _lib.load().nb_set_pdl(int(args.pdl))
+    if args.workload == "cora":
+        if rank != 0:
+            return 0
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's full-graph CPU toolkit (GCN_CPU) loads its "
+                              "graph through the distributed engine, which is not built here; --workload cora reports the C "
+                              "oracle port as cpu_baseline"}))
+            return 0
+        return bench_cora(args, device)
     if args.workload == "papers" and args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the Papers-shaped feature table (57 GB) is a multi-GPU "
                           "scale test; the reference's CPU path is timed on the other workloads"}))

@@ -59,14 +59,14 @@ size_t nb_ws_high_water(const nb_ws *ws);   /* largest value nb_ws_used ever had
  * Aggregation (SpMM).
  *
  * nb_spmm_csc_fwd replaces Cuda_Stream::Gather_By_Dst_From_Src with with_weight=true
- * (cuda/ntsCUDA.hpp:131-135, cuda/ntsCUDAGraphOP.cu:186-210, kernel
+ * (cuda/ntsCUDA.hpp:124-128, cuda/ntsCUDAGraphOP.cu:186-210, kernel
  * cuda/ntsCUDAFuseKernel.cuh:272-290; caller core/ntsMiniBatchGraphOp.hpp:311-315):
  *     y[d,:] = sum_{j in [column_offset[d], column_offset[d+1])} w[j] * x[row_indices[j],:]
  * Every row of y is written (empty columns become zero), so y need not be zeroed first.  The sum is
  * taken edge after edge in CSC order, one multiply and one add per element, exactly like the
  * reference kernel, so results do not depend on the launch shape.
  *
- * nb_spmm_csr_bwd replaces Cuda_Stream::Gather_By_Src_From_Dst (cuda/ntsCUDA.hpp:146-150,
+ * nb_spmm_csr_bwd replaces Cuda_Stream::Gather_By_Src_From_Dst (cuda/ntsCUDA.hpp:139-143,
  * cuda/ntsCUDAGraphOP.cu:269-292, kernel cuda/ntsCUDAFuseKernel.cuh:450-468; caller
  * core/ntsMiniBatchGraphOp.hpp:365-368):
  *     gx[s,:] = sum_{j in [row_offset[s], row_offset[s+1])} w[j] * gy[column_indices[j],:]

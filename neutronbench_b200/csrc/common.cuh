@@ -45,10 +45,12 @@ struct Tuning {
                                  // L2 evict-first policy (1); 2: rows with more uses evict-last as well; 3: only
                                  // rows with at least l2_keep_min_uses uses evict-last; 0: off
   int l2_keep_min_uses = 4;
+  int ring_prefetch = 0;         // ring kernel: groups of rows whose L2 prefetch is issued ahead of the ring's copies
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
   int wide_rows_in_flight = 2;   // source rows in flight per warp of that kernel: 1, 2 or 4
   int wide_col_split = 1;        // warps that share one output row of that kernel, each taking a range of columns
+  int stage_ctas = 0;            // CTAs of the staging gather (0: 32 for a table in host memory, 2 per SM for shards)
   int reserve_sms = 0;           // SMs the one-CTA-per-SM aggregation kernel leaves to kernels that run beside it
   uint32_t ring_group_shift = 1; // ring kernel: 1 << shift row slots share one barrier
   uint64_t l2_panel_bytes = 0;   // working-set target of one column panel (0: no panels)
@@ -164,6 +166,7 @@ struct TmaSpmmArgs {
   uint32_t src_rows_hint;  // number of distinct rows the references can name (0 = unknown): sizes the panels
   uint32_t slot_bytes, copy_bytes, seg, grp_shift, fpad, panels, panel_floats;   // filled by launch_spmm_tma
   int l2_prefetch;
+  uint32_t ring_prefetch;  // ring kernel: groups of rows prefetched into L2 beyond the ring
   int l2_hint;             // ring kernel: L2 eviction policy per copied row (Tuning::l2_hint)
   float keep_uses;         // rows read by at least this many edges of the launch are copied with evict-last
   int y_stream;            // ring kernel: streaming stores for y
@@ -183,11 +186,11 @@ int reset_tc_error_flag();
 int reset_gather_error_flag();
 int reset_loss_error_flag();
 // nb_feature_gather with an output pitch; misses_only = 1 copies only the rows that have no cache slot (row i of the
-// output belongs to source[i] either way).
+// output belongs to source[i] either way); max_ctas > 0 caps the launch (the kernel strides over the rows).
 int feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const float *feat, size_t feat_ld,
                         const float *const *feat_shards, uint32_t num_shards, uint32_t shard_rows, const float *d_cache,
                         size_t cache_ld, const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
-                        void *stream);
+                        void *stream, uint32_t max_ctas);
 int read_tc_error_flag(unsigned int *value);
 int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
                      int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream);

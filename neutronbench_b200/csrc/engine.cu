@@ -354,9 +354,13 @@ int sample_into(nb_gcn *g, nb_gcn_batch *bt, uint32_t draw, const uint32_t *d_se
     bt->stage_ld = (F0 + 3) / 4 * 4;
     NB_TRY(arena(ws, (size_t)b0.s * bt->stage_ld, &bt->stage));
     AggTimer t(g, stream, 0, 3);
+    // A copy over the host link is bound by that link: a few CTAs keep it busy and leave the SMs to the training half
+    // that runs beside this stream.  Peer reads over NVLink need more in flight.
+    const uint32_t ctas = nb::tuning().stage_ctas > 0 ? (uint32_t)nb::tuning().stage_ctas
+                                                      : (c.d_feat_shards ? 2u * (uint32_t)nb::num_sms() : 32u);
     NB_TRY(nb::feature_gather_impl(bt->stage, bt->stage_ld, c.d_hashmap != nullptr, c.feat, c.feat_ld, c.d_feat_shards,
                                    c.num_shards, c.shard_rows, c.d_cache, c.cache_ld, c.d_hashmap, b0.source, b0.s, F0,
-                                   stream));
+                                   stream, ctas));
   }
   NB_CUDA(cudaEventRecord(bt->sampled, nb::as_stream(stream)));
   return 0;
@@ -619,6 +623,8 @@ NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
     NB_REQUIRE(value >= 2 && value <= 1000000, "nb_gcn_set_option: l2_keep_min_uses is at least 2");
     t.l2_keep_min_uses = (int)value;
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
+  else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);
+  else if (n == "stage_ctas") t.stage_ctas = (int)(value > 0 ? value : 0);
   else if (n == "wide_direct") t.wide_direct = value != 0;
   else if (n == "wide_col_split") {
     NB_REQUIRE(value >= 1 && value <= 4, "nb_gcn_set_option: wide_col_split is 1..4");

@@ -47,11 +47,13 @@ template <int VEC>
 __global__ void __launch_bounds__(kWarps * 32) feature_gather_kernel(const GatherArgs a) {
   constexpr int kRows = 4;
   const unsigned lane = threadIdx.x & 31;
-  const uint64_t warp_global = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
   const uint64_t groups = ((uint64_t)a.n + kRows - 1) / kRows;
-  const uint64_t grp = warp_global / a.tiles;
-  if (grp >= groups) return;
-  const uint32_t tile = (uint32_t)(warp_global - grp * a.tiles);
+  const uint64_t total_warps = (uint64_t)gridDim.x * kWarps;
+  // grid-stride over (group of kRows rows, column tile) items: the launch may be much smaller than the work, which
+  // is how a copy that is bound by a slow link (host memory) leaves the SMs to the kernels that run beside it
+  for (uint64_t item = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); item < groups * a.tiles; item += total_warps) {
+  const uint64_t grp = item / a.tiles;
+  const uint32_t tile = (uint32_t)(item - grp * a.tiles);
   const uint32_t col = tile * (32 * VEC) + lane * VEC;
   const float *src[kRows];
 #pragma unroll
@@ -74,10 +76,11 @@ __global__ void __launch_bounds__(kWarps * 32) feature_gather_kernel(const Gathe
       }
     }
   }
-  if (col >= a.F) return;
+  if (col >= a.F) continue;
 #pragma unroll
   for (int k = 0; k < kRows; k++) {
     if (src[k]) copy_vec<VEC>(a.x0 + (grp * kRows + k) * a.x0_ld + col, src[k] + col);
+  }
   }
 }
 
@@ -172,13 +175,13 @@ NB_API int nb_feature_gather(float *d_x0, const float *feat, size_t feat_ld, con
                              const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
                              void *stream) {
   return feature_gather_impl(d_x0, F, 0, feat, feat_ld, feat_shards, num_shards, shard_rows, d_cache, cache_ld, d_hashmap,
-                             d_source, n, F, stream);
+                             d_source, n, F, stream, 0);
 }
 
 int nb::feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const float *feat, size_t feat_ld,
                             const float *const *feat_shards, uint32_t num_shards, uint32_t shard_rows,
                             const float *d_cache, size_t cache_ld, const uint32_t *d_hashmap, const uint32_t *d_source,
-                            uint32_t n, uint32_t F, void *stream) {
+                            uint32_t n, uint32_t F, void *stream, uint32_t max_ctas) {
   if (n == 0) return 0;
   NB_REQUIRE(x0_ld >= F, "nb_feature_gather: output pitch smaller than width");
   NB_REQUIRE(d_x0 && d_source, "nb_feature_gather: null pointer");
@@ -197,7 +200,8 @@ int nb::feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const fl
                            {d_x0, feat, d_cache});
   a.tiles = (F + 32 * vec - 1) / (32 * vec);
   const uint64_t warps = (((uint64_t)n + 3) / 4) * a.tiles;
-  const uint64_t blocks = (warps + kWarps - 1) / kWarps;
+  uint64_t blocks = (warps + kWarps - 1) / kWarps;
+  if (max_ctas > 0 && blocks > max_ctas) blocks = max_ctas;
   NB_REQUIRE(blocks <= 0x7fffffffull, "nb_feature_gather: too many rows for one launch");
   cudaStream_t st = as_stream(stream);
   switch (vec) {

@@ -429,8 +429,26 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     }
   };
 
+  // L2 prefetch of group `gi` (a.ring_prefetch groups beyond the ring): the rows start their way from DRAM while they
+  // hold no shared-memory slot yet, so a warp has ring + prefetch rows in flight instead of the ring's few.  Needs the
+  // group's references in the two operand windows: callers keep (R + ring_prefetch + 1) * G <= 32.
+  auto prefetch_group = [&](uint32_t gi) {
+    if ((gi << Gs) >= n_edges) return;                         // uniform over the warp
+    const uint32_t t = (gi << Gs) + lane;
+    const uint32_t cnt = min(G, n_edges - (gi << Gs));
+    const uint32_t rc = __shfl_sync(0xffffffffu, ref_cur, t & 31), rn = __shfl_sync(0xffffffffu, ref_nxt, t & 31);
+    const uint32_t ref = (j0 + t < win + 32) ? rc : rn;
+    if (lane < cnt && j0 + t < win + 64) {
+      const bool is_miss = (ref & 0x80000000u) != 0;
+      if (!is_miss) prefetch_l2(a.x + (size_t)ref * a.x_ld, a.copy_bytes);
+      else if (a.miss_bulk) prefetch_l2(a.miss + (size_t)(ref & 0x7FFFFFFFu) * a.miss_ld, a.copy_bytes);
+    }
+  };
+  const uint32_t PF = a.ring_prefetch;
+
   // prologue: fill the ring
   for (uint32_t gi = 0; gi < R && (gi << Gs) < n_edges; gi++) issue_group(gi, gi);
+  for (uint32_t gi = R; gi < R + PF; gi++) prefetch_group(gi);
 
   // row bookkeeping: lane holds the end offset of row rw_base + lane
   uint32_t rw_base = r_begin;
@@ -529,6 +547,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       __syncwarp();            // every lane has read the slots
       fence_proxy_async();     // order those reads before the async-proxy refill
       issue_group((t >> Gs) + R, cur_gs);
+      if (PF) prefetch_group((t >> Gs) + R + PF);
     }
   }
   while (row < r_end) finish_row();
@@ -634,6 +653,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (a.y_ld == 0) a.y_ld = a.F;
   a.l2_prefetch = tuning().l2_prefetch;
   a.l2_hint = tuning().l2_hint;
+  a.ring_prefetch = 0;
   a.keep_uses = a.l2_hint == 2 ? 1.5f : (a.l2_hint == 3 ? (float)tuning().l2_keep_min_uses - 0.5f : 3.0e38f);
   a.y_stream = tuning().y_stream_stores;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
@@ -658,6 +678,9 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
     if (R >= 2) {
       a.seg = R;
       a.grp_shift = shift;
+      // groups prefetched into L2 beyond the ring, while their references are still inside the operand windows
+      const uint32_t max_pf = (32u >> shift) > R + 1 ? (32u >> shift) - R - 1 : 0;
+      a.ring_prefetch = (uint32_t)tuning().ring_prefetch < max_pf ? (uint32_t)tuning().ring_prefetch : max_pf;
       const size_t smem = (size_t)kRingWarps * (R << shift) * a.slot_bytes + (size_t)kRingWarps * R * sizeof(uint64_t);
       return a.act ? launch_ring<true>(a, smem, stream) : launch_ring<false>(a, smem, stream);
     }

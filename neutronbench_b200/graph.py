@@ -341,3 +341,49 @@ class Sampler:
             cuda_stream.global_copy_label_move_gpu(ptr(local_label), ptr(global_label), ptr(blk.destination),
                                                    blk.v_size)
         return local_label
+
+
+class PartitionedGraph:
+    """The whole graph as one chunk with precomputed GCN edge weights — what the reference's full-graph operators
+    read (PartitionedGraph::graph_chunks of CSC_segment_pinned, core/PartitionedGraph.hpp; the weights are
+    nts_norm_degree = 1 / ((float)sqrt(out_degree[src]) * (float)sqrt(in_degree[dst])) over the WHOLE graph's
+    degrees, clamped to at least 1 as generate_backward_structure does, core/ntsBaseOp.hpp:183-186,
+    core/graph.hpp:3983-3986).  Holds the CSC by destination with `edge_weight_forward` in CSC order and its
+    transpose (CSR by source, ascending destinations inside a row) with `edge_weight_backward` in CSR order."""
+
+    def __init__(self, graph: FullyRepGraph, ws: Workspace):
+        dev = graph.device
+        V, E = graph.global_vertices, graph.global_edges
+        assert E < 2 ** 32, "block-local offsets are 32-bit"
+        self.graph = graph
+        self.vertices, self.edges = V, E
+        co64 = graph.column_offset
+        self.column_offset = co64.to(torch.int32)          # uint32 bit patterns
+        self.row_indices = graph.row_indices
+        in_deg = (co64[1:] - co64[:-1])
+        # transpose: the CSC of the reversed pairs, built by the same kernel (stable in CSC order, hence ascending
+        # destinations inside every source's row)
+        dst = torch.repeat_interleave(torch.arange(V, device=dev, dtype=torch.int32), in_deg)
+        pairs = torch.stack([dst, graph.row_indices], dim=1).contiguous()     # (dst, src): "source" column is dst
+        ro64 = torch.empty(V + 1, dtype=torch.int64, device=dev)
+        self.column_indices = _i32(max(E, 1), dev)
+        _lib.call("nb_graph_build_csc", ws.handle, ptr(pairs), E, V, ptr(ro64), ptr(self.column_indices), None, None,
+                  torch.cuda.current_stream().cuda_stream)
+        self.row_offset = ro64.to(torch.int32)
+        out_deg = (ro64[1:] - ro64[:-1])
+        # one-time host work, in the reference's arithmetic: sqrt in double rounded to float, float product, 1/x
+        ind = np.maximum(in_deg.cpu().numpy(), 1).astype(np.float64)
+        outd = np.maximum(out_deg.cpu().numpy(), 1).astype(np.float64)
+        s_in, s_out = np.sqrt(ind).astype(np.float32), np.sqrt(outd).astype(np.float32)
+        ri = graph.row_indices.cpu().numpy().view(np.uint32)
+        ci = self.column_indices.cpu().numpy().view(np.uint32)[:E]
+        dst_h = dst.cpu().numpy()
+        src_of_row = np.repeat(np.arange(V, dtype=np.int64), out_deg.cpu().numpy())
+        one = np.float32(1.0)
+        self.edge_weight_forward = torch.from_numpy(one / (s_out[ri] * s_in[dst_h])).to(dev)
+        self.edge_weight_backward = torch.from_numpy(one / (s_out[src_of_row] * s_in[ci])).to(dev)
+        # the two factors per vertex, for the aggregation entry points that form the weight per edge themselves
+        self.src_norm = torch.from_numpy(s_out).to(dev)
+        self.dst_norm = torch.from_numpy(s_in).to(dev)
+        self.in_degree, self.out_degree = in_deg, out_deg
+        del pairs, dst

@@ -72,3 +72,37 @@ class SingleGPUSampleGraphOp(ntsGraphOp):
                                                     ptr(blk.row_offset), ptr(blk.column_indices), 0, 0, 0, 0,
                                                     blk.e_size, blk.src_size, F, True, False)
         return f_input_grad
+
+
+class ForwardSingleGPUfuseOp(ntsGraphOp):
+    """The full-graph GCN aggregation on one GPU (core/ntsSingleGPUFusedGraphOp.hpp:49-70 ->
+    Graph::forward_single / backward_single, core/graph.hpp:3432-3478 -> GatherByDstFromSrc / GatherBySrcFromDst,
+    core/NtsScheduler.hpp:146-178, 239-271): the same two aggregation entry points as the sampled operator, with
+    v = s = |V| and the whole-graph edge weights of a PartitionedGraph.  forward returns a new leaf that requires
+    grad, like NewKeyTensor; backward maps dY to dX through the transposed structure."""
+
+    def __init__(self, partitioned_graph, active=None, cs: Optional[Cuda_Stream] = None):
+        super().__init__(partitioned_graph)
+        self.active_ = active
+        self.cuda_stream = cs if cs is not None else Cuda_Stream()
+
+    def forward(self, f_input: torch.Tensor) -> torch.Tensor:
+        pg = self.graph_
+        assert f_input.is_cuda and f_input.dtype == torch.float32 and f_input.is_contiguous()
+        assert f_input.size(0) == pg.vertices
+        F = f_input.size(1)
+        f_output = torch.empty((pg.vertices, F), dtype=torch.float32, device=f_input.device)
+        self.cuda_stream.Gather_By_Dst_From_Src(ptr(f_input), ptr(f_output), ptr(pg.edge_weight_forward),
+                                                ptr(pg.row_indices), ptr(pg.column_offset), 0, pg.vertices, 0,
+                                                pg.vertices, pg.edges, pg.vertices, F, True, False)
+        return f_output.requires_grad_(True)
+
+    def backward(self, f_output_grad: torch.Tensor) -> torch.Tensor:
+        pg = self.graph_
+        assert f_output_grad.is_cuda and f_output_grad.dtype == torch.float32 and f_output_grad.is_contiguous()
+        F = f_output_grad.size(1)
+        f_input_grad = torch.empty((pg.vertices, F), dtype=torch.float32, device=f_output_grad.device)
+        self.cuda_stream.Gather_By_Src_From_Dst(ptr(f_output_grad), ptr(f_input_grad), ptr(pg.edge_weight_backward),
+                                                ptr(pg.row_offset), ptr(pg.column_indices), 0, pg.vertices, 0,
+                                                pg.vertices, pg.edges, pg.vertices, F, True, False)
+        return f_input_grad

@@ -46,7 +46,7 @@ class GCNConfig:
     sample_rate: float = 0.0                      # SAMPLE_RATE > 0: degree-proportional fan-out for training batches
     lower_fanout: int = 0                         # LOWER_FANOUT of that mode
     # rows that are not cached are copied once per distinct source into a staging table by the sampling half
-    # (None: whenever the feature table is not in this GPU's memory)
+    # (None: only for a table sharded over GPUs, which is read no other way)
     stage_misses: Optional[bool] = None
     reserve_sms: Optional[int] = None             # SMs left to the gradient all-reduce (None: 4 when world_size > 1)
     cache_row_pitch: int = 0                      # floats between rows of the GPU feature cache (0: chosen from the width)
@@ -186,7 +186,10 @@ class GCN_GPU_NEIGHBOR_impl:
         self.dev_cache_node_hashmap = None
         self.cache_node_num = 0
         self.feature_on_device = datum.shards is None and datum.local_feature.is_cuda
-        self.stage_misses = (not self.feature_on_device) if cfg.stage_misses is None else bool(cfg.stage_misses)
+        # Staging is needed for a sharded table.  For a table in mapped host memory it is an option that measured no
+        # gain on one GPU (Products-shaped: 0.72 against 0.71 ms per step): repeated reads of a host row inside one
+        # launch already hit L2, and the staging copy slows the dense kernels that run beside it.
+        self.stage_misses = (datum.shards is not None) if cfg.stage_misses is None else bool(cfg.stage_misses)
         self.reserve_sms = (4 if world_size > 1 else 0) if cfg.reserve_sms is None else int(cfg.reserve_sms)
         self.device_errors_checked = 0
         self.agg_edges_fwd = 0
@@ -820,3 +823,105 @@ def default_workspace_bytes(num_vertices: int, cfg: GCNConfig) -> int:
         v = min(num_vertices, v * (f if f > 0 else 64))
     acts += 4 * v * ((cfg.layers[0] + 3) // 4 * 4)           # gathered input rows (gather not fused) / staged misses
     return int(block + splitk + acts + (64 << 20))
+
+
+class GCN_GPU_impl:
+    """Full-graph GCN on one GPU, the reference's non-sampled trainer (toolkits/GCN.hpp:140-260 with its single-GPU
+    operator, core/ntsSingleGPUFusedGraphOp.hpp:49-70): per layer X_{l+1} = relu(A X_l W_l) with dropout on the
+    inputs of layers l >= 1, last layer without relu, mean NLL of log_softmax over the TRAIN vertices, Adam with weight
+    decay.  Like NtsContext::self_backward the first graph operator is not back-propagated.  Every kernel is from
+    libnb_b200; the aggregation forms 1 / (sqrt(out_deg[src]) * sqrt(in_deg[dst])) from the whole graph's degrees."""
+
+    def __init__(self, partitioned_graph, datum: GNNDatum, cfg: GCNConfig, ws: Optional[Workspace] = None):
+        self.pg, self.datum, self.cfg = partitioned_graph, datum, cfg
+        self.device = partitioned_graph.graph.device
+        self.layers = len(cfg.layers) - 1
+        V = partitioned_graph.vertices
+        assert datum.local_feature.is_cuda and datum.local_feature.size(0) == V
+        widest = max(cfg.layers)
+        self.ws = ws if ws is not None else Workspace(int(4 * V * widest * 2 + 4 * max(cfg.layers[i] * cfg.layers[i + 1]
+                                                          for i in range(self.layers)) * 640 + (64 << 20)))
+        self.P = Parameter(cfg.layers, cfg, self.device, torch.Generator().manual_seed(cfg.seed))
+        self.step_count = 0
+        self.stats = torch.zeros(4, dtype=torch.float32, device=self.device)
+        mask = np.asarray(datum.local_mask)
+        self.ids = [torch.from_numpy(np.nonzero(mask == k)[0].astype(np.int32)).to(self.device) for k in (0, 1, 2)]
+        # position of every train vertex inside the train list, for scattering the loss gradient back to full rows
+        pos = np.zeros(V, dtype=np.int32)
+        train = np.nonzero(mask == 0)[0]
+        pos[train] = np.arange(len(train), dtype=np.int32)
+        self.train_pos = torch.from_numpy(pos).to(self.device)
+        self.agg_edges_fwd = self.agg_edges_bwd = 0
+
+    def _buf(self, rows, cols):
+        return torch.empty((max(int(rows), 1), int(cols)), dtype=torch.float32, device=self.device)
+
+    def _loss_on(self, logits: torch.Tensor, ids: torch.Tensor, dlogits_full: Optional[torch.Tensor]):
+        """Mean NLL and hits over the vertices `ids`; with dlogits_full the gradient rows are written there (other
+        rows of it must already be zero)."""
+        stream = torch.cuda.current_stream().cuda_stream
+        n, C = int(ids.numel()), logits.size(1)
+        rows = self._buf(n, C)
+        _lib.call("nb_feature_gather", ptr(rows), ptr(logits), C, None, 0, 0, None, 0, None, ptr(ids), n, C, stream)
+        lab = torch.empty(max(n, 1), dtype=torch.int64, device=self.device)
+        _lib.call("nb_label_gather", ptr(lab), ptr(self.datum.local_label), ptr(ids), n, 1, stream)
+        drows = self._buf(n, C) if dlogits_full is not None else None
+        _lib.call("nb_softmax_nll", self.ws.handle, ptr(rows), ptr(lab), n, C, ptr(drows), ptr(self.stats), stream)
+        if dlogits_full is not None:
+            _lib.call("nb_feature_gather_indexed", ptr(dlogits_full), C, ptr(drows), C, ptr(self.train_pos), ptr(ids),
+                      None, n, C, stream)
+
+    def epoch(self, train: bool = True):
+        """One full-graph step (Forward, Loss, self_backward, Update of toolkits/GCN.hpp).  Returns the logits."""
+        c, L, pg = self.cfg, self.layers, self.pg
+        V = pg.vertices
+        stream = torch.cuda.current_stream().cuda_stream
+        wsh = self.ws.handle
+        p = c.drop_rate if train else 0.0
+        scale = 1.0 / (1.0 - p) if p > 0 else 1.0
+        X = [self.datum.local_feature]
+        Y = []
+        for l in range(L):
+            Fi, Fo = c.layers[l], c.layers[l + 1]
+            y = self._buf(V, Fi)
+            _lib.call("nb_spmm_csc_fwd_fused", ptr(X[l]), ptr(y), ptr(pg.row_indices), ptr(pg.column_offset),
+                      ptr(pg.src_norm), ptr(pg.dst_norm), V, Fi, stream)
+            Y.append(y)
+            z = self._buf(V, Fo)
+            _lib.call("nb_gemm", wsh, ptr(y), ptr(self.P.w(l)), ptr(z), V, Fo, Fi, 0, 0, stream)
+            if l < L - 1:   # relu, then the dropout that the next layer applies to its input
+                _lib.call("nb_relu_dropout", ptr(z), V * Fo, p, c.seed, l, self.step_count, stream)
+            X.append(z)
+        self.agg_edges_fwd += L * pg.edges
+        if not train:
+            return X[L]
+        C = c.layers[L]
+        dZ = torch.zeros((V, C), dtype=torch.float32, device=self.device)
+        self._loss_on(X[L], self.ids[0], dZ)
+        for l in range(L - 1, -1, -1):
+            Fi, Fo = c.layers[l], c.layers[l + 1]
+            _lib.call("nb_gemm", wsh, ptr(Y[l]), ptr(dZ), ptr(self.P.g(l)), Fi, Fo, V, 1, 0, stream)
+            if l == 0:
+                break   # the first graph operator is not back-propagated (core/ntsContext.hpp:292)
+            dY = self._buf(V, Fi)
+            _lib.call("nb_gemm", wsh, ptr(dZ), ptr(self.P.w(l)), ptr(dY), V, Fi, Fo, 0, 1, stream)
+            dX = self._buf(V, Fi)
+            _lib.call("nb_spmm_csr_bwd_fused", ptr(dY), ptr(dX), ptr(pg.row_offset), ptr(pg.column_indices),
+                      ptr(pg.src_norm), ptr(pg.dst_norm), ptr(X[l]), scale, V, Fi, stream)
+            self.agg_edges_bwd += pg.edges
+            dZ = dX
+        self.P.learn_with_decay_Adam(stream)
+        self.step_count += 1
+        return X[L]
+
+    def read_stats(self):
+        host = self.stats.cpu()
+        return float(host[0]), int(host[1])
+
+    def Test(self, which: int, logits: torch.Tensor) -> float:
+        """Accuracy over the vertices of one split (0 train, 1 val, 2 test)."""
+        ids = self.ids[which]
+        if ids.numel() == 0:
+            return 0.0
+        self._loss_on(logits, ids, None)
+        return self.read_stats()[1] / int(ids.numel())
