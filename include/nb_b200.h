@@ -63,8 +63,10 @@ size_t nb_ws_high_water(const nb_ws *ws);   /* largest value nb_ws_used ever had
  * cuda/ntsCUDAFuseKernel.cuh:272-290; caller core/ntsMiniBatchGraphOp.hpp:311-315):
  *     y[d,:] = sum_{j in [column_offset[d], column_offset[d+1])} w[j] * x[row_indices[j],:]
  * Every row of y is written (empty columns become zero), so y need not be zeroed first.  The sum is
- * taken edge after edge in CSC order, one multiply and one add per element, exactly like the
- * reference kernel, so results do not depend on the launch shape.
+ * taken edge after edge in CSC order with one fused multiply-add per element, y = fma(x, w, y): the
+ * arithmetic of the reference's CPU operator (nts_comp, core/ntsBaseOp.hpp:76-97, as its -O3 -march=native
+ * build compiles it), whose results it reproduces bit for bit; results do not depend on the launch shape.
+ * (The reference's CUDA kernel rounds the product before its atomicAdd and differs in the last bit.)
  *
  * nb_spmm_csr_bwd replaces Cuda_Stream::Gather_By_Src_From_Dst (cuda/ntsCUDA.hpp:139-143,
  * cuda/ntsCUDAGraphOP.cu:269-292, kernel cuda/ntsCUDAFuseKernel.cuh:450-468; caller

@@ -45,6 +45,7 @@ struct Tuning {
                                  // L2 evict-first policy (1); 2: rows with more uses evict-last as well; 3: only
                                  // rows with at least l2_keep_min_uses uses evict-last; 0: off
   int l2_keep_min_uses = 4;
+  int ring_wait_ns = 0;          // ring kernel: a warp waiting for its copies may sleep this long per try (0: plain spin)
   int ring_prefetch = 0;         // ring kernel: groups of rows whose L2 prefetch is issued ahead of the ring's copies
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
@@ -167,6 +168,7 @@ struct TmaSpmmArgs {
   uint32_t slot_bytes, copy_bytes, seg, grp_shift, fpad, panels, panel_floats;   // filled by launch_spmm_tma
   int l2_prefetch;
   uint32_t ring_prefetch;  // ring kernel: groups of rows prefetched into L2 beyond the ring
+  uint32_t wait_ns;        // ring kernel: suspend-time hint of the copy-barrier wait (0: plain try_wait)
   int l2_hint;             // ring kernel: L2 eviction policy per copied row (Tuning::l2_hint)
   float keep_uses;         // rows read by at least this many edges of the launch are copied with evict-last
   int y_stream;            // ring kernel: streaming stores for y
@@ -248,6 +250,21 @@ int exclusive_scan_u32_to_u64(nb_ws *ws, const uint32_t *d_in, uint64_t *d_out, 
 namespace nb {
 
 #if defined(__CUDACC__)
+// Two IEEE fused multiply-adds in one instruction (sm_100 packed f32x2 arithmetic): d = a * b + c per element with
+// a single rounding, exactly what __fmaf_rn gives for each element.
+__device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
 __device__ __forceinline__ void pdl_enter() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -624,6 +624,7 @@ NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
     t.l2_keep_min_uses = (int)value;
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
   else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);
+  else if (n == "ring_wait_ns") t.ring_wait_ns = (int)(value > 0 ? (value < 100000 ? value : 100000) : 0);
   else if (n == "stage_ctas") t.stage_ctas = (int)(value > 0 ? value : 0);
   else if (n == "wide_direct") t.wide_direct = value != 0;
   else if (n == "wide_col_split") {

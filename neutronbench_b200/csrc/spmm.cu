@@ -2,10 +2,12 @@
 // gather-fused variants.  HBM-bound: every lane issues 8- or 16-byte coalesced loads; a warp owns one
 // (output row, chunk of CT tiles of 32*VEC floats) and keeps U source rows x CT tiles in flight.
 //
-// Arithmetic contract: out[k] = (((0 + x0[k]*w0) + x1[k]*w1) + ...) with one IEEE multiply and one
-// IEEE add per edge, in edge order.  __fmul_rn/__fadd_rn are never contracted into an FMA, so the
-// result equals the reference kernel's atomicAdd(out, in*w) sequence
-// (cuda/ntsCUDAFuseKernel.cuh:272-290, 450-468) bit for bit and is independent of the launch shape.
+// Arithmetic contract: out[k] = fma(x_n[k], w_n, ... fma(x1[k], w1, fma(x0[k], w0, 0))) — one IEEE fused multiply-add per
+// edge and element, in edge order.  That is what the reference's CPU operator executes (nts_comp, core/ntsBaseOp.hpp:
+// 76-97: _mm256_add_ps(_mm256_mul_ps(source, w), destination), which its -O3 -march=native build contracts into
+// vfmadd), so results equal MiniBatchFuseOp's bit for bit and do not depend on the launch shape.  The reference's CUDA
+// kernel rounds the product before its atomicAdd (cuda/ntsCUDAFuseKernel.cuh:272-290, 450-468) and therefore differs
+// from its own CPU operator, and from this code, in the last bit of some sums.
 #include <initializer_list>
 
 #include "common.cuh"
@@ -154,9 +156,19 @@ __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmAr
       for (int u = 0; u < U; u++) {
         if ((jj + u) < cnt) {
 #pragma unroll
-          for (int t = 0; t < CT; t++)
+          for (int t = 0; t < CT; t++) {
+            if constexpr (VEC == 1) {
+              acc[t][0] = __fmaf_rn(vals[u][t][0], ws[u], acc[t][0]);
+            } else {   // packed pairs: one fused multiply-add instruction per two elements
 #pragma unroll
-            for (int k = 0; k < VEC; k++) acc[t][k] = __fadd_rn(acc[t][k], __fmul_rn(vals[u][t][k], ws[u]));
+              for (int k = 0; k < VEC; k += 2) {
+                const float2 s = fma2_rn(make_float2(vals[u][t][k], vals[u][t][k + 1]), make_float2(ws[u], ws[u]),
+                                         make_float2(acc[t][k], acc[t][k + 1]));
+                acc[t][k] = s.x;
+                acc[t][k + 1] = s.y;
+              }
+            }
+          }
         }
       }
     }
@@ -347,10 +359,10 @@ __global__ void __launch_bounds__(kWideThreads) spmm_wide_kernel(const WideArgs 
           if ((jj + u) < cnt) {
 #pragma unroll
             for (int t = 0; t < TILES; t++) {
-              acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(v[u][t].x, ws[u]));
-              acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(v[u][t].y, ws[u]));
-              acc[t][2] = __fadd_rn(acc[t][2], __fmul_rn(v[u][t].z, ws[u]));
-              acc[t][3] = __fadd_rn(acc[t][3], __fmul_rn(v[u][t].w, ws[u]));
+              const float2 w2 = make_float2(ws[u], ws[u]);
+              const float2 lo = fma2_rn(make_float2(v[u][t].x, v[u][t].y), w2, make_float2(acc[t][0], acc[t][1]));
+              const float2 hi = fma2_rn(make_float2(v[u][t].z, v[u][t].w), w2, make_float2(acc[t][2], acc[t][3]));
+              acc[t][0] = lo.x; acc[t][1] = lo.y; acc[t][2] = hi.x; acc[t][3] = hi.y;
             }
           }
         }

@@ -42,6 +42,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may sleep up to `ns` nanoseconds waiting for the phase instead of
+// returning at once, so a waiting warp takes no issue slots from the warps that have rows to accumulate.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Non-multicast bulk copy, global -> this CTA's shared memory.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -263,10 +276,10 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
         const uint32_t q = lane + 32 * t;           // float4 index inside the row
         if (q * 4 < pwidth) {
           const float4 v = row[q];
-          acc[t][0] = __fadd_rn(acc[t][0], __fmul_rn(v.x, wu));
-          acc[t][1] = __fadd_rn(acc[t][1], __fmul_rn(v.y, wu));
-          acc[t][2] = __fadd_rn(acc[t][2], __fmul_rn(v.z, wu));
-          acc[t][3] = __fadd_rn(acc[t][3], __fmul_rn(v.w, wu));
+          acc[t][0] = __fmaf_rn(v.x, wu, acc[t][0]);
+          acc[t][1] = __fmaf_rn(v.y, wu, acc[t][1]);
+          acc[t][2] = __fmaf_rn(v.z, wu, acc[t][2]);
+          acc[t][3] = __fmaf_rn(v.w, wu, acc[t][3]);
         }
       }
     }
@@ -352,9 +365,13 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   // Reference and weight (or, without explicit weights, the degree factor of the indexed side) of edge wbase + lane.
   // In the gather form the reference is the cache slot of the edge's source (bit 31 set + global id when the source
   // is not cached and rows come from `miss`; the plain global id when there is no cache at all).
-  auto load_edge = [&](uint32_t wbase, uint32_t &ref, float &w) {
+  // `f` receives the degree factor of the indexed side (the number of edges of this launch that read the row is its
+  // square), `w` the edge's final weight.  With fused weights the lane also finds the output row of its edge (a binary
+  // search over this warp's few offsets) and forms 1 / (f * factor of that row) here, once per edge and one window
+  // ahead of its use, instead of every lane of the warp repeating that division when the edge is consumed.
+  auto load_edge = [&](uint32_t wbase, uint32_t &ref, float &f, float &w) {
     const uint32_t j = wbase + lane;
-    ref = 0u; w = 0.0f;
+    ref = 0u; w = 0.0f; f = 0.0f;
     if (j >= j1) return;
     if (a.gidx) {
       const uint32_t li = __ldg(a.gidx + j);
@@ -362,27 +379,34 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       const uint32_t slot = a.ghashmap ? __ldg(a.ghashmap + g) : 0xFFFFFFFFu;
       // not cached: row g of the table `miss`, or row li of a staging table that holds one row per source
       ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? ((a.miss_local ? li : g) | 0x80000000u) : g);
-      w = __ldg(a.norm_idx + li);
+      f = __ldg(a.norm_idx + li);
     } else {
       ref = __ldg(a.ref + j);
-      w = a.w ? __ldg(a.w + j) : __ldg(a.norm_idx + ref);     // fused form: factor of the indexed side
+      if (a.w) { w = __ldg(a.w + j); return; }
+      f = __ldg(a.norm_idx + ref);                             // fused form: factor of the indexed side
     }
+    uint32_t lo = r_begin, hi = r_end;                         // the last row of this warp that starts at or before j
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (__ldg(a.offs + mid) <= j) lo = mid; else hi = mid;
+    }
+    w = __fdiv_rn(1.0f, __fmul_rn(f, __ldg(a.norm_row + lo)));  // 1 / (sqrt(deg_src) * sqrt(deg_dst))
   };
   uint32_t win = j0;                                          // base of the consume window
   uint32_t ref_cur, ref_nxt;
-  float w_cur, w_nxt;
-  load_edge(win, ref_cur, w_cur);
-  load_edge(win + 32, ref_nxt, w_nxt);
+  float w_cur, w_nxt, f_cur, f_nxt;
+  load_edge(win, ref_cur, f_cur, w_cur);
+  load_edge(win + 32, ref_nxt, f_nxt, w_nxt);
   // L2 policy per copied row.  With fused weights the lane's factor is (float)sqrt(number of edges that use the
   // row in this block), so a factor of exactly 1 marks a row that no other edge of the launch will read: it is
   // copied with the evict-first policy and leaves L2 to the rows that are read again.
   const bool hints = a.l2_hint != 0 && a.w == nullptr;
   const uint64_t pol_first = policy_evict_first(), pol_last = policy_evict_last();
-  unsigned once_cur = hints ? __ballot_sync(0xffffffffu, w_cur == 1.0f) : 0u;
-  unsigned once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
+  unsigned once_cur = hints ? __ballot_sync(0xffffffffu, f_cur == 1.0f) : 0u;
+  unsigned once_nxt = hints ? __ballot_sync(0xffffffffu, f_nxt == 1.0f) : 0u;
   // rows that at least keep_uses edges read (factor^2 = number of uses) are kept with the evict-last policy
-  unsigned keep_cur = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_cur, w_cur) >= a.keep_uses) : 0u;
-  unsigned keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_nxt, w_nxt) >= a.keep_uses) : 0u;
+  unsigned keep_cur = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_cur, f_cur) >= a.keep_uses) : 0u;
+  unsigned keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_nxt, f_nxt) >= a.keep_uses) : 0u;
 
   // Issue the copies of group `gi` (edges j0 + gi*G .. of this warp) into the group's slots `gs`; executed by the
   // whole warp.  Lane u takes the group's u-th edge.  The references come from the two operand windows, which cover
@@ -453,13 +477,12 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   // row bookkeeping: lane holds the end offset of row rw_base + lane
   uint32_t rw_base = r_begin;
   uint32_t rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
-  float rnorm = (!a.w && rw_base + lane < r_end) ? __ldg(a.norm_row + rw_base + lane) : 0.0f;   // same for the row's factor
   uint32_t row = r_begin;
   uint32_t row_end = __shfl_sync(0xffffffffu, rend, 0);
-  float acc[TILES][4];
+  // two packed pairs per float4 column: one packed fused multiply-add covers two elements
+  float2 acc[TILES][2];
 #pragma unroll
-  for (int t = 0; t < TILES; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
-  float nrow = __shfl_sync(0xffffffffu, rnorm, 0);
+  for (int t = 0; t < TILES; t++) acc[t][0] = acc[t][1] = make_float2(0.0f, 0.0f);
 
   auto finish_row = [&]() {      // write the accumulated row, move to the next one
     float *out = a.y + (size_t)row * a.y_ld;
@@ -468,7 +491,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     for (int t = 0; t < TILES; t++) {
       const uint32_t col = (lane + 32 * t) * 4;
       if (col < a.F) {
-        float r[4] = {acc[t][0], acc[t][1], acc[t][2], acc[t][3]};
+        float r[4] = {acc[t][0].x, acc[t][0].y, acc[t][1].x, acc[t][1].y};
 #pragma unroll
         for (int c = 0; c < 4; c++) {
           if (col + c < a.F) {
@@ -489,17 +512,15 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
             if (col + c < a.F) __stcs(out + col + c, r[c]);
         }
       }
-      acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+      acc[t][0] = acc[t][1] = make_float2(0.0f, 0.0f);
     }
     row++;
     if (row < r_end) {
       if (row - rw_base >= 32) {
         rw_base = row;
         rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
-        rnorm = (!a.w && rw_base + lane < r_end) ? __ldg(a.norm_row + rw_base + lane) : 0.0f;
       }
       row_end = __shfl_sync(0xffffffffu, rend, row - rw_base);
-      nrow = __shfl_sync(0xffffffffu, rnorm, row - rw_base);
     }
   };
 
@@ -509,16 +530,16 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     if (j - win >= 32) {                                      // consume window moves on; fetch the one after
       win += 32;
       ref_cur = ref_nxt; w_cur = w_nxt; once_cur = once_nxt; keep_cur = keep_nxt;
-      load_edge(win + 32, ref_nxt, w_nxt);
-      once_nxt = hints ? __ballot_sync(0xffffffffu, w_nxt == 1.0f) : 0u;
-      keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(w_nxt, w_nxt) >= a.keep_uses) : 0u;
+      load_edge(win + 32, ref_nxt, f_nxt, w_nxt);
+      once_nxt = hints ? __ballot_sync(0xffffffffu, f_nxt == 1.0f) : 0u;
+      keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_nxt, f_nxt) >= a.keep_uses) : 0u;
     }
     const uint32_t t = j - j0, in_group = t & (G - 1);
     if (in_group == 0) {                                      // first edge of a group: wait for the group's copies
       if (t != 0 && ++cur_gs == R) { cur_gs = 0; cur_parity ^= 1u; }
       const uint32_t bar = bar0 + 8 * cur_gs;
       uint32_t spins = 0;
-      while (!mbar_try_wait(bar, cur_parity)) {
+      while (!(a.wait_ns ? mbar_try_wait_hint(bar, cur_parity, a.wait_ns) : mbar_try_wait(bar, cur_parity))) {
         if (++spins > kWaitLimit) {
           if (lane == 0) atomicOr(&g_tma_spmm_error, 1u);
           for (uint32_t k = 0; k < kWaitLimit && !mbar_try_wait(bar, cur_parity); k++) {}
@@ -527,19 +548,17 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
       }
     }
     __syncwarp();
-    float wu = __shfl_sync(0xffffffffu, w_cur, t & 31);
-    if (!a.w) wu = __fdiv_rn(1.0f, __fmul_rn(wu, nrow));      // 1 / (sqrt(deg_src) * sqrt(deg_dst))
+    const float wu = __shfl_sync(0xffffffffu, w_cur, t & 31);   // the edge's weight, formed when its window was loaded
     const float4 *rowp =
         reinterpret_cast<const float4 *>(my_smem + (size_t)((cur_gs << Gs) + in_group) * a.slot_bytes);
+    const float2 wu2 = make_float2(wu, wu);
 #pragma unroll
     for (int tl = 0; tl < TILES; tl++) {
       const uint32_t q = lane + 32 * tl;
       if (q * 4 < a.F) {
         const float4 v = rowp[q];
-        acc[tl][0] = __fadd_rn(acc[tl][0], __fmul_rn(v.x, wu));
-        acc[tl][1] = __fadd_rn(acc[tl][1], __fmul_rn(v.y, wu));
-        acc[tl][2] = __fadd_rn(acc[tl][2], __fmul_rn(v.z, wu));
-        acc[tl][3] = __fadd_rn(acc[tl][3], __fmul_rn(v.w, wu));
+        acc[tl][0] = fma2_rn(make_float2(v.x, v.y), wu2, acc[tl][0]);
+        acc[tl][1] = fma2_rn(make_float2(v.z, v.w), wu2, acc[tl][1]);
       }
     }
     // last edge of the group: its slots are free, refill them with the group R groups ahead
@@ -654,6 +673,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   a.l2_prefetch = tuning().l2_prefetch;
   a.l2_hint = tuning().l2_hint;
   a.ring_prefetch = 0;
+  a.wait_ns = (uint32_t)(tuning().ring_wait_ns > 0 ? tuning().ring_wait_ns : 0);
   a.keep_uses = a.l2_hint == 2 ? 1.5f : (a.l2_hint == 3 ? (float)tuning().l2_keep_min_uses - 0.5f : 3.0e38f);
   a.y_stream = tuning().y_stream_stores;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut

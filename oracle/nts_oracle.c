@@ -257,8 +257,12 @@ ORC_API void orc_block_weights(const vid_t *column_offset, const vid_t *row_indi
  * a9  Forward aggregation  Y[d,:] = sum_j w_fwd[j] * X[row_indices[j],:]  over column d.
  * core/ntsMiniBatchGraphOp.hpp:154-184 (MiniBatchFuseOp::forward) with nts_comp
  * (core/ntsBaseOp.hpp:76-97): output += input * weight, edge after edge in CSC order, into a zeroed
- * output.  The GPU reference kernel (cuda/ntsCUDAFuseKernel.cuh:272-290) performs the same
- * multiply-then-add sequence per element.
+ * output.  The reference builds with -O3 -march=native, where its _mm256_add_ps(_mm256_mul_ps(..)) and the
+ * scalar tail are contracted into fused multiply-adds, so the operator's arithmetic is
+ * out = fma(in, w, out) per element (single rounding): restated here with fmaf, which reproduces the
+ * compiled reference bit for bit (tests/test_golden_cpu.py).  The reference's GPU kernel
+ * (cuda/ntsCUDAFuseKernel.cuh:272-290) rounds the product before its atomicAdd and so differs from the
+ * reference's own CPU operator in the last bit of some sums.
  * ------------------------------------------------------------------------------------------ */
 ORC_API void orc_spmm_fwd(const float *x, float *y, const float *w, const vid_t *row_indices,
                           const vid_t *column_offset, vid_t v, vid_t F) {
@@ -269,10 +273,7 @@ ORC_API void orc_spmm_fwd(const float *x, float *y, const float *w, const vid_t 
     for (vid_t j = column_offset[d]; j < column_offset[d + 1]; j++) {
       const float *in = x + (size_t)row_indices[j] * F;
       float wj = w[j];
-      for (vid_t k = 0; k < F; k++) {
-        float p = in[k] * wj;
-        out[k] = out[k] + p;
-      }
+      for (vid_t k = 0; k < F; k++) out[k] = fmaf(in[k], wj, out[k]);
     }
   }
 }
@@ -294,10 +295,7 @@ ORC_API void orc_spmm_bwd(const float *gy, float *gx, const float *w, const vid_
     for (vid_t j = row_offset[r]; j < row_offset[r + 1]; j++) {
       const float *in = gy + (size_t)column_indices[j] * F;
       float wj = w[j];
-      for (vid_t k = 0; k < F; k++) {
-        float p = in[k] * wj;
-        out[k] = out[k] + p;
-      }
+      for (vid_t k = 0; k < F; k++) out[k] = fmaf(in[k], wj, out[k]);
     }
     if (act) {
       const float *a = act + (size_t)r * F;

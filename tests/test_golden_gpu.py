@@ -49,5 +49,6 @@ def test_graph_blocks_and_aggregation_against_reference(cuda_device, ws, path):
             op = SingleGPUSampleGraphOp(ssg, None, l, None, fused_weights=fused)
             y = op.forward(dev_f32(x, cuda_device)).detach().cpu().numpy()
             gx = op.backward(dev_f32(gy, cuda_device)).cpu().numpy()
-            assert np.abs(y - ry).max() <= 1e-5 * np.abs(ry).max()
-            assert np.abs(gx - rgx).max() <= 1e-5 * np.abs(rgx).max()
+            # bar of the north star: 1e-5 relative; met with zero difference (same fused multiply-add per edge)
+            np.testing.assert_array_equal(y.view(np.uint32), ry.view(np.uint32))
+            np.testing.assert_array_equal(gx.view(np.uint32), rgx.view(np.uint32))

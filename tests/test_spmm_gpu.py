@@ -1,8 +1,8 @@
 """Aggregation parity: CUDA SpMM (through the C ABI) against the CPU oracle on identical blocks.
 
-Bar: the north star asks for 1e-5 relative (fp32).  The kernels keep the reference's operation order
-(multiply, add, edge by edge), so the comparison below is bit-exact; the tolerance is only stated for
-the full-size property test at the end.
+Bar: the north star asks for 1e-5 relative (fp32).  The kernels keep the arithmetic of the reference's CPU
+operator (one fused multiply-add per edge and element, edge by edge), so the comparison below is bit-exact; the
+tolerance is only stated for the full-size property test at the end.
 """
 import numpy as np
 import pytest
