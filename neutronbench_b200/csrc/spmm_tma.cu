@@ -365,48 +365,71 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   // Reference and weight (or, without explicit weights, the degree factor of the indexed side) of edge wbase + lane.
   // In the gather form the reference is the cache slot of the edge's source (bit 31 set + global id when the source
   // is not cached and rows come from `miss`; the plain global id when there is no cache at all).
-  // `f` receives the degree factor of the indexed side (the number of edges of this launch that read the row is its
-  // square), `w` the edge's final weight.  With fused weights the lane also finds the output row of its edge (a binary
-  // search over this warp's few offsets) and forms 1 / (f * factor of that row) here, once per edge and one window
-  // ahead of its use, instead of every lane of the warp repeating that division when the edge is consumed.
-  auto load_edge = [&](uint32_t wbase, uint32_t &ref, float &f, float &w) {
+  // row bookkeeping: lane holds the end offset of row rw_base + lane
+  uint32_t rw_base = r_begin;
+  uint32_t rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
+
+  // Operands of edge wbase + lane, requested one window (32 edges) ahead of their use; nothing here waits for a load.
+  // `f` receives the degree factor of the indexed side (its square is the number of edges of this launch that read
+  // the row) and, with fused weights, `nr` the factor of the edge's output row; with explicit weights `nr` is the
+  // weight itself.  The output row of an edge is found without touching memory: it is rw_base + the number of held
+  // row ends at or before the edge (a search over the offsets only for an edge beyond the 32 rows a warp holds).
+  // finish_weight() then forms 1 / (f * nr) once per edge, when the window becomes the current one, instead of every
+  // lane of the warp repeating that division when the edge is consumed.
+  auto load_edge = [&](uint32_t wbase, uint32_t &ref, float &f, float &nr) {
     const uint32_t j = wbase + lane;
-    ref = 0u; w = 0.0f; f = 0.0f;
-    if (j >= j1) return;
-    if (a.gidx) {
-      const uint32_t li = __ldg(a.gidx + j);
-      const uint32_t g = __ldg(a.gsource + li);
-      const uint32_t slot = a.ghashmap ? __ldg(a.ghashmap + g) : 0xFFFFFFFFu;
-      // not cached: row g of the table `miss`, or row li of a staging table that holds one row per source
-      ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? ((a.miss_local ? li : g) | 0x80000000u) : g);
-      f = __ldg(a.norm_idx + li);
-    } else {
-      ref = __ldg(a.ref + j);
-      if (a.w) { w = __ldg(a.w + j); return; }
-      f = __ldg(a.norm_idx + ref);                             // fused form: factor of the indexed side
+    const bool valid = j < j1;
+    ref = 0u; nr = 0.0f; f = 0.0f;
+    uint32_t li = 0;
+    if (valid) {
+      if (a.gidx) {
+        li = __ldg(a.gidx + j);
+        const uint32_t g = __ldg(a.gsource + li);
+        const uint32_t slot = a.ghashmap ? __ldg(a.ghashmap + g) : 0xFFFFFFFFu;
+        // not cached: row g of the table `miss`, or row li of a staging table that holds one row per source
+        ref = slot != 0xFFFFFFFFu ? slot : (a.ghashmap ? ((a.miss_local ? li : g) | 0x80000000u) : g);
+        f = __ldg(a.norm_idx + li);
+      } else {
+        ref = __ldg(a.ref + j);
+        if (a.w) nr = __ldg(a.w + j);
+        else f = __ldg(a.norm_idx + ref);                      // fused form: factor of the indexed side
+      }
     }
-    uint32_t lo = r_begin, hi = r_end;                         // the last row of this warp that starts at or before j
-    while (hi - lo > 1) {
-      const uint32_t mid = (lo + hi) >> 1;
-      if (__ldg(a.offs + mid) <= j) lo = mid; else hi = mid;
+    if (a.w) return;                                           // uniform over the warp
+    uint32_t cnt = 0;
+#pragma unroll
+    for (int k = 0; k < 32; k++) cnt += __shfl_sync(0xffffffffu, rend, k) <= j ? 1u : 0u;
+    uint32_t rr = rw_base + cnt;
+    if (valid && cnt >= 32) {                                  // beyond the rows held in `rend`: search the offsets
+      uint32_t lo = rw_base + 31, hi = r_end;                  // the last row of this warp that starts at or before j
+      while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (__ldg(a.offs + mid) <= j) lo = mid; else hi = mid;
+      }
+      rr = lo;
     }
-    w = __fdiv_rn(1.0f, __fmul_rn(f, __ldg(a.norm_row + lo)));  // 1 / (sqrt(deg_src) * sqrt(deg_dst))
+    if (valid) nr = __ldg(a.norm_row + rr);
+  };
+  auto finish_weight = [&](float f, float nr) -> float {       // 1 / (sqrt(deg_src) * sqrt(deg_dst)); 0 past the end
+    if (a.w) return nr;
+    return (f != 0.0f) ? __fdiv_rn(1.0f, __fmul_rn(f, nr)) : 0.0f;
   };
   uint32_t win = j0;                                          // base of the consume window
   uint32_t ref_cur, ref_nxt;
-  float w_cur, w_nxt, f_cur, f_nxt;
-  load_edge(win, ref_cur, f_cur, w_cur);
-  load_edge(win + 32, ref_nxt, f_nxt, w_nxt);
+  float w_cur, f_cur, f_nxt, nr_nxt;
+  {
+    float nr_cur;
+    load_edge(win, ref_cur, f_cur, nr_cur);
+    w_cur = finish_weight(f_cur, nr_cur);
+  }
+  load_edge(win + 32, ref_nxt, f_nxt, nr_nxt);
   // L2 policy per copied row.  With fused weights the lane's factor is (float)sqrt(number of edges that use the
   // row in this block), so a factor of exactly 1 marks a row that no other edge of the launch will read: it is
   // copied with the evict-first policy and leaves L2 to the rows that are read again.
+  // Rows that at least keep_uses edges read (factor^2 = number of uses) are kept with the evict-last policy.  The
+  // factor is looked at when the copy is issued, not when it is loaded, so that nothing waits for the window's loads.
   const bool hints = a.l2_hint != 0 && a.w == nullptr;
   const uint64_t pol_first = policy_evict_first(), pol_last = policy_evict_last();
-  unsigned once_cur = hints ? __ballot_sync(0xffffffffu, f_cur == 1.0f) : 0u;
-  unsigned once_nxt = hints ? __ballot_sync(0xffffffffu, f_nxt == 1.0f) : 0u;
-  // rows that at least keep_uses edges read (factor^2 = number of uses) are kept with the evict-last policy
-  unsigned keep_cur = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_cur, f_cur) >= a.keep_uses) : 0u;
-  unsigned keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_nxt, f_nxt) >= a.keep_uses) : 0u;
 
   // Issue the copies of group `gi` (edges j0 + gi*G .. of this warp) into the group's slots `gs`; executed by the
   // whole warp.  Lane u takes the group's u-th edge.  The references come from the two operand windows, which cover
@@ -418,8 +441,10 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     const uint32_t rc = __shfl_sync(0xffffffffu, ref_cur, t & 31), rn = __shfl_sync(0xffffffffu, ref_nxt, t & 31);
     const bool in_cur = j0 + t < win + 32;
     const uint32_t ref = in_cur ? rc : rn;
-    const bool once = (((in_cur ? once_cur : once_nxt) >> (t & 31)) & 1u) != 0;
-    const bool keep = (((in_cur ? keep_cur : keep_nxt) >> (t & 31)) & 1u) != 0;
+    const float fc = __shfl_sync(0xffffffffu, f_cur, t & 31), fn = __shfl_sync(0xffffffffu, f_nxt, t & 31);
+    const float fe = in_cur ? fc : fn;
+    const bool once = hints && fe == 1.0f;
+    const bool keep = hints && __fmul_rn(fe, fe) >= a.keep_uses;
     const bool mine = lane < cnt;
     const uint32_t bar = bar0 + 8 * gs;
     unsigned char *dst0 = my_smem + (size_t)(gs << Gs) * a.slot_bytes;
@@ -474,9 +499,6 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   for (uint32_t gi = 0; gi < R && (gi << Gs) < n_edges; gi++) issue_group(gi, gi);
   for (uint32_t gi = R; gi < R + PF; gi++) prefetch_group(gi);
 
-  // row bookkeeping: lane holds the end offset of row rw_base + lane
-  uint32_t rw_base = r_begin;
-  uint32_t rend = (rw_base + lane < r_end) ? __ldg(a.offs + rw_base + lane + 1) : j1;
   uint32_t row = r_begin;
   uint32_t row_end = __shfl_sync(0xffffffffu, rend, 0);
   // two packed pairs per float4 column: one packed fused multiply-add covers two elements
@@ -529,10 +551,8 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
     while (j == row_end && row < r_end) finish_row();        // rows without (more) edges
     if (j - win >= 32) {                                      // consume window moves on; fetch the one after
       win += 32;
-      ref_cur = ref_nxt; w_cur = w_nxt; once_cur = once_nxt; keep_cur = keep_nxt;
-      load_edge(win + 32, ref_nxt, f_nxt, w_nxt);
-      once_nxt = hints ? __ballot_sync(0xffffffffu, f_nxt == 1.0f) : 0u;
-      keep_nxt = hints ? __ballot_sync(0xffffffffu, __fmul_rn(f_nxt, f_nxt) >= a.keep_uses) : 0u;
+      ref_cur = ref_nxt; w_cur = finish_weight(f_nxt, nr_nxt); f_cur = f_nxt;
+      load_edge(win + 32, ref_nxt, f_nxt, nr_nxt);
     }
     const uint32_t t = j - j0, in_group = t & (G - 1);
     if (in_group == 0) {                                      // first edge of a group: wait for the group's copies
