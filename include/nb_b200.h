@@ -448,6 +448,23 @@ int nb_gcn_read_timing_by_class(nb_gcn *g, double ms[2], uint64_t bytes[2], uint
  * of the training half minus graph.  Consumes the same event pairs as the two calls above. */
 int nb_gcn_read_phase_times(nb_gcn *g, double ms[4]);
 
+/* ------------------------------------------------------------------------------------------------
+ * Gradient sum over the ranks of a data-parallel job (libnb_b200_comm.so, a thin layer over NCCL; optional: a host
+ * that already has a collective library, such as torch.distributed, sums the gradient bucket itself between
+ * nb_gcn_compute and nb_gcn_update).  Replaces Parameter::all_reduce_to_gradient -> Network_simple::all_reduce_sum
+ * (core/NtsScheduler.hpp:692-695, comm/network.h:189-193: device -> host copy, MPI_Allreduce(MPI_SUM), host -> device)
+ * and Parameter::init_parameter -> Network_simple::broadcast (core/NtsScheduler.hpp:691) with one in-place call on
+ * the device buffer, enqueued on the caller's stream.
+ *   nb_comm_unique_id   rank 0 creates the 128-byte id and hands it to the other ranks (MPI_Bcast, a file, a store)
+ *   nb_comm_create      collective over all ranks, with the GPU of the rank current
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct nb_comm nb_comm;
+int nb_comm_unique_id(unsigned char id[128]);
+int nb_comm_create(nb_comm **out, const unsigned char id[128], int world, int rank);
+int nb_comm_destroy(nb_comm *comm);
+int nb_allreduce_sum_f32(nb_comm *comm, float *d_buf, size_t n, void *stream);
+int nb_broadcast_f32(nb_comm *comm, float *d_buf, size_t n, int root, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

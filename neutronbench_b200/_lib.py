@@ -117,6 +117,43 @@ SIGNATURES = {
 }
 
 
+# libnb_b200_comm.so: the optional NCCL layer declared at the end of include/nb_b200.h
+COMM_LIB_PATH = os.path.join(_HERE, "libnb_b200_comm.so")
+COMM_SIGNATURES = {
+    "nb_comm_unique_id": (C.c_int, [C.c_char_p]),
+    "nb_comm_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_char_p, C.c_int, C.c_int]),
+    "nb_comm_destroy": (C.c_int, [ptr]),
+    "nb_allreduce_sum_f32": (C.c_int, [ptr, f32p, C.c_size_t, ptr]),
+    "nb_broadcast_f32": (C.c_int, [ptr, f32p, C.c_size_t, C.c_int, ptr]),
+}
+_comm = None
+
+
+def load_comm():
+    """Load libnb_b200_comm.so (needs the NCCL library that PyTorch ships)."""
+    global _comm
+    if _comm is not None:
+        return _comm
+    if not os.path.exists(COMM_LIB_PATH):
+        raise ImportError(f"{COMM_LIB_PATH} is missing: run `make -C neutronbench_b200/csrc`")
+    lib = C.CDLL(COMM_LIB_PATH)
+    for name, (res, args) in COMM_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    lib.nb_last_error.restype = C.c_char_p
+    _comm = lib
+    return lib
+
+
+def call_comm(name: str, *args):
+    lib = load_comm()
+    st = getattr(lib, name)(*args)
+    if st != 0:
+        raise NbError(name, st, lib.nb_last_error().decode("utf-8", "replace"))
+    return st
+
+
 class NbError(RuntimeError):
     """A libnb_b200 entry point returned a non-zero status."""
 

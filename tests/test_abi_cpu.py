@@ -15,17 +15,19 @@ def _declared():
 
 
 def test_library_exports_every_declared_symbol():
+    """libnb_b200.so exports the compute entry points, libnb_b200_comm.so the NCCL layer at the end of the header."""
     from neutronbench_b200 import _lib
-    lib = _lib.load()
+    lib, comm = _lib.load(), _lib.load_comm()
     names = _declared()
     assert len(names) >= 20
     for n in names:
-        assert hasattr(lib, n), f"{n} is declared in include/nb_b200.h but not exported"
+        where = comm if n in _lib.COMM_SIGNATURES else lib
+        assert hasattr(where, n), f"{n} is declared in include/nb_b200.h but not exported"
 
 
 def test_binding_table_matches_header():
     from neutronbench_b200 import _lib
-    assert sorted(_lib.SIGNATURES) == _declared()
+    assert sorted(list(_lib.SIGNATURES) + list(_lib.COMM_SIGNATURES)) == _declared()
 
 
 def test_argument_counts_match_header():
@@ -34,7 +36,8 @@ def test_argument_counts_match_header():
     hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
     for name, args in re.findall(r"\b(nb_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", hdr, flags=re.S):
         n = 0 if args.strip() in ("", "void") else args.count(",") + 1
-        assert len(_lib.SIGNATURES[name][1]) == n, name
+        table = _lib.COMM_SIGNATURES if name in _lib.COMM_SIGNATURES else _lib.SIGNATURES
+        assert len(table[name][1]) == n, name
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -163,3 +163,56 @@ def test_feature_shards_on_a_peer_gpu_equal_the_whole_table(cuda_device):
     training is bit-identical to the run with the whole table in local memory."""
     results = dict(_run(_shard_worker))
     assert results == {0: True, 1: True}
+
+
+def _comm_worker(rank, world, port, out):
+    """libnb_b200_comm.so without torch.distributed: the unique id travels through a file, as a C++ host would pass it
+    with MPI_Bcast."""
+    import ctypes as C
+    import time
+    for p in (ROOT, os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(NCCL_NVLS_ENABLE="0", NCCL_DEBUG="WARN")
+    from neutronbench_b200 import _lib
+    torch.cuda.set_device(rank)
+    path = f"/tmp/nb_comm_id_{port}"
+    if rank == 0:
+        uid = C.create_string_buffer(128)
+        _lib.call_comm("nb_comm_unique_id", uid)
+        with open(path + ".tmp", "wb") as f:
+            f.write(uid.raw)
+        os.replace(path + ".tmp", path)
+    else:
+        for _ in range(600):
+            if os.path.exists(path):
+                break
+            time.sleep(0.05)
+    uid = open(path, "rb").read()
+    assert len(uid) == 128
+    comm = C.c_void_p()
+    _lib.call_comm("nb_comm_create", C.byref(comm), uid, world, rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.arange(1000, dtype=torch.float32, device=f"cuda:{rank}") * (rank + 1)
+    _lib.call_comm("nb_allreduce_sum_f32", comm, g.data_ptr(), g.numel(), stream)
+    w = torch.full((257,), float(rank + 5), device=f"cuda:{rank}")
+    _lib.call_comm("nb_broadcast_f32", comm, w.data_ptr(), w.numel(), 0, stream)
+    torch.cuda.synchronize()
+    expect = torch.arange(1000, dtype=torch.float32) * sum(r + 1 for r in range(world))
+    ok = bool(torch.equal(g.cpu(), expect)) and bool((w.cpu() == 5.0).all())
+    _lib.call_comm("nb_comm_destroy", comm)
+    out.put((rank, ok))
+    if rank == 0:
+        time.sleep(0.5)
+        try:
+            os.remove(path)
+        except OSError:
+            pass
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_nb_allreduce_and_broadcast_over_nccl(cuda_device):
+    """nb_allreduce_sum_f32 is a SUM (MPI_SUM in the reference, comm/network.h:189-193), in place on the device buffer;
+    nb_broadcast_f32 hands rank 0's weights to everyone (Parameter::init_parameter)."""
+    results = dict(_run(_comm_worker))
+    assert results == {0: True, 1: True}
