@@ -82,8 +82,10 @@ def parse_args():
     ap.add_argument("--min-region-s", type=float, default=0.3, help="repeat the K-step region until this much time is measured")
     ap.add_argument("--max-regions", type=int, default=100)
     ap.add_argument("--python-step", action="store_true", help="issue a step kernel by kernel from Python instead of nb_gcn_step")
-    ap.add_argument("--pipelines", type=int, default=4,
-                    help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain loop")
+    ap.add_argument("--pipelines", type=int, default=0,
+                    help="PIPELINES of the reference cfg: P batches in flight (one training, P-1 being sampled), 1 = plain "
+                         "loop; 0 = 4 when the host has at least 4 cores per rank (every batch in flight is a library "
+                         "thread that waits on its stream), else 3")
     ap.add_argument("--pdl", type=int, default=None, help="1 / 0: programmatic dependent launch for the training half's kernels")
     ap.add_argument("--stage-misses", type=int, default=None,
                     help="1 / 0: uncached rows staged once per distinct source by the sampling half (default: only for a "
@@ -633,6 +635,8 @@ def main():
             "pipelines": pipelines,
         }
 
+    if args.pipelines <= 0:
+        args.pipelines = 4 if (os.cpu_count() or 1) >= 4 * world else 3
     pipelines = 1 if args.python_step else max(1, args.pipelines)
     workload_desc = describe(sh, cfg, graph, pipelines, train_ids)
 
