@@ -50,3 +50,35 @@ def test_reference_gpu_classes_on_libnb_b200_match_their_cpu_twin(cuda_device, t
     ref_epoch = g["loss"].astype(np.float64).reshape(g["epochs"], -1).mean(axis=1)
     assert last < first - 0.1
     assert abs(last - ref_epoch[-1]) < 0.15
+
+
+NTS_B200 = os.path.join(ROOT, "bindings", "_build", "nts_b200")
+
+
+@pytest.mark.skipif(not os.path.exists(NTS_B200), reason="bindings/_build/nts_b200 is built only where the reference tree exists")
+@pytest.mark.parametrize("mode,cache,pipelines", [("zerocopy", "CACHE_TYPE:none", 1),
+                                                  ("zerocopy", "CACHE_TYPE:rate\nCACHE_RATE:0.3\nCACHE_POLICY:degree", 1),
+                                                  ("pipeline", "CACHE_TYPE:rate\nCACHE_RATE:0.25\nCACHE_POLICY:sample", 2),
+                                                  ("explicit", "CACHE_TYPE:none", 1)],
+                         ids=["zerocopy", "zerocopy_degree_cache", "pipeline_sample_cache", "explicit"])
+def test_reference_trainer_class_runs_from_a_cfg_on_libnb_b200(cuda_device, tmp_path, mode, cache, pipelines):
+    """bindings/_build/nts_b200 is the reference's GCN_GPU_NEIGHBOR_impl (toolkits/GCN_GPU_NEIGHBOR.hpp), compiled
+    unmodified, with every CUDA call landing in libnb_b200.so.  Driven by a .cfg on a small homophilous dataset it must
+    print the reference's epoch lines, lower the training loss and classify held-out vertices far above chance."""
+    from toy_dataset import write_toy_cfg, write_toy_dataset
+    V, F, C = 1500, 16, 4
+    base = write_toy_dataset(tmp_path, V, F, C)
+    cfg = write_toy_cfg(tmp_path, base, V, F, C, cache=cache, pipelines=pipelines, epochs=8)
+    text = cfg.read_text().replace("MODE:zerocopy", "MODE:" + mode)
+    cfg.write_text(text)
+    out = subprocess.run([NTS_B200, str(cfg)], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    log = out.stdout + out.stderr
+    assert out.returncode == 0, log[-3000:]
+    lines = re.findall(r"Epoch (\d+) train_loss ([0-9.]+) train_acc ([0-9.]+) val_loss ([0-9.]+) val_acc ([0-9.]+) "
+                       r"test_acc ([0-9.]+)", log)
+    assert len(lines) == 8, log[-3000:]
+    first, last = float(lines[0][1]), float(lines[-1][1])
+    assert last < first
+    assert max(float(l[4]) for l in lines) > 0.6      # 4 balanced classes: chance is 0.25
+    best = re.search(r"Best-val-acc: ([0-9.]+)", log)
+    assert best and float(best.group(1)) > 0.6

@@ -1,11 +1,10 @@
 """`nts file.cfg` end to end on a small synthetic dataset written in the reference's file formats."""
 import io
 
-import numpy as np
 import pytest
 
-from neutronbench_b200 import synth
 from neutronbench_b200.nts import run
+from toy_dataset import write_toy_cfg, write_toy_dataset
 
 pytestmark = pytest.mark.gpu
 
@@ -16,35 +15,8 @@ pytestmark = pytest.mark.gpu
                          ids=["rate_degree", "rate_sample_pipelined", "gpu_memory_random_pipelined"])
 def test_cfg_driven_training_learns(tmp_path, cuda_device, cache, pipelines):
     V, F, C = 1500, 16, 4
-    rng = np.random.RandomState(0)
-    label = rng.randint(0, C, V)
-    # homophilous graph: most edges stay inside a class, so a GCN can learn it
-    src = rng.randint(0, V, 30000)
-    same = rng.rand(30000) < 0.9
-    pools = [np.nonzero(label == c)[0] for c in range(C)]
-    dst = np.where(same, np.array([pools[label[s]][rng.randint(len(pools[label[s]]))] for s in src]),
-                   rng.randint(0, V, 30000))
-    loops = np.arange(V)
-    edges = np.stack([np.concatenate([src, dst, loops]), np.concatenate([dst, src, loops])], axis=1).astype("<u4")
-    (tmp_path / "data" / "toy").mkdir(parents=True)
-    base = tmp_path / "data" / "toy" / "toy"
-    edges.tofile(str(base) + ".edge")
-    feat = np.eye(C)[label] + 0.5 * rng.randn(V, C)
-    feat = np.concatenate([feat, rng.randn(V, F - C)], axis=1)
-    with open(str(base) + ".feat", "w") as f:
-        for i in range(V):
-            f.write(str(i) + " " + " ".join(f"{x:.5f}" for x in feat[i]) + "\n")
-    with open(str(base) + ".label", "w") as f:
-        f.writelines(f"{i} {label[i]}\n" for i in range(V))
-    mask = synth.split_mask(V, 1)
-    names = {0: "train", 1: "val", 2: "test"}
-    with open(str(base) + ".mask", "w") as f:
-        f.writelines(f"{i} {names[int(mask[i])]}\n" for i in range(V))
-    cfg = tmp_path / "toy.cfg"
-    cfg.write_text(f"ALGORITHM:GCNNEIGHBORGPU\nVERTICES:{V}\nLAYERS:{F}-32-{C}\nFANOUT:5,10\nVALFANOUT:5,10\n"
-                   f"BATCH_SIZE:256\nBATCH_TYPE:shuffle\nEPOCHS:8\nEDGE_FILE:{base}.edge\nFEATURE_FILE:{base}.feat\n"
-                   f"LABEL_FILE:{base}.label\nMASK_FILE:{base}.mask\nMODE:zerocopy\n{cache}\nPIPELINES:{pipelines}\n"
-                   f"LEARN_RATE:0.01\nWEIGHT_DECAY:0.0001\nDROP_RATE:0.1\nBATCH_NORM:0\n")
+    base = write_toy_dataset(tmp_path, V, F, C)
+    cfg = write_toy_cfg(tmp_path, base, V, F, C, cache=cache, pipelines=pipelines)
     out = io.StringIO()
     best = run(str(cfg), out=out)
     lines = [l for l in out.getvalue().splitlines() if l.startswith("Epoch")]
