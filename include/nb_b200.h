@@ -427,9 +427,15 @@ int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
  * settings.  Names: "gemm_mode" (as nb_set_gemm_mode), "pdl", "fused_output_layer", "staged_spmm", "spmm_ring",
  * "staged_min_width", "ring_group_shift", "l2_panel_bytes", "l2_prefetch", "l2_hint" (0 off; 1 rows that a single
  * edge of the launch uses are copied with the L2 evict-first policy; 2 the others evict-last as well),
- * "y_stream_stores" (streaming stores for the wide layer-0 aggregate), "reserve_sms" (SMs that the
+ * "y_stream_stores" (streaming stores for the wide layer-0 aggregate), "ring_balance" (1: the warps of the wide-row
+ * aggregation kernel take shares of equal edge count cut at row boundaries; 0: of equal row count), "reserve_sms" (SMs that the
  * one-CTA-per-SM aggregation kernel leaves free for a collective running beside it).  Results never depend on them. */
 int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);
+/* The same switch on the process defaults: in force for the stand-alone entry points (nb_spmm_*, nb_gemm_*, ...) and
+ * copied by handles created afterwards.  "hub_min_edges" (rows of at least this many edges of an aggregation over a
+ * plain table, i.e. popular sources in the backward pass, are walked by a team of warps with one column per lane
+ * instead of by one warp; 0 switches that off; same bits either way) is accepted by both calls. */
+int nb_set_option(const char *name, int64_t value);
 /* nb_count_ids over the source list of every block of a sampled batch (one step of the dry-run epoch of
  * CACHE_POLICY:sample); waits for the batch's sampling like nb_gcn_compute. */
 int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_counts, void *stream);

@@ -63,6 +63,7 @@ SIGNATURES = {
     "nb_device_error_flags": (C.c_int, [C.POINTER(C.c_uint32)]),
     "nb_device_error_reset": (C.c_int, []),
     "nb_gcn_set_option": (C.c_int, [ptr, C.c_char_p, C.c_int64]),
+    "nb_set_option": (C.c_int, [C.c_char_p, C.c_int64]),
     "nb_block_build": (C.c_int, [ptr, C.c_uint32, u32p, u32p, C.c_uint32, C.c_uint32, u32p,
                                  C.POINTER(C.c_uint32), u32p, u32p, f32p, f32p, f32p, f32p, ptr]),
     "nb_sample_hop_offsets": (C.c_int, [ptr, u64p, u32p, C.c_uint32, C.c_int, u32p, C.POINTER(C.c_uint32), ptr]),

@@ -47,6 +47,8 @@ struct Tuning {
   int l2_keep_min_uses = 4;
   int ring_wait_ns = 0;          // ring kernel: a warp waiting for its copies may sleep this long per try (0: plain spin)
   int ring_prefetch = 0;         // ring kernel: groups of rows whose L2 prefetch is issued ahead of the ring's copies
+  int hub_min_edges = 256;       // aggregation of plain tables: rows of at least this many edges go to warp teams (0: off)
+  int ring_balance = 0;          // ring kernel: warps take shares of equal edge count (1) or of equal row count (0)
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
   int wide_rows_in_flight = 2;   // source rows in flight per warp of that kernel: 1, 2 or 4
@@ -172,6 +174,7 @@ struct TmaSpmmArgs {
   int l2_hint;             // ring kernel: L2 eviction policy per copied row (Tuning::l2_hint)
   float keep_uses;         // rows read by at least this many edges of the launch are copied with evict-last
   int y_stream;            // ring kernel: streaming stores for y
+  int balance;             // ring kernel: warps take shares of equal edge count (1) or equal row count (0)
   int out_vec;             // widest vector (floats) usable for y and act rows: 4, 2 or 1
 };
 bool tma_spmm_applicable(const float *x, size_t x_ld, uint32_t F);

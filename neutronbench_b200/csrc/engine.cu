@@ -600,9 +600,7 @@ NB_API int nb_set_fused_output_layer(int enabled) {
   return old;
 }
 
-NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
-  NB_REQUIRE(g && name, "nb_gcn_set_option: null pointer");
-  nb::Tuning &t = g->tuning;
+static int apply_option(nb::Tuning &t, const char *name, int64_t value) {
   const std::string n(name);
   if (n == "gemm_mode") {
     NB_REQUIRE((value >= 0 && value <= 2) || (value >= 16 && value <= 18), "nb_gcn_set_option: gemm_mode is 0..2 or 16..18");
@@ -623,6 +621,8 @@ NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
     NB_REQUIRE(value >= 2 && value <= 1000000, "nb_gcn_set_option: l2_keep_min_uses is at least 2");
     t.l2_keep_min_uses = (int)value;
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
+  else if (n == "ring_balance") t.ring_balance = value != 0;
+  else if (n == "hub_min_edges") t.hub_min_edges = (int)(value > 0 ? (value < 32 ? 32 : value) : 0);
   else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);
   else if (n == "ring_wait_ns") t.ring_wait_ns = (int)(value > 0 ? (value < 100000 ? value : 100000) : 0);
   else if (n == "stage_ctas") t.stage_ctas = (int)(value > 0 ? value : 0);
@@ -639,6 +639,16 @@ NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
     t.reserve_sms = (int)value;
   } else return nb::fail(NB_ERR_INVALID, "nb_gcn_set_option: unknown option");
   return 0;
+}
+
+NB_API int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value) {
+  NB_REQUIRE(g && name, "nb_gcn_set_option: null pointer");
+  return apply_option(g->tuning, name, value);
+}
+
+NB_API int nb_set_option(const char *name, int64_t value) {
+  NB_REQUIRE(name != nullptr, "nb_set_option: null pointer");
+  return apply_option(nb::default_tuning(), name, value);
 }
 
 NB_API int nb_gcn_set_sampler_threads(nb_gcn *g, int threads) {

@@ -83,7 +83,85 @@ struct SpmmArgs {
   uint32_t n;
   uint32_t F;
   uint32_t tiles;          // chunks per row: ceil(F / (CT*32*VEC))
+  // Long rows: rows of at least hub_min edges (0 = no such treatment) are left out by the one-warp-per-row part of
+  // the launch and taken by its first hub_ctas CTAs, where a team of ceil(F/32) warps walks one such row with one
+  // column per lane and 32 row reads in flight per lane.
+  uint32_t hub_min, hub_ctas;
 };
+
+template <int MODE, bool MASK>
+__device__ __forceinline__ void hub_one_row(const SpmmArgs &a, uint32_t r, uint32_t col, unsigned lane) {
+  const uint32_t start = __ldg(a.offs + r), end = __ldg(a.offs + r + 1);
+  float nr = 0.0f;
+  if constexpr (MODE != kExplicitW) nr = __ldg(a.norm_row + r);
+  const bool live = col < a.F;
+  // reference (row start) and weight of edge base + lane; lanes past the end hold a null row and weight 0
+  auto refs = [&](uint32_t base, const float *&ptr, float &w) {
+    const uint32_t j = base + lane;
+    ptr = nullptr; w = 0.0f;
+    if (j < end) {
+      const uint32_t li = __ldg(a.idx + j);
+      if constexpr (MODE == kExplicitW) w = __ldg(a.w + j);
+      else w = __fdiv_rn(1.0f, __fmul_rn(__ldg(a.norm_idx + li), nr));
+      ptr = a.x + (size_t)li * a.x_ld;
+    }
+  };
+  const float *p_cur, *p_nxt;
+  float w_cur, w_nxt;
+  refs(start, p_cur, w_cur);
+  float acc = 0.0f;
+  for (uint32_t base = start; base < end; base += 32) {
+    refs(base + 32, p_nxt, w_nxt);                // in flight while the 32 rows below are read
+    const uint32_t cnt = min(32u, end - base);
+    float v[32];
+#pragma unroll
+    for (int u = 0; u < 32; u++) {
+      const uintptr_t p = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)p_cur, u);
+      v[u] = (live && (uint32_t)u < cnt) ? __ldg(reinterpret_cast<const float *>(p) + col) : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < 32; u++) {
+      const float wu = __shfl_sync(0xffffffffu, w_cur, u);
+      if ((uint32_t)u < cnt) acc = __fmaf_rn(v[u], wu, acc);
+    }
+    p_cur = p_nxt;
+    w_cur = w_nxt;
+  }
+  if (live) {
+    if constexpr (MASK) acc = __ldg(a.act + (size_t)r * a.F + col) > 0.0f ? __fmul_rn(acc, a.act_scale) : 0.0f;
+    a.y[(size_t)r * a.y_ld + col] = acc;
+  }
+}
+
+// Long rows of a launch (a source that hundreds or thousands of sampled destinations share, in the transposed
+// aggregation of the backward pass).  One warp per row keeps 8 row reads in flight, so a row of 2,000 edges alone takes
+// longer than all other rows of the block together.  Here the first CTAs of the launch look for such rows, each in its
+// own slice of the row range, and a team of ceil(F/32) warps walks one row: a lane owns ONE column and keeps 32 reads of
+// it in flight, and the references of the next 32 edges are requested before the current 32 are consumed.  Every
+// element is still one fused multiply-add per edge in edge order, so results do not depend on which path took a row.
+template <int MODE, bool MASK>
+__device__ __forceinline__ void hub_rows_part(const SpmmArgs &a) {
+  constexpr uint32_t kThreads = kSpmmWarps * 32;
+  __shared__ uint32_t s_list[kThreads];                        // long rows of one stretch of kThreads rows
+  __shared__ uint32_t s_count;
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t team_warps = (a.F + 31) / 32;                 // <= kSpmmWarps (the launcher checks)
+  const uint32_t teams = kSpmmWarps / team_warps;
+  const uint32_t team = warp / team_warps, col = (warp % team_warps) * 32 + lane;
+  const uint32_t slice = (a.n + a.hub_ctas - 1) / a.hub_ctas;
+  const uint32_t r0 = blockIdx.x * slice, r1 = min(a.n, r0 + slice);
+  for (uint32_t from = r0; from < r1; from += kThreads) {     // one row per thread and stretch
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    const uint32_t r = from + threadIdx.x;
+    if (r < r1 && __ldg(a.offs + r + 1) - __ldg(a.offs + r) >= a.hub_min) s_list[atomicAdd(&s_count, 1u)] = r;
+    __syncthreads();
+    const uint32_t found = s_count;
+    if (team < teams)                                          // uniform over the warp
+      for (uint32_t k = team; k < found; k += teams) hub_one_row<MODE, MASK>(a, s_list[k], col, lane);
+    __syncthreads();
+  }
+}
 
 // A warp owns one (output row, chunk) where a chunk is CT consecutive tiles of 32*VEC floats.  Per
 // edge a lane issues CT independent vector loads, and U edges are in flight, so CT*U loads per lane
@@ -93,13 +171,23 @@ template <int VEC, int CT, int U, int MODE, bool MASK>
 __global__ void __launch_bounds__(kSpmmWarps * 32) spmm_rows_kernel(const SpmmArgs a) {
   pdl_enter();
   const unsigned lane = threadIdx.x & 31;
-  const uint64_t warp_global = (uint64_t)blockIdx.x * kSpmmWarps + (threadIdx.x >> 5);
+  if constexpr (MODE != kFusedGather) {
+    if (blockIdx.x < a.hub_ctas) {   // uniform over the CTA
+      hub_rows_part<MODE, MASK>(a);
+      return;
+    }
+  }
+  const uint64_t warp_global = (uint64_t)(blockIdx.x - (MODE != kFusedGather ? a.hub_ctas : 0u)) * kSpmmWarps +
+                               (threadIdx.x >> 5);
   const uint32_t r = (uint32_t)(warp_global / a.tiles);   // a.tiles = chunks per row
   if (r >= a.n) return;
   const uint32_t chunk = (uint32_t)(warp_global - (uint64_t)r * a.tiles);
   const uint32_t col0 = chunk * (CT * 32 * VEC) + lane * VEC;
 
   const uint32_t start = a.offs[r], end = a.offs[r + 1];
+  if constexpr (MODE != kFusedGather) {
+    if (a.hub_ctas && end - start >= a.hub_min) return;   // a long row: the hub CTAs of this launch take it
+  }
   float acc[CT][VEC];
 #pragma unroll
   for (int t = 0; t < CT; t++)
@@ -207,7 +295,15 @@ static int launch_one(SpmmArgs a, cudaStream_t stream) {
   a.tiles = (a.F + CT * 32 * VEC - 1) / (CT * 32 * VEC);  // chunks per row
   if (a.y_ld == 0) a.y_ld = a.F;
   const uint64_t warps = (uint64_t)a.n * a.tiles;
-  const uint64_t blocks = (warps + kSpmmWarps - 1) / kSpmmWarps;
+  // long rows: only where a team of warps fits a CTA and the rows are plain tables (not the gather-fused forward,
+  // whose rows are as long as the fanout at most)
+  a.hub_min = 0; a.hub_ctas = 0;
+  if (MODE != kFusedGather && tuning().hub_min_edges > 0 && (a.F + 31) / 32 <= (uint32_t)kSpmmWarps &&
+      a.n >= 4u * (uint32_t)num_sms()) {
+    a.hub_min = (uint32_t)tuning().hub_min_edges;
+    a.hub_ctas = (uint32_t)num_sms();
+  }
+  const uint64_t blocks = (warps + kSpmmWarps - 1) / kSpmmWarps + a.hub_ctas;
   if (blocks > 0x7fffffffull) return fail(NB_ERR_INVALID, "spmm: too many rows for one launch");
   NB_CUDA(launch_chained(spmm_rows_kernel<VEC, CT, U, MODE, MASK>, dim3((unsigned)blocks), dim3(kSpmmWarps * 32), 0, stream, a));
   NB_LAUNCH_CHECK();

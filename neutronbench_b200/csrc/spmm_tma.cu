@@ -356,10 +356,48 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
   // CTAs, so that every SM has the same amount of work
   const uint32_t total_warps = gridDim.x * kRingWarps;
   const uint32_t gw = blockIdx.x * kRingWarps + warp;
-  const uint32_t r_begin = (uint32_t)((uint64_t)gw * a.n / total_warps);
-  const uint32_t r_end = (uint32_t)((uint64_t)(gw + 1) * a.n / total_warps);
-  if (r_begin >= r_end) return;
-  const uint32_t j0 = __ldg(a.offs + r_begin), j1 = __ldg(a.offs + r_end);
+  uint32_t r_begin, r_end, j0, j1;
+  if (a.balance) {
+    // Option: shares of equal EDGE count, cut at row boundaries: share p starts at the first row whose offset reaches
+    // p * E / total_warps (rows differ in length, 1 .. fanout edges, so equal row counts give warps unequal byte
+    // counts); a row still belongs to one warp, which adds its edges in order.  Both ends are found together by a
+    // 32-ary search over the offsets (3 rounds for 20 K rows).  Measured on the Reddit-shaped layer-0 block it is
+    // 1-1.5 us SLOWER than equal row counts (67.7 vs 66.0 us in the training step): the kernel runs at the DRAM
+    // throughput this access pattern allows, which all SMs share, so a warp that ends early leaves its bandwidth to
+    // the others, while the search delays every warp's first copy.  Hence off by default.
+    const uint32_t E = __ldg(a.offs + a.n);
+    const uint32_t tgt0 = (uint32_t)((uint64_t)gw * E / total_warps);
+    const uint32_t tgt1 = (uint32_t)((uint64_t)(gw + 1) * E / total_warps);
+    // smallest r in [0, n] with offs[r] >= target; lo = last row known to be below (-1: none), hi = known at/above
+    int lo0 = -1, lo1 = -1;
+    uint32_t hi0 = a.n, hi1 = a.n, v0 = E, v1 = E;              // v = offs[hi]
+    while ((int)hi0 - lo0 > 1 || (int)hi1 - lo1 > 1) {
+      const uint32_t st0 = ((uint32_t)((int)hi0 - lo0) + 31u) / 32u, st1 = ((uint32_t)((int)hi1 - lo1) + 31u) / 32u;
+      const uint32_t p0 = min((uint32_t)(lo0 + (int)((lane + 1) * st0)), hi0);
+      const uint32_t p1 = min((uint32_t)(lo1 + (int)((lane + 1) * st1)), hi1);
+      const uint32_t o0 = __ldg(a.offs + p0), o1 = __ldg(a.offs + p1);
+      const int f0 = __ffs(__ballot_sync(0xffffffffu, o0 >= tgt0)) - 1;   // lane 31 probes hi: always set
+      const int f1 = __ffs(__ballot_sync(0xffffffffu, o1 >= tgt1)) - 1;
+      const uint32_t nh0 = __shfl_sync(0xffffffffu, p0, f0), nh1 = __shfl_sync(0xffffffffu, p1, f1);
+      const uint32_t nv0 = __shfl_sync(0xffffffffu, o0, f0), nv1 = __shfl_sync(0xffffffffu, o1, f1);
+      const uint32_t pl0 = __shfl_sync(0xffffffffu, p0, f0 > 0 ? f0 - 1 : 0);
+      const uint32_t pl1 = __shfl_sync(0xffffffffu, p1, f1 > 0 ? f1 - 1 : 0);
+      if (f0 > 0) lo0 = (int)pl0;
+      if (f1 > 0) lo1 = (int)pl1;
+      hi0 = nh0; v0 = nv0; hi1 = nh1; v1 = nv1;
+    }
+    r_begin = gw == 0 ? 0u : hi0;                               // target 0 is reached by row 0
+    r_end = gw + 1 == total_warps ? a.n : hi1;                  // trailing rows without edges go to the last share
+    if (r_begin >= r_end) return;
+    j0 = gw == 0 ? 0u : v0;
+    j1 = gw + 1 == total_warps ? E : v1;
+  } else {
+    r_begin = (uint32_t)((uint64_t)gw * a.n / total_warps);
+    r_end = (uint32_t)((uint64_t)(gw + 1) * a.n / total_warps);
+    if (r_begin >= r_end) return;
+    j0 = __ldg(a.offs + r_begin);
+    j1 = __ldg(a.offs + r_end);
+  }
 
   // operand windows of 32 edges aligned to j0: `cur` holds the window being consumed, `nxt` the next
   // Reference and weight (or, without explicit weights, the degree factor of the indexed side) of edge wbase + lane.
@@ -696,6 +734,7 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   a.wait_ns = (uint32_t)(tuning().ring_wait_ns > 0 ? tuning().ring_wait_ns : 0);
   a.keep_uses = a.l2_hint == 2 ? 1.5f : (a.l2_hint == 3 ? (float)tuning().l2_keep_min_uses - 0.5f : 3.0e38f);
   a.y_stream = tuning().y_stream_stores;
+  a.balance = tuning().ring_balance;
   // Column panels: when the distinct source rows of the block exceed what L2 keeps, the row is cut
   // into panels whose working set fits, and panels are processed one after the other.
   uint32_t panels = 1;

@@ -156,6 +156,51 @@ def test_long_rows_and_unaligned_views(cuda_device, misalign):
     np.testing.assert_array_equal(host_f32(dy).view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("F", [128, 100, 41, 256, 7])
+@pytest.mark.parametrize("hub_min", [None, 64, 0])
+def test_rows_of_thousands_of_edges_take_the_team_path_with_identical_bits(cuda_device, ws, F, hub_min):
+    """A block whose transposed form has a few sources with 300 .. 3,000 edges among 2,000 short rows (what a popular
+    vertex of a Products-shaped batch looks like in the backward pass).  Rows of at least `hub_min_edges` edges are
+    walked by a team of warps with one column per lane; every element is still one fused multiply-add per edge in edge
+    order, so explicit and fused weights, with and without the activation mask, give the oracle's bits whatever the
+    threshold (None: the default, 0: every row on the one-warp path)."""
+    rng = np.random.RandomState(11 + F)
+    n, s = 2000, 900
+    lens = rng.randint(0, 12, size=n).astype(np.uint32)
+    for r, l in ((3, 3000), (4, 257), (700, 256), (701, 255), (1500, 1031), (1999, 640), (256, 300), (255, 999)):
+        lens[r] = l
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    e = int(offs[-1])
+    idx = rng.randint(0, s, size=e).astype(np.uint32)
+    w = rng.rand(e).astype(np.float32)
+    x = rng.randn(s, F).astype(np.float32)
+    act = np.maximum(rng.randn(n, F), 0).astype(np.float32)
+    row_norm = np.sqrt(rng.randint(1, 50, size=n)).astype(np.float32)
+    idx_norm = np.sqrt(rng.randint(1, 50, size=s)).astype(np.float32)
+    rows = np.repeat(np.arange(n), lens)
+    w_fused = (np.float32(1.0) / (idx_norm[idx] * row_norm[rows])).astype(np.float32)
+    d = cuda_device
+    st = torch.cuda.current_stream().cuda_stream
+    if hub_min is not None:
+        _lib.call("nb_set_option", b"hub_min_edges", hub_min)
+    try:
+        dy = torch.full((n, F), float("nan"), device=d)
+        _lib.call("nb_spmm_csc_fwd", ptr(dev_f32(x, d)), ptr(dy), ptr(dev_f32(w, d)), ptr(dev_i32(idx, d)),
+                  ptr(dev_i32(offs, d)), n, F, st)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(host_f32(dy).view(np.uint32), oracle.spmm_fwd(x, w, idx, offs).view(np.uint32))
+        # transposed form with fused weights and the relu/dropout mask: rows are sources, x rows are destinations
+        dgx = torch.full((n, F), float("nan"), device=d)
+        _lib.call("nb_spmm_csr_bwd_fused", ptr(dev_f32(x, d)), ptr(dgx), ptr(dev_i32(offs, d)), ptr(dev_i32(idx, d)),
+                  ptr(dev_f32(row_norm, d)), ptr(dev_f32(idx_norm, d)), ptr(dev_f32(act, d)), 2.0, n, F, st)
+        torch.cuda.synchronize()
+        ref = oracle.spmm_bwd(x, w_fused, offs, idx, act=act, scale=2.0)
+        np.testing.assert_array_equal(host_f32(dgx).view(np.uint32), ref.view(np.uint32))
+    finally:
+        if hub_min is not None:
+            _lib.call("nb_set_option", b"hub_min_edges", 256)
+
+
 def test_linearity_at_full_size(cuda_device):
     """Reddit-shaped input block sizes (v=25k, fanout 10, F=602): A(x1 + 2 x2) == A x1 + 2 A x2 within
     1e-5 relative — a size-independent property checked without the CPU oracle."""

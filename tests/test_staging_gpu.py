@@ -89,7 +89,8 @@ def test_sharded_table_needs_staging(cuda_device):
 @pytest.mark.parametrize("options", [(("l2_hint", 0),), (("l2_hint", 2),), (("y_stream_stores", 0),),
                                      (("reserve_sms", 8),), (("ring_group_shift", 0),), (("gemm_mode", 1), ("pdl", 0)),
                                      (("l2_hint", 3), ("l2_keep_min_uses", 3)), (("wide_direct", 1),), (("ring_prefetch", 4),),
-                                     (("ring_prefetch", 14), ("l2_hint", 0)),
+                                     (("ring_prefetch", 14), ("l2_hint", 0)), (("ring_balance", 0),),
+                                     (("ring_balance", 0), ("reserve_sms", 5)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 4), ("y_stream_stores", 0))])
 def test_handle_options_change_no_result(cuda_device, options):
