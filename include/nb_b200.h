@@ -434,7 +434,9 @@ int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);
 /* The same switch on the process defaults: in force for the stand-alone entry points (nb_spmm_*, nb_gemm_*, ...) and
  * copied by handles created afterwards.  "hub_min_edges" (rows of at least this many edges of an aggregation over a
  * plain table, i.e. popular sources in the backward pass, are walked by a team of warps with one column per lane
- * instead of by one warp; 0 switches that off; same bits either way) is accepted by both calls. */
+ * instead of by one warp; 0 switches that off; same bits either way) and "fuse_relu" (ReLU + dropout of a hidden layer
+ * leave with the product from the tensor-core GEMM's epilogue instead of a kernel of their own; same bits) are
+ * accepted by both calls. */
 int nb_set_option(const char *name, int64_t value);
 /* nb_count_ids over the source list of every block of a sampled batch (one step of the dry-run epoch of
  * CACHE_POLICY:sample); waits for the batch's sampling like nb_gcn_compute. */

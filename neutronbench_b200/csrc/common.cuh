@@ -48,6 +48,11 @@ struct Tuning {
   int ring_wait_ns = 0;          // ring kernel: a warp waiting for its copies may sleep this long per try (0: plain spin)
   int ring_prefetch = 0;         // ring kernel: groups of rows whose L2 prefetch is issued ahead of the ring's copies
   int hub_min_edges = 256;       // aggregation of plain tables: rows of at least this many edges go to warp teams (0: off)
+  // ReLU + dropout of a hidden layer applied in the GEMM's epilogue where the kernel can.  Off: measured no faster.
+  // The row-balanced kernel holds one column per thread, so its four-column Philox words cost a round of shuffles per
+  // row (Reddit-shaped step 0.230 -> 0.238 ms); the 128-row-tile kernel saves two launches per Products-shaped step
+  // and the step time stays at 0.697 ms.
+  int fuse_relu = 0;
   int ring_balance = 0;          // ring kernel: warps take shares of equal edge count (1) or of equal row count (0)
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
@@ -197,15 +202,27 @@ int feature_gather_impl(float *d_x0, size_t x0_ld, int misses_only, const float 
                         size_t cache_ld, const uint32_t *d_hashmap, const uint32_t *d_source, uint32_t n, uint32_t F,
                         void *stream, uint32_t max_ctas);
 int read_tc_error_flag(unsigned int *value);
+// ReLU followed by inverted dropout applied to a product C as it leaves the GEMM (what nb_relu_dropout does to C
+// afterwards: element i takes word i & 3 of Philox4x32-10 at counter (i >> 2, layer, step, 1) under the seed).
+// on == 0: nothing is applied.
+struct ReluEpi {
+  int on;
+  float p, scale;
+  uint32_t seed_lo, seed_hi, layer, step;
+};
+// `epi` (nullable) asks for ReLU + dropout in the epilogue; *applied says whether the kernel that ran could do it
+// (tensor-core kernels with TMA operands, no split-K, N a multiple of 4) - if not, the caller runs nb_relu_dropout.
 int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
-                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream);
+                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream,
+                     const ReluEpi *epi = nullptr, bool *applied = nullptr);
 int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M, int64_t N,
-            int64_t K, int trans_a, int trans_b, cudaStream_t stream);
+            int64_t K, int trans_a, int trans_b, cudaStream_t stream, const ReluEpi *epi = nullptr,
+            bool *applied = nullptr);
 bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K);
 bool tma_gemm_applicable(const float *d_a, int64_t lda, const float *d_b, int64_t ldb);
 int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *c, int64_t M, int64_t N,
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
-                    cudaStream_t stream);
+                    cudaStream_t stream, const ReluEpi *epi = nullptr);
 int read_tma_gemm_error_flag(unsigned int *value);
 int reset_tma_gemm_error_flag();
 int sample_hop_impl(const uint64_t *d_graph_column_offset, const uint32_t *d_graph_row_indices, const uint32_t *d_dst,
@@ -217,7 +234,7 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
                      uint32_t *marked, void *stream);
 bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K);
 int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
-                         int64_t K, int mode, cudaStream_t stream);
+                         int64_t K, int mode, cudaStream_t stream, const ReluEpi *epi = nullptr);
 int spmm_csc_fwd_gather_fused_ld(nb_ws *ws, const float *feat, size_t feat_ld, const float *d_cache, size_t cache_ld,
                                  const uint32_t *d_hashmap, const uint32_t *d_source, float *d_y, size_t y_ld,
                                  const uint32_t *d_row_indices, const uint32_t *d_column_offset,

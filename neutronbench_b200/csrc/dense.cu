@@ -373,7 +373,8 @@ bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K) {
 
 // nb_gemm with operand pitches (floats): A is stored with pitch lda >= its row length, B with ldb; C is dense.
 int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M, int64_t N,
-            int64_t K, int trans_a, int trans_b, cudaStream_t stream) {
+            int64_t K, int trans_a, int trans_b, cudaStream_t stream, const ReluEpi *epi, bool *applied) {
+  if (applied) *applied = false;
   if (M == 0 || N == 0) return 0;
   NB_REQUIRE(d_a && d_b && d_c, "nb_gemm: null pointer");
   NB_REQUIRE(M > 0 && N > 0 && K >= 0, "nb_gemm: negative dimension");
@@ -386,7 +387,8 @@ int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t 
   // Small products (the output layer and its gradients) finish sooner on the CUDA cores than the
   // tensor-core kernel takes to set up its pipeline (TMEM allocation, 200 KB of staging buffers).
   if (gemm_uses_tensor_cores(M, N, K))
-    return gemm_tensor_core(ws, d_a, lda, d_b, ldb, d_c, M, N, K, trans_a, trans_b, tuning().gemm_mode, stream);
+    return gemm_tensor_core(ws, d_a, lda, d_b, ldb, d_c, M, N, K, trans_a, trans_b, tuning().gemm_mode, stream, epi,
+                            applied);
   GemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K;
   g.sa_i = trans_a ? 1 : lda;  g.sa_k = trans_a ? lda : 1;

@@ -501,7 +501,9 @@ static int vec_of(const float *p, int64_t ld) {
 // tests and comparisons: NB_TC_NO_TMA (set: always the cp.async kernel) and NB_TC_NO_ROWS_FORM (set: Y W in plain
 // 128-row tiles); results are bit-identical either way.
 int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *d_c, int64_t M,
-                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream) {
+                     int64_t N, int64_t K, int trans_a, int trans_b, int mode, cudaStream_t stream, const ReluEpi *epi,
+                     bool *applied) {
+  if (applied) *applied = false;
   TcGemmArgs g{};
   g.a = d_a; g.b = d_b; g.M = M; g.N = N; g.K = K; g.mode = mode;
   // op(A)(i,k): NN/NT -> A[i*lda + k];  TN -> A[k*lda + i]
@@ -547,10 +549,15 @@ int gemm_tensor_core(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b,
   // Y W with a short W: rows dealt evenly to the SMs (one wave whatever the row count, up to 160 rows per SM)
   const bool rows_form = use_tma && !trans_a && !trans_b && splits == 1 && !getenv("NB_TC_NO_ROWS_FORM") &&
                          tma_rows_form_applicable(M, N, K);
+  // ReLU + dropout in the epilogue: whole quads of four elements per row, final values (no split-K partials)
+  const bool epi_ok = epi != nullptr && epi->on && applied != nullptr && splits == 1 && (N % 4) == 0 && use_tma;
   if (rows_form) {
-    st = gemm_tma_rows_launch(d_a, lda, d_b, ldb, d_c, M, N, K, mode, stream);
+    st = gemm_tma_rows_launch(d_a, lda, d_b, ldb, d_c, M, N, K, mode, stream, epi_ok ? epi : nullptr);
+    if (st == 0 && epi_ok) *applied = true;
   } else if (use_tma) {
-    st = gemm_tma_launch(d_a, lda, d_b, ldb, g.c, M, N, K, trans_a, trans_b, bn, splits, g.k_per_split, mode, stream);
+    st = gemm_tma_launch(d_a, lda, d_b, ldb, g.c, M, N, K, trans_a, trans_b, bn, splits, g.k_per_split, mode, stream,
+                         epi_ok ? epi : nullptr);
+    if (st == 0 && epi_ok) *applied = true;
   } else {
     switch (bn) {
       case 128: st = launch_layout<128>(g, trans_a, trans_b, grid, stream); break;

@@ -24,6 +24,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "philox.cuh"
 #include "tc_common.cuh"
 
 namespace nb {
@@ -40,7 +41,19 @@ struct TmaGemmArgs {
   int64_t M, N, K;
   int64_t k_per_split;      // multiple of kTmaBK
   int mode;                 // 1: 3xTF32, 2: 1xTF32
+  ReluEpi epi;              // ReLU + dropout on the way out (needs N % 4 == 0 and no split-K)
 };
+
+// What nb_relu_dropout does to one element, given the element's Philox word.
+__device__ __forceinline__ uint32_t relu_drop_bits(uint32_t zbits, uint32_t rnd, const ReluEpi &e) {
+  const float z = __uint_as_float(zbits);
+  float val = z > 0.0f ? z : 0.0f;
+  if (e.p > 0.0f) {
+    const float u = (float)(rnd >> 8) * (1.0f / 16777216.0f);
+    val = (u >= e.p) ? __fmul_rn(val, e.scale) : 0.0f;
+  }
+  return __float_as_uint(val);
+}
 
 template <bool MN> struct TmaDesc {};
 template <> struct TmaDesc<false> { static constexpr uint32_t lbo = 16, sbo = 1024, kstep = 32, layout = 2; };
@@ -205,6 +218,18 @@ __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_kernel(const __grid_c
 #pragma unroll
         for (int q = 0; q < 32; q++) r[q] = 0u;
       }
+      if (g.epi.on) {
+        // this thread holds columns col0 + cb*32 .. +31 of row row0 + quarter*32 + lane: eight whole Philox quads
+        const int64_t e0 = (row0 + quarter * 32 + lane) * g.N + col0 + cb * 32;
+#pragma unroll
+        for (int q8 = 0; q8 < 8; q8++) {
+          uint32_t rnd[4] = {0u, 0u, 0u, 0u};
+          if (g.epi.p > 0.0f)
+            philox4x32_10((uint32_t)((e0 + 4 * q8) >> 2), g.epi.layer, g.epi.step, 1u, g.epi.seed_lo, g.epi.seed_hi, rnd);
+#pragma unroll
+          for (int k = 0; k < 4; k++) r[4 * q8 + k] = relu_drop_bits(r[4 * q8 + k], rnd[k], g.epi);
+        }
+      }
       float *stage = reinterpret_cast<float *>(tc_smem) + warp * (32 * 33);
       __syncwarp();
 #pragma unroll
@@ -240,6 +265,7 @@ struct TmaRowsArgs {
   int64_t M, N, K;
   int rows_per_cta;         // multiple of 16, <= kRowsMax
   int mode;
+  ReluEpi epi;              // ReLU + dropout on the way out (needs N % 4 == 0)
 };
 
 __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_rows_kernel(const __grid_constant__ CUtensorMap map_y,
@@ -370,6 +396,34 @@ __global__ void __launch_bounds__(kTmaThreads, 1) gemm_tma_rows_kernel(const __g
             "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
           : "r"(taddr) : "memory");
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (g.epi.on) {
+        // This thread holds ONE column of 32 rows, while a Philox call yields the words of four neighbouring columns
+        // of one row.  The four lanes that share a quad of columns each draw for one of four rows and pass the words
+        // round: in round u lane d reads from the lane of its group that drew for row (d + u) & 3 the word of d's
+        // own column.
+        const uint32_t k = lane & 3;
+#pragma unroll
+        for (int jb = 0; jb < 8; jb++) {
+          uint32_t got[4] = {0u, 0u, 0u, 0u};
+          if (g.epi.p > 0.0f) {
+            const int64_t e0 = ((int64_t)row0 + cb * 32 + jb * 4 + k) * g.N + (col & ~(int64_t)3);
+            uint32_t pr[4];
+            philox4x32_10((uint32_t)(e0 >> 2), g.epi.layer, g.epi.step, 1u, g.epi.seed_lo, g.epi.seed_hi, pr);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              const uint32_t sel = (k - u) & 3;
+              const uint32_t give = sel == 0 ? pr[0] : (sel == 1 ? pr[1] : (sel == 2 ? pr[2] : pr[3]));
+              got[u] = __shfl_sync(0xffffffffu, give, (lane & ~3u) + ((lane + u) & 3));
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            const uint32_t u = ((uint32_t)t - k) & 3;     // the round in which row jb*4 + t came round
+            const uint32_t rnd = u == 0 ? got[0] : (u == 1 ? got[1] : (u == 2 ? got[2] : got[3]));
+            r[jb * 4 + t] = relu_drop_bits(r[jb * 4 + t], rnd, g.epi);
+          }
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 32; j++) {
         const int64_t grow = (int64_t)row0 + cb * 32 + j;
@@ -452,13 +506,14 @@ bool tma_gemm_applicable(const float *d_a, int64_t lda, const float *d_b, int64_
 // C (or the split-K partials) = op(A) op(B) for one launch; `c` is dense [splits][M][N].
 int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *c, int64_t M, int64_t N,
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, const ReluEpi *epi) {
   const bool a_mn = trans_a != 0, b_mn = trans_b == 0;
   CUtensorMap ma, mb;
   if (!make_operand_map(&ma, d_a, a_mn, M, K, lda, kBM) || !make_operand_map(&mb, d_b, b_mn, N, K, ldb, bn))
     return fail(NB_ERR_CUDA, "nb_gemm: cuTensorMapEncodeTiled failed");
   TmaGemmArgs g{};
   g.c = c; g.M = M; g.N = N; g.K = K; g.k_per_split = k_per_split; g.mode = mode;
+  if (epi && splits == 1 && (N % 4) == 0) g.epi = *epi;
   dim3 grid((unsigned)((M + kBM - 1) / kBM), (unsigned)((N + bn - 1) / bn), (unsigned)splits);
   switch (bn) {
     case 128: return launch_tma_layout<128>(ma, mb, g, a_mn, b_mn, grid, stream);
@@ -475,13 +530,14 @@ bool tma_rows_form_applicable(int64_t M, int64_t N, int64_t K) {
 }
 
 int gemm_tma_rows_launch(const float *d_y, int64_t ldy, const float *d_w, int64_t ldw, float *c, int64_t M, int64_t N,
-                         int64_t K, int mode, cudaStream_t stream) {
+                         int64_t K, int mode, cudaStream_t stream, const ReluEpi *epi) {
   const int rows = (int)(((M + num_sms() - 1) / num_sms() + 15) / 16 * 16);
   CUtensorMap my, mw;
   if (!make_operand_map(&my, d_y, false, M, K, ldy, rows) || !make_operand_map(&mw, d_w, true, N, K, ldw, 0))
     return fail(NB_ERR_CUDA, "nb_gemm: cuTensorMapEncodeTiled failed");
   TmaRowsArgs g{};
   g.c = c; g.M = M; g.N = N; g.K = K; g.rows_per_cta = rows; g.mode = mode;
+  if (epi && (N % 4) == 0) g.epi = *epi;
   constexpr size_t smem = (size_t)kTmaStages * 2 * (kBM + kRowsMax) * kTmaBK * 4 + 256;
   static PerDeviceOnce configured;   // the attribute is kept per device
   if (configured.need()) {

@@ -422,8 +422,16 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
     fused_out = l + 1 == L && c.classes <= 1 && y_ld[l] == Fi && nb::tuning().fuse_output_layer && nb_output_layer_supported(Fi, Fo);
     if (fused_out) break;
     NB_TRY(arena(ws, (size_t)b.v * Fo, &X[l + 1]));
-    NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], c.d_W + g->w_off[l], Fo, X[l + 1], b.v, Fo, Fi, 0, 0, nb::as_stream(stream)));
-    if (l + 1 < L) NB_TRY(nb_relu_dropout(X[l + 1], (int64_t)b.v * Fo, p, c.seed, l, g->steps, stream));
+    // hidden layers: ReLU + dropout leave with the product where the GEMM kernel that runs can apply them
+    nb::ReluEpi epi{};
+    if (l + 1 < L && nb::tuning().fuse_relu) {
+      epi.on = 1; epi.p = p; epi.scale = scale;
+      epi.seed_lo = (uint32_t)c.seed; epi.seed_hi = (uint32_t)(c.seed >> 32); epi.layer = l; epi.step = g->steps;
+    }
+    bool relu_done = false;
+    NB_TRY(nb::gemm_ld(ws, Y[l], y_ld[l], c.d_W + g->w_off[l], Fo, X[l + 1], b.v, Fo, Fi, 0, 0, nb::as_stream(stream),
+                       epi.on ? &epi : nullptr, &relu_done));
+    if (l + 1 < L && !relu_done) NB_TRY(nb_relu_dropout(X[l + 1], (int64_t)b.v * Fo, p, c.seed, l, g->steps, stream));
   }
 
   // ---- loss (utils/torch_func.hpp:67-82)
@@ -622,6 +630,7 @@ static int apply_option(nb::Tuning &t, const char *name, int64_t value) {
     t.l2_keep_min_uses = (int)value;
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
   else if (n == "ring_balance") t.ring_balance = value != 0;
+  else if (n == "fuse_relu") t.fuse_relu = value != 0;
   else if (n == "hub_min_edges") t.hub_min_edges = (int)(value > 0 ? (value < 32 ? 32 : value) : 0);
   else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);
   else if (n == "ring_wait_ns") t.ring_wait_ns = (int)(value > 0 ? (value < 100000 ? value : 100000) : 0);

@@ -15,8 +15,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _train(cuda_device, F, hidden, classes, fanout, cache_rate, where, stage, options=(), shards=0, pipelines=1,
-           steps=4, V=5000, batch=300):
-    edges, co, ri = small_graph(V, 70000, seed=8)
+           steps=4, V=5000, batch=300, E=70000):
+    edges, co, ri = small_graph(V, E, seed=8)
     rng = np.random.RandomState(1)
     feat = rng.randn(V, F).astype(np.float32)
     label = rng.randint(0, classes, size=V).astype(np.int64)
@@ -90,13 +90,26 @@ def test_sharded_table_needs_staging(cuda_device):
                                      (("reserve_sms", 8),), (("ring_group_shift", 0),), (("gemm_mode", 1), ("pdl", 0)),
                                      (("l2_hint", 3), ("l2_keep_min_uses", 3)), (("wide_direct", 1),), (("ring_prefetch", 4),),
                                      (("ring_prefetch", 14), ("l2_hint", 0)), (("ring_balance", 0),),
-                                     (("ring_balance", 0), ("reserve_sms", 5)),
+                                     (("ring_balance", 1),), (("ring_balance", 1), ("reserve_sms", 5)),
+                                     (("fuse_relu", 1),), (("hub_min_edges", 0),),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 4), ("y_stream_stores", 0))])
 def test_handle_options_change_no_result(cuda_device, options):
     """nb_gcn_set_option acts on one handle only and never on results (wide rows: the ring kernel runs)."""
     w0, l0 = _train(cuda_device, 602, 128, 41, (10, 5), 1.0, "device", stage=None)
     w1, l1 = _train(cuda_device, 602, 128, 41, (10, 5), 1.0, "device", stage=None, options=options)
+    np.testing.assert_array_equal(w0.view(np.uint32), w1.view(np.uint32))
+    assert l0 == l1
+
+
+@pytest.mark.parametrize("F,hidden,fanout", [(100, 128, (4, 4)), (64, 64, (3, 3, 3)), (100, 100, (4, 4))])
+def test_relu_and_dropout_in_the_gemm_epilogue_change_no_result(cuda_device, F, hidden, fanout):
+    """Blocks of more than 148 x 160 rows take the tensor-core kernel with 128-row tiles, smaller ones the row-balanced
+    one; both can apply ReLU + dropout as the product leaves TMEM (`fuse_relu`), drawing the same Philox words as the
+    separate kernel: weights after three steps are bit-identical."""
+    kw = dict(steps=3, V=120000, batch=12000, E=900000)
+    w0, l0 = _train(cuda_device, F, hidden, 10, fanout, 0.0, "device", stage=None, **kw)
+    w1, l1 = _train(cuda_device, F, hidden, 10, fanout, 0.0, "device", stage=None, options=(("fuse_relu", 1),), **kw)
     np.testing.assert_array_equal(w0.view(np.uint32), w1.view(np.uint32))
     assert l0 == l1
 
