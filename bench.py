@@ -454,6 +454,38 @@ def roofline_of(events, peak, peak_src, traffic, cfg):
     return roofline, all_agg
 
 
+def sharded_gather_report(tk, graph, cfg, primary, rank, world):
+    """Rows of one sampled batch that the staging gather of this rank reads from other GPUs, against the NVLink
+    ingress of one GPU.  One batch drawn here (outside the timed regions) stands for the step: the input block of a
+    Papers-shaped batch has several hundred thousand distinct sources."""
+    import torch
+    from neutronbench_b200 import Sampler
+    shards = tk.datum.shards
+    if shards is None:
+        return None
+    ids = np.arange(cfg.batch_size, dtype=np.uint32) * max(1, graph.global_vertices // cfg.batch_size) + rank
+    smp = Sampler(graph, ids, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed + 1, with_edge_weights=False)
+    blk = smp.sample_one().sampled_sgs[0]
+    src = blk.src().to(torch.int64)
+    owner = src // int(shards.shard_rows)
+    rows = int(src.numel())
+    remote = int((owner != rank).sum().item())
+    row_bytes = int(cfg.layers[0]) * 4
+    ph = primary["phase_ms_per_step"] or {}
+    gather_ms = ph.get("trans") or 0.0          # device time of one batch's staging gather (its own stream)
+    step_ms = primary["ms_per_step"]
+    out = {"rows_per_batch": rows, "remote_rows_per_batch": remote, "remote_fraction": remote / max(rows, 1),
+           "remote_bytes_per_batch": remote * row_bytes, "gather_ms_per_batch": gather_ms,
+           "batches_in_flight": int(cfg.pipelines),
+           "remote_GBps_sustained": remote * row_bytes / (step_ms * 1e-3) / 1e9 if step_ms > 0 else 0.0,
+           "remote_GBps_inside_one_gather": remote * row_bytes / (gather_ms * 1e-3) / 1e9 if gather_ms > 0 else 0.0,
+           "nvlink_ingress_GBps": {"measured_peer_copy": 770.0, "nominal": 900.0},
+           "what": "rank 0's figures; sustained = remote bytes of a batch / step time (what the link has to carry), "
+                   "inside one gather = the same bytes / that gather's own device time while up to batches_in_flight "
+                   "gathers and the training kernels share the GPU"}
+    return out
+
+
 # ------------------------------------------------------------------------------------------ full-graph workload
 def bench_cora(args, device):
     """--workload cora: the full-graph GCN (configuration of the reference's CPU-runnable case: 2,708 vertices, 13,264
@@ -736,8 +768,8 @@ def main():
         "stage_misses": stage_primary,
     }
     if args.workload == "papers":
-        # remote rows of the staging gathers against the NVLink ingress of one GPU
         line["config"]["feature_table"] = f"sharded by node-id range over {world} GPUs, peers read with plain loads"
+        line["sharded_gather"] = sharded_gather_report(tk, graph, cfg, primary, rank, world)
     if secondary is not None:
         line["secondary"] = secondary
     if base is not None:

@@ -77,9 +77,31 @@ __global__ void __launch_bounds__(kWarps * 32) feature_gather_kernel(const Gathe
     }
   }
   if (col >= a.F) continue;
+  // all kRows reads first, then the writes: over a link of a few microseconds (a peer GPU, host memory) a lane must
+  // have its reads in flight together, and a store between two loads would keep the second one back
+  float v[kRows][VEC];
 #pragma unroll
   for (int k = 0; k < kRows; k++) {
-    if (src[k]) copy_vec<VEC>(a.x0 + (grp * kRows + k) * a.x0_ld + col, src[k] + col);
+    if (src[k]) {
+      if constexpr (VEC == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(src[k] + col));
+        v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
+      } else if constexpr (VEC == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2 *>(src[k] + col));
+        v[k][0] = t.x; v[k][1] = t.y;
+      } else {
+        v[k][0] = __ldg(src[k] + col);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kRows; k++) {
+    if (src[k]) {
+      float *dst = a.x0 + (grp * kRows + k) * a.x0_ld + col;
+      if constexpr (VEC == 4) *reinterpret_cast<float4 *>(dst) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+      else if constexpr (VEC == 2) *reinterpret_cast<float2 *>(dst) = make_float2(v[k][0], v[k][1]);
+      else *dst = v[k][0];
+    }
   }
   }
 }

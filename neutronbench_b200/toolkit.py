@@ -46,7 +46,7 @@ class GCNConfig:
     sample_rate: float = 0.0                      # SAMPLE_RATE > 0: degree-proportional fan-out for training batches
     lower_fanout: int = 0                         # LOWER_FANOUT of that mode
     # rows that are not cached are copied once per distinct source into a staging table by the sampling half
-    # (None: only for a table sharded over GPUs, which is read no other way)
+    # (None: for a table sharded over GPUs, which is read no other way, and for a host table when world_size > 1)
     stage_misses: Optional[bool] = None
     reserve_sms: Optional[int] = None             # SMs left to the gradient all-reduce (None: 4 when world_size > 1)
     cache_row_pitch: int = 0                      # floats between rows of the GPU feature cache (0: chosen from the width)
@@ -186,10 +186,15 @@ class GCN_GPU_NEIGHBOR_impl:
         self.dev_cache_node_hashmap = None
         self.cache_node_num = 0
         self.feature_on_device = datum.shards is None and datum.local_feature.is_cuda
-        # Staging is needed for a sharded table.  For a table in mapped host memory it is an option that measured no
-        # gain on one GPU (Products-shaped: 0.72 against 0.71 ms per step): repeated reads of a host row inside one
-        # launch already hit L2, and the staging copy slows the dense kernels that run beside it.
-        self.stage_misses = (datum.shards is not None) if cfg.stage_misses is None else bool(cfg.stage_misses)
+        # Staging is needed for a sharded table.  For a table in mapped host memory it measured no gain on one GPU
+        # (Products-shaped: 0.72 against 0.70 ms per step: repeated reads of a host row inside one launch already hit
+        # L2, and the staging copy slows the dense kernels that run beside it), but with several ranks reading the
+        # same host memory it takes the host reads out of the training stream (4 ranks: 0.70 against 0.75 ms), so
+        # it is the default when world_size > 1 and some rows are not cached.
+        host_misses = (not self.feature_on_device) and world_size > 1 and \
+            not (cfg.cache_type == "rate" and cfg.cache_rate >= 1.0)
+        self.stage_misses = (datum.shards is not None or host_misses) if cfg.stage_misses is None \
+            else bool(cfg.stage_misses)
         self.reserve_sms = (4 if world_size > 1 else 0) if cfg.reserve_sms is None else int(cfg.reserve_sms)
         self.device_errors_checked = 0
         self.agg_edges_fwd = 0
