@@ -769,7 +769,10 @@ def main():
     }
     if args.workload == "papers":
         line["config"]["feature_table"] = f"sharded by node-id range over {world} GPUs, peers read with plain loads"
-        line["sharded_gather"] = sharded_gather_report(tk, graph, cfg, primary, rank, world)
+        try:
+            line["sharded_gather"] = sharded_gather_report(tk, graph, cfg, primary, rank, world)
+        except Exception as exc:   # a reporting aid: never loses the measured line
+            line["sharded_gather"] = {"unavailable": repr(exc)}
     if secondary is not None:
         line["secondary"] = secondary
     if base is not None:
