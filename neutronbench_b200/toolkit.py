@@ -178,6 +178,14 @@ class GCN_GPU_NEIGHBOR_impl:
         # 0.234 against 0.254 ms/step end to end.  NB_OVERLAP_UPDATE=0 / 1 overrides.
         self.overlap_update = os.environ.get("NB_OVERLAP_UPDATE", "1" if world_size > 1 else "0") == "1"
         self._update_stream = None
+        # The per-step gradient sum goes through the library's own NCCL communicator (nb_allreduce_sum_f32): three
+        # C calls per step on the update stream instead of a torch.distributed collective, whose host-side cost per call
+        # is a visible share of a 0.23 ms step.  torch.distributed stays for set-up, per-epoch scalars and as the
+        # fallback (NB_NATIVE_ALLREDUCE=0, a backend other than NCCL, or the communication library not built).
+        self._native_comm = None
+        if world_size > 1 and use_engine and os.environ.get("NB_NATIVE_ALLREDUCE", "0") == "1" and \
+                torch.distributed.get_backend() == "nccl":
+            self._native_comm = _open_native_comm(rank, world_size, self.device)
         self.fuse_output_layer = True   # last layer + loss + its gradients in two launches (nb_output_layer)
         if self.multi_label:
             assert int(cfg.classes) == int(cfg.layers[-1]), "CLASSES > 1 needs one output per class"
@@ -610,6 +618,13 @@ class GCN_GPU_NEIGHBOR_impl:
             if self._update_stream is None:
                 self._update_stream = torch.cuda.Stream(device=self.device, priority=-1)
             us = self._update_stream
+            if self._native_comm is not None:
+                eng = self._ensure_engine()
+                _lib.call("nb_gcn_wait_gradients", eng, us.cuda_stream)
+                _lib.call_comm("nb_allreduce_sum_f32", self._native_comm, self.P.grad.data_ptr(), self.P.grad.numel(),
+                               us.cuda_stream)
+                _lib.call("nb_gcn_update", eng, us.cuda_stream)
+                return
             with torch.cuda.stream(us):
                 _lib.call("nb_gcn_wait_gradients", self._ensure_engine(), us.cuda_stream)
                 sum_gradients(self.P.grad, self.world_size)
@@ -641,7 +656,11 @@ class GCN_GPU_NEIGHBOR_impl:
             with torch.cuda.stream(us):
                 _lib.call("nb_gcn_wait_gradients", self._ensure_engine(), us.cuda_stream)
                 self.P.grad.zero_()
-                sum_gradients(self.P.grad, self.world_size)
+                if self._native_comm is not None:
+                    _lib.call_comm("nb_allreduce_sum_f32", self._native_comm, self.P.grad.data_ptr(),
+                                   self.P.grad.numel(), us.cuda_stream)
+                else:
+                    sum_gradients(self.P.grad, self.world_size)
                 _lib.call("nb_gcn_update", self._ensure_engine(), us.cuda_stream)
             return
         self.P.grad.zero_()      # same stream as the previous update: stream order is enough
@@ -796,6 +815,26 @@ def epoch_steps(n_ids_total: int, batch_size: int, world_size: int) -> int:
     toolkits/GCN_GPU_NEIGHBOR.hpp:309-313), so all ranks issue the same number of collectives."""
     largest = (n_ids_total + world_size - 1) // world_size
     return batches_of(largest, batch_size)
+
+
+def _open_native_comm(rank: int, world_size: int, device):
+    """A communicator of libnb_b200_comm.so over the ranks of the default process group: rank 0 draws the NCCL id and
+    torch.distributed carries it to the others (what a C++ host does with MPI_Bcast).  None where the library was not
+    built."""
+    import ctypes as C
+    try:
+        _lib.load_comm()
+    except (ImportError, OSError):
+        return None
+    uid = torch.zeros(128, dtype=torch.uint8, device=device)
+    if rank == 0:
+        buf = C.create_string_buffer(128)
+        _lib.call_comm("nb_comm_unique_id", buf)
+        uid.copy_(torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8))
+    torch.distributed.broadcast(uid, src=0)
+    comm = C.c_void_p()
+    _lib.call_comm("nb_comm_create", C.byref(comm), bytes(uid.cpu().numpy().tobytes()), world_size, rank)
+    return comm
 
 
 def sum_gradients(grad: torch.Tensor, world_size: int):
