@@ -93,6 +93,9 @@ def parse_args():
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="nb_gcn_set_option on the trainer's handle (tuning switches; results never depend on them)")
     ap.add_argument("--cache-row-pitch", type=int, default=0, help="floats between rows of the GPU feature cache (0: default)")
+    ap.add_argument("--value-readback", type=int, default=0,
+                    help="1: the device-resident region also reads every step's loss back (one step late), like a "
+                         "training loop that logs its loss; 0: nothing is read inside that region")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload's node and edge counts (functional checks)")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
@@ -344,18 +347,19 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
         return t.tolist()
 
     def steps(smp, n, staged):
+        read = (not staged) or bool(args.value_readback)
         if cfg.pipelines > 1:
-            done = tk.run_pipelined(smp, max_batches=n, train=True, read_back=not staged, pad_to_steps=n)[3]
+            done = tk.run_pipelined(smp, max_batches=n, train=True, read_back=read, pad_to_steps=n)[3]
             assert done == n
             return
         for _ in range(n):
             tk.train_step(smp)
-            if not staged:
+            if read:
                 tk.read_stats()
 
     def run(staged, record_events):
         regions_cap = max(1, args.max_regions)
-        need = (W + K * regions_cap) * cfg.batch_size
+        need = (W + K * (regions_cap + 1)) * cfg.batch_size     # + the fully timed region after the timed ones
         reps = (need + len(shard) - 1) // len(shard)
         seeds_all = np.tile(shard, reps)[:need]
         smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
@@ -368,7 +372,11 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
         barrier()
         tk.events = [] if (record_events and not tk.use_engine) else None
         if record_events and tk.use_engine:
-            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 1)
+            # inside the timed regions only the dominant kernel is bracketed by events (two records per step); the
+            # other aggregation launches and the per-phase times are taken in one more region after them, which does
+            # not count towards `value`: an event record between two kernels keeps the second from starting under
+            # the first one's tail, and eight of them per step cost 13 us of a 0.23 ms step (more with several ranks)
+            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 2)
         launches0 = _lib.load().nb_launch_count()
         phase = None
         region_ms, region_edges = [], []
@@ -394,14 +402,21 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
         tk.events = None
         if record_events and tk.use_engine:
             import ctypes
+            eng = tk._ensure_engine()
             a_ms, a_b, a_n = (ctypes.c_double * 2)(), (ctypes.c_uint64 * 2)(), (ctypes.c_uint64 * 2)()
-            _lib.call("nb_gcn_read_timing_by_class", tk._ensure_engine(), a_ms, a_b, a_n)
+            _lib.call("nb_gcn_read_timing_by_class", eng, a_ms, a_b, a_n)
+            dominant = (a_ms[0], int(a_b[0]), int(a_n[0]))          # layer-0 aggregation over the timed regions
+            _lib.call("nb_gcn_set_timing", eng, 1)                   # one more region of K steps, every class timed
+            steps(smp, K, staged)
+            barrier()
+            f_ms, f_b, f_n = (ctypes.c_double * 2)(), (ctypes.c_uint64 * 2)(), (ctypes.c_uint64 * 2)()
+            _lib.call("nb_gcn_read_timing_by_class", eng, f_ms, f_b, f_n)
             ph = (ctypes.c_double * 4)()
-            _lib.call("nb_gcn_read_phase_times", tk._ensure_engine(), ph)
-            _lib.call("nb_gcn_set_timing", tk._ensure_engine(), 0)
-            ev = ("engine", list(a_ms), [int(x) for x in a_b], [int(x) for x in a_n])
-            n_steps = K * len(region_ms)
-            phase = {"sample_host": ph[0] / n_steps, "trans": ph[1] / n_steps, "graph": ph[2] / n_steps, "nn": ph[3] / n_steps}
+            _lib.call("nb_gcn_read_phase_times", eng, ph)
+            _lib.call("nb_gcn_set_timing", eng, 0)
+            ev = ("engine", dominant, list(f_ms), [int(x) for x in f_b], [int(x) for x in f_n])
+            phase = {"sample_host": ph[0] / K, "trans": ph[1] / K, "graph": ph[2] / K, "nn": ph[3] / K,
+                     "region": "one region of K steps with every launch class timed, after the regions that make up `value`"}
         tk.check_device_errors()     # a bounded wait that gave up, or an id outside its table, voids the numbers
         ms_max = reduce_vec(region_ms, dist.ReduceOp.MAX if world > 1 else None)
         edges_sum = reduce_vec(region_edges, dist.ReduceOp.SUM if world > 1 else None)
@@ -421,11 +436,10 @@ def roofline_of(events, peak, peak_src, traffic, cfg):
         return nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
 
     if isinstance(events, tuple):      # native step: totals measured by the library's own CUDA events
-        _, cls_ms, cls_bytes, cls_n = events
-        dom_ms, dom_bytes, dom_n = cls_ms[0], cls_bytes[0], cls_n[0]
+        _, (dom_ms, dom_bytes, dom_n), cls_ms, cls_bytes, cls_n = events
         all_ms, all_bytes, all_n = sum(cls_ms), sum(cls_bytes), sum(cls_n)
-        per_call = {"layer0_forward": {"GBps": gbps(cls_bytes[0], cls_ms[0]), "ms_avg": cls_ms[0] / max(cls_n[0], 1),
-                                       "bytes_avg": cls_bytes[0] / max(cls_n[0], 1)},
+        per_call = {"layer0_forward": {"GBps": gbps(dom_bytes, dom_ms), "ms_avg": dom_ms / max(dom_n, 1),
+                                       "bytes_avg": dom_bytes / max(dom_n, 1)},
                     "other_aggregation": {"GBps": gbps(cls_bytes[1], cls_ms[1]), "ms_avg": cls_ms[1] / max(cls_n[1], 1),
                                           "bytes_avg": cls_bytes[1] / max(cls_n[1], 1)}}
     else:                              # Python step: one event pair per aggregation call
@@ -450,7 +464,8 @@ def roofline_of(events, peak, peak_src, traffic, cfg):
                 "algorithmic_bytes_per_launch": dom_bytes / max(dom_n, 1), "per_call": per_call}
     all_agg = {"bound": "hbm", "achieved": gbps(all_bytes, all_ms), "peak": peak, "unit": "GB/s",
                "frac": gbps(all_bytes, all_ms) / peak, "launches": all_n,
-               "what": "every aggregation launch (forward and backward) of the timed regions"}
+               "what": "every aggregation launch (forward and backward) of one region of K steps that follows the timed regions, "
+                       "with every launch bracketed by events"}
     return roofline, all_agg
 
 
@@ -689,6 +704,11 @@ def main():
         cfg.pipelines = pipelines
         tk = GCN_GPU_NEIGHBOR_impl(graph, datum, cfg, rank=rank, world_size=world, use_engine=not args.python_step)
         tk.init_cache()
+        # fewer cores than threads that would spin (a main thread, an NCCL proxy and the sampler threads per rank): the
+        # sampling half then waits for the GPU on blocking events
+        if not args.python_step and os.environ.get("NB_BLOCKING_SYNC_AUTO", "0") == "1" and \
+                (os.cpu_count() or 1) < world * (pipelines + 2):
+            _lib.call("nb_gcn_set_option", tk._ensure_engine(), b"blocking_sync", 1)
         for opt in args.option:
             name, value = opt.split("=", 1)
             _lib.call("nb_gcn_set_option", tk._ensure_engine(), name.encode(), int(value))

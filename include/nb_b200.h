@@ -435,15 +435,18 @@ int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);
  * copied by handles created afterwards.  "hub_min_edges" (rows of at least this many edges of an aggregation over a
  * plain table, i.e. popular sources in the backward pass, are walked by a team of warps with one column per lane
  * instead of by one warp; 0 switches that off; same bits either way) and "fuse_relu" (ReLU + dropout of a hidden layer
- * leave with the product from the tensor-core GEMM's epilogue instead of a kernel of their own; same bits) are
- * accepted by both calls. */
+ * leave with the product from the tensor-core GEMM's epilogue instead of a kernel of their own; same bits) and
+ * "blocking_sync" (host waits of the sampling half sleep on blocking events instead of spinning: for nodes with fewer
+ * cores than sampler threads) are accepted by both calls. */
 int nb_set_option(const char *name, int64_t value);
 /* nb_count_ids over the source list of every block of a sampled batch (one step of the dry-run epoch of
  * CACHE_POLICY:sample); waits for the batch's sampling like nb_gcn_compute. */
 int nb_gcn_count_sources(nb_gcn *g, nb_gcn_batch *batch, uint32_t *d_counts, void *stream);
 /* Measurement aid: with timing on, every aggregation launch of nb_gcn_step is bracketed by CUDA events on the
  * step's stream; nb_gcn_read_timing waits for them and returns the summed device time, the summed
- * algorithmic bytes and the launch count since timing was switched on (or last read). */
+ * algorithmic bytes and the launch count since timing was switched on (or last read).  enabled == 2 brackets only the
+ * layer-0 forward aggregation (two event records per step instead of eight; an event record between two kernels
+ * keeps the second from starting under the first one's tail, so full timing costs several microseconds per step). */
 int nb_gcn_set_timing(nb_gcn *g, int enabled);
 int nb_gcn_read_timing(nb_gcn *g, double *agg_ms, uint64_t *agg_bytes, uint64_t *agg_launches);
 /* The same, split in two classes: [0] the layer-0 forward aggregation (the launch that reads the feature rows,

@@ -333,7 +333,7 @@ int block_build_impl(nb_ws *ws, uint32_t num_vertices, uint32_t *d_row_indices, 
   }
   NB_CUDA(cudaMemcpyAsync(ws->mailbox, prefix + words, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 1, flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
-  NB_CUDA(cudaStreamSynchronize(stream));
+  NB_CUDA(wait_stream_host(stream));
   const uint32_t s = ws->mailbox[0];
   if (ws->mailbox[1] != 0) return fail(NB_ERR_INVALID, "nb_block_build: a source id is >= num_vertices");
   *src_size = s;

@@ -13,6 +13,11 @@ namespace nb {
 
 // Number of SMs of the current device (148 on B200: 2 dies x 74), asked from the driver once per device.
 int num_sms();
+// Host wait for everything enqueued on `stream` so far.  With Tuning::blocking_sync the calling thread sleeps on an
+// event created with cudaEventBlockingSync instead of spinning in cudaStreamSynchronize: the sampler threads of
+// several ranks (and several batches in flight per rank) then leave the cores to the threads that launch kernels
+// when a node has fewer cores than such threads.
+cudaError_t wait_stream_host(cudaStream_t stream);
 
 // Flag per device for set-up that CUDA keeps per device (function attributes such as the dynamic shared-memory
 // limit): need() is true until done() has been called with that device current.
@@ -53,6 +58,7 @@ struct Tuning {
   // row (Reddit-shaped step 0.230 -> 0.238 ms); the 128-row-tile kernel saves two launches per Products-shaped step
   // and the step time stays at 0.697 ms.
   int fuse_relu = 0;
+  int blocking_sync = 0;         // host waits of the sampling half sleep on a blocking event instead of spinning
   int ring_balance = 0;          // ring kernel: warps take shares of equal edge count (1) or of equal row count (0)
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring

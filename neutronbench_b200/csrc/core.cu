@@ -54,6 +54,23 @@ NB_API int nb_shard_close(void *d_ptr) {
 }
 
 namespace nb {
+cudaError_t wait_stream_host(cudaStream_t stream) {
+  if (!tuning().blocking_sync) return cudaStreamSynchronize(stream);
+  // one blocking event per thread and device, created on first use and kept for the life of the thread
+  thread_local cudaEvent_t ev[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t st = cudaGetDevice(&dev);
+  if (st != cudaSuccess) return st;
+  if (dev < 0 || dev >= kMaxDevices) return cudaStreamSynchronize(stream);
+  if (!ev[dev]) {
+    st = cudaEventCreateWithFlags(&ev[dev], cudaEventBlockingSync | cudaEventDisableTiming);
+    if (st != cudaSuccess) return st;
+  }
+  st = cudaEventRecord(ev[dev], stream);
+  if (st != cudaSuccess) return st;
+  return cudaEventSynchronize(ev[dev]);
+}
+
 int num_sms() {
   static int cached[kMaxDevices] = {};
   int d = 0;

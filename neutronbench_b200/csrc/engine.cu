@@ -53,7 +53,7 @@ struct nb_gcn {
   float beta1_t, beta2_t;
   size_t w_off[NB_MAX_LAYERS + 1];
   // optional timing of the aggregation launches with CUDA events on the step's stream
-  bool timing = false;
+  int timing = 0;                    // 0 off, 1 every class, 2 only the layer-0 forward aggregation (class 0)
   std::vector<cudaEvent_t> ev_pool;   // pairs: start, stop
   size_t ev_used = 0;
   uint64_t timed_bytes = 0;
@@ -108,7 +108,7 @@ struct AggTimer {
   cudaEvent_t stop = nullptr;
   // The pool is shared by the thread that enqueues the training half and the sampler threads (class 3): a pair is
   // reserved under the handle's mutex and its two events are recorded outside it.
-  AggTimer(nb_gcn *g_, void *stream, uint64_t bytes, int cls = 1) : g(g_), st(nb::as_stream(stream)), on(g_->timing) {
+  AggTimer(nb_gcn *g_, void *stream, uint64_t bytes, int cls = 1) : g(g_), st(nb::as_stream(stream)), on(g_->timing == 1 || (g_->timing == 2 && cls == 0)) {
     if (!on) return;
     cudaEvent_t start;
     {
@@ -196,7 +196,7 @@ NB_API int nb_gcn_destroy(nb_gcn *g) {
 NB_API int nb_gcn_set_timing(nb_gcn *g, int enabled) {
   NB_REQUIRE(g != nullptr, "nb_gcn_set_timing: null pointer");
   std::lock_guard<std::mutex> lk(g->mu);
-  g->timing = enabled != 0;
+  g->timing = enabled == 2 ? 2 : (enabled != 0 ? 1 : 0);
   g->sample_host_ms = 0.0;
   for (int k = 0; k < 4; k++) { g->cls_ms[k] = g->phase_ms[k] = 0.0; g->cls_bytes[k] = g->cls_launches[k] = 0; }
   g->ev_used = 0;
@@ -268,7 +268,10 @@ namespace {
 
 int ensure_events(nb_gcn_batch *bt) {
   if (!bt->sampled) NB_CUDA(cudaEventCreateWithFlags(&bt->sampled, cudaEventDisableTiming));
-  if (!bt->consumed) NB_CUDA(cudaEventCreateWithFlags(&bt->consumed, cudaEventDisableTiming));
+  // a sampler thread may wait long for a slot to be consumed: with blocking_sync it sleeps instead of spinning
+  if (!bt->consumed)
+    NB_CUDA(cudaEventCreateWithFlags(&bt->consumed, cudaEventDisableTiming |
+                                                        (nb::tuning().blocking_sync ? cudaEventBlockingSync : 0)));
   return 0;
 }
 
@@ -631,6 +634,7 @@ static int apply_option(nb::Tuning &t, const char *name, int64_t value) {
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
   else if (n == "ring_balance") t.ring_balance = value != 0;
   else if (n == "fuse_relu") t.fuse_relu = value != 0;
+  else if (n == "blocking_sync") t.blocking_sync = value != 0;
   else if (n == "hub_min_edges") t.hub_min_edges = (int)(value > 0 ? (value < 32 ? 32 : value) : 0);
   else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);
   else if (n == "ring_wait_ns") t.ring_wait_ns = (int)(value > 0 ? (value < 100000 ? value : 100000) : 0);

@@ -261,7 +261,7 @@ NB_API int nb_sample_hop_offsets(nb_ws *ws, const uint64_t *d_graph_column_offse
     NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   }
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 2, d_column_offset + v, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
-  NB_CUDA(cudaStreamSynchronize(stream));
+  NB_CUDA(wait_stream_host(stream));
   *e_size = ws->mailbox[2];
   return 0;
 }
@@ -281,7 +281,7 @@ NB_API int nb_sample_hop_offsets_rate(nb_ws *ws, const uint64_t *d_graph_column_
   }
   NB_TRY(exclusive_scan_u32(ws, d_column_offset, d_column_offset, v, true, stream));
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 2, d_column_offset + v, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
-  NB_CUDA(cudaStreamSynchronize(stream));
+  NB_CUDA(wait_stream_host(stream));
   *e_size = ws->mailbox[2];
   return 0;
 }
@@ -357,7 +357,7 @@ NB_API int nb_graph_build_csc(nb_ws *ws, const uint32_t *d_edges, uint64_t num_e
     NB_LAUNCH_CHECK();
   }
   NB_CUDA(cudaMemcpyAsync(ws->mailbox + 3, err, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream));
-  NB_CUDA(cudaStreamSynchronize(stream));
+  NB_CUDA(wait_stream_host(stream));
   if (ws->mailbox[3] != 0) return fail(NB_ERR_INVALID, "nb_graph_build_csc: an edge endpoint is >= num_vertices");
   return 0;
 }
