@@ -93,9 +93,10 @@ def parse_args():
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="nb_gcn_set_option on the trainer's handle (tuning switches; results never depend on them)")
     ap.add_argument("--cache-row-pitch", type=int, default=0, help="floats between rows of the GPU feature cache (0: default)")
-    ap.add_argument("--value-readback", type=int, default=0,
-                    help="1: the device-resident region also reads every step's loss back (one step late), like a "
-                         "training loop that logs its loss; 0: nothing is read inside that region")
+    ap.add_argument("--value-readback", type=int, default=1,
+                    help="1: the device-resident region also reads every step's loss back (one step late), as a "
+                         "training loop that logs its loss does; 0: nothing is read inside that region (3 %% faster on "
+                         "one GPU, but with several ranks the unthrottled host threads cost more than that)")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload's node and edge counts (functional checks)")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
@@ -680,6 +681,11 @@ def main():
                     ("native (nb_gcn_sample on library threads overlapping nb_gcn_compute)" if pipelines > 1
                      else "native (nb_gcn_step)"),
             "pipelines": pipelines,
+            "timed_region": ("seeds resident on the device; every step's loss is read back one step late"
+                             if args.value_readback else "seeds resident on the device; nothing is read back"),
+            "gradient_sum": "none (one rank)" if world == 1 else
+                            ("libnb_b200_comm (NCCL) on the update stream"
+                             if os.environ.get("NB_NATIVE_ALLREDUCE", "1") == "1" else "torch.distributed (NCCL)"),
         }
 
     if args.pipelines <= 0:
