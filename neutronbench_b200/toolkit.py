@@ -485,6 +485,8 @@ class GCN_GPU_NEIGHBOR_impl:
         self._slot_seeds = [torch.empty(self.cfg.batch_size, dtype=torch.int32).pin_memory() for _ in range(slots)]
         self._slot_refs = [None] * slots
         self._stats_ring = [torch.zeros(4, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self._stats_dev_ring = [torch.zeros(4, dtype=torch.float32, device=self.device) for _ in range(2)]
+        self._readback_stream = torch.cuda.Stream(device=self.device)
         self._batches = []
         for w in self._batch_ws:
             h = C.c_void_p()
@@ -516,12 +518,13 @@ class GCN_GPU_NEIGHBOR_impl:
         _lib.call("nb_gcn_sample_from_edges", self._ensure_engine(), self._batches[slot], ptr(seeds), int(seeds.numel()),
                   ptrs, counts, self._sample_streams[slot].cuda_stream)
 
-    def compute_batch(self, slot: int, train: bool = True):
-        """nb_gcn_compute on subgraph `slot`, on the current stream; never blocks the host."""
+    def compute_batch(self, slot: int, train: bool = True, stats: Optional[torch.Tensor] = None):
+        """nb_gcn_compute on subgraph `slot`, on the current stream; never blocks the host.  Loss and hits go to
+        `stats` (default: self.stats)."""
         import ctypes as C
         info = _lib.GcnStepInfo()
-        _lib.call("nb_gcn_compute", self._ensure_engine(), self._batches[slot], 1 if train else 0, ptr(self.stats),
-                  C.byref(info), torch.cuda.current_stream().cuda_stream)
+        _lib.call("nb_gcn_compute", self._ensure_engine(), self._batches[slot], 1 if train else 0,
+                  ptr(self.stats if stats is None else stats), C.byref(info), torch.cuda.current_stream().cuda_stream)
         L = self.layers
         self.agg_edges_fwd += sum(info.e[l] for l in range(L))
         if train:
@@ -582,7 +585,8 @@ class GCN_GPU_NEIGHBOR_impl:
             if more_to_issue():   # the sampler threads draw ahead while this thread enqueues batch i
                 self.sample_batch(sampler, issued % slots, train)
                 issued += 1
-            info = self.compute_batch(slot, train=train)
+            dev_stats = self._stats_dev_ring[batches & 1] if read_back else None
+            info = self.compute_batch(slot, train=train, stats=dev_stats)
             if train:
                 self.Update()
                 self.step_count += 1
@@ -592,10 +596,18 @@ class GCN_GPU_NEIGHBOR_impl:
                     loss, score = self._loss_and_score(pending_read[0])
                     loss_sum += loss
                     correct += score
+                # The copy runs on a stream of its own, behind an event of the training stream, and each of two
+                # device buffers is written by every other step: a copy enqueued on the training stream itself would
+                # put a DMA operation, and the switch back from it, in front of the next step's first kernel.
                 host = self._stats_ring[batches & 1]
-                host.copy_(self.stats, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
+                done = torch.cuda.Event()
+                done.record()
+                rb = self._readback_stream
+                rb.wait_event(done)
+                with torch.cuda.stream(rb):
+                    host.copy_(dev_stats, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record()
                 pending_read = (host, ev)
             batches += 1
             nodes += info.v[self.layers - 1]
