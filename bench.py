@@ -647,6 +647,11 @@ def main():
         # The only collective is a 329 KB gradient sum per step: a few channels carry it, and every channel is a CTA
         # that holds an SM beside the one-CTA-per-SM aggregation kernel (which leaves that many SMs free).
         os.environ.setdefault("NCCL_MAX_CTAS", "4")
+        # NCCL launches its CTAs as one thread-block cluster by default, and a cluster needs free SMs that sit
+        # together.  The SMs the aggregation kernel leaves free are wherever the scheduler put its CTAs, so the
+        # gradient sum of step i would wait for the layer-0 aggregation of step i+1 to end instead of running beside
+        # it (measured on 4 GPUs: 0.241 against 0.213 ms per step).  Independent CTAs fit the free SMs.
+        os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "1")
         dist.init_process_group("nccl", device_id=device)
 
     from neutronbench_b200 import GCN_GPU_NEIGHBOR_impl, _lib

@@ -231,6 +231,10 @@ def run(cfg_path: str, out=sys.stdout) -> float:
     if world > 1:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         if not torch.distributed.is_initialized():
+            # the per-step gradient sum runs beside the next batch's layer-0 aggregation, on the few SMs that kernel
+            # leaves free: few channels, and CTAs that do not have to be placed together as one cluster
+            os.environ.setdefault("NCCL_MAX_CTAS", "4")
+            os.environ.setdefault("NCCL_CGA_CLUSTER_SIZE", "1")
             torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
         if rank != 0:
             out = open(os.devnull, "w")

@@ -487,6 +487,7 @@ class GCN_GPU_NEIGHBOR_impl:
         self._stats_ring = [torch.zeros(4, dtype=torch.float32).pin_memory() for _ in range(2)]
         self._stats_dev_ring = [torch.zeros(4, dtype=torch.float32, device=self.device) for _ in range(2)]
         self._readback_stream = torch.cuda.Stream(device=self.device)
+        self._readback_on_side_stream = os.environ.get("NB_READBACK_STREAM", "1") == "1"
         self._batches = []
         for w in self._batch_ws:
             h = C.c_void_p()
@@ -600,11 +601,16 @@ class GCN_GPU_NEIGHBOR_impl:
                 # device buffers is written by every other step: a copy enqueued on the training stream itself would
                 # put a DMA operation, and the switch back from it, in front of the next step's first kernel.
                 host = self._stats_ring[batches & 1]
-                done = torch.cuda.Event()
-                done.record()
-                rb = self._readback_stream
-                rb.wait_event(done)
-                with torch.cuda.stream(rb):
+                if self._readback_on_side_stream:
+                    done = torch.cuda.Event()
+                    done.record()
+                    rb = self._readback_stream
+                    rb.wait_event(done)
+                    with torch.cuda.stream(rb):
+                        host.copy_(dev_stats, non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record()
+                else:
                     host.copy_(dev_stats, non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record()
