@@ -427,7 +427,8 @@ int nb_gcn_set_sampler_threads(nb_gcn *g, int threads);
  * settings.  Names: "gemm_mode" (as nb_set_gemm_mode), "pdl", "fused_output_layer", "staged_spmm", "spmm_ring",
  * "staged_min_width", "ring_group_shift", "l2_panel_bytes", "l2_prefetch", "l2_hint" (0 off; 1 rows that a single
  * edge of the launch uses are copied with the L2 evict-first policy; 2 the others evict-last as well),
- * "y_stream_stores" (streaming stores for the wide layer-0 aggregate), "ring_balance" (1: the warps of the wide-row
+ * "y_stream_stores" (streaming stores for the wide layer-0 aggregate), "ring_warps" (20, 22 or 24 warps per CTA of the wide-row aggregation kernel, four row
+ * slots each; 24 fill the shared memory of an SM), "ring_balance" (1: the warps of the wide-row
  * aggregation kernel take shares of equal edge count cut at row boundaries; 0: of equal row count), "reserve_sms" (SMs that the
  * one-CTA-per-SM aggregation kernel leaves free for a collective running beside it).  Results never depend on them. */
 int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);

@@ -59,6 +59,7 @@ struct Tuning {
   // and the step time stays at 0.697 ms.
   int fuse_relu = 0;
   int blocking_sync = 0;         // host waits of the sampling half sleep on a blocking event instead of spinning
+  int ring_warps = 24;           // ring kernel: warps per CTA (20, 22 or 24), i.e. row slots in flight per SM
   int ring_balance = 0;          // ring kernel: warps take shares of equal edge count (1) or of equal row count (0)
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring

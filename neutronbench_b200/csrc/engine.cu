@@ -634,6 +634,10 @@ static int apply_option(nb::Tuning &t, const char *name, int64_t value) {
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
   else if (n == "ring_balance") t.ring_balance = value != 0;
   else if (n == "fuse_relu") t.fuse_relu = value != 0;
+  else if (n == "ring_warps") {
+    NB_REQUIRE(value == 20 || value == 22 || value == 24, "nb_gcn_set_option: ring_warps is 20, 22 or 24");
+    t.ring_warps = (int)value;
+  }
   else if (n == "blocking_sync") t.blocking_sync = value != 0;
   else if (n == "hub_min_edges") t.hub_min_edges = (int)(value > 0 ? (value < 32 ? 32 : value) : 0);
   else if (n == "ring_prefetch") t.ring_prefetch = (int)(value > 0 ? (value < 14 ? value : 14) : 0);

@@ -336,17 +336,18 @@ __global__ void __launch_bounds__(kTmaWarps * 32, 1) spmm_tma_kernel(const TmaSp
 // so pairs of rows per wait and 20 warps per CTA (about 10.8 KB of slots each) beat deeper rings.
 // Arithmetic and order are those of every other path.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRingWarps = 20;
+constexpr int kRingWarps = 20;      // default warps per CTA; 22 and 24 are built as well (Tuning::ring_warps)
+constexpr uint32_t kRingSmemMax = 227 * 1024;   // dynamic shared memory one CTA can have
 
-template <int TILES, bool MASK>
-__global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const TmaSpmmArgs a) {
+template <int TILES, bool MASK, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) spmm_ring_kernel(const TmaSpmmArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   pdl_enter();
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t R = a.seg;                                   // groups per warp, one barrier each
   const uint32_t Gs = a.grp_shift, G = 1u << Gs;              // row slots per group
   unsigned char *my_smem = smem_raw + (size_t)warp * R * G * a.slot_bytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)kRingWarps * R * G * a.slot_bytes) + warp * R;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + (size_t)WARPS * R * G * a.slot_bytes) + warp * R;
   const uint32_t bar0 = smem_u32(bars);
   if (lane < R) mbar_init(bar0 + 8 * lane, 1);
   fence_proxy_async();
@@ -354,8 +355,8 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) spmm_ring_kernel(const Tma
 
   // rows of this warp: a contiguous share; shares differ by at most one row and the longer ones are spread over all
   // CTAs, so that every SM has the same amount of work
-  const uint32_t total_warps = gridDim.x * kRingWarps;
-  const uint32_t gw = blockIdx.x * kRingWarps + warp;
+  const uint32_t total_warps = gridDim.x * WARPS;
+  const uint32_t gw = blockIdx.x * WARPS + warp;
   uint32_t r_begin, r_end, j0, j1;
   if (a.balance) {
     // Option: shares of equal EDGE count, cut at row boundaries: share p starts at the first row whose offset reaches
@@ -666,38 +667,47 @@ static int launch_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) 
   return 0;
 }
 
-template <int TILES, bool MASK>
+template <int TILES, bool MASK, int WARPS>
 static int launch_ring_tiles(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
   static PerDeviceOnce configured;   // the attribute is kept per device
   if (configured.need()) {
-    NB_CUDA(cudaFuncSetAttribute(spmm_ring_kernel<TILES, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 220 * 1024));
+    NB_CUDA(cudaFuncSetAttribute(spmm_ring_kernel<TILES, MASK, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 227 * 1024));
     configured.done();
   }
   // enough CTAs that every warp gets at least a few rows, at most one CTA per SM
-  const unsigned want = (a.n + kRingWarps * 4 - 1) / (kRingWarps * 4);
+  const unsigned want = (a.n + WARPS * 4 - 1) / (WARPS * 4);
   // one CTA per SM; SMs held by a kernel that runs beside this one (a gradient all-reduce on another stream) would
   // make their CTAs wait for a second wave, so the caller can keep a few SMs out of the grid
   const int reserve = tuning().reserve_sms > 0 ? tuning().reserve_sms : 0;
   const unsigned sms = (unsigned)(num_sms() > reserve + 1 ? num_sms() - reserve : 1);
   const unsigned grid = want < sms ? (want ? want : 1) : sms;
-  NB_CUDA(launch_chained(spmm_ring_kernel<TILES, MASK>, dim3(grid), dim3(kRingWarps * 32), smem, stream, a));
+  NB_CUDA(launch_chained(spmm_ring_kernel<TILES, MASK, WARPS>, dim3(grid), dim3(WARPS * 32), smem, stream, a));
   NB_LAUNCH_CHECK();
   return 0;
 }
 
-template <bool MASK>
-static int launch_ring(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
+template <bool MASK, int WARPS>
+static int launch_ring_w(const TmaSpmmArgs &a, size_t smem, cudaStream_t stream) {
   switch ((a.F + 127) / 128) {
-    case 1: return launch_ring_tiles<1, MASK>(a, smem, stream);
-    case 2: return launch_ring_tiles<2, MASK>(a, smem, stream);
-    case 3: return launch_ring_tiles<3, MASK>(a, smem, stream);
-    case 4: return launch_ring_tiles<4, MASK>(a, smem, stream);
-    case 5: return launch_ring_tiles<5, MASK>(a, smem, stream);
-    case 6: return launch_ring_tiles<6, MASK>(a, smem, stream);
-    case 7: return launch_ring_tiles<7, MASK>(a, smem, stream);
-    case 8: return launch_ring_tiles<8, MASK>(a, smem, stream);
+    case 1: return launch_ring_tiles<1, MASK, WARPS>(a, smem, stream);
+    case 2: return launch_ring_tiles<2, MASK, WARPS>(a, smem, stream);
+    case 3: return launch_ring_tiles<3, MASK, WARPS>(a, smem, stream);
+    case 4: return launch_ring_tiles<4, MASK, WARPS>(a, smem, stream);
+    case 5: return launch_ring_tiles<5, MASK, WARPS>(a, smem, stream);
+    case 6: return launch_ring_tiles<6, MASK, WARPS>(a, smem, stream);
+    case 7: return launch_ring_tiles<7, MASK, WARPS>(a, smem, stream);
+    case 8: return launch_ring_tiles<8, MASK, WARPS>(a, smem, stream);
     default: return fail(NB_ERR_INVALID, "spmm (ring): feature width above 1024");
+  }
+}
+
+template <bool MASK>
+static int launch_ring(const TmaSpmmArgs &a, int warps, size_t smem, cudaStream_t stream) {
+  switch (warps) {
+    case 24: return launch_ring_w<MASK, 24>(a, smem, stream);
+    case 22: return launch_ring_w<MASK, 22>(a, smem, stream);
+    default: return launch_ring_w<MASK, kRingWarps>(a, smem, stream);
   }
 }
 
@@ -748,7 +758,19 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
   if (panels == 1 && tuning().spmm_ring) {
     // ring variant: whole rows, per-warp ring of R slots out of about 13.5 KB
     a.panels = 1; a.panel_floats = a.fpad; a.copy_bytes = a.fpad * 4; a.slot_bytes = a.copy_bytes;
-    uint32_t slots = (216 * 1024 / kRingWarps) / a.slot_bytes;   // the CTA's warps share 216 KB of row slots
+    // the CTA's warps share its shared memory as row slots; more warps (22, 24) are taken only where each still gets
+    // the four slots that two pairs in flight need
+    auto slots_for = [&](int w) -> uint32_t {
+      if (w == kRingWarps) return (216u * 1024u / (uint32_t)w) / a.slot_bytes;          // the measured default
+      for (uint32_t sl = 16; sl >= 1; sl--) {
+        const uint32_t groups = sl >= 4 ? sl >> tuning().ring_group_shift : sl;
+        if ((uint64_t)w * ((uint64_t)sl * a.slot_bytes + groups * 8ull) <= kRingSmemMax) return sl;
+      }
+      return 0;
+    };
+    int warps = tuning().ring_warps == 22 || tuning().ring_warps == 24 ? tuning().ring_warps : kRingWarps;
+    if (slots_for(warps) < 4) warps = kRingWarps;
+    uint32_t slots = slots_for(warps);
     if (slots > 16) slots = 16;
     // two rows per barrier (one wait and one refill per pair of edges) where at least two pairs fit; measured on the
     // layer-0 block of the Reddit-shaped model: 78 us against 81 us with a barrier per row (65 against 75 from L2)
@@ -760,8 +782,8 @@ int launch_spmm_tma(TmaSpmmArgs a, cudaStream_t stream) {
       // groups prefetched into L2 beyond the ring, while their references are still inside the operand windows
       const uint32_t max_pf = (32u >> shift) > R + 1 ? (32u >> shift) - R - 1 : 0;
       a.ring_prefetch = (uint32_t)tuning().ring_prefetch < max_pf ? (uint32_t)tuning().ring_prefetch : max_pf;
-      const size_t smem = (size_t)kRingWarps * (R << shift) * a.slot_bytes + (size_t)kRingWarps * R * sizeof(uint64_t);
-      return a.act ? launch_ring<true>(a, smem, stream) : launch_ring<false>(a, smem, stream);
+      const size_t smem = (size_t)warps * (R << shift) * a.slot_bytes + (size_t)warps * R * sizeof(uint64_t);
+      return a.act ? launch_ring<true>(a, warps, smem, stream) : launch_ring<false>(a, warps, smem, stream);
     }
   }
   if (a.ref == nullptr) return fail(NB_ERR_INVALID, "spmm (staged): the segment kernel needs per-edge references");

@@ -91,7 +91,8 @@ def test_sharded_table_needs_staging(cuda_device):
                                      (("l2_hint", 3), ("l2_keep_min_uses", 3)), (("wide_direct", 1),), (("ring_prefetch", 4),),
                                      (("ring_prefetch", 14), ("l2_hint", 0)), (("ring_balance", 0),),
                                      (("ring_balance", 1),), (("ring_balance", 1), ("reserve_sms", 5)),
-                                     (("fuse_relu", 1),), (("hub_min_edges", 0),),
+                                     (("fuse_relu", 1),), (("hub_min_edges", 0),), (("ring_warps", 22),),
+                                     (("ring_warps", 24),), (("ring_warps", 24), ("reserve_sms", 4), ("ring_balance", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 4), ("y_stream_stores", 0))])
 def test_handle_options_change_no_result(cuda_device, options):
