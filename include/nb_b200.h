@@ -437,6 +437,7 @@ int nb_gcn_set_option(nb_gcn *g, const char *name, int64_t value);
  * plain table, i.e. popular sources in the backward pass, are walked by a team of warps with one column per lane
  * instead of by one warp; 0 switches that off; same bits either way) and "fuse_relu" (ReLU + dropout of a hidden layer
  * leave with the product from the tensor-core GEMM's epilogue instead of a kernel of their own; same bits) and
+ * "fuse_last_aggregation" (the fused output layer forms the last block's aggregate itself; same bits),
  * "blocking_sync" (host waits of the sampling half sleep on blocking events instead of spinning: for nodes with fewer
  * cores than sampler threads) are accepted by both calls. */
 int nb_set_option(const char *name, int64_t value);

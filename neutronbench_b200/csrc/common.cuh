@@ -60,6 +60,7 @@ struct Tuning {
   int fuse_relu = 0;
   int blocking_sync = 0;         // host waits of the sampling half sleep on a blocking event instead of spinning
   int ring_warps = 24;           // ring kernel: warps per CTA (20, 22 or 24), i.e. row slots in flight per SM
+  int fuse_last_aggregation = 1; // the fused output layer aggregates the last block itself (one launch fewer)
   int ring_balance = 0;          // ring kernel: warps take shares of equal edge count (1) or of equal row count (0)
   int y_stream_stores = 1;       // ring kernel: output rows written with streaming stores (1) or default stores (0)
   int wide_direct = 0;           // wide rows: plain-load kernel (one warp per row, many warps resident) instead of the ring
@@ -226,6 +227,12 @@ int gemm_ld(nb_ws *ws, const float *d_a, int64_t lda, const float *d_b, int64_t 
             int64_t K, int trans_a, int trans_b, cudaStream_t stream, const ReluEpi *epi = nullptr,
             bool *applied = nullptr);
 bool gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K);
+// nb_output_layer that forms the aggregate of the last block itself (dense.cu)
+bool output_layer_can_aggregate(const float *d_x, size_t x_ld, uint32_t H, uint32_t C);
+int output_layer_aggregating(nb_ws *ws, const float *d_x, size_t x_ld, const uint32_t *d_row_indices,
+                             const uint32_t *d_column_offset, const float *d_src_norm, const float *d_dst_norm,
+                             const float *d_w, const int64_t *d_label, const uint32_t *d_dst, uint32_t B, uint32_t H,
+                             uint32_t C, int train, float *d_dw, float *d_dy, float *d_stats, void *stream);
 bool tma_gemm_applicable(const float *d_a, int64_t lda, const float *d_b, int64_t ldb);
 int gemm_tma_launch(const float *d_a, int64_t lda, const float *d_b, int64_t ldb, float *c, int64_t M, int64_t N,
                     int64_t K, int trans_a, int trans_b, int bn, int splits, int64_t k_per_split, int mode,

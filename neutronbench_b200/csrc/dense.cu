@@ -235,10 +235,20 @@ __global__ void __launch_bounds__(1024) bce_reduce_kernel(const float4 *__restri
 constexpr int kOutRows = 8;          // rows per CTA = warps per CTA
 constexpr int kOutMaxC = 64;
 
+// Where the aggregate of the last block comes from when the kernel forms it itself (x != nullptr) instead of reading it
+// from y: row r of the aggregate = sum over the edges j of column r, in edge order, of fma(x[idx[j]], w_j, .) with
+// w_j = 1 / (norm_idx[idx[j]] * norm_row[r]) - what nb_spmm_csc_fwd_fused computes, element for element.
+struct OutAgg {
+  const float *x;             // rows of the layer's input (H floats each, 16-byte aligned, pitch x_ld), or null
+  size_t x_ld;
+  const uint32_t *offs, *idx;
+  const float *norm_idx, *norm_row;
+};
+
 __global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
     const float *__restrict__ y, const float *__restrict__ w, const int64_t *__restrict__ label_table,
     const uint32_t *__restrict__ dst, uint32_t B, uint32_t H, uint32_t C, uint32_t CP, int train, float *dy,
-    float *dw_part, float *row_loss, float *row_hit) {
+    float *dw_part, float *row_loss, float *row_hit, const OutAgg ag) {
   pdl_enter();
   extern __shared__ float out_smem[];
   float *ws = out_smem;                       // [H][CP]
@@ -247,10 +257,64 @@ __global__ void __launch_bounds__(kOutRows * 32) output_layer_rows_kernel(
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row = blockIdx.x * kOutRows + warp;
   for (uint32_t i = threadIdx.x; i < H * C; i += blockDim.x) ws[(i / C) * CP + (i % C)] = w[i];
-  if (row < B)
+  if (row < B && ag.x != nullptr) {
+    // the warp aggregates its row: lane holds float4 columns 4*lane + 128*t (H <= 256, a multiple of 4)
+    const uint32_t start = __ldg(ag.offs + row), end = __ldg(ag.offs + row + 1);
+    const float nr = __ldg(ag.norm_row + row);
+    float2 acc[2][2];
+#pragma unroll
+    for (int t = 0; t < 2; t++) acc[t][0] = acc[t][1] = make_float2(0.0f, 0.0f);
+    for (uint32_t base = start; base < end; base += 32) {
+      const uint32_t j = base + lane;
+      const float *my_ptr = nullptr;
+      float my_w = 0.0f;
+      if (j < end) {
+        const uint32_t li = __ldg(ag.idx + j);
+        my_w = __fdiv_rn(1.0f, __fmul_rn(__ldg(ag.norm_idx + li), nr));
+        my_ptr = ag.x + (size_t)li * ag.x_ld;
+      }
+      const uint32_t cnt = min(32u, end - base);
+      for (uint32_t jj = 0; jj < cnt; jj += 8) {
+        float4 v[8][2];
+        float wu[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const uintptr_t p = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_ptr, (jj + u) & 31);
+          wu[u] = __shfl_sync(0xffffffffu, my_w, (jj + u) & 31);
+          const bool valid = jj + u < cnt;
+#pragma unroll
+          for (int t = 0; t < 2; t++) {
+            const uint32_t col = 4 * lane + 128 * t;
+            v[u][t] = (valid && col < H) ? __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + col))
+                                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          if (jj + u < cnt) {
+            const float2 w2 = make_float2(wu[u], wu[u]);
+#pragma unroll
+            for (int t = 0; t < 2; t++) {
+              acc[t][0] = fma2_rn(make_float2(v[u][t].x, v[u][t].y), w2, acc[t][0]);
+              acc[t][1] = fma2_rn(make_float2(v[u][t].z, v[u][t].w), w2, acc[t][1]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+      const uint32_t col = 4 * lane + 128 * t;
+      if (col < H) {
+        ys[warp * H + col] = acc[t][0].x; ys[warp * H + col + 1] = acc[t][0].y;
+        ys[warp * H + col + 2] = acc[t][1].x; ys[warp * H + col + 3] = acc[t][1].y;
+      }
+    }
+  } else if (row < B) {
     for (uint32_t h = lane; h < H; h += 32) ys[warp * H + h] = y[(size_t)row * H + h];
-  else
+  } else {
     for (uint32_t h = lane; h < H; h += 32) ys[warp * H + h] = 0.0f;
+  }
   dzs[warp * kOutMaxC + lane] = 0.0f;
   dzs[warp * kOutMaxC + lane + 32] = 0.0f;
   __syncthreads();
@@ -501,10 +565,39 @@ NB_API int nb_output_layer_supported(uint32_t H, uint32_t C) {
   return (H > 0 && C > 0 && C <= (uint32_t)kOutMaxC && output_layer_smem(H, C) <= 96 * 1024) ? 1 : 0;
 }
 
+namespace nb {
+static int output_layer_impl(nb_ws *ws, const float *d_y, const OutAgg &ag, const float *d_w, const int64_t *d_label,
+                             const uint32_t *d_dst, uint32_t B, uint32_t H, uint32_t C, int train, float *d_dw, float *d_dy,
+                             float *d_stats, void *stream_);
+
+// nb_output_layer with the aggregation of the last block done by the same kernel: the aggregate never goes to memory.
+bool output_layer_can_aggregate(const float *d_x, size_t x_ld, uint32_t H, uint32_t C) {
+  return nb_output_layer_supported(H, C) && H <= 256 && (H & 3) == 0 && (x_ld & 3) == 0 &&
+         (reinterpret_cast<uintptr_t>(d_x) & 15) == 0;
+}
+int output_layer_aggregating(nb_ws *ws, const float *d_x, size_t x_ld, const uint32_t *d_row_indices,
+                             const uint32_t *d_column_offset, const float *d_src_norm, const float *d_dst_norm,
+                             const float *d_w, const int64_t *d_label, const uint32_t *d_dst, uint32_t B, uint32_t H,
+                             uint32_t C, int train, float *d_dw, float *d_dy, float *d_stats, void *stream) {
+  NB_REQUIRE(d_x && d_row_indices && d_column_offset && d_src_norm && d_dst_norm, "nb_output_layer: null pointer");
+  NB_REQUIRE(output_layer_can_aggregate(d_x, x_ld, H, C), "nb_output_layer: rows not usable by the aggregating form");
+  OutAgg ag{d_x, x_ld, d_column_offset, d_row_indices, d_src_norm, d_dst_norm};
+  return output_layer_impl(ws, nullptr, ag, d_w, d_label, d_dst, B, H, C, train, d_dw, d_dy, d_stats, stream);
+}
+}  // namespace nb
+
 NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const int64_t *d_label, const uint32_t *d_dst,
                            uint32_t B, uint32_t H, uint32_t C, int train, float *d_dw, float *d_dy, float *d_stats,
                            void *stream_) {
-  NB_REQUIRE(ws && d_y && d_w && d_label && d_dst && d_stats, "nb_output_layer: null pointer");
+  NB_REQUIRE(d_y != nullptr, "nb_output_layer: null pointer");
+  return nb::output_layer_impl(ws, d_y, nb::OutAgg{}, d_w, d_label, d_dst, B, H, C, train, d_dw, d_dy, d_stats, stream_);
+}
+
+namespace nb {
+static int output_layer_impl(nb_ws *ws, const float *d_y, const OutAgg &ag, const float *d_w, const int64_t *d_label,
+                             const uint32_t *d_dst, uint32_t B, uint32_t H, uint32_t C, int train, float *d_dw, float *d_dy,
+                             float *d_stats, void *stream_) {
+  NB_REQUIRE(ws && d_w && d_label && d_dst && d_stats, "nb_output_layer: null pointer");
   NB_REQUIRE(B > 0, "nb_output_layer: empty batch");
   NB_REQUIRE(nb_output_layer_supported(H, C), "nb_output_layer: layer too wide for the fused form (C <= 64, H*C*4 <= ~90 KB)");
   NB_REQUIRE(!train || d_dw, "nb_output_layer: training needs the weight-gradient buffer");
@@ -521,7 +614,7 @@ NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const 
     configured.done();
   }
   NB_CUDA(launch_chained(output_layer_rows_kernel, dim3(ctas), dim3(kOutRows * 32), smem, stream, d_y, d_w, d_label, d_dst, B,
-                         H, C, C | 1u, train ? 1 : 0, train ? d_dy : (float *)nullptr, part, row_loss, row_hit));
+                         H, C, C | 1u, train ? 1 : 0, train ? d_dy : (float *)nullptr, part, row_loss, row_hit, ag));
   NB_LAUNCH_CHECK();
   const unsigned blocks = (train ? (hc + 255) / 256 : 0) + 1;
   NB_CUDA(launch_chained(output_layer_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float *)part, ctas, hc,
@@ -529,6 +622,7 @@ NB_API int nb_output_layer(nb_ws *ws, const float *d_y, const float *d_w, const 
   NB_LAUNCH_CHECK();
   return 0;
 }
+}  // namespace nb
 
 NB_API int nb_set_pdl(int enabled) {
   const int old = nb::default_tuning().use_pdl;

@@ -388,7 +388,7 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   float *Y[NB_MAX_LAYERS], *X[NB_MAX_LAYERS + 1];
   size_t y_ld[NB_MAX_LAYERS];
   X[0] = nullptr;
-  bool fused_out = false;
+  bool fused_out = false, fused_agg = false;
   for (uint32_t l = 0; l < L; l++) {
     const Block &b = blk[l];
     const uint32_t Fi = c.layer_size[l], Fo = c.layer_size[l + 1];
@@ -414,8 +414,14 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
         agg_bytes += bytes_fwd(b, Fi, false, false);
       }
     } else {
-      AggTimer t(g, stream, bytes_fwd(b, Fi, false, false));
-      NB_TRY(nb_spmm_csc_fwd_fused(X[l], Y[l], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi, stream));
+      // The last block of a model with one label per vertex: the fused output layer forms the aggregate itself, row by
+      // row, and it never goes to memory (same arithmetic and edge order as nb_spmm_csc_fwd_fused).
+      fused_agg = l + 1 == L && c.classes <= 1 && nb::tuning().fuse_output_layer && nb::tuning().fuse_last_aggregation &&
+                  nb_output_layer_supported(Fi, Fo) && nb::output_layer_can_aggregate(X[l], Fi, Fi, Fo);
+      if (!fused_agg) {
+        AggTimer t(g, stream, bytes_fwd(b, Fi, false, false));
+        NB_TRY(nb_spmm_csc_fwd_fused(X[l], Y[l], b.row_indices, b.column_offset, b.src_norm, b.dst_norm, b.v, Fi, stream));
+      }
       agg_bytes += bytes_fwd(b, Fi, false, false);
     }
     // First reader of the weights in this step: if the previous update ran on another stream, wait for it here,
@@ -445,8 +451,13 @@ int compute_from(nb_gcn *g, nb_gcn_batch *bt, int train, float *d_stats, nb_gcn_
   if (fused_out) {
     const uint32_t H = c.layer_size[L - 1];
     if (train && L > 1) NB_TRY(arena(ws, (size_t)B * H, &dY_out));
-    NB_TRY(nb_output_layer(ws, Y[L - 1], c.d_W + g->w_off[L - 1], c.d_label, last.destination, (uint32_t)B, H, (uint32_t)C,
-                           train, c.d_grad + g->w_off[L - 1], dY_out, d_stats, stream));
+    if (fused_agg)
+      NB_TRY(nb::output_layer_aggregating(ws, X[L - 1], H, last.row_indices, last.column_offset, last.src_norm,
+                                          last.dst_norm, c.d_W + g->w_off[L - 1], c.d_label, last.destination, (uint32_t)B,
+                                          H, (uint32_t)C, train, c.d_grad + g->w_off[L - 1], dY_out, d_stats, stream));
+    else
+      NB_TRY(nb_output_layer(ws, Y[L - 1], c.d_W + g->w_off[L - 1], c.d_label, last.destination, (uint32_t)B, H,
+                             (uint32_t)C, train, c.d_grad + g->w_off[L - 1], dY_out, d_stats, stream));
   } else {
     int64_t *lab;
     NB_TRY(arena(ws, (size_t)(multi ? B * C : B), &lab));
@@ -634,6 +645,7 @@ static int apply_option(nb::Tuning &t, const char *name, int64_t value) {
   } else if (n == "y_stream_stores") t.y_stream_stores = value != 0;
   else if (n == "ring_balance") t.ring_balance = value != 0;
   else if (n == "fuse_relu") t.fuse_relu = value != 0;
+  else if (n == "fuse_last_aggregation") t.fuse_last_aggregation = value != 0;
   else if (n == "ring_warps") {
     NB_REQUIRE(value == 20 || value == 22 || value == 24, "nb_gcn_set_option: ring_warps is 20, 22 or 24");
     t.ring_warps = (int)value;

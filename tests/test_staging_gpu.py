@@ -92,6 +92,7 @@ def test_sharded_table_needs_staging(cuda_device):
                                      (("ring_prefetch", 14), ("l2_hint", 0)), (("ring_balance", 0),),
                                      (("ring_balance", 1),), (("ring_balance", 1), ("reserve_sms", 5)),
                                      (("fuse_relu", 1),), (("hub_min_edges", 0),), (("ring_warps", 22),),
+                                     (("fuse_last_aggregation", 0),),
                                      (("ring_warps", 24),), (("ring_warps", 24), ("reserve_sms", 4), ("ring_balance", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 1)),
                                      (("wide_direct", 1), ("wide_rows_in_flight", 4), ("y_stream_stores", 0))])
@@ -99,6 +100,18 @@ def test_handle_options_change_no_result(cuda_device, options):
     """nb_gcn_set_option acts on one handle only and never on results (wide rows: the ring kernel runs)."""
     w0, l0 = _train(cuda_device, 602, 128, 41, (10, 5), 1.0, "device", stage=None)
     w1, l1 = _train(cuda_device, 602, 128, 41, (10, 5), 1.0, "device", stage=None, options=options)
+    np.testing.assert_array_equal(w0.view(np.uint32), w1.view(np.uint32))
+    assert l0 == l1
+
+
+@pytest.mark.parametrize("F,hidden,classes,fanout", [(100, 128, 47, (5, 4, 3)), (64, 256, 7, (6, 4)), (32, 100, 64, (4, 4)),
+                                                     (48, 36, 3, (30, 3))])
+def test_output_layer_that_aggregates_its_own_rows_changes_no_result(cuda_device, F, hidden, classes, fanout):
+    """The last block's aggregation inside the fused output-layer kernel (hidden widths up to 256, rows longer than
+    one 32-edge pass) against the separate aggregation launch: bit-identical weights and losses."""
+    w0, l0 = _train(cuda_device, F, hidden, classes, fanout, 0.3, "device", stage=None,
+                    options=(("fuse_last_aggregation", 0),))
+    w1, l1 = _train(cuda_device, F, hidden, classes, fanout, 0.3, "device", stage=None)
     np.testing.assert_array_equal(w0.view(np.uint32), w1.view(np.uint32))
     assert l0 == l1
 
