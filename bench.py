@@ -178,7 +178,8 @@ class ClockSampler:
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "50", "-i", str(self.index)], stdout=self.out,
+                                          "-lms", os.environ.get("NB_CLOCK_LMS", "200"), "-i", str(self.index)],
+                                         stdout=self.out,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
