@@ -97,6 +97,8 @@ def parse_args():
                     help="1: the device-resident region also reads every step's loss back (one step late), as a "
                          "training loop that logs its loss does; 0: nothing is read inside that region (3 %% faster on "
                          "one GPU, but with several ranks the unthrottled host threads cost more than that)")
+    ap.add_argument("--settle-s", type=float, default=0.5,
+                    help="seconds of untimed regions (after the W warm-up steps) before the first timed region")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the workload's node and edge counts (functional checks)")
     ap.add_argument("--seed", type=int, default=2000)
     return ap.parse_args()
@@ -359,9 +361,11 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
             if read:
                 tk.read_stats()
 
-    def run(staged, record_events):
+    def run(staged, record_events, settle=False):
         regions_cap = max(1, args.max_regions)
-        need = (W + K * (regions_cap + 1)) * cfg.batch_size     # + the fully timed region after the timed ones
+        settle_cap = max(1, 4000 // max(K, 1)) if (settle and args.settle_s > 0) else 0
+        # + the fully timed region after the timed ones, + the untimed settling regions before them
+        need = (W + K * (regions_cap + 1 + settle_cap)) * cfg.batch_size
         reps = (need + len(shard) - 1) // len(shard)
         seeds_all = np.tile(shard, reps)[:need]
         smp = Sampler(graph, seeds_all, cfg.fanout, cfg.batch_size, tk.ws, seed=cfg.seed, with_edge_weights=False)
@@ -372,6 +376,21 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
             clocks.start()           # nvidia-smi needs ~0.1 s to produce its first sample: start before warm-up
         steps(smp, W, staged)
         barrier()
+        if settle and args.settle_s > 0:
+            # Untimed regions of K steps until the job has run for settle_s seconds: with eight ranks on a host of 32
+            # cores the first few tenths of a second after start-up run up to 10 % slower than the steady state
+            # (whichever pass comes first shows it, the other one does not), and W warm-up steps are over in a millisecond.
+            s0 = torch.cuda.Event(enable_timing=True)
+            s1 = torch.cuda.Event(enable_timing=True)
+            s0.record()
+            steps(smp, K, staged)
+            s1.record()
+            barrier()
+            one = reduce_vec([s0.elapsed_time(s1)], dist.ReduceOp.MAX if world > 1 else None)[0]
+            more = min(settle_cap, max(1, math.ceil(args.settle_s * 1e3 / max(one, 1e-3)))) - 1
+            for _ in range(more):
+                steps(smp, K, staged)
+            barrier()
         tk.events = [] if (record_events and not tk.use_engine) else None
         if record_events and tk.use_engine:
             # inside the timed regions only the dominant kernel is bracketed by events (two records per step); the
@@ -428,7 +447,7 @@ def measure(tk, graph, cfg, train_ids, args, K, W, rank, world, local_rank, devi
                 "ms_max": max(ms_max), "launches_per_region": launches / len(ms_max), "clocks": clk, "events": ev,
                 "total_steps": K * len(ms_max), "phase_ms_per_step": phase}
 
-    a = run(staged=True, record_events=want_events)
+    a = run(staged=True, record_events=want_events, settle=True)
     b = run(staged=False, record_events=False)
     return K, a, b
 
@@ -687,6 +706,7 @@ def main():
                     ("native (nb_gcn_sample on library threads overlapping nb_gcn_compute)" if pipelines > 1
                      else "native (nb_gcn_step)"),
             "pipelines": pipelines,
+            "settle_s": args.settle_s,
             "timed_region": ("seeds resident on the device; every step's loss is read back one step late"
                              if args.value_readback else "seeds resident on the device; nothing is read back"),
             "gradient_sum": "none (one rank)" if world == 1 else
