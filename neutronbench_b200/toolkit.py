@@ -200,10 +200,7 @@ class GCN_GPU_NEIGHBOR_impl:
         # L2, and the staging copy slows the dense kernels that run beside it), but with several ranks reading the
         # same host memory it takes the host reads out of the training stream (4 ranks: 0.70 against 0.75 ms), so
         # it is the default when world_size > 1 and some rows are not cached.
-        host_misses = (not self.feature_on_device) and world_size > 1 and \
-            not (cfg.cache_type == "rate" and cfg.cache_rate >= 1.0)
-        self.stage_misses = (datum.shards is not None or host_misses) if cfg.stage_misses is None \
-            else bool(cfg.stage_misses)
+        self.stage_misses = default_stage_misses(cfg, datum.shards is not None, self.feature_on_device, world_size)
         self.reserve_sms = (4 if world_size > 1 else 0) if cfg.reserve_sms is None else int(cfg.reserve_sms)
         self.device_errors_checked = 0
         self.agg_edges_fwd = 0
@@ -834,6 +831,16 @@ def epoch_steps(n_ids_total: int, batch_size: int, world_size: int) -> int:
     toolkits/GCN_GPU_NEIGHBOR.hpp:309-313), so all ranks issue the same number of collectives."""
     largest = (n_ids_total + world_size - 1) // world_size
     return batches_of(largest, batch_size)
+
+
+def default_stage_misses(cfg: GCNConfig, sharded: bool, feature_on_device: bool, world_size: int) -> bool:
+    """Whether the sampling half copies a batch's uncached rows into a staging table.  An explicit setting wins; a
+    sharded table is read no other way; a table in host memory is staged when several ranks share that memory and some
+    rows are not cached."""
+    if cfg.stage_misses is not None:
+        return bool(cfg.stage_misses)
+    all_cached = cfg.cache_type == "rate" and cfg.cache_rate >= 1.0
+    return bool(sharded or (not feature_on_device and world_size > 1 and not all_cached))
 
 
 def _open_native_comm(rank: int, world_size: int, device):
